@@ -1,0 +1,258 @@
+/*
+ * b200moe.h — C ABI of the B200 (sm_100a) fused Mixture-of-Experts kernels.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers, sizes and
+ * small enums, enqueues its kernels on the CUDA stream it is given and returns
+ * before they finish.  None of them synchronises.  None of them allocates
+ * device memory: where a kernel needs scratch the caller passes it (see the
+ * *_workspace_bytes helpers).  Return value: 0 on success, a negative
+ * B200MOE_E_* code otherwise (b200moe_status_string() names it and
+ * b200moe_last_error() holds a message for the calling thread).
+ *
+ * Each declaration names the reference interface it replaces, by the file's
+ * path inside the vllm-xpu-kernels project.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types of buffers crossing the boundary. */
+typedef enum {
+  B200MOE_F32 = 0,
+  B200MOE_F16 = 1,
+  B200MOE_BF16 = 2,
+  B200MOE_FP8_E4M3 = 3, /* float8_e4m3fn                                  */
+  B200MOE_U8 = 4,       /* raw bytes: e8m0 scales, packed e2m1 pairs      */
+  B200MOE_I32 = 5,
+  B200MOE_I64 = 6,
+  B200MOE_U32 = 7,
+  B200MOE_FP4X2 = 8 /* float4_e2m1fn_x2: two e2m1 codes per byte, low nibble first */
+} b200moe_dtype;
+
+/* Status codes. */
+enum {
+  B200MOE_OK = 0,
+  B200MOE_E_BADARG = -1,      /* shape / dtype / alignment rejected before launch */
+  B200MOE_E_UNSUPPORTED = -2, /* valid request this build has no kernel for       */
+  B200MOE_E_CUDA = -3,        /* a CUDA runtime / driver call failed              */
+  B200MOE_E_WORKSPACE = -4,   /* workspace missing or too small                   */
+  B200MOE_E_DEVICE_TIMEOUT = -5 /* a bounded device-side wait gave up             */
+};
+
+typedef void* b200moe_stream; /* a cudaStream_t */
+
+const char* b200moe_status_string(int status);
+/* Message of the last failing call made by this thread ("" if none). */
+const char* b200moe_last_error(void);
+/* ABI version: bumped when a signature changes. */
+int b200moe_abi_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* Routing                                                                    */
+/* ------------------------------------------------------------------------- */
+
+/* Softmax top-k gating.  Replaces `topk_softmax` (csrc/moe/topk.cpp:848-898,
+ * kernel :281-599; schema csrc/moe/torch_bindings.cpp:59-63).
+ * gating [T,E] (f32/f16/bf16) -> topk_weights [T,K] f32, topk_indices [T,K]
+ * (i32/u32/i64), token_expert_indices [T,K] i32 (= k*T + t).
+ * bias (fp32 [E], may be NULL) is added for selection only. */
+int b200moe_topk_softmax(float* topk_weights, void* topk_indices,
+                         b200moe_dtype index_dtype,
+                         int32_t* token_expert_indices, const void* gating,
+                         b200moe_dtype gating_dtype, int64_t num_tokens,
+                         int num_experts, int topk, int renormalize,
+                         const float* bias, b200moe_stream stream);
+
+/* Sigmoid top-k gating.  Replaces `topk_sigmoid` (csrc/moe/topk.cpp:900-952;
+ * schema csrc/moe/torch_bindings.cpp:65-69). */
+int b200moe_topk_sigmoid(float* topk_weights, void* topk_indices,
+                         b200moe_dtype index_dtype,
+                         int32_t* token_expert_indices, const void* gating,
+                         b200moe_dtype gating_dtype, int64_t num_tokens,
+                         int num_experts, int topk, int renormalize,
+                         const float* bias, double routed_scaling_factor,
+                         b200moe_stream stream);
+
+/* Group-limited top-k on already activated scores.  Replaces `grouped_topk`
+ * (csrc/moe/grouped_topk.cpp:782-876, kernels :404-695; schema
+ * csrc/moe/torch_bindings.cpp:53-57).
+ * scores, scores_with_bias [T,E] (same dtype) -> topk_values [T,K] (same
+ * dtype), topk_indices [T,K] i32. */
+int b200moe_grouped_topk(void* topk_values, int32_t* topk_indices,
+                         const void* scores, const void* scores_with_bias,
+                         b200moe_dtype dtype, int64_t num_tokens,
+                         int num_experts, int n_group, int topk_group,
+                         int topk, int renormalize,
+                         double routed_scaling_factor, b200moe_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Alignment / permutation                                                    */
+/* ------------------------------------------------------------------------- */
+
+/* Scratch needed by b200moe_moe_align_block_size and
+ * b200moe_remap_hidden_states for `numel` (= T*K) routed slots over
+ * `num_experts` buckets.  0 when the single-block path is taken. */
+size_t b200moe_sort_workspace_bytes(int64_t numel, int num_experts);
+
+/* Replaces `moe_align_block_size` (csrc/moe/moe_align_sum_kernels.cpp:1034-1181;
+ * schema csrc/moe/torch_bindings.cpp:14-20).
+ * topk_ids [numel] (i32/i64/u32...) -> sorted_token_ids [sorted_len] i32 (slot
+ * indices grouped by expert, each expert padded to block_size with `numel`),
+ * expert_ids [expert_ids_len] i32, num_tokens_post_pad [1] i32.
+ * Within one expert the slots appear in ascending order (the reference leaves
+ * that order unspecified). */
+int b200moe_moe_align_block_size(const void* topk_ids, b200moe_dtype ids_dtype,
+                                 int64_t numel, int num_experts,
+                                 int block_size, int32_t* sorted_token_ids,
+                                 int64_t sorted_len, int32_t* expert_ids,
+                                 int64_t expert_ids_len,
+                                 int32_t* num_tokens_post_pad,
+                                 const int32_t* expert_map, void* workspace,
+                                 size_t workspace_bytes,
+                                 b200moe_stream stream);
+
+/* Replaces `init_expert_map` (csrc/moe/init_expert_map.cpp:78-95; schema
+ * csrc/moe/torch_bindings.cpp:93-98). expert_map has num_local*ep_size ints. */
+int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,
+                            int ep_rank, int ep_size, b200moe_stream stream);
+
+/* Replaces `remap_hidden_states` (csrc/moe/remap_hidden_states.cpp:418-568;
+ * schema csrc/moe/torch_bindings.cpp:99-108).
+ * hidden [T,H] (elem_bytes per element: 1, 2 or 4), optional scales
+ * [T,scale_cols] (scale_elem_bytes each) -> remapped [T*K,H] expert-major,
+ * remapped_scales, rows_per_expert [E_local] i32,
+ * row_map (= unpermuted_row_to_permuted_row) [T,K] i32 (-1 = not local).
+ * Rows of one expert keep ascending (t,k) order. */
+int b200moe_remap_hidden_states(const void* hidden, const void* scales,
+                                void* remapped, void* remapped_scales,
+                                const int32_t* expert_map,
+                                int32_t* rows_per_expert, int32_t* row_map,
+                                const void* topk_ids, b200moe_dtype ids_dtype,
+                                int64_t num_rows, int hidden_size,
+                                int elem_bytes, int scale_cols,
+                                int scale_elem_bytes, int topk,
+                                int total_experts, int local_experts,
+                                void* workspace, size_t workspace_bytes,
+                                b200moe_stream stream);
+
+/* Fused permute + dynamic per-1x128 fp8 (e4m3) quantisation of bf16/f16
+ * activations: same bookkeeping as b200moe_remap_hidden_states, but the
+ * remapped rows are written as fp8 [T*K,H] with fp32 scales [T*K,H/128]
+ * (the math of b200moe_per_token_group_fp8_quant with group 128, eps 1e-10).
+ * No counterpart op in the reference: it runs `quant_fp8_block_act`
+ * (vllm_xpu_kernels/moe_utils.py:150-166) and `remap_hidden_states` as two
+ * steps. */
+int b200moe_remap_quant_fp8(const void* hidden, b200moe_dtype dtype,
+                            void* remapped_q, float* remapped_scales,
+                            const int32_t* expert_map,
+                            int32_t* rows_per_expert, int32_t* row_map,
+                            const void* topk_ids, b200moe_dtype ids_dtype,
+                            int64_t num_rows, int hidden_size, int topk,
+                            int total_experts, int local_experts,
+                            void* workspace, size_t workspace_bytes,
+                            b200moe_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Grouped GEMM                                                               */
+/* ------------------------------------------------------------------------- */
+
+typedef enum {
+  B200MOE_W_BF16_KN = 0,  /* 16-bit weights [E,K,N] (dtype = activation dtype)      */
+  B200MOE_W_BF16_NK = 1,  /* 16-bit weights [E,N,K]                                 */
+  B200MOE_W_FP8_TENSOR_KN = 2, /* fp8 e4m3 [E,K,N] + fp32 scale [E]                 */
+  B200MOE_W_FP8_BLOCK_NK = 3,  /* fp8 e4m3 [E,N,K] + fp32 scales [E,N/128,K/128]    */
+  B200MOE_W_FP8_BLOCK_KN = 4,  /* fp8 e4m3 [E,K,N] + same scales                    */
+  B200MOE_W_MXFP4_NK = 5  /* e2m1 pairs [E,N,K/2] + e8m0 bytes [E,N,K/32]           */
+} b200moe_weight_format;
+
+typedef enum {
+  B200MOE_EPI_NONE = 0,      /* D = acc (+bias)                                     */
+  B200MOE_EPI_SILU_MUL = 1,  /* D[m,i] = silu(acc[m,i]) * acc[m,I+i], D is [M,N/2]  */
+  B200MOE_EPI_SWIGLUOAI = 2  /* D[m,i] from acc[m,2i], acc[m,2i+1], D is [M,N/2]    */
+} b200moe_epilogue;
+
+/* Arguments of the grouped GEMM.  Replaces `cutlass_grouped_gemm_interface`
+ * (csrc/xpu/grouped_gemm/grouped_gemm_interface.cpp:12-60 ->
+ * xe_2/grouped_gemm_xe2_interface.hpp:162-431; schema
+ * csrc/xpu/torch_bindings.cpp:46-53).
+ * For each expert e with rows_e = rows_per_expert[e] > 0 and r0 = sum of the
+ * earlier experts' rows:  D[r0:r0+rows_e, :] = A[r0:r0+rows_e, :] * W_e^T
+ * (+ bias_e), fp32 accumulation, result cast to d_dtype. */
+typedef struct {
+  const void* a;          /* [M,K] a_dtype, row-major, 16-byte aligned            */
+  b200moe_dtype a_dtype;  /* BF16, F16, or FP8_E4M3 (with a_scale)                */
+  const float* a_scale;   /* fp8 activations: [M,K/128] fp32 row-major, else NULL */
+  const void* w;          /* weights, layout per w_format                         */
+  b200moe_weight_format w_format;
+  const void* w_scale;    /* per w_format, else NULL                              */
+  const void* bias;       /* [E,N] in d_dtype, or NULL                            */
+  void* d;                /* [M,N] (or [M,N/2] with a gated epilogue) d_dtype     */
+  b200moe_dtype d_dtype;  /* BF16 or F16                                          */
+  const int32_t* rows_per_expert; /* [E] device                                   */
+  int64_t m;              /* rows of A and D (upper bound of the rows in use)     */
+  int n, k, num_experts;
+  b200moe_epilogue epilogue;
+  float act_alpha, act_limit; /* SwigluOAI parameters                             */
+  float clamp_limit;      /* >0: gate=min(gate,L), up=clamp(up,-L,L) before the
+                             gated epilogue (only with a gated epilogue)          */
+  int32_t* status;        /* device int, written non-zero if a bounded wait gave
+                             up; may be NULL                                      */
+  int impl;               /* 0 = auto, 1 = tensor-core kernel, 2 = plain-CUDA
+                             checking kernel                                      */
+} b200moe_gemm_args;
+
+int b200moe_grouped_gemm(const b200moe_gemm_args* args, b200moe_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Activations, quantisation, reductions                                      */
+/* ------------------------------------------------------------------------- */
+
+/* Replaces `silu_and_mul` (csrc/activation.cpp:492-499, kernel :146-184;
+ * schema csrc/torch_bindings.cpp:80-81). in [rows,2d] -> out [rows,d]. */
+int b200moe_silu_and_mul(void* out, const void* in, b200moe_dtype dtype,
+                         int64_t rows, int d, b200moe_stream stream);
+
+/* Replaces `swigluoai_and_mul` (csrc/activation.cpp:683-689, kernel :313-346;
+ * schema csrc/torch_bindings.cpp:187-191). Interleaved gate/up. */
+int b200moe_swigluoai_and_mul(void* out, const void* in, b200moe_dtype dtype,
+                              int64_t rows, int d, float alpha, float limit,
+                              b200moe_stream stream);
+
+/* Replaces `per_token_group_fp8_quant` (csrc/quantization/fp8/fp8_quant.cpp:724-840,
+ * kernel :278-390; schema csrc/torch_bindings.cpp:170-177).
+ * x [rows,cols] -> q [rows,cols] e4m3, s [rows,cols/group] fp32 with element
+ * strides (s_stride_row, s_stride_col). */
+int b200moe_per_token_group_fp8_quant(const void* x, b200moe_dtype dtype,
+                                      void* q, float* s, int64_t rows,
+                                      int cols, int group_size, float eps,
+                                      int scale_ue8m0, int64_t s_stride_row,
+                                      int64_t s_stride_col,
+                                      b200moe_stream stream);
+
+/* Replaces `moe_gather` (csrc/moe/moe_gather.cpp:161-204; schema
+ * csrc/moe/torch_bindings.cpp:78-82).
+ * out[t,:] = sum_k w[t,k] * moe_out[row_map[t,k],:] (fp32), skipping -1. */
+int b200moe_moe_gather(void* out, const void* moe_out,
+                       const float* topk_weights, const int32_t* row_map,
+                       b200moe_dtype dtype, int64_t num_tokens, int hidden,
+                       int topk, b200moe_stream stream);
+
+/* Replaces `moe_sum` (csrc/moe/moe_align_sum_kernels.cpp:1224-1372; schema
+ * csrc/moe/torch_bindings.cpp:7-10).
+ * out[t,:] = sum_k in[t,k,:] (fp32); with topk_ids a slot is skipped when its
+ * id < 0 or expert_map[id] < 0. */
+int b200moe_moe_sum(void* out, const void* in, b200moe_dtype dtype,
+                    int64_t num_tokens, int topk, int hidden,
+                    const void* topk_ids, b200moe_dtype ids_dtype,
+                    const int32_t* expert_map, b200moe_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

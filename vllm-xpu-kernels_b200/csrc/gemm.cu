@@ -1,0 +1,60 @@
+// b200moe_grouped_gemm: argument checks (messages follow
+// csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:184-243, 267-287,
+// 322-383 of vllm-xpu-kernels) and the choice between the tensor-core kernel
+// and the plain-CUDA checking kernel.
+#include "common.cuh"
+
+namespace b200moe {
+int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st);
+int grouped_gemm_check(const b200moe_gemm_args* a, cudaStream_t st);
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream stream) {
+  B200_CHECK_ARG(a != nullptr, "grouped_gemm: null argument struct");
+  B200_CHECK_ARG(a->n % 8 == 0, "N must be divisible by 8");
+  B200_CHECK_ARG(a->m >= 0 && a->n >= 0 && a->k > 0 && a->num_experts >= 1,
+                 "grouped_gemm: bad sizes (m=%lld n=%d k=%d experts=%d)", (long long)a->m, a->n,
+                 a->k, a->num_experts);
+  B200_CHECK_ARG(a->d_dtype == B200MOE_BF16 || a->d_dtype == B200MOE_F16,
+                 "grouped_gemm: ptr_D must be bfloat16 or float16");
+  const bool a_fp8 = a->a_dtype == B200MOE_FP8_E4M3;
+  B200_CHECK_ARG(a_fp8 || a->a_dtype == a->d_dtype,
+                 "grouped_gemm: ptr_A must be fp8 (with scales) or have ptr_D's dtype");
+  switch (a->w_format) {
+    case B200MOE_W_BF16_KN:
+    case B200MOE_W_BF16_NK:
+      B200_CHECK_ARG(a->w_scale == nullptr, "w16a16 grouped gemm must not have scales");
+      B200_CHECK_ARG(!a_fp8, "grouped_gemm: fp8 activations need block-scaled fp8 weights");
+      break;
+    case B200MOE_W_FP8_TENSOR_KN:
+      B200_CHECK_ARG(a->w_scale != nullptr, "w8a16 grouped gemm must have scales");
+      B200_CHECK_ARG(!a_fp8, "grouped_gemm: fp8 activations need block-scaled fp8 weights");
+      break;
+    case B200MOE_W_FP8_BLOCK_NK:
+    case B200MOE_W_FP8_BLOCK_KN:
+      B200_CHECK_ARG(a->w_scale != nullptr, "w8a16 grouped gemm must have scales");
+      B200_CHECK_ARG(a->n % 128 == 0 && a->k % 128 == 0,
+                     "block-scaled grouped GEMM requires N and K divisible by 128");
+      B200_CHECK_ARG(!a_fp8 || a->a_scale != nullptr,
+                     "grouped_gemm: fp8 activations need ptr_A_scale [M, K / 128]");
+      break;
+    case B200MOE_W_MXFP4_NK:
+      B200_CHECK_ARG(a->w_scale != nullptr, "w8a16 grouped gemm must have scales");
+      B200_CHECK_ARG(a->k % 32 == 0, "group_size must be 32, 64, 128 or 256");
+      B200_CHECK_ARG(!a_fp8, "grouped_gemm: fp8 activations need block-scaled fp8 weights");
+      break;
+    default:
+      return fail(B200MOE_E_BADARG, "grouped_gemm: unknown weight format %d", (int)a->w_format);
+  }
+  B200_CHECK_ARG(a->epilogue == B200MOE_EPI_NONE || a->n % 2 == 0,
+                 "grouped_gemm: a gated epilogue needs an even N");
+  if (a->m == 0 || a->n == 0) return B200MOE_OK;
+  B200_CHECK_ARG(a->a && a->w && a->d && a->rows_per_expert, "grouped_gemm: null pointer");
+  cudaStream_t st = as_stream(stream);
+  if (a->impl == 2) return grouped_gemm_check(a, st);
+  int rc = grouped_gemm_tc(a, st);
+  if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) return grouped_gemm_check(a, st);
+  return rc;
+}

@@ -1,0 +1,512 @@
+// Grouped GEMM over ragged expert segments on the sm_100a tensor cores.
+//
+//   D[r0:r0+rows_e, :] = A[r0:r0+rows_e, :] * W_e^T (+ bias_e)      per expert e
+//
+// Orientation: the weight's output features are the 128-row M side of
+// tcgen05.mma and the tokens are its N side (16..256 wide), so a decode-sized
+// expert segment of a few rows costs a 16-column MMA instead of a 128-row one
+// while the weights stream through shared memory exactly once.  The fp32
+// accumulator therefore sits in tensor memory as [128 features (lanes)] x
+// [BT tokens (columns)].
+//
+// One persistent CTA per SM walks the tile list (expert, feature tile, token
+// tile) derived from rows_per_expert on the device — the host never reads it:
+//   warp 0  : TMA producer  (weights through a 3-D map [E, N, K], activations
+//             through a 2-D map [M, K]; 128-byte swizzle; ring of kStages)
+//   warp 1  : MMA issuer    (one lane), owns the tensor-memory allocation
+//   warps 2-5: epilogue     (tcgen05.ld -> registers -> global)
+// 16-bit inputs use kind::f16 with the whole K loop accumulated in tensor
+// memory (two accumulator stages, so the epilogue of one tile overlaps the
+// MMAs of the next).  fp8 inputs use kind::f8f6f4 per 128-wide K block; the
+// epilogue warps promote each block's partial sum into fp32 registers with
+// a_scale[row, kb] * w_scale[e, n/128, kb], as the block-scaled recipe needs.
+//
+// Every wait on an mbarrier is bounded (see sm100_ptx.cuh): on expiry the CTA
+// raises an abort flag, all roles leave their loops, tensor memory is freed and
+// *status is set to 1.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kFeat = 128;        // features per tile (UMMA M)
+constexpr int kWTileBytes = 16384;  // 128 rows x 128 bytes, or the same area K-by-N
+constexpr int kThreads = 192;
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxStages = 8;
+
+struct TcParams {
+  const float* a_scale;
+  const float* w_scale;
+  const void* bias;
+  void* d;
+  const int32_t* rows_per_expert;
+  int32_t* status;
+  int64_t m;
+  int n, k, num_experts;
+  int n_tiles;  // ceil(n / 128)
+  int num_kb;   // K blocks of 128 bytes
+  uint32_t idesc;
+  int out_f16;  // 1: D and bias are float16, 0: bfloat16
+};
+
+template <int BT>
+struct Ctrl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float sc[4][2][BT];  // per epilogue warp, double buffered
+  int tile_start[kMaxExperts + 1];
+  int row_start[kMaxExperts + 1];
+};
+
+template <int BT>
+__host__ __device__ constexpr int stage_bytes() { return kWTileBytes + BT * 128; }
+template <int BT>
+__host__ __device__ constexpr int num_stages() {
+  return (200 * 1024) / stage_bytes<BT>() > kMaxStages ? kMaxStages
+                                                        : (200 * 1024) / stage_bytes<BT>();
+}
+template <int BT>
+__host__ __device__ constexpr size_t smem_bytes() {
+  return 1024 + (size_t)num_stages<BT>() * stage_bytes<BT>() + sizeof(Ctrl<BT>);
+}
+template <int BT>
+__host__ __device__ constexpr uint32_t tmem_cols() {
+  return 2 * BT < 32 ? 32u : (uint32_t)(2 * BT);
+}
+
+struct TileInfo {
+  int e, n_tile, m_tile, row0, valid;
+};
+
+// Tiles of one expert are numbered feature-tile-major with the token tiles
+// adjacent, so CTAs that run at the same time share a weight tile in L2.
+template <int BT>
+__device__ __forceinline__ void locate_tile(const int* tile_start, const int* row_start, int t,
+                                            int& cursor, TileInfo& ti) {
+  while (t >= tile_start[cursor + 1]) ++cursor;
+  const int local = t - tile_start[cursor];
+  const int rows = row_start[cursor + 1] - row_start[cursor];
+  const int m_tiles = (rows + BT - 1) / BT;
+  ti.e = cursor;
+  ti.n_tile = local / m_tiles;
+  ti.m_tile = local - ti.n_tile * m_tiles;
+  ti.row0 = row_start[cursor] + ti.m_tile * BT;
+  const int left = rows - ti.m_tile * BT;
+  ti.valid = left < BT ? left : BT;
+}
+
+__device__ __forceinline__ void store_out(void* d, int out_f16, int64_t idx, float v) {
+  if (out_f16) reinterpret_cast<__half*>(d)[idx] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(d)[idx] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float load_bias(const void* b, int out_f16, int64_t idx) {
+  if (out_f16) return __half2float(reinterpret_cast<const __half*>(b)[idx]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[idx]);
+}
+
+template <int BT, bool kFp8, bool kWKn>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                       const __grid_constant__ CUtensorMap tmap_w, const TcParams p) {
+  static_assert(!kFp8 || BT <= 128, "fp8 promotion keeps BT accumulators per thread");
+  constexpr int kStages = num_stages<BT>();
+  constexpr int kStageBytes = stage_bytes<BT>();
+  constexpr int kElemsPerKb = kFp8 ? 128 : 64;  // K elements per 128-byte row
+  constexpr int kChunk = BT >= 32 ? 32 : 16;    // columns per tcgen05.ld
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  Ctrl<BT>* ctrl = reinterpret_cast<Ctrl<BT>*>(smem + kStages * kStageBytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (warp == 0) {
+    // Prefix sums over the experts: rows and tiles.
+    int carry_r = 0, carry_t = 0;
+    if (lane == 0) { ctrl->row_start[0] = 0; ctrl->tile_start[0] = 0; }
+    for (int base = 0; base < p.num_experts; base += 32) {
+      const int e = base + lane;
+      int r = (e < p.num_experts) ? p.rows_per_expert[e] : 0;
+      if (r < 0) r = 0;
+      int tl = ((r + BT - 1) / BT) * p.n_tiles;
+      int ir = r, it = tl;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o_r = __shfl_up_sync(0xffffffffu, ir, d);
+        const int o_t = __shfl_up_sync(0xffffffffu, it, d);
+        if (lane >= d) { ir += o_r; it += o_t; }
+      }
+      if (e < p.num_experts) {
+        ctrl->row_start[e + 1] = carry_r + ir;
+        ctrl->tile_start[e + 1] = carry_t + it;
+      }
+      carry_r += __shfl_sync(0xffffffffu, ir, 31);
+      carry_t += __shfl_sync(0xffffffffu, it, 31);
+    }
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_w);
+    }
+  } else if (warp == 1) {
+    ptx::tmem_alloc(&ctrl->tmem_base, tmem_cols<BT>());
+    ptx::tmem_relinquish();
+  } else if (warp == 2 && lane == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&ctrl->full[s], 1);
+      ptx::mbar_init(&ctrl->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&ctrl->acc_full[a], 1);
+      ptx::mbar_init(&ctrl->acc_empty[a], 4);
+    }
+    ctrl->abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const int total_tiles = ctrl->tile_start[p.num_experts];
+  const int* tile_start = ctrl->tile_start;
+  const int* row_start = ctrl->row_start;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      int cursor = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        TileInfo ti;
+        locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+        const int n0 = ti.n_tile * kFeat;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* wdst = smem + s * kStageBytes;
+          uint8_t* adst = wdst + kWTileBytes;
+          ptx::mbar_expect_tx(&ctrl->full[s], kStageBytes);
+          const int k0 = kb * kElemsPerKb;
+          if (!kWKn) {
+            ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], k0, n0, ti.e);
+          } else if (kFp8) {
+            ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], n0, k0, ti.e);
+          } else {
+            ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], n0, k0, ti.e);
+            ptx::tma_load_3d(wdst + kWTileBytes / 2, &tmap_w, &ctrl->full[s], n0 + 64, k0, ti.e);
+          }
+          ptx::tma_load_2d(adst, &tmap_a, &ctrl->full[s], k0, ti.row0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, acc_it = 0;
+      int cursor = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        TileInfo ti;
+        locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+        uint32_t a = acc_it & 1;
+        if (!kFp8) {
+          if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) break;
+          ptx::tc_fence_after();
+        }
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          if (kFp8) {
+            a = acc_it & 1;
+            if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          }
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t wbase = ptx::smem_u32(smem + s * kStageBytes);
+          const uint32_t abase = wbase + kWTileBytes;
+          const uint32_t d_tmem = tmem_base + a * BT;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint64_t wdesc;
+            if (!kWKn) wdesc = ptx::make_smem_desc(wbase + j * 32, 16, 1024);
+            else if (kFp8) wdesc = ptx::make_smem_desc(wbase + j * 4096, 16384, 1024);
+            else wdesc = ptx::make_smem_desc(wbase + j * 2048, 8192, 1024);
+            const uint64_t adesc = ptx::make_smem_desc(abase + j * 32, 16, 1024);
+            const uint32_t accumulate = kFp8 ? (j > 0) : (kb > 0 || j > 0);
+            ptx::umma<kFp8>(d_tmem, wdesc, adesc, p.idesc, accumulate);
+          }
+          ptx::umma_commit(&ctrl->empty[s]);
+          if (kFp8) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+        }
+        if (!kFp8 && ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int et = q * 32 + lane;           // feature row inside the tile
+    const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+    uint32_t acc_it = 0;
+    int cursor = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      TileInfo ti;
+      locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+      const int feat = ti.n_tile * kFeat + et;
+      const bool feat_ok = feat < p.n;
+      float bias_v = 0.f;
+      if (p.bias != nullptr && feat_ok) bias_v = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat);
+
+      if (!kFp8) {
+        const uint32_t a = acc_it & 1;
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
+          *abort_flag = 1; ok = false; break;
+        }
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < BT; c0 += kChunk) {
+          if (c0 < ti.valid) {
+            uint32_t v[kChunk];
+            if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
+            else ptx::tmem_ld_32x16(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
+            ptx::tmem_wait_ld();
+            if (feat_ok) {
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i) {
+                if (c0 + i < ti.valid && ti.row0 + c0 + i < p.m)
+                  store_out(p.d, p.out_f16, (int64_t)(ti.row0 + c0 + i) * p.n + feat,
+                            __uint_as_float(v[i]) + bias_v);
+              }
+            }
+          }
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
+        ++acc_it;
+      } else {
+        float acc[BT];
+#pragma unroll
+        for (int i = 0; i < BT; ++i) acc[i] = 0.f;
+        const int kbs = p.k / 128;  // scale blocks along K
+        const int64_t ws_base = ((int64_t)ti.e * (p.n / 128) + ti.n_tile) * kbs;
+        // Each warp stages its own copy of the BT combined scales of a K block
+        // (lane l owns tokens l, l+32, ..), so no barrier couples the warps.
+        constexpr int kPerLane = (BT + 31) / 32;
+        float next_sc[kPerLane];
+        auto fetch_scales = [&](int kb) {
+          const float ws = p.w_scale[ws_base + kb];
+#pragma unroll
+          for (int u = 0; u < kPerLane; ++u) {
+            const int c = lane + 32 * u;
+            const int row = ti.row0 + c;
+            next_sc[u] = (c < ti.valid && row < p.m) ? p.a_scale[(int64_t)row * kbs + kb] * ws : 0.f;
+          }
+        };
+        fetch_scales(0);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          float* sc = ctrl->sc[warp - 2][kb & 1];
+#pragma unroll
+          for (int u = 0; u < kPerLane; ++u)
+            if (lane + 32 * u < BT) sc[lane + 32 * u] = next_sc[u];
+          __syncwarp();
+          if (kb + 1 < p.num_kb) fetch_scales(kb + 1);
+          const uint32_t a = acc_it & 1;
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
+            *abort_flag = 1; ok = false; break;
+          }
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int c0 = 0; c0 < BT; c0 += kChunk) {
+            if (c0 < ti.valid) {
+              uint32_t v[kChunk];
+              if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
+              else ptx::tmem_ld_32x16(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
+              ptx::tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i)
+                acc[c0 + i] = fmaf(__uint_as_float(v[i]), sc[c0 + i], acc[c0 + i]);
+            }
+          }
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
+          ++acc_it;
+        }
+        if (ok && feat_ok) {
+#pragma unroll
+          for (int i = 0; i < BT; ++i) {
+            if (i < ti.valid && ti.row0 + i < p.m)
+              store_out(p.d, p.out_f16, (int64_t)(ti.row0 + i) * p.n + feat, acc[i] + bias_v);
+          }
+        }
+      }
+    }
+  }
+
+  // Teardown: everyone meets here, also after an aborted wait.
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    if (*abort_flag != 0) __nanosleep(20000);  // let copies still in flight land
+    ptx::tmem_dealloc(tmem_base, tmem_cols<BT>());
+  }
+  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+// ------------------------------ host side ------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,
+               const cuuint64_t* dims, const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return fail(B200MOE_E_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200MOE_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return B200MOE_OK;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BT, bool kFp8, bool kWKn>
+int launch_tc(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, int grid,
+              cudaStream_t st) {
+  auto kern = grouped_gemm_tc_kernel<BT, kFp8, kWKn>;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem_bytes<BT>()));
+    configured = true;
+  }
+  kern<<<grid, kThreads, smem_bytes<BT>(), st>>>(ta, tw, p);
+  B200_LAUNCH_OK("grouped_gemm_tc_kernel");
+  return B200MOE_OK;
+}
+
+}  // namespace
+
+// Returns B200MOE_E_UNSUPPORTED (without a launch) for requests the
+// tensor-core kernel does not cover; the caller decides what to do then.
+int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
+  const bool a_fp8 = a->a_dtype == B200MOE_FP8_E4M3;
+  const bool w16 = a->w_format == B200MOE_W_BF16_KN || a->w_format == B200MOE_W_BF16_NK;
+  const bool w8b = a->w_format == B200MOE_W_FP8_BLOCK_NK || a->w_format == B200MOE_W_FP8_BLOCK_KN;
+  if (a->epilogue != B200MOE_EPI_NONE)
+    return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: gated epilogues not available");
+  if (!((w16 && !a_fp8) || (w8b && a_fp8)))
+    return fail(B200MOE_E_UNSUPPORTED,
+                "tensor-core grouped GEMM takes 16-bit x 16-bit or fp8 x block-scaled fp8");
+  if (a->num_experts > kMaxExperts)
+    return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: more than %d experts", kMaxExperts);
+  const bool kn = a->w_format == B200MOE_W_BF16_KN || a->w_format == B200MOE_W_FP8_BLOCK_KN;
+  const int es = a_fp8 ? 1 : 2;
+  if (((int64_t)a->k * es) % 16 != 0 || ((int64_t)a->n * es) % 16 != 0)
+    return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: row pitch must be a multiple of 16 bytes");
+  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15))
+    return fail(B200MOE_E_BADARG, "grouped GEMM: A and W must be 16-byte aligned");
+  if (a->m == 0 || a->n == 0) return B200MOE_OK;
+
+  const int kpb = a_fp8 ? 128 : 64;
+  TcParams p;
+  p.a_scale = a->a_scale; p.w_scale = reinterpret_cast<const float*>(a->w_scale);
+  p.bias = a->bias; p.d = a->d; p.rows_per_expert = a->rows_per_expert; p.status = a->status;
+  p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
+  p.n_tiles = (a->n + kFeat - 1) / kFeat;
+  p.num_kb = (a->k + kpb - 1) / kpb;
+  p.out_f16 = a->d_dtype == B200MOE_F16;
+
+  const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
+  int bt;
+  if (avg <= 16) bt = 16;
+  else if (avg <= 64) bt = 64;
+  else if (avg <= 192 || a_fp8) bt = 128;
+  else bt = 256;
+
+  const uint32_t fmt = a_fp8 ? 0u : (a->a_dtype == B200MOE_BF16 ? 1u : 0u);
+  p.idesc = ptx::make_idesc(fmt, fmt, kn ? 1u : 0u, 0u, kFeat, (uint32_t)bt);
+
+  const CUtensorMapDataType dt = a_fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                       : (a->a_dtype == B200MOE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  CUtensorMap ta, tw;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)a->k, (cuuint64_t)a->m};
+    cuuint64_t strides[1] = {(cuuint64_t)a->k * es};
+    cuuint32_t box[2] = {(cuuint32_t)kpb, (cuuint32_t)bt};
+    int rc = encode_map(&ta, dt, 2, a->a, dims, strides, box);
+    if (rc) return rc;
+  }
+  if (!kn) {
+    cuuint64_t dims[3] = {(cuuint64_t)a->k, (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
+    cuuint64_t strides[2] = {(cuuint64_t)a->k * es, (cuuint64_t)a->k * a->n * es};
+    cuuint32_t box[3] = {(cuuint32_t)kpb, (cuuint32_t)kFeat, 1};
+    int rc = encode_map(&tw, dt, 3, a->w, dims, strides, box);
+    if (rc) return rc;
+  } else {
+    cuuint64_t dims[3] = {(cuuint64_t)a->n, (cuuint64_t)a->k, (cuuint64_t)a->num_experts};
+    cuuint64_t strides[2] = {(cuuint64_t)a->n * es, (cuuint64_t)a->k * a->n * es};
+    cuuint32_t box[3] = {(cuuint32_t)(a_fp8 ? 128 : 64), (cuuint32_t)kpb, 1};
+    int rc = encode_map(&tw, dt, 3, a->w, dims, strides, box);
+    if (rc) return rc;
+  }
+
+  const int64_t tile_bound = ((a->m + bt - 1) / bt + a->num_experts) * (int64_t)p.n_tiles;
+  int grid = sm_count();
+  if (tile_bound < grid) grid = (int)tile_bound;
+  if (grid < 1) grid = 1;
+
+#define B200_TC_CASE(BT_)                                                         \
+  if (bt == BT_) {                                                                \
+    if (a_fp8) {                                                                  \
+      if (kn) return launch_tc<(BT_ > 128 ? 128 : BT_), true, true>(ta, tw, p, grid, st);  \
+      return launch_tc<(BT_ > 128 ? 128 : BT_), true, false>(ta, tw, p, grid, st);         \
+    }                                                                             \
+    if (kn) return launch_tc<BT_, false, true>(ta, tw, p, grid, st);              \
+    return launch_tc<BT_, false, false>(ta, tw, p, grid, st);                     \
+  }
+  B200_TC_CASE(16)
+  B200_TC_CASE(64)
+  B200_TC_CASE(128)
+  B200_TC_CASE(256)
+#undef B200_TC_CASE
+  return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: no tile for %d", bt);
+}
+
+}  // namespace b200moe

@@ -1,0 +1,582 @@
+// Token -> expert bookkeeping: moe_align_block_size, remap_hidden_states,
+// init_expert_map and the fused permute + fp8 group quantisation.
+//
+// Both ops are a stable counting sort of the T*K routed slots by (mapped)
+// expert id.  The slots are cut into chunks of 256 handled by one warp each:
+//   1. count : every warp builds a histogram of its chunk,
+//   2. scan  : per expert an exclusive scan over the chunks, then a scan over
+//              the experts (padded to block_size for the align op),
+//   3. rank  : every warp walks its chunk 32 slots at a time; the rank of a
+//              slot among equal ids in the same step comes from
+//              __match_any_sync, so slots of one expert keep ascending order.
+// Up to 2048 slots all three steps run in one block without any scratch;
+// beyond that they are three launches that exchange the histograms through a
+// caller-provided workspace.  The result is deterministic: no atomics decide
+// an order.
+//
+// Semantics follow csrc/moe/moe_align_sum_kernels.cpp:135-273, 1034-1181 and
+// csrc/moe/remap_hidden_states.cpp:42-116, 181-330 of vllm-xpu-kernels, which
+// leave the order inside an expert unspecified.
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kChunk = 256;          // slots per warp
+constexpr int kBlockThreads = 256;   // 8 warps
+constexpr int kWarps = kBlockThreads / 32;
+constexpr int kBlockSlots = kChunk * kWarps;  // 2048
+constexpr int kMaxBuckets = 1024;
+
+struct SortParams {
+  const void* ids;
+  b200moe_dtype ids_dtype;
+  const int32_t* map;  // optional id -> bucket map
+  int64_t numel;
+  int id_limit;        // ids >= id_limit (or < 0) are dropped
+  int n_buckets;
+  int block_size;      // align: pad every bucket to a multiple of this; remap: 1
+};
+
+__device__ __forceinline__ int bucket_of(const SortParams& p, int64_t i) {
+  int64_t e;
+  switch (p.ids_dtype) {
+    case B200MOE_I64: e = reinterpret_cast<const int64_t*>(p.ids)[i]; break;
+    case B200MOE_U32: e = reinterpret_cast<const uint32_t*>(p.ids)[i]; break;
+    default: e = reinterpret_cast<const int32_t*>(p.ids)[i]; break;
+  }
+  if (e < 0 || e >= p.id_limit) return -1;
+  int b = (int)e;
+  if (p.map != nullptr) b = p.map[b];
+  if (b < 0 || b >= p.n_buckets) return -1;
+  return b;
+}
+
+// In-place exclusive scan of data[0..n) (n <= 1024, shared memory) by a block
+// of kBlockThreads threads; data[n] receives the total.  `warp_tot` is scratch
+// for kWarps ints.
+__device__ void block_exclusive_scan(int* data, int n, int* warp_tot) {
+  const int t = threadIdx.x;
+  const int lane = t & 31, warp = t >> 5;
+  int x[4];
+  int local = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int idx = 4 * t + j;
+    x[j] = (idx < n) ? data[idx] : 0;
+    local += x[j];
+  }
+  int incl = local;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += o;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  int base = 0;
+  for (int w = 0; w < warp; ++w) base += warp_tot[w];
+  int run = base + incl - local;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int idx = 4 * t + j;
+    if (idx < n) data[idx] = run;
+    run += x[j];
+  }
+  if (t == kBlockThreads - 1) data[n] = run;
+  __syncthreads();
+}
+
+// Walks one warp's chunk and calls emit(slot, bucket, position) for every
+// slot; `run` (shared, per warp, n_buckets ints) holds the next free position
+// of each bucket for this warp and is advanced as the walk proceeds.
+template <typename Emit>
+__device__ __forceinline__ void rank_walk(const SortParams& p, int64_t chunk_begin,
+                                          int* run, Emit emit) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t lt = (1u << lane) - 1u;
+  for (int step = 0; step < kChunk / 32; ++step) {
+    const int64_t i = chunk_begin + step * 32 + lane;
+    const bool in = i < p.numel;
+    const int b = in ? bucket_of(p, i) : -1;
+    // Lanes without a bucket use distinct keys so they never match a real one.
+    const int key = (b >= 0) ? b : (kMaxBuckets + lane);
+    const uint32_t peers = __match_any_sync(0xffffffffu, key);
+    int pos = -1;
+    if (b >= 0) pos = run[b] + __popc(peers & lt);
+    __syncwarp();
+    if (b >= 0 && (peers & lt) == 0) run[b] += __popc(peers);
+    __syncwarp();
+    if (in) emit(i, b, pos);
+  }
+}
+
+// ------------------------- single-block path --------------------------------
+// mode 0: align (sorted ids, expert ids, post-pad count);
+// mode 1: remap (rows_per_expert, row map).
+struct AlignOut {
+  int32_t* sorted; int64_t sorted_len;
+  int32_t* expert_ids; int64_t expert_ids_len;
+  int32_t* post_pad;
+};
+struct RemapOut {
+  int32_t* rows_per_expert;
+  int32_t* row_map;
+};
+
+template <int kMode>
+__global__ void __launch_bounds__(kBlockThreads)
+sort_single_block_kernel(SortParams p, AlignOut ao, RemapOut ro) {
+  extern __shared__ int smem[];
+  int* hist = smem;                              // [kWarps][n_buckets]
+  int* base = hist + kWarps * p.n_buckets;       // [n_buckets + 1]
+  int* warp_tot = base + p.n_buckets + 1;        // [kWarps]
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int nb = p.n_buckets;
+
+  for (int i = t; i < kWarps * nb; i += kBlockThreads) hist[i] = 0;
+  if (kMode == 0) {
+    for (int64_t i = t; i < ao.sorted_len; i += kBlockThreads) ao.sorted[i] = (int32_t)p.numel;
+  }
+  __syncthreads();
+  {
+    const int64_t begin = (int64_t)warp * kChunk;
+    for (int s = 0; s < kChunk / 32; ++s) {
+      const int64_t i = begin + s * 32 + lane;
+      if (i < p.numel) {
+        const int b = bucket_of(p, i);
+        if (b >= 0) atomicAdd(&hist[warp * nb + b], 1);
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = t; e < nb; e += kBlockThreads) {
+    int run = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = hist[w * nb + e];
+      hist[w * nb + e] = run;
+      run += c;
+    }
+    if (kMode == 1) ro.rows_per_expert[e] = run;
+    base[e] = (kMode == 0) ? ((run + p.block_size - 1) / p.block_size) * p.block_size : run;
+  }
+  __syncthreads();
+  int padded[4];  // align: remember the padded sizes for expert_ids
+#pragma unroll
+  for (int j = 0; j < 4; ++j) padded[j] = (4 * t + j < nb) ? base[4 * t + j] : 0;
+  block_exclusive_scan(base, nb, warp_tot);
+  if (kMode == 0) {
+    const int total = base[nb];
+    if (t == 0) ao.post_pad[0] = total;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = 4 * t + j;
+      if (e < nb) {
+        for (int o = 0; o < padded[j]; o += p.block_size) {
+          const int64_t blk = (base[e] + o) / p.block_size;
+          if (blk < ao.expert_ids_len) ao.expert_ids[blk] = e;
+        }
+      }
+    }
+    for (int64_t blk = total / p.block_size + t; blk < ao.expert_ids_len; blk += kBlockThreads)
+      ao.expert_ids[blk] = 0;
+  }
+  // hist[w][e] += base[e]  -> absolute next-free position per warp and bucket
+  for (int i = t; i < kWarps * nb; i += kBlockThreads) hist[i] += base[i % nb];
+  __syncthreads();
+  rank_walk(p, (int64_t)warp * kChunk, hist + warp * nb,
+            [&](int64_t i, int b, int pos) {
+              if (kMode == 0) {
+                if (b >= 0 && pos < ao.sorted_len) ao.sorted[pos] = (int32_t)i;
+              } else {
+                ro.row_map[i] = pos;  // -1 when the slot has no local expert
+              }
+            });
+}
+
+// ------------------------- multi-block path ---------------------------------
+// workspace: counts[n_buckets][n_chunks] ints, then base[n_buckets + 1] ints.
+__global__ void __launch_bounds__(kBlockThreads)
+sort_count_kernel(SortParams p, int n_chunks, int* counts, int32_t* fill,
+                  int64_t fill_len) {
+  extern __shared__ int smem[];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int nb = p.n_buckets;
+  int* hist = smem + warp * nb;
+  for (int i = t; i < kWarps * nb; i += kBlockThreads) smem[i] = 0;
+  if (fill != nullptr) {
+    for (int64_t i = (int64_t)blockIdx.x * kBlockThreads + t; i < fill_len;
+         i += (int64_t)gridDim.x * kBlockThreads)
+      fill[i] = (int32_t)p.numel;
+  }
+  __syncthreads();
+  const int chunk = blockIdx.x * kWarps + warp;
+  const int64_t begin = (int64_t)chunk * kChunk;
+  for (int s = 0; s < kChunk / 32; ++s) {
+    const int64_t i = begin + s * 32 + lane;
+    if (i < p.numel) {
+      const int b = bucket_of(p, i);
+      if (b >= 0) atomicAdd(&hist[b], 1);
+    }
+  }
+  __syncwarp();
+  if (chunk < n_chunks) {
+    for (int e = lane; e < nb; e += 32) counts[(int64_t)e * n_chunks + chunk] = hist[e];
+  }
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(1024)
+sort_scan_kernel(SortParams p, int n_chunks, int* counts, int* base_out,
+                 AlignOut ao, RemapOut ro) {
+  __shared__ int base[kMaxBuckets + 1];
+  __shared__ int sizes[kMaxBuckets];
+  __shared__ int warp_tot[32];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int nb = p.n_buckets;
+  // One warp per expert: exclusive scan over the chunks, 32 at a time.
+  for (int e = warp; e < nb; e += 32) {
+    int* row = counts + (int64_t)e * n_chunks;
+    int carry = 0;
+    for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+      const int c = c0 + lane;
+      const int x = (c < n_chunks) ? row[c] : 0;
+      int incl = x;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      if (c < n_chunks) row[c] = carry + incl - x;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      if (kMode == 1) ro.rows_per_expert[e] = carry;
+      sizes[e] = (kMode == 0) ? ((carry + p.block_size - 1) / p.block_size) * p.block_size : carry;
+    }
+  }
+  __syncthreads();
+  // Exclusive scan over the experts (1024 threads, one value each).
+  {
+    const int x = (t < nb) ? sizes[t] : 0;
+    int incl = x;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int b0 = 0;
+    for (int w = 0; w < warp; ++w) b0 += warp_tot[w];
+    if (t < nb) base[t] = b0 + incl - x;
+    if (t == 1023) base[nb] = b0 + incl;
+    __syncthreads();
+  }
+  for (int e = t; e <= nb; e += 1024) base_out[e] = base[e];
+  if (kMode == 0) {
+    const int total = base[nb];
+    if (t == 0) ao.post_pad[0] = total;
+    for (int e = t; e < nb; e += 1024) {
+      for (int o = 0; o < sizes[e]; o += p.block_size) {
+        const int64_t blk = (base[e] + o) / p.block_size;
+        if (blk < ao.expert_ids_len) ao.expert_ids[blk] = e;
+      }
+    }
+    for (int64_t blk = total / p.block_size + t; blk < ao.expert_ids_len; blk += 1024)
+      ao.expert_ids[blk] = 0;
+  }
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kBlockThreads)
+sort_rank_kernel(SortParams p, int n_chunks, const int* counts, const int* base,
+                 AlignOut ao, RemapOut ro) {
+  extern __shared__ int smem[];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int nb = p.n_buckets;
+  int* run = smem + warp * nb;
+  const int chunk = blockIdx.x * kWarps + warp;
+  if (chunk < n_chunks) {
+    for (int e = lane; e < nb; e += 32) run[e] = base[e] + counts[(int64_t)e * n_chunks + chunk];
+  }
+  __syncwarp();
+  if (chunk >= n_chunks) return;
+  rank_walk(p, (int64_t)chunk * kChunk, run, [&](int64_t i, int b, int pos) {
+    if (kMode == 0) {
+      if (b >= 0 && pos < ao.sorted_len) ao.sorted[pos] = (int32_t)i;
+    } else {
+      ro.row_map[i] = pos;
+    }
+  });
+}
+
+template <int kMode>
+int run_sort(const SortParams& p, const AlignOut& ao, const RemapOut& ro,
+             void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  const int nb = p.n_buckets;
+  if (p.numel <= kBlockSlots) {
+    const size_t smem = (size_t)(kWarps * nb + nb + 1 + kWarps) * sizeof(int);
+    sort_single_block_kernel<kMode><<<1, kBlockThreads, smem, st>>>(p, ao, ro);
+    B200_LAUNCH_OK("sort_single_block_kernel");
+    return B200MOE_OK;
+  }
+  const size_t need = b200moe_sort_workspace_bytes(p.numel, nb);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(B200MOE_E_WORKSPACE, "workspace of %zu bytes needed, got %zu", need,
+                workspace_bytes);
+  const int n_chunks = (int)((p.numel + kChunk - 1) / kChunk);
+  const int n_blocks = (n_chunks + kWarps - 1) / kWarps;
+  int* counts = reinterpret_cast<int*>(workspace);
+  int* base = counts + (size_t)nb * n_chunks;
+  const size_t smem = (size_t)kWarps * nb * sizeof(int);
+  sort_count_kernel<<<n_blocks, kBlockThreads, smem, st>>>(
+      p, n_chunks, counts, kMode == 0 ? ao.sorted : nullptr, kMode == 0 ? ao.sorted_len : 0);
+  B200_LAUNCH_OK("sort_count_kernel");
+  sort_scan_kernel<kMode><<<1, 1024, 0, st>>>(p, n_chunks, counts, base, ao, ro);
+  B200_LAUNCH_OK("sort_scan_kernel");
+  sort_rank_kernel<kMode><<<n_blocks, kBlockThreads, smem, st>>>(p, n_chunks, counts, base, ao, ro);
+  B200_LAUNCH_OK("sort_rank_kernel");
+  return B200MOE_OK;
+}
+
+// ------------------------- row copy ------------------------------------------
+// One block per token: the row is read once and written to its K destinations.
+__global__ void __launch_bounds__(256)
+remap_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                  const uint8_t* __restrict__ src_s, uint8_t* __restrict__ dst_s,
+                  const int32_t* __restrict__ row_map, int row_bytes,
+                  int scale_row_bytes, int K) {
+  const int64_t tok = blockIdx.x;
+  __shared__ int dest[32];
+  if (threadIdx.x < K) dest[threadIdx.x] = row_map[tok * K + threadIdx.x];
+  __syncthreads();
+  const uint8_t* s = src + tok * (int64_t)row_bytes;
+  const int nvec = row_bytes >> 4;
+  for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+    const vec16 v = ld16(s + (int64_t)j * 16);
+    for (int k = 0; k < K; ++k) {
+      const int r = dest[k];
+      if (r >= 0) st16(dst + (int64_t)r * row_bytes + (int64_t)j * 16, v);
+    }
+  }
+  if (src_s != nullptr) {
+    const uint8_t* ss = src_s + tok * (int64_t)scale_row_bytes;
+    if ((scale_row_bytes & 3) == 0) {
+      for (int j = threadIdx.x; j < (scale_row_bytes >> 2); j += blockDim.x) {
+        const uint32_t v = reinterpret_cast<const uint32_t*>(ss)[j];
+        for (int k = 0; k < K; ++k) {
+          const int r = dest[k];
+          if (r >= 0) reinterpret_cast<uint32_t*>(dst_s + (int64_t)r * scale_row_bytes)[j] = v;
+        }
+      }
+    } else {
+      for (int j = threadIdx.x; j < scale_row_bytes; j += blockDim.x) {
+        const uint8_t v = ss[j];
+        for (int k = 0; k < K; ++k) {
+          const int r = dest[k];
+          if (r >= 0) dst_s[(int64_t)r * scale_row_bytes + j] = v;
+        }
+      }
+    }
+  }
+}
+
+// Row copy fused with the per-1x128 dynamic e4m3 quantisation.  A lane holds 8
+// consecutive elements, 16 lanes cover one 128-wide group.
+template <typename T>
+__global__ void __launch_bounds__(256)
+remap_quant_kernel(const T* __restrict__ src, uint8_t* __restrict__ dst_q,
+                   float* __restrict__ dst_s, const int32_t* __restrict__ row_map,
+                   int H, int K) {
+  const int64_t tok = blockIdx.x;
+  __shared__ int dest[32];
+  if (threadIdx.x < K) dest[threadIdx.x] = row_map[tok * K + threadIdx.x];
+  __syncthreads();
+  const T* s = src + tok * (int64_t)H;
+  const int groups = H / 128;
+  const int nvec = H / 8;
+  // Full warps iterate together so the 16-lane shuffles stay converged.
+  for (int j0 = (threadIdx.x & ~31); j0 < nvec; j0 += blockDim.x) {
+    const int j = j0 + (threadIdx.x & 31);
+    float x[8];
+    float amax = 0.f;
+    if (j < nvec) {
+      const vec16 v = ld16(s + (int64_t)j * 8);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { x[i] = to_f32<T>(e[i]); amax = fmaxf(amax, fabsf(x[i])); }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = 0.f;
+    }
+#pragma unroll
+    for (int mask = 8; mask > 0; mask >>= 1)
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, mask));
+    amax = fmaxf(amax, 1e-10f);
+    const float scale = fmaxf(__fdiv_rn(amax, 448.f), 1.0f / (448.f * 512.f));
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (j < nvec) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float q = fminf(fmaxf(__fmul_rn(x[i], inv), -448.f), 448.f);
+        lo |= (uint32_t)f32_to_e4m3(q) << (8 * i);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float q = fminf(fmaxf(__fmul_rn(x[4 + i], inv), -448.f), 448.f);
+        hi |= (uint32_t)f32_to_e4m3(q) << (8 * i);
+      }
+      const int g = j / 16;
+      for (int k = 0; k < K; ++k) {
+        const int r = dest[k];
+        if (r >= 0) {
+          *reinterpret_cast<uint2*>(dst_q + (int64_t)r * H + (int64_t)j * 8) = make_uint2(lo, hi);
+          if ((j & 15) == 0) dst_s[(int64_t)r * groups + g] = scale;
+        }
+      }
+    }
+  }
+}
+
+__global__ void init_expert_map_kernel(int32_t* map, int n_local, int ep_rank, int total) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g < total) {
+    const int lo = ep_rank * n_local;
+    map[g] = (g >= lo && g < lo + n_local) ? g - lo : -1;
+  }
+}
+
+int check_ids_dtype(b200moe_dtype t, const char* name) {
+  if (t == B200MOE_I32 || t == B200MOE_I64 || t == B200MOE_U32) return 0;
+  return fail(B200MOE_E_BADARG, "%s: topk_ids must be int64 or int32", name);
+}
+
+int remap_bookkeeping(const int32_t* expert_map, int32_t* rows_per_expert,
+                      int32_t* row_map, const void* topk_ids, b200moe_dtype ids_dtype,
+                      int64_t num_rows, int topk, int total_experts, int local_experts,
+                      void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (check_ids_dtype(ids_dtype, "remap_hidden_states")) return B200MOE_E_BADARG;
+  B200_CHECK_ARG(topk >= 1 && topk <= 32, "Unsupported TopK value");
+  B200_CHECK_ARG(local_experts >= 1 && local_experts <= kMaxBuckets,
+                 "local_experts_num exceeds the maximum supported number");
+  B200_CHECK_ARG(rows_per_expert && row_map && topk_ids, "remap_hidden_states: null pointer");
+  SortParams p;
+  p.ids = topk_ids; p.ids_dtype = ids_dtype; p.map = expert_map;
+  p.numel = num_rows * topk;
+  p.id_limit = expert_map ? total_experts : local_experts;
+  p.n_buckets = local_experts;
+  p.block_size = 1;
+  AlignOut ao = {};
+  RemapOut ro = {rows_per_expert, row_map};
+  return run_sort<1>(p, ao, ro, workspace, workspace_bytes, st);
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" size_t b200moe_sort_workspace_bytes(int64_t numel, int num_experts) {
+  if (numel <= kBlockSlots) return 0;
+  const int64_t n_chunks = (numel + kChunk - 1) / kChunk;
+  const size_t ints = (size_t)num_experts * n_chunks + num_experts + 1;
+  return (ints * sizeof(int) + 255) & ~(size_t)255;
+}
+
+extern "C" int b200moe_moe_align_block_size(
+    const void* topk_ids, b200moe_dtype ids_dtype, int64_t numel, int num_experts,
+    int block_size, int32_t* sorted_token_ids, int64_t sorted_len, int32_t* expert_ids,
+    int64_t expert_ids_len, int32_t* num_tokens_post_pad, const int32_t* expert_map,
+    void* workspace, size_t workspace_bytes, b200moe_stream stream) {
+  B200_CHECK_ARG(ids_dtype == B200MOE_I32 || ids_dtype == B200MOE_I64 || ids_dtype == B200MOE_U32,
+                 "moe_align_block_size: topk_ids must be an integer tensor");
+  B200_CHECK_ARG(num_experts >= 1 && ((num_experts + 31) / 32) * 32 < 1024,
+                 "padded_num_experts must be less than 1024");
+  B200_CHECK_ARG(block_size >= 1, "moe_align_block_size: block_size must be positive");
+  B200_CHECK_ARG(numel >= 0 && sorted_len >= 0 && expert_ids_len >= 0,
+                 "moe_align_block_size: negative size");
+  B200_CHECK_ARG(sorted_token_ids && expert_ids && num_tokens_post_pad,
+                 "moe_align_block_size: null output");
+  B200_CHECK_ARG(numel == 0 || topk_ids, "moe_align_block_size: null topk_ids");
+  SortParams p;
+  p.ids = topk_ids; p.ids_dtype = ids_dtype; p.map = expert_map;
+  p.numel = numel; p.id_limit = num_experts; p.n_buckets = num_experts;
+  p.block_size = block_size;
+  AlignOut ao = {sorted_token_ids, sorted_len, expert_ids, expert_ids_len, num_tokens_post_pad};
+  RemapOut ro = {};
+  return run_sort<0>(p, ao, ro, workspace, workspace_bytes, as_stream(stream));
+}
+
+extern "C" int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,
+                                       int ep_rank, int ep_size, b200moe_stream stream) {
+  B200_CHECK_ARG(expert_map, "init_expert_map: null pointer");
+  B200_CHECK_ARG(num_local_experts >= 1 && ep_size >= 1 && ep_rank >= 0 && ep_rank < ep_size,
+                 "init_expert_map: bad ep_rank/ep_size");
+  const int total = num_local_experts * ep_size;
+  init_expert_map_kernel<<<(total + 255) / 256, 256, 0, as_stream(stream)>>>(
+      expert_map, num_local_experts, ep_rank, total);
+  B200_LAUNCH_OK("init_expert_map_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_remap_hidden_states(
+    const void* hidden, const void* scales, void* remapped, void* remapped_scales,
+    const int32_t* expert_map, int32_t* rows_per_expert, int32_t* row_map,
+    const void* topk_ids, b200moe_dtype ids_dtype, int64_t num_rows, int hidden_size,
+    int elem_bytes, int scale_cols, int scale_elem_bytes, int topk, int total_experts,
+    int local_experts, void* workspace, size_t workspace_bytes, b200moe_stream stream) {
+  B200_CHECK_ARG(elem_bytes == 1 || elem_bytes == 2 || elem_bytes == 4,
+                 "Unsupported data type in hidden_states");
+  B200_CHECK_ARG((scales == nullptr) == (remapped_scales == nullptr),
+                 "if hidden_states_scales is provided, remapped_hidden_states_scales "
+                 "must also be provided");
+  B200_CHECK_ARG(((int64_t)hidden_size * elem_bytes) % 16 == 0,
+                 "hidden_size must be divisible by ElemsPerItem");
+  B200_CHECK_ARG(num_rows >= 0, "remap_hidden_states: negative num_rows");
+  cudaStream_t st = as_stream(stream);
+  int rc = remap_bookkeeping(expert_map, rows_per_expert, row_map, topk_ids, ids_dtype,
+                             num_rows, topk, total_experts, local_experts, workspace,
+                             workspace_bytes, st);
+  if (rc != B200MOE_OK || num_rows == 0) return rc;
+  B200_CHECK_ARG(hidden && remapped, "remap_hidden_states: null pointer");
+  B200_CHECK_ARG(((uintptr_t)hidden & 15) == 0 && ((uintptr_t)remapped & 15) == 0,
+                 "remap_hidden_states: buffers must be 16-byte aligned");
+  remap_copy_kernel<<<(unsigned)num_rows, 256, 0, st>>>(
+      (const uint8_t*)hidden, (uint8_t*)remapped, (const uint8_t*)scales,
+      (uint8_t*)remapped_scales, row_map, hidden_size * elem_bytes,
+      scale_cols * scale_elem_bytes, topk);
+  B200_LAUNCH_OK("remap_copy_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_remap_quant_fp8(
+    const void* hidden, b200moe_dtype dtype, void* remapped_q, float* remapped_scales,
+    const int32_t* expert_map, int32_t* rows_per_expert, int32_t* row_map,
+    const void* topk_ids, b200moe_dtype ids_dtype, int64_t num_rows, int hidden_size,
+    int topk, int total_experts, int local_experts, void* workspace,
+    size_t workspace_bytes, b200moe_stream stream) {
+  B200_CHECK_ARG(dtype == B200MOE_BF16 || dtype == B200MOE_F16,
+                 "remap_quant_fp8: activations must be bfloat16 or float16");
+  B200_CHECK_ARG(hidden_size % 128 == 0, "remap_quant_fp8: hidden_size must be a multiple of 128");
+  cudaStream_t st = as_stream(stream);
+  int rc = remap_bookkeeping(expert_map, rows_per_expert, row_map, topk_ids, ids_dtype,
+                             num_rows, topk, total_experts, local_experts, workspace,
+                             workspace_bytes, st);
+  if (rc != B200MOE_OK || num_rows == 0) return rc;
+  B200_CHECK_ARG(hidden && remapped_q && remapped_scales, "remap_quant_fp8: null pointer");
+  B200_CHECK_ARG(((uintptr_t)hidden & 15) == 0 && ((uintptr_t)remapped_q & 7) == 0,
+                 "remap_quant_fp8: buffers must be 16-byte aligned");
+  if (dtype == B200MOE_BF16)
+    remap_quant_kernel<__nv_bfloat16><<<(unsigned)num_rows, 256, 0, st>>>(
+        (const __nv_bfloat16*)hidden, (uint8_t*)remapped_q, remapped_scales, row_map,
+        hidden_size, topk);
+  else
+    remap_quant_kernel<__half><<<(unsigned)num_rows, 256, 0, st>>>(
+        (const __half*)hidden, (uint8_t*)remapped_q, remapped_scales, row_map, hidden_size,
+        topk);
+  B200_LAUNCH_OK("remap_quant_kernel");
+  return B200MOE_OK;
+}

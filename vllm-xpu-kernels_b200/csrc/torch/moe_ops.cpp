@@ -1,0 +1,338 @@
+// torch.ops._moe_C.*: routing, alignment, permutation and top-k reductions.
+// Schemas are the ones of csrc/moe/torch_bindings.cpp in vllm-xpu-kernels
+// (registered there for the XPU dispatch key; here for CUDA).
+#include "shim.h"
+
+using namespace b200shim;
+
+namespace {
+
+void topk_softmax(at::Tensor& topk_weights, at::Tensor& topk_indices,
+                  at::Tensor& token_expert_indices, at::Tensor& gating_output,
+                  bool renormalize, std::optional<at::Tensor> bias) {
+  check_cuda(gating_output, "gating_output");
+  const int num_experts = gating_output.size(-1);
+  const int64_t num_tokens = num_experts ? gating_output.numel() / num_experts : 0;
+  const int topk = topk_weights.size(-1);
+  TORCH_CHECK(topk_indices.scalar_type() == at::kInt || topk_indices.scalar_type() == at::kUInt32 ||
+              topk_indices.scalar_type() == at::kLong,
+              "topk_indices must be int32, uint32 or int64");
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, "topk_weights must be float32");
+  TORCH_CHECK(gating_output.is_contiguous() && topk_weights.is_contiguous() &&
+              topk_indices.is_contiguous() && token_expert_indices.is_contiguous(),
+              "topk_softmax expects contiguous tensors");
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->is_contiguous(), "bias must be contiguous float32");
+  const c10::cuda::CUDAGuard guard(gating_output.device());
+  check_status(b200moe_topk_softmax(
+      topk_weights.data_ptr<float>(), topk_indices.data_ptr(), index_dtype(topk_indices),
+      token_expert_indices.data_ptr<int32_t>(), gating_output.data_ptr(),
+      float_dtype(gating_output, "topk_softmax"), num_tokens, num_experts, topk, renormalize,
+      bias.has_value() ? bias->data_ptr<float>() : nullptr, current_stream()));
+}
+
+void topk_sigmoid(at::Tensor& topk_weights, at::Tensor& topk_indices,
+                  at::Tensor& token_expert_indices, at::Tensor& gating_output,
+                  bool renormalize, std::optional<at::Tensor> bias,
+                  double routed_scaling_factor) {
+  check_cuda(gating_output, "gating_output");
+  const int num_experts = gating_output.size(-1);
+  const int64_t num_tokens = num_experts ? gating_output.numel() / num_experts : 0;
+  const int topk = topk_weights.size(-1);
+  TORCH_CHECK(topk_indices.scalar_type() == at::kInt || topk_indices.scalar_type() == at::kUInt32 ||
+              topk_indices.scalar_type() == at::kLong,
+              "topk_indices must be int32, uint32 or int64");
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, "topk_weights must be float32");
+  TORCH_CHECK(gating_output.is_contiguous() && topk_weights.is_contiguous() &&
+              topk_indices.is_contiguous() && token_expert_indices.is_contiguous(),
+              "topk_sigmoid expects contiguous tensors");
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->is_contiguous(), "bias must be contiguous float32");
+  const c10::cuda::CUDAGuard guard(gating_output.device());
+  check_status(b200moe_topk_sigmoid(
+      topk_weights.data_ptr<float>(), topk_indices.data_ptr(), index_dtype(topk_indices),
+      token_expert_indices.data_ptr<int32_t>(), gating_output.data_ptr(),
+      float_dtype(gating_output, "topk_sigmoid"), num_tokens, num_experts, topk, renormalize,
+      bias.has_value() ? bias->data_ptr<float>() : nullptr, routed_scaling_factor,
+      current_stream()));
+}
+
+std::tuple<at::Tensor, at::Tensor> grouped_topk(const at::Tensor& scores,
+                                                const at::Tensor& scores_with_bias,
+                                                int64_t n_group, int64_t topk_group, int64_t topk,
+                                                bool renormalize, double routed_scaling_factor) {
+  check_cuda(scores, "scores");
+  TORCH_CHECK(scores_with_bias.dim() == 2, "scores_with_bias must be a 2D Tensor");
+  TORCH_CHECK(scores.sizes() == scores_with_bias.sizes() &&
+              scores.scalar_type() == scores_with_bias.scalar_type(),
+              "scores and scores_with_bias must have the same shape and dtype");
+  const int64_t num_tokens = scores_with_bias.size(0);
+  const int64_t num_experts = scores_with_bias.size(1);
+  TORCH_CHECK(n_group > 0 && num_experts % n_group == 0, "num_experts should be divisible by n_group");
+  TORCH_CHECK(n_group <= 32, "n_group should be smaller than or equal to 32 for now");
+  TORCH_CHECK(topk <= 32, "topk should be smaller than or equal to 32 for now");
+  if (scores.scalar_type() != at::kFloat && scores.scalar_type() != at::kHalf &&
+      scores.scalar_type() != at::kBFloat16)
+    throw std::invalid_argument("Invalid dtype, only supports float16, float32, and bfloat16");
+  const c10::cuda::CUDAGuard guard(scores.device());
+  at::Tensor s = scores.contiguous(), sb = scores_with_bias.contiguous();
+  at::Tensor values = at::empty({num_tokens, topk}, s.options());
+  at::Tensor indices = at::empty({num_tokens, topk}, s.options().dtype(at::kInt));
+  check_status(b200moe_grouped_topk(values.data_ptr(), indices.data_ptr<int32_t>(), s.data_ptr(),
+                                    sb.data_ptr(), float_dtype(s, "grouped_topk"), num_tokens,
+                                    (int)num_experts, (int)n_group, (int)topk_group, (int)topk,
+                                    renormalize, routed_scaling_factor, current_stream()));
+  return {values, indices};
+}
+
+void moe_align_block_size(at::Tensor topk_ids, int64_t num_experts, int64_t block_size,
+                          at::Tensor sorted_token_ids, at::Tensor experts_ids,
+                          at::Tensor num_tokens_post_pad,
+                          std::optional<at::Tensor> maybe_expert_map) {
+  check_cuda(topk_ids, "topk_ids");
+  TORCH_CHECK(((num_experts + 31) / 32) * 32 < 1024, "padded_num_experts must be less than 1024");
+  TORCH_CHECK(sorted_token_ids.scalar_type() == at::kInt && experts_ids.scalar_type() == at::kInt &&
+              num_tokens_post_pad.scalar_type() == at::kInt,
+              "moe_align_block_size outputs must be int32");
+  TORCH_CHECK(topk_ids.is_contiguous() && sorted_token_ids.is_contiguous() &&
+              experts_ids.is_contiguous(), "moe_align_block_size expects contiguous tensors");
+  if (maybe_expert_map.has_value())
+    TORCH_CHECK(maybe_expert_map->scalar_type() == at::kInt && maybe_expert_map->is_contiguous(),
+                "expert_map must be int32");
+  const c10::cuda::CUDAGuard guard(topk_ids.device());
+  at::Tensor ws = sort_workspace(topk_ids, topk_ids.numel(), num_experts);
+  check_status(b200moe_moe_align_block_size(
+      topk_ids.data_ptr(), index_dtype(topk_ids), topk_ids.numel(), (int)num_experts,
+      (int)block_size, sorted_token_ids.data_ptr<int32_t>(), sorted_token_ids.numel(),
+      experts_ids.data_ptr<int32_t>(), experts_ids.numel(), num_tokens_post_pad.data_ptr<int32_t>(),
+      maybe_expert_map.has_value() ? maybe_expert_map->data_ptr<int32_t>() : nullptr,
+      ws.numel() ? ws.data_ptr() : nullptr, (size_t)ws.numel(), current_stream()));
+}
+
+void moe_sum(at::Tensor& input, at::Tensor& output, const std::optional<at::Tensor>& topk_ids,
+             const std::optional<at::Tensor>& expert_map) {
+  check_cuda(input, "input");
+  const int hidden_size = input.size(-1);
+  const int64_t num_tokens = hidden_size ? output.numel() / hidden_size : 0;
+  const int topk = input.size(1);
+  TORCH_CHECK(input.scalar_type() == output.scalar_type(),
+              "moe_sum: input and output must have the same dtype");
+  TORCH_CHECK(input.device() == output.device(),
+              "moe_sum: input and output must be on the same device");
+  TORCH_CHECK(input.is_contiguous() && output.is_contiguous(),
+              "moe_sum expects contiguous input and output");
+  TORCH_CHECK(input.numel() == output.numel() * topk,
+              "moe_sum: input shape must be [num_tokens, topk, hidden] matching output "
+              "[num_tokens, hidden]");
+  TORCH_CHECK(!(expert_map.has_value() && !topk_ids.has_value()),
+              "moe_sum: expert_map requires topk_ids to be provided");
+  if (topk_ids.has_value()) {
+    const auto& tk = topk_ids.value();
+    TORCH_CHECK(tk.is_contiguous(), "moe_sum: topk_ids must be contiguous");
+    TORCH_CHECK(tk.device() == input.device(), "moe_sum: topk_ids must be on the same device as input");
+    TORCH_CHECK(tk.dim() == 2 && tk.size(0) == num_tokens && tk.size(1) == topk,
+                "moe_sum: topk_ids must have shape [num_tokens, topk]");
+    TORCH_CHECK(tk.scalar_type() == at::kInt || tk.scalar_type() == at::kLong,
+                "moe_sum: topk_ids must be int32 or int64");
+    if (expert_map.has_value()) {
+      const auto& em = expert_map.value();
+      TORCH_CHECK(em.scalar_type() == at::kInt, "moe_sum: expert_map must be int32");
+      TORCH_CHECK(em.is_contiguous(), "moe_sum: expert_map must be contiguous");
+      TORCH_CHECK(em.device() == input.device(), "moe_sum: expert_map must be on the same device as input");
+    }
+  }
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(b200moe_moe_sum(
+      output.data_ptr(), input.data_ptr(), float_dtype(input, "moe_sum"), num_tokens, topk,
+      hidden_size, topk_ids.has_value() ? topk_ids->data_ptr() : nullptr,
+      topk_ids.has_value() ? index_dtype(*topk_ids) : B200MOE_I32,
+      expert_map.has_value() ? expert_map->data_ptr<int32_t>() : nullptr, current_stream()));
+}
+
+void moe_gather(at::Tensor& output, const at::Tensor& moe_output, const at::Tensor& topk_weights,
+                const at::Tensor& unpermuted_row_to_permuted_row, int64_t num_experts) {
+  check_cuda(output, "output");
+  const int64_t num_tokens = topk_weights.size(0);
+  const int topk = topk_weights.size(1);
+  const int hidden_size = output.size(1);
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, "topk_weights must be float32");
+  if (output.scalar_type() != at::kHalf && output.scalar_type() != at::kBFloat16 &&
+      output.scalar_type() != at::kFloat)
+    throw std::runtime_error("Unsupported data type in moe_gather");
+  TORCH_CHECK(moe_output.scalar_type() == output.scalar_type(),
+              "moe_gather: moe_output and output must have the same dtype");
+  TORCH_CHECK(unpermuted_row_to_permuted_row.scalar_type() == at::kInt,
+              "moe_gather: unpermuted_row_to_permuted_row must be int32");
+  TORCH_CHECK(output.is_contiguous() && moe_output.is_contiguous() && topk_weights.is_contiguous() &&
+              unpermuted_row_to_permuted_row.is_contiguous(), "moe_gather expects contiguous tensors");
+  const c10::cuda::CUDAGuard guard(output.device());
+  check_status(b200moe_moe_gather(output.data_ptr(), moe_output.data_ptr(),
+                                  topk_weights.data_ptr<float>(),
+                                  unpermuted_row_to_permuted_row.data_ptr<int32_t>(),
+                                  float_dtype(output, "moe_gather"), num_tokens, hidden_size, topk,
+                                  current_stream()));
+}
+
+void init_expert_map(at::Tensor& expert_map, int64_t num_experts, int64_t ep_rank, int64_t ep_size) {
+  check_cuda(expert_map, "expert_map");
+  TORCH_CHECK(expert_map.scalar_type() == at::kInt, "expert_map must be int32");
+  TORCH_CHECK(expert_map.numel() == num_experts * ep_size, "expert_map must be [num_experts * ep_size]");
+  const c10::cuda::CUDAGuard guard(expert_map.device());
+  check_status(b200moe_init_expert_map(expert_map.data_ptr<int32_t>(), (int)num_experts,
+                                       (int)ep_rank, (int)ep_size, current_stream()));
+}
+
+struct RemapChecked {
+  int64_t num_rows; int hidden, topk;
+};
+
+RemapChecked check_remap(const at::Tensor& hidden_states, const at::Tensor& remapped,
+                         const std::optional<at::Tensor>& expert_map, const at::Tensor& rows_per_expert,
+                         const at::Tensor& row_map, const at::Tensor& topk_ids,
+                         int64_t total_experts_num, int64_t local_experts_num) {
+  if (expert_map.has_value())
+    TORCH_CHECK(expert_map->scalar_type() == at::kInt, "expert_map must be int32");
+  TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt, "rows_per_expert must be int32");
+  TORCH_CHECK(topk_ids.scalar_type() == at::kLong || topk_ids.scalar_type() == at::kInt,
+              "topk_ids must be int64 or int32");
+  TORCH_CHECK(row_map.scalar_type() == at::kInt, "unpermuted_row_to_permuted_row must be int32");
+  RemapChecked r;
+  r.num_rows = hidden_states.size(0);
+  r.hidden = hidden_states.size(1);
+  r.topk = topk_ids.size(1);
+  TORCH_CHECK(remapped.size(0) == r.num_rows * r.topk && hidden_states.size(1) == remapped.size(1),
+              "remapped_hidden_states must be [num_rows * TopK, hidden_size]");
+  if (expert_map.has_value())
+    TORCH_CHECK(expert_map->size(0) == total_experts_num, "expert_map must be [total_experts_num]");
+  TORCH_CHECK(rows_per_expert.size(0) == local_experts_num, "rows_per_expert must be [local_experts_num]");
+  TORCH_CHECK(topk_ids.size(0) == r.num_rows && topk_ids.size(1) == r.topk,
+              "topk_ids must be [num_rows, TopK]");
+  TORCH_CHECK(hidden_states.is_contiguous() && remapped.is_contiguous() && topk_ids.is_contiguous() &&
+              rows_per_expert.is_contiguous() && row_map.is_contiguous(),
+              "remap_hidden_states expects contiguous tensors");
+  if (local_experts_num > 1024)
+    throw std::runtime_error("local_experts_num exceeds the maximum supported number");
+  return r;
+}
+
+void remap_hidden_states(at::Tensor& hidden_states, const std::optional<at::Tensor>& hidden_states_scales,
+                         at::Tensor& remapped_hidden_states,
+                         const std::optional<at::Tensor>& remapped_hidden_states_scales,
+                         const std::optional<at::Tensor>& expert_map, at::Tensor& rows_per_expert,
+                         at::Tensor& unpermuted_row_to_permuted_row, at::Tensor& topk_ids,
+                         int64_t total_experts_num, int64_t local_experts_num) {
+  check_cuda(hidden_states, "hidden_states");
+  TORCH_CHECK(hidden_states.scalar_type() == remapped_hidden_states.scalar_type(),
+              "hidden_states and remapped_hidden_states must have save dtype");
+  if (hidden_states_scales.has_value()) {
+    TORCH_CHECK(remapped_hidden_states_scales.has_value(),
+                "if hidden_states_scales is provided, remapped_hidden_states_scales "
+                "must also be provided");
+    TORCH_CHECK(hidden_states_scales->scalar_type() == remapped_hidden_states_scales->scalar_type(),
+                "hidden_states_scales and remapped_hidden_states_scales must have save dtype");
+  }
+  RemapChecked r = check_remap(hidden_states, remapped_hidden_states, expert_map, rows_per_expert,
+                               unpermuted_row_to_permuted_row, topk_ids, total_experts_num,
+                               local_experts_num);
+  int scale_cols = 0, scale_bytes = 0;
+  if (hidden_states_scales.has_value()) {
+    TORCH_CHECK(remapped_hidden_states_scales->size(0) == r.num_rows * r.topk &&
+                hidden_states_scales->size(1) == remapped_hidden_states_scales->size(1),
+                "remapped_hidden_states_scales must be [num_rows * TopK, hidden_size // block_k]");
+    TORCH_CHECK(hidden_states_scales->is_contiguous() && remapped_hidden_states_scales->is_contiguous(),
+                "remap_hidden_states expects contiguous scales");
+    scale_cols = hidden_states_scales->size(1);
+    scale_bytes = hidden_states_scales->element_size();
+  }
+  const int elem = hidden_states.element_size();
+  if (elem != 1 && elem != 2 && elem != 4) throw std::runtime_error("Unsupported data type in hidden_states");
+  const c10::cuda::CUDAGuard guard(hidden_states.device());
+  at::Tensor ws = sort_workspace(hidden_states, r.num_rows * r.topk, local_experts_num);
+  check_status(b200moe_remap_hidden_states(
+      hidden_states.data_ptr(), hidden_states_scales.has_value() ? hidden_states_scales->data_ptr() : nullptr,
+      remapped_hidden_states.data_ptr(),
+      remapped_hidden_states_scales.has_value() ? remapped_hidden_states_scales->data_ptr() : nullptr,
+      expert_map.has_value() ? expert_map->data_ptr<int32_t>() : nullptr,
+      rows_per_expert.data_ptr<int32_t>(), unpermuted_row_to_permuted_row.data_ptr<int32_t>(),
+      topk_ids.data_ptr(), index_dtype(topk_ids), r.num_rows, r.hidden, elem, scale_cols, scale_bytes,
+      r.topk, (int)total_experts_num, (int)local_experts_num, ws.numel() ? ws.data_ptr() : nullptr,
+      (size_t)ws.numel(), current_stream()));
+}
+
+// Not in the reference: permute fused with the dynamic 1x128 e4m3 quantisation.
+void b200_remap_quant_fp8(at::Tensor& hidden_states, at::Tensor& remapped_q, at::Tensor& remapped_scales,
+                          const std::optional<at::Tensor>& expert_map, at::Tensor& rows_per_expert,
+                          at::Tensor& unpermuted_row_to_permuted_row, at::Tensor& topk_ids,
+                          int64_t total_experts_num, int64_t local_experts_num) {
+  check_cuda(hidden_states, "hidden_states");
+  TORCH_CHECK(remapped_q.scalar_type() == at::kFloat8_e4m3fn, "remapped_q must be float8_e4m3fn");
+  TORCH_CHECK(remapped_scales.scalar_type() == at::kFloat && remapped_scales.is_contiguous(),
+              "remapped_scales must be contiguous float32");
+  RemapChecked r = check_remap(hidden_states, remapped_q, expert_map, rows_per_expert,
+                               unpermuted_row_to_permuted_row, topk_ids, total_experts_num,
+                               local_experts_num);
+  TORCH_CHECK(r.hidden % 128 == 0 && remapped_scales.size(0) == r.num_rows * r.topk &&
+              remapped_scales.size(1) == r.hidden / 128,
+              "remapped_scales must be [num_rows * TopK, hidden_size / 128]");
+  const c10::cuda::CUDAGuard guard(hidden_states.device());
+  at::Tensor ws = sort_workspace(hidden_states, r.num_rows * r.topk, local_experts_num);
+  check_status(b200moe_remap_quant_fp8(
+      hidden_states.data_ptr(), float_dtype(hidden_states, "b200_remap_quant_fp8"), remapped_q.data_ptr(),
+      remapped_scales.data_ptr<float>(), expert_map.has_value() ? expert_map->data_ptr<int32_t>() : nullptr,
+      rows_per_expert.data_ptr<int32_t>(), unpermuted_row_to_permuted_row.data_ptr<int32_t>(),
+      topk_ids.data_ptr(), index_dtype(topk_ids), r.num_rows, r.hidden, r.topk, (int)total_experts_num,
+      (int)local_experts_num, ws.numel() ? ws.data_ptr() : nullptr, (size_t)ws.numel(), current_stream()));
+}
+
+}  // namespace
+
+TORCH_LIBRARY_FRAGMENT(_moe_C, m) {
+  m.def("moe_sum(Tensor input, Tensor! output, Tensor? topk_ids, Tensor? expert_map) -> ()");
+  m.def(
+      "moe_align_block_size(Tensor topk_ids, int num_experts,"
+      "                     int block_size, Tensor! sorted_token_ids,"
+      "                     Tensor! experts_ids,"
+      "                     Tensor! num_tokens_post_pad,"
+      "                     Tensor? maybe_expert_map) -> ()");
+  m.def(
+      "grouped_topk(Tensor scores, Tensor scores_with_bias, int n_group, int "
+      "topk_group, int topk, bool renormalize, float "
+      "routed_scaling_factor) -> (Tensor, Tensor)");
+  m.def(
+      "topk_softmax(Tensor! topk_weights, Tensor! topk_indices, Tensor! "
+      "token_expert_indices, Tensor gating_output, bool renormalize, Tensor? "
+      "bias) -> ()");
+  m.def(
+      "topk_sigmoid(Tensor! topk_weights, Tensor! topk_indices, Tensor! "
+      "token_expert_indices, Tensor gating_output, bool renormalize, Tensor? "
+      "bias, float routed_scaling_factor) -> ()");
+  m.def(
+      "moe_gather(Tensor! output, Tensor moe_output, Tensor topk_weights, "
+      "Tensor unpermuted_row_to_permuted_row, int num_experts) -> ()");
+  m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
+  m.def(
+      "remap_hidden_states(Tensor hidden_states, Tensor? hidden_states_scales, "
+      "Tensor remapped_hidden_states,"
+      "Tensor? remapped_hidden_states_scales,"
+      "Tensor? expert_map, Tensor rows_per_expert,"
+      "Tensor unpermuted_row_to_permuted_row, Tensor topk_ids,"
+      "int total_experts_num, int "
+      "local_experts_num) -> "
+      "()");
+  m.def(
+      "b200_remap_quant_fp8(Tensor hidden_states, Tensor! remapped_q, Tensor! remapped_scales, "
+      "Tensor? expert_map, Tensor! rows_per_expert, Tensor! unpermuted_row_to_permuted_row, "
+      "Tensor topk_ids, int total_experts_num, int local_experts_num) -> ()");
+}
+
+TORCH_LIBRARY_IMPL(_moe_C, CUDA, m) {
+  m.impl("moe_sum", &moe_sum);
+  m.impl("moe_align_block_size", &moe_align_block_size);
+  m.impl("grouped_topk", &grouped_topk);
+  m.impl("topk_softmax", &topk_softmax);
+  m.impl("topk_sigmoid", &topk_sigmoid);
+  m.impl("moe_gather", &moe_gather);
+  m.impl("init_expert_map", &init_expert_map);
+  m.impl("remap_hidden_states", &remap_hidden_states);
+  m.impl("b200_remap_quant_fp8", &b200_remap_quant_fp8);
+}
+
+B200_REGISTER_EXTENSION(_moe_C)
