@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-MoE layer (routing + XpuFusedMoe.apply) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2_mixtral_bf16] [--tokens T]
+
+A step is one pass of the layer over one batch of T synthetic tokens: top-k
+routing followed by the eight stages of ``XpuFusedMoe.apply``.  The default
+workload is the Mixtral-8x7B-shaped bf16 layer at T=4096 tokens per GPU.  With
+N > 1 (launched under torch.distributed.run) every rank runs its own replica on
+its own tokens; no collective is on the data path, so scaling is weak.
+
+Rank 0 prints one JSON line: whole-job tokens/s with inputs resident in HBM
+(``value``), the same metric through the public API with host buffers and the
+copies inside the timed region (``e2e``), the roofline of the grouped GEMM
+kernel measured live with CUDA events, SM clocks sampled during the timed
+region, and - at N=1 - the CPU oracle timed on a bounded sample of the same
+workload.  ``--impl reference`` times that CPU path alone, with all host
+threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "vllm-xpu-kernels_b200"))
+
+import torch  # noqa: E402
+
+METRIC = "fused_moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=float(d["hbm_gbs"]), tensor=float(d["bf16_tflops_sustained"]),
+                    tensor_burst=float(d["bf16_tflops"]), source="measured")
+    return dict(hbm=6650.0, tensor=1400.0, tensor_burst=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only)."""
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.reasons = index, [], set()
+        self.max_mhz, self._stop, self._thr = None, threading.Event(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40,
+                 "sw_thermal_slowdown": 0x20, "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        med = s[len(s) // 2] if s else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def _physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_layer_tokens_per_s(cfg, seconds_budget: float, steps: int, warmup: int):
+    """Times the oracle's whole-layer restatement on the host cores.  Each step
+    processes a bounded sample of T_s tokens of the workload; returns
+    (tokens/s, T_s, ms per step, cores)."""
+    from oracle import torch_oracle as to
+    from oracle import workloads as wl
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    w = wl.make_weights(cfg, seed=0)
+    d13, d2 = wl.dequant_weights(cfg, w)  # fp32 once, outside the timed steps
+
+    def run(T):
+        x, logits, bias = wl.make_inputs(cfg, T, seed=0)
+        t0 = time.perf_counter()
+        tw, ids = wl.route_cpu(cfg, logits, bias)
+        if cfg.recipe == "bf16":
+            to.fused_moe_bf16(x, d13, w["w13_bias"], d2, w["w2_bias"], tw, ids, cfg.E)
+        else:
+            to.fused_moe_staged(x, d13, w["w13_bias"], d2, w["w2_bias"], tw, ids, cfg.E,
+                                activation=cfg.activation, act_quant=cfg.recipe == "fp8block")
+        return time.perf_counter() - t0
+
+    run(4)
+    t_small = run(16)
+    per_tok = max(t_small / 16, 1e-6)
+    per_step = seconds_budget / max(1, steps + warmup)
+    T_s = int(max(8, min(4096, per_step / per_tok)))
+    for _ in range(warmup):
+        run(T_s)
+    t = [run(T_s) for _ in range(steps)]
+    total = sum(t)
+    return T_s * steps / total, T_s, 1e3 * total / steps, cores
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def launches_per_step(M: int, quant: bool) -> int:
+    """Kernels of ours launched by one step: routing 1; permute bookkeeping 1
+    (<= 2048 routed slots) or 3, row copy 1; GEMM 2; activation 1; (fp8: act
+    quant 1); gather 1."""
+    return 1 + (1 if M <= 2048 else 3) + 1 + 2 + 1 + (1 if quant else 0) + 1
+
+
+def build_gpu_workload(cfg, T, dev):
+    import vllm_xpu_kernels.fused_moe_interface as fmi
+    from oracle import workloads as wl
+    assert fmi.FUSEDMOE_AVAILABLE, fmi.FUSEDMOE_UNAVAILABLE_REASON
+    g = torch.Generator(device=dev).manual_seed(1234)
+    E, H, I = cfg.E, cfg.H, cfg.I
+    if cfg.recipe == "bf16":
+        # op layout [E,K,N], drawn on the device expert by expert
+        w13 = torch.empty(E, H, 2 * I, dtype=torch.bfloat16, device=dev)
+        w2 = torch.empty(E, I, H, dtype=torch.bfloat16, device=dev)
+        for e in range(E):
+            w13[e] = (torch.randn(H, 2 * I, generator=g, device=dev) * H ** -0.5).to(torch.bfloat16)
+            w2[e] = (torch.randn(I, H, generator=g, device=dev) * I ** -0.5).to(torch.bfloat16)
+        s13 = s2 = b13 = b2 = None
+    else:
+        w = wl.make_weights(cfg, seed=0)
+        w13, s13, w2, s2 = [t.to(dev) if t is not None else None for t in wl.to_op_layout(cfg, w)]
+        b13 = w["w13_bias"].to(dev) if w["w13_bias"] is not None else None
+        b2 = w["w2_bias"].to(dev) if w["w2_bias"] is not None else None
+    layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
+    x_cpu, logits_cpu, bias_cpu = wl.make_inputs(cfg, T, seed=0)
+    return layer, x_cpu, logits_cpu, bias_cpu
+
+
+def make_step(cfg, layer, dev, T):
+    K, E = cfg.K, cfg.E
+    tw = torch.empty(T, K, dtype=torch.float32, device=dev)
+    ids = torch.empty(T, K, dtype=torch.int32, device=dev)
+    src = torch.empty(T, K, dtype=torch.int32, device=dev)
+    out = torch.empty(T, cfg.H, dtype=torch.bfloat16, device=dev)
+
+    def step(x, logits, bias):
+        if cfg.routing == "softmax":
+            torch.ops._moe_C.topk_softmax(tw, ids, src, logits, cfg.renormalize, None)
+            layer.apply(out, x, tw, ids)
+        else:
+            scores = torch.sigmoid(logits)
+            v, i = torch.ops._moe_C.grouped_topk(scores, scores + bias, cfg.n_group, cfg.topk_group, K,
+                                                 cfg.renormalize, cfg.routed_scaling_factor)
+            layer.apply(out, x, v, i)
+        return out
+
+    return step, (tw, ids)
+
+
+def time_gemms(cfg, layer, ids, T, dev, iters):
+    """Average duration of the two grouped-GEMM launches of a step, CUDA events
+    on the launching stream, on this step's real row distribution."""
+    E, H, I, K = cfg.E, cfg.H, cfg.I, cfg.K
+    M = T * K
+    rows = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
+    fp8 = cfg.recipe == "fp8block"
+    adt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    a1 = torch.randn(M, H, device=dev).to(adt)
+    a2 = torch.randn(M, I, device=dev).to(adt)
+    s1 = torch.rand(M, H // 128, device=dev) if fp8 else None
+    s2 = torch.rand(M, I // 128, device=dev) if fp8 else None
+    d1 = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=dev)
+    d2 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    f = torch.ops._xpu_C.cutlass_grouped_gemm_interface
+
+    def both():
+        f(a1, s1, layer.w13, layer.gemm1_wei_scales, layer.w13_bias, d1, rows, 2 * I, H, E)
+        f(a2, s2, layer.w2, layer.gemm2_wei_scales, layer.w2_bias, d2, rows, H, I, E)
+
+    for _ in range(3):
+        both()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        both()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_pair = e0.elapsed_time(e1) / iters
+    e_act = int((rows > 0).sum())
+    return ms_pair, e_act
+
+
+def weight_bytes_per_expert(cfg):
+    n = 3 * cfg.H * cfg.I
+    if cfg.recipe == "bf16":
+        return 2 * n
+    if cfg.recipe == "fp8block":
+        return n + 4 * (3 * cfg.H * cfg.I // (128 * 128))
+    return n // 2 + n // 32 + (2 * (2 * cfg.I + cfg.H) if cfg.has_bias else 0)
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from oracle import workloads as wl
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = wl.CONFIGS[args.workload]
+    T = args.tokens
+    layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev)
+    step, (tw, ids) = make_step(cfg, layer, dev, T)
+    x, logits = x_cpu.to(dev), logits_cpu.to(dev)
+    bias = bias_cpu.to(dev) if bias_cpu is not None else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput ------------------------------------------------
+    for _ in range(max(3, args.warmup)):
+        step(x, logits, bias)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(_physical_gpu_index(local_rank)) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            step(x, logits, bias)
+        e1.record()
+        barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms)
+    ms_per_step = ms_total / args.steps
+    value = world * T * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end: host buffers, copies inside the timed region -----------------------
+    x_pin, lg_pin = x_cpu.pin_memory(), logits_cpu.pin_memory()
+    out_pin = torch.empty(T, cfg.H, dtype=torch.bfloat16).pin_memory()
+    x_d, lg_d = torch.empty_like(x), torch.empty_like(logits)
+
+    def e2e_step():
+        x_d.copy_(x_pin, non_blocking=True)
+        lg_d.copy_(lg_pin, non_blocking=True)
+        o = step(x_d, lg_d, bias)
+        out_pin.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms2 = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+    e2e_value = world * T * args.steps / (float(ms2) * 1e-3)
+    h2d = x_pin.numel() * 2 + lg_pin.numel() * 4
+    d2h = out_pin.numel() * 2
+
+    # ---- roofline of the grouped GEMM kernel ---------------------------------------------
+    peaks = _peaks()
+    ms_pair, e_act = time_gemms(cfg, layer, ids, T, dev, max(3, min(20, args.steps)))
+    flops = 6.0 * T * cfg.K * cfg.H * cfg.I
+    wbytes = e_act * weight_bytes_per_expert(cfg)
+    act_bytes = T * cfg.K * (cfg.H + 2 * cfg.I + cfg.I + cfg.H) * 2  # A and D of both launches
+    t_tensor = flops / (peaks["tensor"] * 1e12)
+    t_hbm = (wbytes + act_bytes) / (peaks["hbm"] * 1e9)
+    if t_tensor >= t_hbm:
+        ach = flops / (ms_pair * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": peaks["tensor"], "unit": "TFLOP/s",
+                "frac": round(ach / peaks["tensor"], 4)}
+    else:
+        ach = (wbytes + act_bytes) / (ms_pair * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm"], "unit": "GB/s",
+                "frac": round(ach / peaks["hbm"], 4)}
+    roof.update({"traffic": None, "kernel": "grouped_gemm_tc_kernel (gemm1 + gemm2 of one step)",
+                 "ms_per_launch_pair": round(ms_pair, 4), "peak_source": peaks["source"] + " (sustained)",
+                 "experts_active": e_act})
+
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": {"bf16": "bf16", "fp8block": "fp8_e4m3",
+                                                          "mxfp4": "mxfp4"}[cfg.recipe],
+        "data": "synthetic",
+        "config": {"workload": f"{cfg.name} T={T} per GPU", "H": cfg.H, "I": cfg.I, "E": cfg.E, "top_k": cfg.K,
+                   "tokens_per_gpu": T, "routing": cfg.routing, "parallelism": f"replicas x{world}",
+                   "l2": "inputs exceed L2: the weights streamed per step are larger than the 126 MB L2"
+                         if e_act * weight_bytes_per_expert(cfg) > 126e6 else "inputs smaller than L2",
+                   "seed": 0},
+        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_per_step(T * cfg.K, cfg.recipe == "fp8block") * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": roof,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        v, T_s, ms_cpu, cores = cpu_layer_tokens_per_s(cfg, 20.0, 2, 1)
+        line["cpu_baseline"] = {"value": round(v, 2), "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"{T_s} tokens of the same layer per step, 2 timed steps, "
+                                          f"weights pre-converted to fp32, {ms_cpu:.0f} ms per step"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference's own CPU path for this layer (its pure-torch test
+    reference, restated in oracle/), timed on the host cores of this box."""
+    from oracle import workloads as wl
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    cfg = wl.CONFIGS[args.workload]
+    v, T_s, ms_cpu, cores = cpu_layer_tokens_per_s(cfg, 120.0, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(v, 2), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_cpu, 2), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{cfg.name} T={args.tokens} per GPU", "H": cfg.H, "I": cfg.I, "E": cfg.E,
+                   "top_k": cfg.K, "tokens_per_gpu": args.tokens, "routing": cfg.routing, "seed": 0},
+        "cpu_baseline": {"value": round(v, 2), "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{T_s} tokens of the same layer per step"},
+        "e2e": {"value": round(v, 2), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2_mixtral_bf16")
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

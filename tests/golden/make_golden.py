@@ -1,0 +1,190 @@
+"""Generates the golden vectors in this folder from the reference's own
+pure-torch test references, run on CPU.
+
+Usage:  python tests/golden/make_golden.py [/path/to/vllm-xpu-kernels]
+
+The reference's test helpers import its compiled extensions at module level;
+those imports are satisfied here with empty stand-in modules, which is enough
+because only the pure-torch reference functions are called.  Each .pt file
+holds the seeded inputs and the reference's outputs for one op, so that the
+checks in tests/test_oracle_golden.py need neither the reference nor this
+script at run time.
+"""
+from __future__ import annotations
+
+import sys
+import types
+from pathlib import Path
+
+import torch
+
+OUT = Path(__file__).resolve().parent
+
+
+def _stub(name):
+    m = types.ModuleType(name)
+    sys.modules[name] = m
+    return m
+
+
+def load_reference(root: str):
+    sys.path.insert(0, root)
+    import importlib
+    pkg = importlib.import_module("vllm_xpu_kernels")  # plain package, no native code
+    for sub in ("_C", "_moe_C", "_xpu_C"):
+        setattr(pkg, sub, _stub(f"vllm_xpu_kernels.{sub}"))
+    import tests.ops.topk_op as topk_op
+    import tests.ops.grouped_topk_op as grouped_op
+    import tests.test_moe_align_block_size as align_t
+    import tests.fused_moe.test_remap_hidden_states as remap_t
+    import tests.test_moe_gather as gather_t
+    import tests.fused_moe.test_fused_moe as layer_t
+    import tests.ops.activation_op as act_op
+    import tests.ops.swigluoai_and_mul_op as swi_op
+    import tests.test_fp8_quant as fp8_t
+    import vllm_xpu_kernels.moe_utils as mu
+    return dict(topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
+                layer=layer_t, act=act_op, swi=swi_op, fp8=fp8_t, mu=mu)
+
+
+def main():
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = load_reference(root)
+    g = torch.Generator().manual_seed(0)
+
+    # ---- routing: softmax / sigmoid top-k -------------------------------------------
+    cases = []
+    for (T, E, K, renorm, with_bias) in [(33, 8, 2, True, False), (17, 128, 8, True, False),
+                                         (9, 128, 4, False, True), (5, 60, 6, True, True),
+                                         (64, 256, 8, True, False)]:
+        gating = torch.randn(T, E, generator=g)
+        bias = torch.randn(E, generator=g) * 0.1 if with_bias else None
+        hidden = torch.zeros(T, 4)
+        w, ids = ref["topk"].topk_softmax(hidden, gating, K, renorm, bias)
+        ws, ids_s = ref["topk"].topk_sigmoid(hidden, gating, K, renorm, bias, None, 2.5)
+        cases.append(dict(gating=gating, bias=bias, topk=K, renormalize=renorm,
+                          softmax_w=w, softmax_ids=ids, sigmoid_w=ws, sigmoid_ids=ids_s,
+                          routed_scaling_factor=2.5))
+    torch.save(cases, OUT / "routing_topk.pt")
+
+    # ---- routing: grouped top-k (ids are compared as sets: torch.topk(sorted=False)) ---
+    cases = []
+    for (T, E, ng, tg, K, scoring, renorm, rsf) in [(33, 16, 8, 2, 2, "softmax", True, 1.0),
+                                                    (33, 16, 8, 2, 2, "sigmoid", False, 2.5),
+                                                    (64, 256, 8, 4, 8, "sigmoid", True, 2.5),
+                                                    (7, 64, 4, 2, 6, "sigmoid", True, 1.0)]:
+        gating = torch.randn(T, E, generator=g)
+        bias = torch.randn(E, generator=g) * (0.1 if E == 256 else 1.0)
+        w, ids = ref["grouped"].grouped_topk(torch.zeros(T, 4), gating, K, renorm, ng, tg, scoring,
+                                             rsf, bias)
+        cases.append(dict(gating=gating, bias=bias, topk=K, n_group=ng, topk_group=tg,
+                          scoring=scoring, renormalize=renorm, routed_scaling_factor=rsf,
+                          weights=w, ids=ids))
+    torch.save(cases, OUT / "routing_grouped.pt")
+
+    # ---- moe_align_block_size ---------------------------------------------------------
+    cases = []
+    for (m, topk, E, bs, use_map) in [(1, 1, 32, 32, False), (3, 2, 32, 128, False),
+                                      (256, 2, 160, 32, False), (300, 16, 257, 128, False),
+                                      (16, 2, 8, 64, True), (32, 4, 8, 64, True)]:
+        topk_ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(m)]).to(torch.int32)
+        emap = None
+        if use_map:
+            emap = torch.full((E,), -1, dtype=torch.int32)
+            for i, e in enumerate(range(0, E, 2)):
+                emap[e] = i
+        s, eids, post = ref["align"].torch_moe_align_block_size(topk_ids, bs, E, emap)
+        cases.append(dict(topk_ids=topk_ids, num_experts=E, block_size=bs, expert_map=emap,
+                          sorted_ids=s, expert_ids=eids, num_tokens_post_pad=post))
+    torch.save(cases, OUT / "moe_align.pt")
+
+    # ---- remap_hidden_states ----------------------------------------------------------
+    cases = []
+    for (T, H, E_tot, K, use_map) in [(8, 32, 16, 2, False), (33, 64, 16, 4, True), (64, 32, 32, 8, True)]:
+        hidden = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        topk_ids = torch.stack([torch.randperm(E_tot, generator=g)[:K] for _ in range(T)]).to(torch.int64)
+        if use_map:
+            E_loc = E_tot // 4
+            emap = torch.full((E_tot,), -1, dtype=torch.int32)
+            emap[E_loc:2 * E_loc] = torch.arange(E_loc, dtype=torch.int32)
+        else:
+            E_loc, emap = E_tot, None
+        remapped = torch.zeros(T * K, H, dtype=torch.bfloat16)
+        rows = torch.zeros(E_loc, dtype=torch.int32)
+        row_map = torch.zeros(T, K, dtype=torch.int32)
+        ref["remap"].ref_remap_hidden_states(hidden, None, remapped, None, emap, rows, row_map,
+                                             topk_ids, E_tot, E_loc)
+        cases.append(dict(hidden=hidden, topk_ids=topk_ids, expert_map=emap, total_experts=E_tot,
+                          local_experts=E_loc, remapped=remapped, rows_per_expert=rows, row_map=row_map))
+    torch.save(cases, OUT / "remap.pt")
+
+    # (init_expert_map has no CPU-runnable reference: its test helper allocates on the
+    #  reference's device.  It is checked against the semantic statement instead.)
+
+    # ---- moe_gather -----------------------------------------------------------------------
+    cases = []
+    for (T, H, K) in [(8, 128, 2), (5, 64, 8)]:
+        moe_out = torch.randn(T * K, H, generator=g).to(torch.bfloat16)
+        w = torch.rand(T, K, generator=g)
+        perm = torch.randperm(T * K, generator=g).to(torch.int32).view(T, K)
+        perm[0, 0] = -1
+        out = torch.empty(T, H, dtype=torch.bfloat16)
+        ref["gather"].ref_moe_gather(out, moe_out, w, perm, 16)
+        cases.append(dict(moe_output=moe_out, topk_weights=w, row_map=perm, output=out))
+    torch.save(cases, OUT / "moe_gather.pt")
+
+    # ---- activations --------------------------------------------------------------------------
+    x = (torch.randn(7, 256, generator=g) * 3).to(torch.bfloat16)
+    xf = torch.randn(5, 128, generator=g) * 4
+    torch.save(dict(x_bf16=x, silu_bf16=ref["act"].SiluAndMul.forward_native(None, x),
+                    swiglu_bf16=ref["swi"].SwigluOAIAndMul().forward_native(x),
+                    x_f32=xf, silu_f32=ref["act"].SiluAndMul.forward_native(None, xf),
+                    swiglu_f32=ref["swi"].SwigluOAIAndMul().forward_native(xf)),
+               OUT / "activations.pt")
+
+    # ---- fp8 per-1x128 group quant (reference divides; tolerance applies, see its test) ----------
+    x = torch.randn(6, 512, generator=g)
+    q, s = ref["fp8"].ref_per_block_quant(x, 1, 128)
+    torch.save(dict(x=x, q=q, s=s), OUT / "fp8_group_quant.pt")
+
+    # ---- weight dequantisers ---------------------------------------------------------------------
+    mu = ref["mu"]
+    packed = torch.randint(0, 256, (4, 64), generator=g, dtype=torch.int32).to(torch.uint8)
+    sc = torch.randint(117, 124, (4, 4), generator=g, dtype=torch.int32).to(torch.uint8)
+    deq4 = mu.dequant_mxfp4(packed.view(torch.float4_e2m1fn_x2), sc.view(torch.float8_e8m0fnu))
+    w8 = (torch.randn(128, 256, generator=g)).to(torch.float8_e4m3fn)
+    s8 = torch.rand(1, 2, generator=g) + 0.5
+    torch.save(dict(mxfp4_packed=packed, mxfp4_scale=sc, mxfp4_deq=deq4,
+                    fp8_w=w8, fp8_scale=s8, fp8_deq=mu.dequant_fp8_block_wei(w8, s8)),
+               OUT / "dequant.pt")
+
+    # ---- whole layer, bf16 (tests/fused_moe/test_fused_moe.py:119-176) -----------------------------
+    cases = []
+    for (T, H, I, E, K, has_bias, clamp) in [(16, 128, 64, 4, 1, False, None), (12, 128, 64, 4, 2, True, None),
+                                              (8, 64, 64, 8, 2, True, 0.5)]:
+        a = (torch.randn(T, H, generator=g) / 4).to(torch.bfloat16)
+        w13 = (torch.randn(E, 2 * I, H, generator=g) / 8).to(torch.bfloat16)
+        w2 = (torch.randn(E, H, I, generator=g) / 8).to(torch.bfloat16)
+        b13 = (torch.randn(E, 2 * I, generator=g) / 8).to(torch.bfloat16) if has_bias else None
+        b2 = (torch.randn(E, H, generator=g) / 8).to(torch.bfloat16) if has_bias else None
+        scores = torch.randn(T, E, generator=g)
+        tw, tid = torch.topk(scores, k=K, dim=-1, sorted=False)
+        out = ref["layer"].ref_fused_moe(a, w13, b13, w2, b2, tw.reshape(-1, 1), tid.reshape(-1), K,
+                                         "silu", E, gemm1_clamp_limit=clamp)
+        cases.append(dict(x=a, w13=w13, w2=w2, w13_bias=b13, w2_bias=b2, topk_weights=tw,
+                          topk_ids=tid, num_experts=E, clamp=clamp, output=out))
+    # expert-parallel variant: rank 1 of 2
+    a = (torch.randn(10, 64, generator=g) / 4).to(torch.bfloat16)
+    w13 = (torch.randn(8, 128, 64, generator=g) / 8).to(torch.bfloat16)
+    w2 = (torch.randn(8, 64, 64, generator=g) / 8).to(torch.bfloat16)
+    tw, tid = torch.topk(torch.randn(10, 8, generator=g), k=2, dim=-1, sorted=False)
+    out = ref["layer"].ref_fused_moe(a, w13, None, w2, None, tw.reshape(-1, 1), tid.reshape(-1), 2, "silu",
+                                     4, ep_rank=1, ep_size=2)
+    cases.append(dict(x=a, w13=w13, w2=w2, w13_bias=None, w2_bias=None, topk_weights=tw, topk_ids=tid,
+                      num_experts=4, ep_rank=1, ep_size=2, clamp=None, output=out))
+    torch.save(cases, OUT / "layer_bf16.pt")
+    print("wrote", sorted(p.name for p in OUT.glob("*.pt")))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,181 @@
+"""GPU parity: the grouped GEMM.  The plain-CUDA checking kernel (impl=2) and
+the tcgen05 tensor-core kernel (impl=1) are each compared with the CPU oracle
+on ragged expert segments; tolerances are the reference's (bf16 2e-2) and the
+benchmark's (fp8 5e-2, mxfp4 1e-1)."""
+import pytest
+import torch
+
+from gpu_utils import DEV, grouped_gemm, random_rows
+from oracle import torch_oracle as to
+
+pytestmark = pytest.mark.gpu
+
+CHECK, TC = 2, 1
+
+
+def _bf16_case(E, M, N, K, gen, has_bias, zero_frac=0.25):
+    rows = random_rows(E, M, gen, zero_frac)
+    a = (torch.randn(M, K, generator=gen)).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, generator=gen) * K ** -0.5).to(torch.bfloat16)
+    bias = (torch.randn(E, N, generator=gen) * 0.1).to(torch.bfloat16) if has_bias else None
+    return rows, a, w, bias
+
+
+def _close(out, ref, rows, tol):
+    n = int(rows.sum())
+    torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("impl", [CHECK, TC])
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("E,M,N,K", [(4, 37, 256, 128), (8, 64, 2816, 512), (8, 5, 384, 256), (3, 700, 128, 192),
+                                     (16, 2100, 512, 320), (2, 1, 128, 64), (5, 300, 200, 136)])
+@pytest.mark.parametrize("has_bias", [False, True])
+def test_grouped_gemm_bf16(native, impl, layout, E, M, N, K, has_bias):
+    g = torch.Generator().manual_seed(E * M + N)
+    rows, a, w, bias = _bf16_case(E, M, N, K, g, has_bias)
+    ref = to.grouped_gemm(a.float(), w.float(), bias, rows, torch.bfloat16)
+    wd = w.to(DEV) if layout == "nk" else w.transpose(1, 2).contiguous().to(DEV)
+    out = grouped_gemm(a.to(DEV), None, wd, None, bias.to(DEV) if has_bias else None, rows.to(DEV), N, K,
+                       layout=1 if layout == "nk" else 2, impl=impl)
+    _close(out, ref, rows, 2e-2)
+    # rows past the routed ones are never written
+    n = int(rows.sum())
+    assert bool(torch.isnan(out[n:].float()).all())
+
+
+@pytest.mark.parametrize("impl", [CHECK, TC])
+def test_grouped_gemm_fp16(native, impl):
+    g = torch.Generator().manual_seed(9)
+    rows, a, w, bias = _bf16_case(4, 100, 256, 256, g, True)
+    a, w, bias = a.half(), w.half(), bias.half()
+    ref = to.grouped_gemm(a.float(), w.float(), bias, rows, torch.float16)
+    out = grouped_gemm(a.to(DEV), None, w.transpose(1, 2).contiguous().to(DEV), None, bias.to(DEV), rows.to(DEV),
+                       256, 256, layout=2, impl=impl, out_dtype=torch.float16)
+    _close(out, ref, rows, 1e-2)
+
+
+def _fp8_case(E, M, N, K, gen):
+    rows = random_rows(E, M, gen)
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    wq, ws = zip(*[to.quant_fp8_block_wei(torch.randn(N, K, generator=gen) * K ** -0.5) for _ in range(E)])
+    return rows, x, torch.stack(wq), torch.stack(ws)
+
+
+@pytest.mark.parametrize("impl", [CHECK, TC])
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+@pytest.mark.parametrize("E,M,N,K", [(4, 40, 256, 256), (8, 9, 1536, 2048), (6, 900, 384, 512), (32, 64, 256, 128)])
+def test_grouped_gemm_fp8_block_w8a8(native, impl, layout, E, M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    rows, x, wq, ws = _fp8_case(E, M, N, K, g)
+    aq, a_s = to.per_token_group_fp8_quant(x, 128, 1e-10)
+    wdeq = torch.stack([to.dequant_fp8_block_wei(wq[e], ws[e]) for e in range(E)])
+    ref = to.grouped_gemm(to.dequant_fp8_block_act(aq, a_s), wdeq, None, rows, torch.bfloat16)
+    wd = wq.to(DEV) if layout == "nk" else wq.transpose(1, 2).contiguous().to(DEV)
+    out = grouped_gemm(aq.to(DEV), a_s.to(DEV), wd, ws.to(DEV), None, rows.to(DEV), N, K,
+                       layout=1 if layout == "nk" else 2, impl=impl)
+    _close(out, ref, rows, 2e-2)  # same quantised operands on both sides: only fp32 order differs
+
+
+def test_grouped_gemm_fp8_block_w8a16_and_per_tensor(native):
+    g = torch.Generator().manual_seed(77)
+    rows, x, wq, ws = _fp8_case(4, 50, 256, 256, g)
+    wdeq = torch.stack([to.dequant_fp8_block_wei(wq[e], ws[e]) for e in range(4)]).to(torch.bfloat16)
+    ref = to.grouped_gemm(x.float(), wdeq.float(), None, rows, torch.bfloat16)
+    out = grouped_gemm(x.to(DEV), None, wq.to(DEV), ws.to(DEV), None, rows.to(DEV), 256, 256, layout=1, impl=0)
+    _close(out, ref, rows, 2e-2)
+    # per-tensor fp8 [E,K,N] with one scale per expert
+    sc = torch.tensor([0.5, 2.0, 1.0, 0.25])
+    ref = to.grouped_gemm(x.float(), wq.float() * sc.view(4, 1, 1), None, rows, torch.bfloat16)
+    out = grouped_gemm(x.to(DEV), None, wq.transpose(1, 2).contiguous().to(DEV), sc.to(DEV), None,
+                       rows.to(DEV), 256, 256, impl=0)
+    _close(out, ref, rows, 2e-2)
+
+
+@pytest.mark.parametrize("impl", [CHECK, TC])
+def test_fp8_block_identity_known_answer_is_exact(native, impl):
+    """Identity activations x every finite e4m3 code x block scales {0.5, 2}
+    reproduce code * scale exactly (tests/fused_moe/test_grouped_gemm.py:275-307)."""
+    codes = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    finite = codes[torch.isfinite(codes.float())]
+    K = N = 256
+    w = finite[torch.arange(N * K) % finite.numel()].view(1, N, K).contiguous()
+    ws = torch.tensor([[[0.5, 2.0], [2.0, 0.5]]])
+    eye = torch.eye(K)
+    rows = torch.tensor([K], dtype=torch.int32)
+    expect = (to.dequant_fp8_block_wei(w[0], ws[0]).T).to(torch.bfloat16)
+    if impl == CHECK:
+        out = grouped_gemm(eye.to(torch.bfloat16).to(DEV), None, w.to(DEV), ws.to(DEV), None, rows.to(DEV),
+                           N, K, layout=1, impl=impl)
+    else:
+        a_s = torch.ones(K, K // 128)
+        out = grouped_gemm(eye.to(torch.float8_e4m3fn).to(DEV), a_s.to(DEV), w.to(DEV), ws.to(DEV), None,
+                           rows.to(DEV), N, K, layout=1, impl=impl)
+    torch.testing.assert_close(out.cpu(), expect, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("E,M,N,K", [(4, 30, 256, 128), (8, 130, 5760 // 8, 2880 // 4)])
+@pytest.mark.parametrize("has_bias", [False, True])
+def test_grouped_gemm_mxfp4(native, E, M, N, K, has_bias):
+    g = torch.Generator().manual_seed(N + K)
+    rows = random_rows(E, M, g)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    packed = torch.randint(0, 256, (E, N, K // 2), generator=g, dtype=torch.int32).to(torch.uint8)
+    sc = torch.randint(117, 124, (E, N, K // 32), generator=g, dtype=torch.int32).to(torch.uint8)
+    bias = (torch.randn(E, N, generator=g) * 0.02).to(torch.bfloat16) if has_bias else None
+    wdeq = to.dequant_mxfp4(packed, sc).to(torch.bfloat16).float()
+    ref = to.grouped_gemm(x.float(), wdeq, bias, rows, torch.bfloat16)
+    out = grouped_gemm(x.to(DEV), None, packed.to(DEV).view(torch.float4_e2m1fn_x2), sc.to(DEV),
+                       bias.to(DEV) if has_bias else None, rows.to(DEV), N, K, impl=0)
+    n = int(rows.sum())
+    torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("epi", [1, 2])
+def test_gated_epilogue_matches_unfused(native, epi):
+    g = torch.Generator().manual_seed(epi)
+    rows, a, w, bias = _bf16_case(4, 60, 512, 256, g, True)
+    wd = w.transpose(1, 2).contiguous().to(DEV)
+    full = grouped_gemm(a.to(DEV), None, wd, None, bias.to(DEV), rows.to(DEV), 512, 256, layout=2, impl=CHECK)
+    fused = grouped_gemm(a.to(DEV), None, wd, None, bias.to(DEV), rows.to(DEV), 512, 256, layout=2, epilogue=epi,
+                         impl=0)
+    n = int(rows.sum())
+    expect = to.silu_and_mul(full.cpu().float()) if epi == 1 else to.swigluoai_and_mul(full.cpu().float())
+    torch.testing.assert_close(fused.cpu()[:n].float(), expect[:n], rtol=2e-2, atol=2e-2)
+
+
+def test_tensor_core_kernel_matches_checking_kernel_on_mixtral_tile_shapes(native):
+    """One expert segment per tile size (decode, mid, prefill) and a feature
+    count that is not a multiple of the 128-wide tile."""
+    g = torch.Generator().manual_seed(1)
+    for (E, M, N, K) in [(8, 16, 1024, 4096), (8, 500, 1024, 1024), (4, 1500, 1152, 512), (2, 3000, 192, 256)]:
+        rows, a, w, bias = _bf16_case(E, M, N, K, g, True, zero_frac=0.1)
+        wd = w.transpose(1, 2).contiguous().to(DEV)
+        ref = grouped_gemm(a.to(DEV), None, wd, None, bias.to(DEV), rows.to(DEV), N, K, layout=2, impl=CHECK)
+        out = grouped_gemm(a.to(DEV), None, wd, None, bias.to(DEV), rows.to(DEV), N, K, layout=2, impl=TC)
+        n = int(rows.sum())
+        torch.testing.assert_close(out[:n].float(), ref[:n].float(), rtol=1e-2, atol=1e-2)
+
+
+def test_grouped_gemm_argument_checks(native):
+    a = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(2, 64, 36, dtype=torch.bfloat16, device=DEV)
+    d = torch.zeros(4, 36, dtype=torch.bfloat16, device=DEV)
+    rows = torch.tensor([2, 2], dtype=torch.int32, device=DEV)
+    f = torch.ops._xpu_C.cutlass_grouped_gemm_interface
+    with pytest.raises(RuntimeError, match="N must be divisible by 8"):
+        f(a, None, w, None, None, d, rows, 36, 64, 2)
+    w = torch.zeros(2, 64, 32, dtype=torch.bfloat16, device=DEV)
+    d = torch.zeros(4, 32, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="ptr_B.size\\(0\\) must match num_experts"):
+        f(a, None, w, None, None, d, rows, 32, 64, 3)
+    with pytest.raises(RuntimeError, match="w16a16 grouped gemm must not have scales"):
+        f(a, None, w, torch.ones(2, device=DEV), None, d, rows, 32, 64, 2)
+    with pytest.raises(RuntimeError, match="ptr_A.size\\(0\\) must match ptr_D.size\\(0\\)"):
+        f(a, None, w, None, None, torch.zeros(5, 32, dtype=torch.bfloat16, device=DEV), rows, 32, 64, 2)
+    w8 = torch.zeros(2, 128, 128, dtype=torch.float8_e4m3fn, device=DEV)
+    with pytest.raises(RuntimeError, match="block scales must have shape"):
+        f(torch.zeros(4, 128, dtype=torch.bfloat16, device=DEV), None, w8, torch.ones(2, 2, 1, device=DEV), None,
+          torch.zeros(4, 128, dtype=torch.bfloat16, device=DEV), rows, 128, 128, 2)
+    out = f(a, None, w, None, None, d, rows, 32, 64, 2)
+    assert out.data_ptr() == d.data_ptr()

@@ -1,0 +1,138 @@
+"""CPU: the oracle (torch restatement and plain-C restatement) against the
+golden vectors produced by the reference's own pure-torch test references."""
+import torch
+
+from conftest import load_golden
+from oracle import c_oracle as co
+from oracle import torch_oracle as to
+
+
+def _rows_as_sets(ids):
+    return [sorted(r) for r in ids.tolist()]
+
+
+def test_topk_softmax_sigmoid_against_reference_vectors():
+    for c in load_golden("routing_topk.pt"):
+        w, ids = to.topk_softmax(c["gating"], c["topk"], c["renormalize"], c["bias"])
+        assert torch.equal(ids, c["softmax_ids"])
+        assert torch.equal(w, c["softmax_w"])
+        w, ids = to.topk_sigmoid(c["gating"], c["topk"], c["renormalize"], c["bias"],
+                                 c["routed_scaling_factor"])
+        assert torch.equal(ids, c["sigmoid_ids"])
+        assert torch.equal(w, c["sigmoid_w"])
+        # plain-C restatement: ids exact, weights to float rounding (its exp and its
+        # summation order are its own; the reference's bar is atol 2e-2)
+        cw, cids, src = co.topk_gating(c["gating"], c["topk"], c["renormalize"], c["bias"], True)
+        assert torch.equal(cids, c["softmax_ids"])
+        torch.testing.assert_close(cw, c["softmax_w"], rtol=2e-6, atol=1e-7)
+        T = c["gating"].shape[0]
+        expect_src = torch.arange(c["topk"]).unsqueeze(0) * T + torch.arange(T).unsqueeze(1)
+        assert torch.equal(src, expect_src.to(torch.int32))
+        cw, cids, _ = co.topk_gating(c["gating"], c["topk"], c["renormalize"], c["bias"], False,
+                                     c["routed_scaling_factor"])
+        assert torch.equal(cids, c["sigmoid_ids"])
+        torch.testing.assert_close(cw, c["sigmoid_w"], rtol=2e-6, atol=1e-7)
+
+
+def test_grouped_topk_against_reference_vectors():
+    for c in load_golden("routing_grouped.pt"):
+        scores = torch.softmax(c["gating"], -1) if c["scoring"] == "softmax" else c["gating"].sigmoid()
+        swb = scores + c["bias"].unsqueeze(0)
+        for fn in (to.grouped_topk, co.grouped_topk):
+            w, ids = fn(scores, swb, c["n_group"], c["topk_group"], c["topk"], c["renormalize"],
+                        c["routed_scaling_factor"])
+            # the reference uses torch.topk(sorted=False): compare each row as a set,
+            # and the weights after sorting both sides by expert id
+            assert _rows_as_sets(ids) == _rows_as_sets(c["ids"])
+            o1, o2 = ids.long().argsort(-1), c["ids"].long().argsort(-1)
+            torch.testing.assert_close(w.float().gather(1, o1), c["weights"].gather(1, o2),
+                                       rtol=2e-6, atol=1e-7)
+            # definite order: descending biased score
+            picked = swb.gather(1, ids.long())
+            assert bool((picked[:, :-1] >= picked[:, 1:]).all())
+
+
+def test_grouped_topk_c_equals_torch_restatement():
+    g = torch.Generator().manual_seed(3)
+    scores = torch.rand(40, 256, generator=g)
+    swb = scores + torch.randn(256, generator=g) * 0.1
+    w1, i1 = to.grouped_topk(scores, swb, 8, 4, 8, True, 2.5)
+    w2, i2 = co.grouped_topk(scores, swb, 8, 4, 8, True, 2.5)
+    assert torch.equal(i1, i2)
+    torch.testing.assert_close(w1, w2, rtol=2e-6, atol=1e-7)
+    # a row without any finite score falls back to experts 0..K-1 with weight 1/K
+    bad = torch.full((1, 256), float("-inf"))
+    w, i = co.grouped_topk(bad, bad, 8, 4, 8, True, 2.5)
+    assert i.tolist() == [list(range(8))] and torch.allclose(w, torch.full((1, 8), 0.125))
+
+
+def test_moe_align_against_reference_vectors():
+    for c in load_golden("moe_align.pt"):
+        n_sorted, n_blocks = c["sorted_ids"].numel(), c["expert_ids"].numel()
+        for fn in (
+            lambda: to.moe_align_block_size(c["topk_ids"], c["block_size"], c["num_experts"],
+                                            n_sorted, n_blocks, c["expert_map"]),
+            lambda: co.moe_align_block_size(c["topk_ids"], c["num_experts"], c["block_size"],
+                                            n_sorted, n_blocks, c["expert_map"]),
+        ):
+            s, e, post = fn()
+            assert torch.equal(post, c["num_tokens_post_pad"])
+            assert torch.equal(e, c["expert_ids"])
+            assert torch.equal(s, c["sorted_ids"])  # the golden is stable too
+
+
+def test_remap_against_reference_vectors():
+    for c in load_golden("remap.pt"):
+        remapped, _, rows, row_map = to.remap_hidden_states(c["hidden"], None, c["topk_ids"],
+                                                            c["expert_map"], c["local_experts"])
+        assert torch.equal(rows, c["rows_per_expert"])
+        assert torch.equal(row_map, c["row_map"])
+        n = int(rows.sum())
+        assert torch.equal(remapped[:n], c["remapped"][:n])
+        crows, cmap = co.remap_bookkeeping(c["topk_ids"], c["expert_map"], c["total_experts"],
+                                           c["local_experts"])
+        assert torch.equal(crows, c["rows_per_expert"]) and torch.equal(cmap, c["row_map"])
+
+
+def test_init_expert_map_semantics():
+    for (n, r, s) in [(4, 0, 4), (4, 3, 4), (32, 5, 8)]:
+        a, b = to.init_expert_map(n, r, s), co.init_expert_map(n, r, s)
+        assert torch.equal(a, b)
+        assert a[r * n:(r + 1) * n].tolist() == list(range(n)) and int((a >= 0).sum()) == n
+
+
+def test_gather_activation_quant_dequant_against_reference_vectors():
+    for c in load_golden("moe_gather.pt"):
+        out = to.moe_gather(c["moe_output"], c["topk_weights"], c["row_map"], torch.bfloat16)
+        assert torch.equal(out, c["output"])
+    a = load_golden("activations.pt")
+    assert torch.equal(to.silu_and_mul(a["x_bf16"]), a["silu_bf16"])
+    assert torch.equal(to.swigluoai_and_mul(a["x_bf16"]), a["swiglu_bf16"])
+    assert torch.equal(to.silu_and_mul(a["x_f32"]), a["silu_f32"])
+    assert torch.equal(to.swigluoai_and_mul(a["x_f32"]), a["swiglu_f32"])
+    q = load_golden("fp8_group_quant.pt")
+    oq, os_ = to.per_token_group_fp8_quant(q["x"], 128, 1e-10)
+    # the reference's golden divides by the scale, the kernel multiplies by its
+    # reciprocal: scales agree exactly, codes may differ by one e4m3 step
+    assert torch.equal(os_, q["s"])
+    diff = (oq.float() - q["q"].float()).abs()
+    assert float((diff > 0).float().mean()) < 0.02
+    assert bool((diff <= q["q"].float().abs() * 0.13 + 2 ** -9).all())
+    d = load_golden("dequant.pt")
+    assert torch.equal(to.dequant_mxfp4(d["mxfp4_packed"], d["mxfp4_scale"]), d["mxfp4_deq"])
+    assert torch.equal(to.dequant_fp8_block_wei(d["fp8_w"], d["fp8_scale"]), d["fp8_deq"])
+
+
+def test_layer_bf16_against_reference_vectors():
+    for c in load_golden("layer_bf16.pt"):
+        out = to.fused_moe_bf16(c["x"], c["w13"], c["w13_bias"], c["w2"], c["w2_bias"],
+                                c["topk_weights"], c["topk_ids"], c["num_experts"],
+                                c.get("ep_rank", 0), c.get("ep_size", 1), c["clamp"])
+        torch.testing.assert_close(out, c["output"], rtol=0, atol=0)
+        # the staged form (what the kernel path computes) agrees within the
+        # reference's own bf16 tolerance
+        if c.get("ep_size", 1) == 1:
+            staged = to.fused_moe_staged(c["x"], c["w13"].float(), c["w13_bias"], c["w2"].float(),
+                                         c["w2_bias"], c["topk_weights"], c["topk_ids"],
+                                         c["num_experts"], gemm1_clamp_limit=c["clamp"])
+            torch.testing.assert_close(staged, c["output"], rtol=2e-2, atol=2e-2)

@@ -498,7 +498,8 @@ extern "C" int b200moe_moe_align_block_size(
   B200_CHECK_ARG(block_size >= 1, "moe_align_block_size: block_size must be positive");
   B200_CHECK_ARG(numel >= 0 && sorted_len >= 0 && expert_ids_len >= 0,
                  "moe_align_block_size: negative size");
-  B200_CHECK_ARG(sorted_token_ids && expert_ids && num_tokens_post_pad,
+  B200_CHECK_ARG((sorted_len == 0 || sorted_token_ids) && (expert_ids_len == 0 || expert_ids) &&
+                     num_tokens_post_pad,
                  "moe_align_block_size: null output");
   B200_CHECK_ARG(numel == 0 || topk_ids, "moe_align_block_size: null topk_ids");
   SortParams p;

@@ -1,0 +1,351 @@
+# SPDX-License-Identifier: Apache-2.0
+"""Fused Mixture-of-Experts layer: the Python entry point.
+
+Mirrors ``vllm_xpu_kernels/fused_moe_interface.py`` of vllm-xpu-kernels
+(``XpuFusedMoe`` :165-419, ``xpu_fused_moe`` :421-619): same class and function
+names, argument order, defaults and weight-layout contract, so a caller of the
+reference can switch without edits.  The work is done by the CUDA kernels
+registered as ``torch.ops._moe_C / _C / _xpu_C`` (hand-written for sm_100a);
+there is no CPU or eager-torch fallback: if the native libraries are missing,
+``FUSEDMOE_AVAILABLE`` is False and every call raises.
+
+Weight layouts (as in the reference, :47-69 and
+csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:200-223):
+
+* bf16 / fp16 and per-tensor fp8:  ``[E, K, N]`` (the transposed checkpoint);
+* block fp8 (fp32 scales ``[E, N/128, K/128]``): ``[E, N, K]`` or ``[E, K, N]``;
+* MXFP4 (``float4_e2m1fn_x2``): ``[E, N, K/2]`` with e8m0 scales ``[E, N, K/32]``.
+"""
+import os
+from typing import Optional
+
+import torch
+
+try:
+    from . import _C  # noqa: F401
+    from . import _moe_C  # noqa: F401
+    from . import _xpu_C  # noqa: F401
+    FUSEDMOE_UNAVAILABLE_REASON = None
+    FUSEDMOE_AVAILABLE = True
+except ImportError as e:  # native libraries not built
+    FUSEDMOE_UNAVAILABLE_REASON = str(e)
+    FUSEDMOE_AVAILABLE = False
+
+from .moe_utils import quant_act_xpu
+
+REF_FUSED_MOE_ENV = "VLLM_XPU_FUSED_MOE_USE_REF"
+USE_MXFP4_FP8_ENV = "VLLM_XPU_FUSED_MOE_USE_MXFP4_FP8"
+FP8_BLOCK_SIZE = 128
+
+# Epilogue codes of torch.ops._xpu_C.b200_grouped_gemm (b200moe_epilogue).
+_EPI_NONE, _EPI_SILU, _EPI_SWIGLUOAI = 0, 1, 2
+
+
+def _require_native():
+    if not FUSEDMOE_AVAILABLE:
+        raise RuntimeError(
+            "vllm_xpu_kernels: the native CUDA libraries are not built "
+            f"({FUSEDMOE_UNAVAILABLE_REASON}); run build.py - there is no fallback path")
+
+
+def _is_env_enabled(env_name: str, default: str = "0") -> bool:
+    value = os.environ.get(env_name, default).strip().upper()
+    return value in ("1", "ON", "TRUE", "YES", "Y")
+
+
+def _get_recipe(is_fp8, is_mxfp8, is_mxfp4, is_int4, is_block_fp8):
+    if is_mxfp8:
+        return "mxfp8"
+    elif is_block_fp8:
+        return "fp8block"
+    elif is_mxfp4:
+        return "mxfp4_fp8" if _is_env_enabled(USE_MXFP4_FP8_ENV) else "mxfp4"
+    elif is_int4:
+        return "int4"
+    elif is_fp8:
+        return "fp8"
+    else:
+        return "bf16"
+
+
+def _get_weights_dtype(weight, scales):
+    weight_dtype = weight.dtype
+    is_fp8 = weight_dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
+    is_int4 = weight_dtype == torch.uint8
+    is_mxfp4 = weight_dtype == torch.float4_e2m1fn_x2
+    is_mxfp8 = (is_fp8 and scales is not None and scales.dtype == torch.uint8)
+    is_block_fp8 = (is_fp8 and scales is not None
+                    and scales.dtype == torch.float32 and scales.ndim == 3)
+    is_fp8 = is_fp8 and not is_mxfp8 and not is_block_fp8
+    return is_fp8, is_int4, is_mxfp4, is_mxfp8, is_block_fp8
+
+
+def _get_inter_size(w13, w13_scales, is_int4, is_mxfp4, is_block_fp8):
+    if is_block_fp8:
+        return w13_scales.shape[-2] * FP8_BLOCK_SIZE // 2
+    if is_int4 or is_mxfp4:
+        return w13.shape[-2] // 2
+    return w13.shape[-1] // 2
+
+
+def cutlass_grouped_gemm_xe2(input_A, input_B, scales, bias, output,
+                             num_rows_per_expert, n, k, num_experts):
+    """Same helper as the reference (:92-104): one grouped GEMM call."""
+    _require_native()
+    torch.ops._xpu_C.cutlass_grouped_gemm_interface(
+        ptr_A=input_A, ptr_A_scale=None, ptr_B=input_B, ptr_B_scale=scales,
+        ptr_bias=bias, ptr_D=output, rows_per_expert=num_rows_per_expert,
+        N=n, K=k, num_experts=num_experts)
+
+
+def cutlass_grouped_gemm(input_A, input_A_scale, input_B, input_B_scale, bias,
+                         output, expert_token_count, n, k, num_experts):
+    """Reference helper (:72-89) taking the row counts as a host list."""
+    _require_native()
+    num_rows_per_expert = torch.tensor(expert_token_count, dtype=torch.int32,
+                                       device=input_A.device)
+    torch.ops._xpu_C.cutlass_grouped_gemm_interface(
+        ptr_A=input_A, ptr_A_scale=input_A_scale, ptr_B=input_B,
+        ptr_B_scale=input_B_scale, ptr_bias=bias, ptr_D=output,
+        rows_per_expert=num_rows_per_expert, N=n, K=k, num_experts=num_experts)
+
+
+def ceilDiv(a, b):
+    return (a + b - 1) // b
+
+
+def compute_num_tokens_per_block(num_tokens, num_experts_per_node):
+    for num_tokens_per_block in [32, 64, 128, 256, 512, 1024]:
+        num_blocks_per_seq = ceilDiv(num_tokens, num_tokens_per_block)
+        if num_blocks_per_seq * num_experts_per_node <= num_tokens_per_block:
+            return num_tokens_per_block
+    return 1024
+
+
+def _activation_kind(activation):
+    """Maps the reference's activation names (:119-133, :239-254) to an op."""
+    if activation == "silu":
+        return "silu"
+    if activation == "swigluoai" or ("SWIGLUOAI" in str(activation)):
+        return "swigluoai"
+    raise ValueError(f"Unsupported FusedMoe activation: {activation}.")
+
+
+def fused_moe_activation(act_output, gemm1_output, activation):
+    kind = _activation_kind(activation)
+    if kind == "silu":
+        torch.ops._C.silu_and_mul(act_output, gemm1_output)
+    else:
+        torch.ops._C.swigluoai_and_mul(act_output, gemm1_output, 1.702, 7.0)
+
+
+class XpuFusedMoe:
+    """The fused-MoE layer object (reference :165-419).
+
+    ``fuse_activation`` (not in the reference; keyword only) applies the gated
+    activation inside the first grouped GEMM's epilogue when the kernel for
+    this recipe offers it, instead of a separate pass over ``[T*K, 2I]``.
+    """
+
+    def __init__(
+        self,
+        w13,
+        w13_scales,
+        w13_bias,
+        w2,
+        w2_scales,
+        w2_bias,
+        n_experts_per_token,
+        activation,
+        num_experts,
+        ep_rank=0,
+        ep_size=1,
+        expert_map=None,
+        gemm1_clamp_limit: Optional[float] = None,
+        *,
+        fuse_activation: bool = False,
+    ):
+        assert w13.is_contiguous() and w2.is_contiguous()
+        _require_native()
+
+        (is_fp8, is_int4, is_mxfp4, is_mxfp8,
+         is_block_fp8) = _get_weights_dtype(w13, w13_scales)
+        if is_int4:
+            raise NotImplementedError("int4 (w4a16) weights are not built for sm_100a yet")
+        if is_mxfp8:
+            raise NotImplementedError("mxfp8 weights are not built for sm_100a yet")
+        if w13.dtype == torch.float8_e5m2:
+            raise NotImplementedError("float8_e5m2 weights are not built for sm_100a yet")
+        if _is_env_enabled(REF_FUSED_MOE_ENV):
+            raise NotImplementedError(
+                f"{REF_FUSED_MOE_ENV} selects the reference's eager qdq simulation, "
+                "which this build does not ship: only the CUDA kernels run")
+
+        self.inter_size = _get_inter_size(w13, w13_scales, is_int4, is_mxfp4, is_block_fp8)
+        self.w13 = w13
+        self.w2 = w2
+        if not (is_fp8 or is_mxfp4 or is_block_fp8):
+            self.gemm1_wei_scales = None
+            self.gemm2_wei_scales = None
+        else:
+            self.gemm1_wei_scales = w13_scales
+            self.gemm2_wei_scales = w2_scales
+        self.w13_bias = w13_bias
+        self.w2_bias = w2_bias
+
+        self.n_experts_per_token = n_experts_per_token
+        self.activation = activation
+        self._act_kind = _activation_kind(activation)
+        self.inter_size_scale = 1
+        self.num_experts = num_experts
+        self.ep_rank = ep_rank
+        self.ep_size = ep_size
+        self.is_fp8 = is_fp8
+        self.is_int4 = is_int4
+        self.is_mxfp4 = is_mxfp4
+        self.is_mxfp8 = is_mxfp8
+        self.is_block_fp8 = is_block_fp8
+        self.gemm1_clamp_limit = gemm1_clamp_limit
+        self.recipe = _get_recipe(is_fp8, is_mxfp8, is_mxfp4, is_int4, is_block_fp8)
+        self._use_ref = False
+        self.fuse_activation = fuse_activation
+        if self._act_kind == "silu":
+            self.act_func = torch.ops._C.silu_and_mul
+        else:
+            self.act_func = torch.ops._C.swigluoai_and_mul
+
+        self.expert_map = expert_map
+        if self.expert_map is None and self.ep_size > 1:
+            self.expert_map = torch.empty((self.num_experts * self.ep_size),
+                                          dtype=torch.int32, device=w13.device)
+            torch.ops._moe_C.init_expert_map(self.expert_map, self.num_experts,
+                                             self.ep_rank, self.ep_size)
+        if self.expert_map is not None:
+            self.total_experts_num = self.expert_map.shape[0]
+        else:
+            self.total_experts_num = self.num_experts * self.ep_size
+        self.local_experts_num = self.num_experts
+
+    def apply(self, output, hidden_states, topk_weights, topk_ids,
+              expert_map=None, a1q_scale=None):
+        self._apply_kernel(output, hidden_states, topk_weights, topk_ids,
+                           expert_map, a1q_scale)
+
+    # The stages below are the reference's eight steps (:328-419); what differs
+    # is inside the ops and, for block fp8, that activations really are
+    # quantised to e4m3 per 1x128 group and multiplied on the fp8 tensor cores.
+    def _apply_kernel(self, output, hidden_states, topk_weights, topk_ids,
+                      expert_map=None, a1q_scale=None):
+        num_rows, hidden_size = hidden_states.shape
+        K = self.n_experts_per_token
+        num_moe_inputs = K * num_rows
+        dev = hidden_states.device
+        E = self.num_experts
+        I = self.inter_size
+        if expert_map is None and self.ep_size > 1:
+            expert_map = self.expert_map
+
+        rows_per_expert = torch.empty((E,), dtype=torch.int32, device=dev)
+        row_map = torch.empty((num_rows, K), dtype=torch.int32, device=dev)
+
+        quant_acts = self.is_block_fp8
+        if quant_acts and a1q_scale is None:
+            # permute + dynamic 1x128 e4m3 quantisation in one pass
+            remapped = torch.empty((num_moe_inputs, hidden_size), dtype=torch.float8_e4m3fn, device=dev)
+            remapped_scales = torch.empty((num_moe_inputs, hidden_size // FP8_BLOCK_SIZE),
+                                          dtype=torch.float32, device=dev)
+            torch.ops._moe_C.b200_remap_quant_fp8(
+                hidden_states, remapped, remapped_scales, expert_map, rows_per_expert,
+                row_map, topk_ids, self.total_experts_num, self.local_experts_num)
+        else:
+            if a1q_scale is not None:
+                remapped_scales = torch.empty((num_moe_inputs, a1q_scale.shape[1]),
+                                              dtype=a1q_scale.dtype, device=dev)
+            else:
+                remapped_scales = None
+            remapped = torch.empty((num_moe_inputs, hidden_size), dtype=hidden_states.dtype, device=dev)
+            torch.ops._moe_C.remap_hidden_states(
+                hidden_states=hidden_states, hidden_states_scales=a1q_scale,
+                remapped_hidden_states=remapped,
+                remapped_hidden_states_scales=remapped_scales, expert_map=expert_map,
+                rows_per_expert=rows_per_expert,
+                unpermuted_row_to_permuted_row=row_map, topk_ids=topk_ids,
+                total_experts_num=self.total_experts_num,
+                local_experts_num=self.local_experts_num)
+
+        a_scale1 = remapped_scales if quant_acts else None
+        clamp = float(self.gemm1_clamp_limit) if (self.gemm1_clamp_limit is not None
+                                                   and self.gemm1_clamp_limit > 0) else 0.0
+
+        # ---- gemm1 (+ activation) ----
+        if self.fuse_activation:
+            act_output = torch.empty((num_moe_inputs, I), dtype=output.dtype, device=dev)
+            torch.ops._xpu_C.b200_grouped_gemm(
+                remapped, a_scale1, self.w13, self.gemm1_wei_scales, self.w13_bias, act_output,
+                rows_per_expert, 2 * I, hidden_size, E, 0,
+                _EPI_SILU if self._act_kind == "silu" else _EPI_SWIGLUOAI, 1.702, 7.0, clamp, 0)
+        else:
+            gemm1_output = torch.empty((num_moe_inputs, 2 * I), dtype=output.dtype, device=dev)
+            torch.ops._xpu_C.cutlass_grouped_gemm_interface(
+                ptr_A=remapped, ptr_A_scale=a_scale1, ptr_B=self.w13,
+                ptr_B_scale=self.gemm1_wei_scales, ptr_bias=self.w13_bias,
+                ptr_D=gemm1_output, rows_per_expert=rows_per_expert, N=2 * I,
+                K=hidden_size, num_experts=E)
+            if clamp > 0:
+                gate = gemm1_output[:, :I]
+                up = gemm1_output[:, I:]
+                gate.clamp_(max=clamp)
+                up.clamp_(min=-clamp, max=clamp)
+            act_output = torch.empty((num_moe_inputs, I), dtype=output.dtype, device=dev)
+            self.act_func(act_output, gemm1_output)
+
+        # ---- gemm2 ----
+        gemm2_output = torch.empty((num_moe_inputs, hidden_size), dtype=output.dtype, device=dev)
+        if quant_acts:
+            act_q, gemm2_act_scale = quant_act_xpu(act_output, self.recipe)
+        else:
+            act_q, gemm2_act_scale = act_output, None
+        torch.ops._xpu_C.cutlass_grouped_gemm_interface(
+            ptr_A=act_q, ptr_A_scale=gemm2_act_scale, ptr_B=self.w2,
+            ptr_B_scale=self.gemm2_wei_scales, ptr_bias=self.w2_bias,
+            ptr_D=gemm2_output, rows_per_expert=rows_per_expert, N=hidden_size,
+            K=I, num_experts=E)
+
+        torch.ops._moe_C.moe_gather(output, gemm2_output, topk_weights, row_map, E)
+
+
+def xpu_fused_moe(hidden_states,
+                  w13,
+                  w13_scales,
+                  w13_bias,
+                  w2,
+                  w2_scales,
+                  w2_bias,
+                  topk_weights,
+                  topk_ids,
+                  n_experts_per_token,
+                  activation,
+                  num_experts,
+                  ep_rank=0,
+                  ep_size=1,
+                  expert_map=None,
+                  output=None,
+                  is_fp8=False,
+                  is_int4=False,
+                  is_mxfp4=False,
+                  is_mxfp8=False,
+                  is_block_fp8=False,
+                  gemm1_clamp_limit: Optional[float] = None):
+    """Functional form (reference :421-619).  The recipe flags are accepted for
+    signature compatibility; as in the class, the recipe is read off the weight
+    and scale dtypes."""
+    if output is None:
+        output = torch.empty_like(hidden_states)
+    else:
+        assert output.shape == hidden_states.shape, \
+            "output shape must be the same as hidden_states shape"
+    layer = XpuFusedMoe(w13, w13_scales, w13_bias, w2, w2_scales, w2_bias,
+                        n_experts_per_token, activation, num_experts, ep_rank,
+                        ep_size, expert_map, gemm1_clamp_limit)
+    layer.apply(output, hidden_states, topk_weights, topk_ids)
+    return output
