@@ -117,6 +117,36 @@ int b200moe_moe_align_block_size(const void* topk_ids, b200moe_dtype ids_dtype,
                                  size_t workspace_bytes,
                                  b200moe_stream stream);
 
+/* Same result as b200moe_moe_align_block_size, for callers that cannot supply
+ * scratch memory: foreign-function hosts (cgo, JNI, ctypes) that are handed
+ * only input and output buffers and own no device allocator, and serving
+ * loops that must keep cudaMalloc - which serialises the device and can fail
+ * once a framework's pool holds all memory - off their hot path.  The
+ * scratch is a fixed 1 MiB array inside the library (held by every GPU that
+ * loads it until the process ends; b200moe_noalloc_scratch_capacity() returns
+ * its size); the call allocates nothing, neither directly nor through a
+ * library.  Requests whose scratch need (b200moe_sort_workspace_bytes)
+ * exceeds the array are refused with B200MOE_E_WORKSPACE before any launch.
+ * The first call on each device looks up the array's device address, so make
+ * that first call before any stream capture begins.  All calls on a device
+ * share the one array: two calls whose kernels overlap on the GPU (different
+ * streams, no ordering between them) race on it - serialise them.  The array
+ * keeps whatever the previous call left; the kernels rewrite every cell they
+ * read, so nothing needs clearing.
+ * This entry point has no counterpart in the reference. */
+int b200moe_moe_align_block_size_noalloc(const void* topk_ids,
+                                         b200moe_dtype ids_dtype,
+                                         int64_t numel, int num_experts,
+                                         int block_size,
+                                         int32_t* sorted_token_ids,
+                                         int64_t sorted_len,
+                                         int32_t* expert_ids,
+                                         int64_t expert_ids_len,
+                                         int32_t* num_tokens_post_pad,
+                                         const int32_t* expert_map,
+                                         b200moe_stream stream);
+size_t b200moe_noalloc_scratch_capacity(void);
+
 /* Replaces `init_expert_map` (csrc/moe/init_expert_map.cpp:78-95; schema
  * csrc/moe/torch_bindings.cpp:93-98). expert_map has num_local*ep_size ints. */
 int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,

@@ -581,3 +581,59 @@ extern "C" int b200moe_remap_quant_fp8(
   B200_LAUNCH_OK("remap_quant_kernel");
   return B200MOE_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the align op.
+//
+// Some hosts of this library cannot hand over scratch memory: a cgo / JNI /
+// ctypes binding usually receives only the input and output buffers that its
+// serving framework allocated and owns no device allocator of its own, and a
+// latency-critical serving loop must not call cudaMalloc on its hot path
+// (the call serialises the whole device and fails once the framework's pool
+// has claimed all memory).  For them the histogram exchange buffer of the
+// multi-block sort lives in a fixed array inside the library image.  Every GPU
+// that loads the library holds these kNoAllocScratchBytes until the process
+// exits.
+// ---------------------------------------------------------------------------
+namespace b200moe {
+namespace {
+constexpr size_t kNoAllocScratchBytes = 1u << 20;  // 1 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {};
+}  // namespace
+}  // namespace b200moe
+
+extern "C" size_t b200moe_noalloc_scratch_capacity(void) { return b200moe::kNoAllocScratchBytes; }
+
+extern "C" int b200moe_moe_align_block_size_noalloc(
+    const void* topk_ids, b200moe_dtype ids_dtype, int64_t numel, int num_experts, int block_size,
+    int32_t* sorted_token_ids, int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len,
+    int32_t* num_tokens_post_pad, const int32_t* expert_map, b200moe_stream stream) {
+  B200_CHECK_ARG(num_experts >= 1 && numel >= 0, "moe_align_block_size_noalloc: bad sizes");
+  const size_t need = b200moe_sort_workspace_bytes(numel, num_experts);
+  if (need > kNoAllocScratchBytes)
+    return fail(B200MOE_E_WORKSPACE,
+                "moe_align_block_size_noalloc: %lld slots over %d experts need %zu bytes of scratch, "
+                "the built-in buffer holds %zu; use b200moe_moe_align_block_size with a workspace",
+                (long long)numel, num_experts, need, (size_t)kNoAllocScratchBytes);
+  int dev = -1;
+  B200_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(B200MOE_E_UNSUPPORTED, "moe_align_block_size_noalloc: device ordinal %d out of range", dev);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // In host code `g_noalloc_scratch` is only a handle for the symbol, not a
+    // device address: resolve it once per device, with that device current.
+    void* ptr = nullptr;
+    B200_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    if (ptr == nullptr) return fail(B200MOE_E_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_noalloc_ptr[dev] = ptr;
+  }
+  // Nothing in the buffer has to start at zero: the count pass overwrites every
+  // histogram cell it later reads and the scan pass writes the prefix array.
+  return b200moe_moe_align_block_size(topk_ids, ids_dtype, numel, num_experts, block_size,
+                                      sorted_token_ids, sorted_len, expert_ids, expert_ids_len,
+                                      num_tokens_post_pad, expert_map, g_noalloc_ptr[dev],
+                                      kNoAllocScratchBytes, stream);
+}
