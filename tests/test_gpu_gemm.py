@@ -114,9 +114,11 @@ def test_fp8_block_identity_known_answer_is_exact(native, impl):
     torch.testing.assert_close(out.cpu(), expect, rtol=0, atol=0)
 
 
-@pytest.mark.parametrize("E,M,N,K", [(4, 30, 256, 128), (8, 130, 5760 // 8, 2880 // 5)])
+@pytest.mark.parametrize("impl", [CHECK, TC])
+@pytest.mark.parametrize("E,M,N,K", [(4, 30, 256, 128), (8, 130, 5760 // 8, 2880 // 5), (6, 900, 360, 2880),
+                                     (16, 40, 2880, 704)])
 @pytest.mark.parametrize("has_bias", [False, True])
-def test_grouped_gemm_mxfp4(native, E, M, N, K, has_bias):
+def test_grouped_gemm_mxfp4(native, impl, E, M, N, K, has_bias):
     g = torch.Generator().manual_seed(N + K)
     rows = random_rows(E, M, g)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
@@ -126,9 +128,15 @@ def test_grouped_gemm_mxfp4(native, E, M, N, K, has_bias):
     wdeq = to.dequant_mxfp4(packed, sc).to(torch.bfloat16).float()
     ref = to.grouped_gemm(x.float(), wdeq, bias, rows, torch.bfloat16)
     out = grouped_gemm(x.to(DEV), None, packed.to(DEV).view(torch.float4_e2m1fn_x2), sc.to(DEV),
-                       bias.to(DEV) if has_bias else None, rows.to(DEV), N, K, impl=0)
+                       bias.to(DEV) if has_bias else None, rows.to(DEV), N, K, impl=impl)
     n = int(rows.sum())
     torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=2e-2, atol=2e-2)
+    if has_bias:  # SwigluOAI fused into the epilogue (interleaved gate / up columns)
+        fused = grouped_gemm(x.to(DEV), None, packed.to(DEV).view(torch.float4_e2m1fn_x2), sc.to(DEV),
+                             bias.to(DEV), rows.to(DEV), N, K, epilogue=2, impl=impl)
+        full = to.grouped_gemm(x.float(), wdeq, bias, rows, torch.float32)
+        expect = to.swigluoai_and_mul(full)
+        torch.testing.assert_close(fused.cpu()[:n].float(), expect[:n], rtol=2e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("epi", [1, 2])

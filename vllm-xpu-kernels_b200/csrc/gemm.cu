@@ -6,6 +6,7 @@
 
 namespace b200moe {
 int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st);
+int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st);
 int grouped_gemm_check(const b200moe_gemm_args* a, cudaStream_t st);
 }  // namespace b200moe
 
@@ -54,7 +55,7 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
   B200_CHECK_ARG(a->a && a->w && a->d && a->rows_per_expert, "grouped_gemm: null pointer");
   cudaStream_t st = as_stream(stream);
   if (a->impl == 2) return grouped_gemm_check(a, st);
-  int rc = grouped_gemm_tc(a, st);
+  int rc = (a->w_format == B200MOE_W_MXFP4_NK) ? grouped_gemm_tc_dq(a, st) : grouped_gemm_tc(a, st);
   if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) return grouped_gemm_check(a, st);
   return rc;
 }

@@ -14,7 +14,8 @@
 //   warp 0  : TMA producer  (weights through a 3-D map [E, N, K], activations
 //             through a 2-D map [M, K]; 128-byte swizzle; ring of kStages)
 //   warp 1  : MMA issuer    (one lane), owns the tensor-memory allocation
-//   warps 2-5: epilogue     (tcgen05.ld -> registers -> global)
+//   warps 2-5 (2-9 for the fp8 128-token tile): epilogue (tcgen05.ld ->
+//             registers -> global)
 // 16-bit inputs use kind::f16 with the whole K loop accumulated in tensor
 // memory (two accumulator stages, so the epilogue of one tile overlaps the
 // MMAs of the next).  fp8 inputs use kind::f8f6f4 per 128-wide K block; the
@@ -26,14 +27,13 @@
 // *status is set to 1.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "gemm_tc_common.cuh"
 
 namespace b200moe {
 namespace {
 
-constexpr int kFeat = 128;        // features per tile (UMMA M)
 constexpr int kWTileBytes = 16384;  // 128 rows x 128 bytes, or the same area K-by-N
-constexpr int kThreads = 192;
-constexpr int kMaxExperts = 1024;
+constexpr int kMaxAccStages = 8;
 constexpr int kMaxStages = 8;
 
 struct TcParams {
@@ -55,11 +55,11 @@ template <int BT>
 struct Ctrl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
+  uint64_t acc_full[kMaxAccStages];
+  uint64_t acc_empty[kMaxAccStages];
   uint32_t tmem_base;
   int abort_flag;
-  float sc[4][2][BT];  // per epilogue warp, double buffered
+  alignas(16) float sc[8][2][BT];  // per epilogue warp, double buffered
   int tile_start[kMaxExperts + 1];
   int row_start[kMaxExperts + 1];
 };
@@ -75,50 +75,37 @@ template <int BT>
 __host__ __device__ constexpr size_t smem_bytes() {
   return 1024 + (size_t)num_stages<BT>() * stage_bytes<BT>() + sizeof(Ctrl<BT>);
 }
-template <int BT>
+// Accumulator stages in tensor memory.  16-bit inputs hand over one whole tile
+// per stage (two are enough); fp8 hands over every 128-wide K block, so more
+// stages let the MMA issuer run ahead of the promoting epilogue warps.
+template <int BT, bool kFp8>
+__host__ __device__ constexpr int acc_stages() {
+  return !kFp8 ? 2 : (512 / BT > kMaxAccStages ? kMaxAccStages : 512 / BT);
+}
+template <int BT, bool kFp8>
 __host__ __device__ constexpr uint32_t tmem_cols() {
-  return 2 * BT < 32 ? 32u : (uint32_t)(2 * BT);
+  const int c = acc_stages<BT, kFp8>() * BT;
+  return c <= 32 ? 32u : c <= 64 ? 64u : c <= 128 ? 128u : c <= 256 ? 256u : 512u;
 }
-
-struct TileInfo {
-  int e, n_tile, m_tile, row0, valid;
-};
-
-// Tiles of one expert are numbered feature-tile-major with the token tiles
-// adjacent, so CTAs that run at the same time share a weight tile in L2.
-template <int BT>
-__device__ __forceinline__ void locate_tile(const int* tile_start, const int* row_start, int t,
-                                            int& cursor, TileInfo& ti) {
-  while (t >= tile_start[cursor + 1]) ++cursor;
-  const int local = t - tile_start[cursor];
-  const int rows = row_start[cursor + 1] - row_start[cursor];
-  const int m_tiles = (rows + BT - 1) / BT;
-  ti.e = cursor;
-  ti.n_tile = local / m_tiles;
-  ti.m_tile = local - ti.n_tile * m_tiles;
-  ti.row0 = row_start[cursor] + ti.m_tile * BT;
-  const int left = rows - ti.m_tile * BT;
-  ti.valid = left < BT ? left : BT;
-}
-
-__device__ __forceinline__ void store_out(void* d, int out_f16, int64_t idx, float v) {
-  if (out_f16) reinterpret_cast<__half*>(d)[idx] = __float2half_rn(v);
-  else reinterpret_cast<__nv_bfloat16*>(d)[idx] = __float2bfloat16_rn(v);
-}
-__device__ __forceinline__ float load_bias(const void* b, int out_f16, int64_t idx) {
-  if (out_f16) return __half2float(reinterpret_cast<const __half*>(b)[idx]);
-  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[idx]);
-}
+// Epilogue warps: four cover the 128 TMEM lanes; the fp8 128-token tile uses
+// eight (two per lane quarter, half the columns each) to keep up with the MMAs.
+template <int BT, bool kFp8>
+__host__ __device__ constexpr int epi_warps() { return (kFp8 && BT >= 128) ? 8 : 4; }
+template <int BT, bool kFp8>
+__host__ __device__ constexpr int num_threads() { return 64 + 32 * epi_warps<BT, kFp8>(); }
 
 template <int BT, bool kFp8, bool kWKn>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(num_threads<BT, kFp8>(), 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_w, const TcParams p) {
   static_assert(!kFp8 || BT <= 128, "fp8 promotion keeps BT accumulators per thread");
   constexpr int kStages = num_stages<BT>();
   constexpr int kStageBytes = stage_bytes<BT>();
   constexpr int kElemsPerKb = kFp8 ? 128 : 64;  // K elements per 128-byte row
-  constexpr int kChunk = BT >= 32 ? 32 : 16;    // columns per tcgen05.ld
+  constexpr int kAccStages = acc_stages<BT, kFp8>();
+  constexpr int kEpiWarps = epi_warps<BT, kFp8>();
+  constexpr int kCols = BT / (kEpiWarps / 4);   // token columns one epilogue warp owns
+  constexpr int kChunk = kCols >= 32 ? 32 : 16;  // columns per tcgen05.ld
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -128,43 +115,23 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (warp == 0) {
-    // Prefix sums over the experts: rows and tiles.
-    int carry_r = 0, carry_t = 0;
-    if (lane == 0) { ctrl->row_start[0] = 0; ctrl->tile_start[0] = 0; }
-    for (int base = 0; base < p.num_experts; base += 32) {
-      const int e = base + lane;
-      int r = (e < p.num_experts) ? p.rows_per_expert[e] : 0;
-      if (r < 0) r = 0;
-      int tl = ((r + BT - 1) / BT) * p.n_tiles;
-      int ir = r, it = tl;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int o_r = __shfl_up_sync(0xffffffffu, ir, d);
-        const int o_t = __shfl_up_sync(0xffffffffu, it, d);
-        if (lane >= d) { ir += o_r; it += o_t; }
-      }
-      if (e < p.num_experts) {
-        ctrl->row_start[e + 1] = carry_r + ir;
-        ctrl->tile_start[e + 1] = carry_t + it;
-      }
-      carry_r += __shfl_sync(0xffffffffu, ir, 31);
-      carry_t += __shfl_sync(0xffffffffu, it, 31);
-    }
+    build_tile_prefix<BT>(p.rows_per_expert, p.num_experts, p.n_tiles, ctrl->row_start,
+                          ctrl->tile_start);
     if (lane == 0) {
       ptx::prefetch_tensormap(&tmap_a);
       ptx::prefetch_tensormap(&tmap_w);
     }
   } else if (warp == 1) {
-    ptx::tmem_alloc(&ctrl->tmem_base, tmem_cols<BT>());
+    ptx::tmem_alloc(&ctrl->tmem_base, tmem_cols<BT, kFp8>());
     ptx::tmem_relinquish();
   } else if (warp == 2 && lane == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&ctrl->full[s], 1);
       ptx::mbar_init(&ctrl->empty[s], 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kAccStages; ++a) {
       ptx::mbar_init(&ctrl->acc_full[a], 1);
-      ptx::mbar_init(&ctrl->acc_empty[a], 4);
+      ptx::mbar_init(&ctrl->acc_empty[a], kEpiWarps);
     }
     ctrl->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -216,15 +183,15 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
-        uint32_t a = acc_it & 1;
+        uint32_t a = acc_it % kAccStages;
         if (!kFp8) {
-          if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) break;
+          if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) break;
           ptx::tc_fence_after();
         }
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           if (kFp8) {
-            a = acc_it & 1;
-            if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            a = acc_it % kAccStages;
+            if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
           }
           const uint32_t s = it % kStages, ph = (it / kStages) & 1;
           if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
@@ -253,6 +220,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int et = q * 32 + lane;           // feature row inside the tile
     const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+    const int col0 = ((warp - 2) / 4) * kCols;   // first token column of this warp
     uint32_t acc_it = 0;
     int cursor = 0;
     bool ok = true;
@@ -265,8 +233,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (p.bias != nullptr && feat_ok) bias_v = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat);
 
       if (!kFp8) {
-        const uint32_t a = acc_it & 1;
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
+        const uint32_t a = acc_it % kAccStages;
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
           *abort_flag = 1; ok = false; break;
         }
         ptx::tc_fence_after();
@@ -292,22 +260,24 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
         ++acc_it;
       } else {
-        float acc[BT];
+        float acc[kCols];
 #pragma unroll
-        for (int i = 0; i < BT; ++i) acc[i] = 0.f;
+        for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
         const int kbs = p.k / 128;  // scale blocks along K
         const int64_t ws_base = ((int64_t)ti.e * (p.n / 128) + ti.n_tile) * kbs;
-        // Each warp stages its own copy of the BT combined scales of a K block
-        // (lane l owns tokens l, l+32, ..), so no barrier couples the warps.
-        constexpr int kPerLane = (BT + 31) / 32;
+        // Each warp stages its own copy of the combined scales of its columns
+        // for a K block (lane l owns columns l, l+32, ..), so no barrier couples
+        // the warps.
+        constexpr int kPerLane = (kCols + 31) / 32;
         float next_sc[kPerLane];
         auto fetch_scales = [&](int kb) {
           const float ws = p.w_scale[ws_base + kb];
 #pragma unroll
           for (int u = 0; u < kPerLane; ++u) {
-            const int c = lane + 32 * u;
+            const int c = col0 + lane + 32 * u;
             const int row = ti.row0 + c;
-            next_sc[u] = (c < ti.valid && row < p.m) ? p.a_scale[(int64_t)row * kbs + kb] * ws : 0.f;
+            next_sc[u] = (lane + 32 * u < kCols && c < ti.valid && row < p.m)
+                             ? p.a_scale[(int64_t)row * kbs + kb] * ws : 0.f;
           }
         };
         fetch_scales(0);
@@ -315,24 +285,29 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           float* sc = ctrl->sc[warp - 2][kb & 1];
 #pragma unroll
           for (int u = 0; u < kPerLane; ++u)
-            if (lane + 32 * u < BT) sc[lane + 32 * u] = next_sc[u];
+            if (lane + 32 * u < kCols) sc[lane + 32 * u] = next_sc[u];
           __syncwarp();
           if (kb + 1 < p.num_kb) fetch_scales(kb + 1);
-          const uint32_t a = acc_it & 1;
-          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
+          const uint32_t a = acc_it % kAccStages;
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
             *abort_flag = 1; ok = false; break;
           }
           ptx::tc_fence_after();
 #pragma unroll
-          for (int c0 = 0; c0 < BT; c0 += kChunk) {
-            if (c0 < ti.valid) {
+          for (int c0 = 0; c0 < kCols; c0 += kChunk) {
+            if (col0 + c0 < ti.valid) {
               uint32_t v[kChunk];
-              if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
-              else ptx::tmem_ld_32x16(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
+              if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
+              else ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
               ptx::tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < kChunk; ++i)
-                acc[c0 + i] = fmaf(__uint_as_float(v[i]), sc[c0 + i], acc[c0 + i]);
+              for (int i = 0; i < kChunk; i += 4) {
+                const float4 s4 = *reinterpret_cast<const float4*>(sc + c0 + i);
+                acc[c0 + i + 0] = fmaf(__uint_as_float(v[i + 0]), s4.x, acc[c0 + i + 0]);
+                acc[c0 + i + 1] = fmaf(__uint_as_float(v[i + 1]), s4.y, acc[c0 + i + 1]);
+                acc[c0 + i + 2] = fmaf(__uint_as_float(v[i + 2]), s4.z, acc[c0 + i + 2]);
+                acc[c0 + i + 3] = fmaf(__uint_as_float(v[i + 3]), s4.w, acc[c0 + i + 3]);
+              }
             }
           }
           ptx::tc_fence_before();
@@ -342,9 +317,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (ok && feat_ok) {
 #pragma unroll
-          for (int i = 0; i < BT; ++i) {
-            if (i < ti.valid && ti.row0 + i < p.m)
-              store_out(p.d, p.out_f16, (int64_t)(ti.row0 + i) * p.n + feat, acc[i] + bias_v);
+          for (int i = 0; i < kCols; ++i) {
+            const int c = col0 + i;
+            if (c < ti.valid && ti.row0 + c < p.m)
+              store_out(p.d, p.out_f16, (int64_t)(ti.row0 + c) * p.n + feat, acc[i] + bias_v);
           }
         }
       }
@@ -357,52 +333,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 1) {
     ptx::tc_fence_after();
     if (*abort_flag != 0) __nanosleep(20000);  // let copies still in flight land
-    ptx::tmem_dealloc(tmem_base, tmem_cols<BT>());
+    ptx::tmem_dealloc(tmem_base, tmem_cols<BT, kFp8>());
   }
   if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
-}
-
-// ------------------------------ host side ------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,
-               const cuuint64_t* dims, const cuuint64_t* strides_bytes, const cuuint32_t* box) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return fail(B200MOE_E_CUDA, "cuTensorMapEncodeTiled is not available");
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes, box,
-                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return fail(B200MOE_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return B200MOE_OK;
-}
-
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
 }
 
 template <int BT, bool kFp8, bool kWKn>
@@ -415,7 +348,7 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, i
                                       (int)smem_bytes<BT>()));
     configured = true;
   }
-  kern<<<grid, kThreads, smem_bytes<BT>(), st>>>(ta, tw, p);
+  kern<<<grid, num_threads<BT, kFp8>(), smem_bytes<BT>(), st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_tc_kernel");
   return B200MOE_OK;
 }

@@ -1,0 +1,120 @@
+// Pieces shared by the tensor-core grouped GEMM kernels: the tile walk over
+// ragged expert segments, output conversion, and host-side tensor-map encoding.
+#pragma once
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kFeat = 128;          // features per tile (UMMA M)
+constexpr int kMaxExperts = 1024;
+
+struct TileInfo {
+  int e, n_tile, m_tile, row0, valid;
+};
+
+// Tiles of one expert are numbered feature-tile-major with the token tiles
+// adjacent, so CTAs that run at the same time share a weight tile in L2.
+template <int BT>
+__device__ __forceinline__ void locate_tile(const int* tile_start, const int* row_start, int t,
+                                            int& cursor, TileInfo& ti) {
+  while (t >= tile_start[cursor + 1]) ++cursor;
+  const int local = t - tile_start[cursor];
+  const int rows = row_start[cursor + 1] - row_start[cursor];
+  const int m_tiles = (rows + BT - 1) / BT;
+  ti.e = cursor;
+  ti.n_tile = local / m_tiles;
+  ti.m_tile = local - ti.n_tile * m_tiles;
+  ti.row0 = row_start[cursor] + ti.m_tile * BT;
+  const int left = rows - ti.m_tile * BT;
+  ti.valid = left < BT ? left : BT;
+}
+
+__device__ __forceinline__ void store_out(void* d, int out_f16, int64_t idx, float v) {
+  if (out_f16) reinterpret_cast<__half*>(d)[idx] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(d)[idx] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float load_bias(const void* b, int out_f16, int64_t idx) {
+  if (out_f16) return __half2float(reinterpret_cast<const __half*>(b)[idx]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[idx]);
+}
+
+
+// Warp-cooperative prefix sums over the experts: row_start[e], tile_start[e]
+// (tiles of expert e = ceil(rows_e / BT) * n_tiles).  Called by one full warp.
+template <int BT>
+__device__ __forceinline__ void build_tile_prefix(const int32_t* rows_per_expert, int num_experts,
+                                                  int n_tiles, int* row_start, int* tile_start) {
+  const int lane = threadIdx.x & 31;
+  int carry_r = 0, carry_t = 0;
+  if (lane == 0) { row_start[0] = 0; tile_start[0] = 0; }
+  for (int base = 0; base < num_experts; base += 32) {
+    const int e = base + lane;
+    int r = (e < num_experts) ? rows_per_expert[e] : 0;
+    if (r < 0) r = 0;
+    int tl = ((r + BT - 1) / BT) * n_tiles;
+    int ir = r, it = tl;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o_r = __shfl_up_sync(0xffffffffu, ir, d);
+      const int o_t = __shfl_up_sync(0xffffffffu, it, d);
+      if (lane >= d) { ir += o_r; it += o_t; }
+    }
+    if (e < num_experts) {
+      row_start[e + 1] = carry_r + ir;
+      tile_start[e + 1] = carry_t + it;
+    }
+    carry_r += __shfl_sync(0xffffffffu, ir, 31);
+    carry_t += __shfl_sync(0xffffffffu, it, 31);
+  }
+}
+
+// ------------------------------ host side ------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,
+               const cuuint64_t* dims, const cuuint64_t* strides_bytes, const cuuint32_t* box,
+               CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return fail(B200MOE_E_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200MOE_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return B200MOE_OK;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+
+}  // namespace
+}  // namespace b200moe

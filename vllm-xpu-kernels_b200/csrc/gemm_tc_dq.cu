@@ -1,0 +1,376 @@
+// Tensor-core grouped GEMM for weights that are dequantised on the way in:
+// MXFP4 (two e2m1 codes per byte, [E,N,K/2], one e8m0 scale per 32 elements,
+// [E,N,K/32]) times 16-bit activations.
+//
+// Same orientation, tile walk and epilogue as grouped_gemm_tc_kernel (weights'
+// output features on the 128-row M side of tcgen05.mma, tokens on the N side),
+// with one more role between the TMA producer and the MMA issuer:
+//   warp 0   : TMA producer: packed weight tile (128 rows x 32 bytes, no
+//              swizzle) and activation tile (BT rows x 128 bytes, 128B swizzle)
+//   warps 2-5: converters: thread r expands row r of the packed tile to 64
+//              16-bit values (code * 2^(scale-127), exact in bf16/fp16 range)
+//              and writes them in the 128-byte-swizzled K-major layout the MMA
+//              reads; generic-proxy writes are fenced before the hand-over
+//   warp 1   : MMA issuer (kind::f16), owns tensor memory
+//   warps 6-9: epilogue
+// HBM sees only the 4-bit weights (0.53 bytes per element with scales).
+//
+// Numerics follow csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:411-419, 455-471 of
+// vllm-xpu-kernels: LUT[code] * 2^(byte-127) rounded to the activation type
+// before the multiply, fp32 accumulation, bias added in fp32.
+#include <cuda_fp4.h>
+
+#include "common.cuh"
+#include "gemm_tc_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kOpBytes = 16384;   // 128 rows x 64 sixteen-bit values
+constexpr int kRawBytes = 4096;   // 128 rows x 32 packed bytes
+constexpr int kDqThreads = 320;
+constexpr int kDqMaxStages = 8;
+
+struct DqParams {
+  const uint8_t* w_scale;  // [E, N, K/32] e8m0
+  const void* bias;
+  void* d;
+  const int32_t* rows_per_expert;
+  int32_t* status;
+  int64_t m;
+  int n, k, num_experts;
+  int n_tiles, num_kb;
+  uint32_t idesc;
+  int out_f16;
+  int swiglu;      // 1: D[m, f/2] = swigluoai(acc[m,f], acc[m,f+1]) for even f
+  float alpha, limit, clamp_limit;
+};
+
+template <int BT>
+struct DqCtrl {
+  uint64_t full_raw[kDqMaxStages];
+  uint64_t full_op[kDqMaxStages];
+  uint64_t empty[kDqMaxStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int tile_start[kMaxExperts + 1];
+  int row_start[kMaxExperts + 1];
+};
+
+template <int BT>
+__host__ __device__ constexpr int dq_stage_bytes() { return kOpBytes + BT * 128 + kRawBytes; }
+template <int BT>
+__host__ __device__ constexpr int dq_stages() {
+  return (196 * 1024) / dq_stage_bytes<BT>() > kDqMaxStages ? kDqMaxStages
+                                                            : (196 * 1024) / dq_stage_bytes<BT>();
+}
+template <int BT>
+__host__ __device__ constexpr size_t dq_smem_bytes() {
+  return 1024 + (size_t)dq_stages<BT>() * dq_stage_bytes<BT>() + sizeof(DqCtrl<BT>);
+}
+template <int BT>
+__host__ __device__ constexpr uint32_t dq_tmem_cols() { return 2 * BT < 32 ? 32u : (uint32_t)(2 * BT); }
+
+// Two e2m1 codes (low nibble = even k) -> two fp32 values.
+__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t byte) {
+  const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)byte, __NV_E2M1);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int out_f16) {
+  if (out_f16) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int BT>
+__global__ void __launch_bounds__(kDqThreads, 1)
+grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                       const __grid_constant__ CUtensorMap tmap_w, const DqParams p) {
+  constexpr int kStages = dq_stages<BT>();
+  constexpr int kStageBytes = dq_stage_bytes<BT>();
+  constexpr int kChunk = BT >= 32 ? 32 : 16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  DqCtrl<BT>* ctrl = reinterpret_cast<DqCtrl<BT>*>(smem + kStages * kStageBytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (warp == 0) {
+    build_tile_prefix<BT>(p.rows_per_expert, p.num_experts, p.n_tiles, ctrl->row_start,
+                          ctrl->tile_start);
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_w);
+    }
+  } else if (warp == 1) {
+    ptx::tmem_alloc(&ctrl->tmem_base, dq_tmem_cols<BT>());
+    ptx::tmem_relinquish();
+  } else if (warp == 2 && lane == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&ctrl->full_raw[s], 1);
+      ptx::mbar_init(&ctrl->full_op[s], 4);
+      ptx::mbar_init(&ctrl->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&ctrl->acc_full[a], 1);
+      ptx::mbar_init(&ctrl->acc_empty[a], 4);
+    }
+    ctrl->abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const int total_tiles = ctrl->tile_start[p.num_experts];
+  const int* tile_start = ctrl->tile_start;
+  const int* row_start = ctrl->row_start;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      int cursor = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        TileInfo ti;
+        locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+        const int n0 = ti.n_tile * kFeat;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* st = smem + s * kStageBytes;
+          ptx::mbar_expect_tx(&ctrl->full_raw[s], kRawBytes + BT * 128);
+          ptx::tma_load_3d(st + kOpBytes + BT * 128, &tmap_w, &ctrl->full_raw[s], kb * 32, n0, ti.e);
+          ptx::tma_load_2d(st + kOpBytes, &tmap_a, &ctrl->full_raw[s], kb * 64, ti.row0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, acc_it = 0;
+      int cursor = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        TileInfo ti;
+        locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+        const uint32_t a = acc_it & 1;
+        if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) break;
+        ptx::tc_fence_after();
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!ptx::mbar_wait(&ctrl->full_op[s], ph, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t wbase = ptx::smem_u32(smem + s * kStageBytes);
+          const uint32_t abase = wbase + kOpBytes;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t wdesc = ptx::make_smem_desc(wbase + j * 32, 16, 1024);
+            const uint64_t adesc = ptx::make_smem_desc(abase + j * 32, 16, 1024);
+            ptx::umma<false>(tmem_base + a * BT, wdesc, adesc, p.idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(&ctrl->empty[s]);
+        }
+        if (ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------ converters --------------------------------
+    const int r = (warp - 2) * 32 + lane;  // row of the tile
+    const int kgroups = p.k / 32;           // scale bytes per weight row
+    uint32_t it = 0;
+    int cursor = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      TileInfo ti;
+      locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+      const int feat = ti.n_tile * kFeat + r;
+      const bool feat_ok = feat < p.n;
+      const uint8_t* srow = p.w_scale + ((int64_t)ti.e * p.n + (feat_ok ? feat : 0)) * kgroups;
+      // scale bytes of K block kb: groups 2kb and 2kb+1 (the second may lie past K)
+      auto fetch = [&](int kb, uint32_t& s0, uint32_t& s1) {
+        s0 = (feat_ok && 2 * kb < kgroups) ? srow[2 * kb] : 127u;
+        s1 = (feat_ok && 2 * kb + 1 < kgroups) ? srow[2 * kb + 1] : 127u;
+      };
+      uint32_t n0s, n1s;
+      fetch(0, n0s, n1s);
+      for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+        const uint32_t c0s = n0s, c1s = n1s;
+        if (kb + 1 < p.num_kb) fetch(kb + 1, n0s, n1s);
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->full_raw[s], ph, abort_flag))) {
+          *abort_flag = 1; ok = false; break;
+        }
+        uint8_t* st = smem + s * kStageBytes;
+        const uint4* raw = reinterpret_cast<const uint4*>(st + kOpBytes + BT * 128 + r * 32);
+        const uint4 q0 = raw[0], q1 = raw[1];
+        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const float sc0 = e8m0_to_f32(c0s), sc1 = e8m0_to_f32(c1s);
+        uint8_t* orow = st + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {  // 8 values = one 16-byte chunk of the row
+          const float sc = c < 4 ? sc0 : sc1;
+          const uint32_t w = words[c];
+          uint32_t o[4];
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const float2 f = e2m1x2_to_float2((w >> (8 * b)) & 0xffu);
+            o[b] = pack16(f.x * sc, f.y * sc, p.out_f16);
+          }
+          *reinterpret_cast<uint4*>(orow + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctrl->full_op[s]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;
+    const int et = q * 32 + lane;
+    const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+    const int n_out = p.swiglu ? p.n / 2 : p.n;
+    uint32_t acc_it = 0;
+    int cursor = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      TileInfo ti;
+      locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+      const int feat = ti.n_tile * kFeat + et;
+      const bool feat_ok = feat < p.n;
+      float bias_v = 0.f;
+      if (p.bias != nullptr && feat_ok) bias_v = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat);
+      const uint32_t a = acc_it & 1;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
+        *abort_flag = 1; ok = false; break;
+      }
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < BT; c0 += kChunk) {
+        if (c0 < ti.valid) {
+          uint32_t v[kChunk];
+          if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
+          else ptx::tmem_ld_32x16(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < kChunk; ++i) {
+            float x = __uint_as_float(v[i]) + bias_v;
+            const bool row_ok = (c0 + i < ti.valid) && (ti.row0 + c0 + i < p.m);
+            if (p.swiglu) {
+              // gate sits on even features, up on the next odd one: neighbours in the warp
+              const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+              float gate = (lane & 1) ? other : x;
+              float up = (lane & 1) ? x : other;
+              if (p.clamp_limit > 0.f) {
+                gate = fminf(gate, p.clamp_limit);
+                up = fminf(fmaxf(up, -p.clamp_limit), p.clamp_limit);
+              }
+              gate = fminf(gate, p.limit);
+              up = fminf(fmaxf(up, -p.limit), p.limit);
+              x = (up + 1.0f) * gate * (1.0f / (1.0f + __expf(-gate * p.alpha)));
+              if (row_ok && feat_ok && !(lane & 1))
+                store_out(p.d, p.out_f16, (int64_t)(ti.row0 + c0 + i) * n_out + (feat >> 1), x);
+            } else if (row_ok && feat_ok) {
+              store_out(p.d, p.out_f16, (int64_t)(ti.row0 + c0 + i) * n_out + feat, x);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
+      ++acc_it;
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    if (*abort_flag != 0) __nanosleep(20000);
+    ptx::tmem_dealloc(tmem_base, dq_tmem_cols<BT>());
+  }
+  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+template <int BT>
+int launch_dq(const CUtensorMap& ta, const CUtensorMap& tw, const DqParams& p, int grid,
+              cudaStream_t st) {
+  auto kern = grouped_gemm_dq_kernel<BT>;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)dq_smem_bytes<BT>()));
+    configured = true;
+  }
+  kern<<<grid, kDqThreads, dq_smem_bytes<BT>(), st>>>(ta, tw, p);
+  B200_LAUNCH_OK("grouped_gemm_dq_kernel");
+  return B200MOE_OK;
+}
+
+}  // namespace
+
+// MXFP4 weights x 16-bit activations on the tensor cores.  Returns
+// B200MOE_E_UNSUPPORTED (no launch) for anything else.
+int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
+  if (a->w_format != B200MOE_W_MXFP4_NK || a->a_dtype == B200MOE_FP8_E4M3)
+    return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM takes MXFP4 weights only");
+  if (a->epilogue == B200MOE_EPI_SILU_MUL)
+    return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM: SiLU epilogue not available");
+  if (a->num_experts > kMaxExperts || a->k % 64 != 0 || (a->k / 2) % 16 != 0)
+    return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM: K must be a multiple of 64");
+  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15))
+    return fail(B200MOE_E_BADARG, "grouped GEMM: A and W must be 16-byte aligned");
+  if (a->m == 0 || a->n == 0) return B200MOE_OK;
+
+  DqParams p;
+  p.w_scale = reinterpret_cast<const uint8_t*>(a->w_scale);
+  p.bias = a->bias; p.d = a->d; p.rows_per_expert = a->rows_per_expert; p.status = a->status;
+  p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
+  p.n_tiles = (a->n + kFeat - 1) / kFeat;
+  p.num_kb = a->k / 64;
+  p.out_f16 = a->d_dtype == B200MOE_F16;
+  p.swiglu = a->epilogue == B200MOE_EPI_SWIGLUOAI;
+  p.alpha = a->act_alpha; p.limit = a->act_limit; p.clamp_limit = a->clamp_limit;
+
+  const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
+  const int bt = avg <= 16 ? 16 : (avg <= 64 ? 64 : 128);
+  const uint32_t fmt = a->a_dtype == B200MOE_BF16 ? 1u : 0u;
+  p.idesc = ptx::make_idesc(fmt, fmt, 0u, 0u, kFeat, (uint32_t)bt);
+
+  CUtensorMap ta, tw;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)a->k, (cuuint64_t)a->m};
+    cuuint64_t strides[1] = {(cuuint64_t)a->k * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)bt};
+    int rc = encode_map(&ta, fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                        a->a, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)(a->k / 2), (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
+    cuuint64_t strides[2] = {(cuuint64_t)(a->k / 2), (cuuint64_t)(a->k / 2) * a->n};
+    cuuint32_t box[3] = {32, (cuuint32_t)kFeat, 1};
+    int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  }
+  const int64_t tile_bound = ((a->m + bt - 1) / bt + a->num_experts) * (int64_t)p.n_tiles;
+  int grid = sm_count();
+  if (tile_bound < grid) grid = (int)tile_bound;
+  if (grid < 1) grid = 1;
+  if (bt == 16) return launch_dq<16>(ta, tw, p, grid, st);
+  if (bt == 64) return launch_dq<64>(ta, tw, p, grid, st);
+  return launch_dq<128>(ta, tw, p, grid, st);
+}
+
+}  // namespace b200moe

@@ -36,8 +36,6 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   if (ptr_bias.has_value()) TORCH_CHECK(ptr_bias->is_contiguous(), "ptr_bias must be contiguous");
   TORCH_CHECK(!is_B_int4, "int4 grouped GEMM is not available in this build");
   TORCH_CHECK(B_dtype != at::kFloat8_e5m2, "float8_e5m2 weights are not available in this build");
-  TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
-              rows_per_expert.numel() == num_experts, "rows_per_expert must be int32 [num_experts]");
 
   const int64_t A_total_M = ptr_A.size(0), A_K = ptr_A.size(1);
   const int64_t B_E = ptr_B.size(0);
@@ -64,6 +62,8 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   const int64_t D_total_M = ptr_D.size(0), D_N = ptr_D.size(1);
   const int64_t n_out = epilogue ? N / 2 : N;
   TORCH_CHECK(B_E == num_experts, "ptr_B.size(0) must match num_experts");
+  TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
+              rows_per_expert.numel() == num_experts, "rows_per_expert must be int32 [num_experts]");
   TORCH_CHECK(A_total_M == D_total_M, "ptr_A.size(0) must match ptr_D.size(0)");
   TORCH_CHECK(A_K == B_K && B_K == K, "ptr_A K dimension must match ptr_B logical K dimension and K");
   TORCH_CHECK(B_N == N && D_N == n_out, "ptr_B logical N dimension must match ptr_D N dimension and N");

@@ -143,8 +143,9 @@ class XpuFusedMoe:
     """The fused-MoE layer object (reference :165-419).
 
     ``fuse_activation`` (not in the reference; keyword only) applies the gated
-    activation inside the first grouped GEMM's epilogue when the kernel for
-    this recipe offers it, instead of a separate pass over ``[T*K, 2I]``.
+    activation inside the first grouped GEMM's epilogue instead of a separate
+    pass over ``[T*K, 2I]``; the default picks it where the tensor-core kernel
+    of the recipe has that epilogue (MXFP4 with SwigluOAI).
     """
 
     def __init__(
@@ -163,7 +164,7 @@ class XpuFusedMoe:
         expert_map=None,
         gemm1_clamp_limit: Optional[float] = None,
         *,
-        fuse_activation: bool = False,
+        fuse_activation: Optional[bool] = None,
     ):
         assert w13.is_contiguous() and w2.is_contiguous()
         _require_native()
@@ -208,6 +209,9 @@ class XpuFusedMoe:
         self.gemm1_clamp_limit = gemm1_clamp_limit
         self.recipe = _get_recipe(is_fp8, is_mxfp8, is_mxfp4, is_int4, is_block_fp8)
         self._use_ref = False
+        if fuse_activation is None:
+            # fused where the tensor-core kernel of this recipe has the epilogue
+            fuse_activation = self.is_mxfp4 and self._act_kind == "swigluoai"
         self.fuse_activation = fuse_activation
         if self._act_kind == "silu":
             self.act_func = torch.ops._C.silu_and_mul
