@@ -200,6 +200,7 @@ def make_step(cfg, layer, dev, T):
             v, i = torch.ops._moe_C.grouped_topk(scores, scores + bias, cfg.n_group, cfg.topk_group, K,
                                                  cfg.renormalize, cfg.routed_scaling_factor)
             layer.apply(out, x, v, i)
+            ids.copy_(i)  # keep the routed ids for the roofline's row distribution
         return out
 
     return step, (tw, ids)

@@ -1,0 +1,94 @@
+"""Worker bodies of the multi-rank expert-parallel tests (spawned processes)."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+for p in (str(ROOT), str(ROOT / "vllm-xpu-kernels_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def _case(rank, T, cfg_name, dims, seed):
+    from oracle import workloads as wl
+    cfg = wl.scaled(wl.CONFIGS[cfg_name], **dims)
+    w = wl.make_weights(cfg, seed=seed)                     # all experts, same on every rank
+    x, logits, bias = wl.make_inputs(cfg, T, seed=seed * 10 + rank)   # this rank's own tokens
+    tw, ids = wl.route_cpu(cfg, logits, bias)
+    return cfg, w, x, tw, ids
+
+
+def _oracle_full(cfg, w, x, tw, ids):
+    from oracle import torch_oracle as to
+    from oracle import workloads as wl
+    d13, d2 = wl.dequant_weights(cfg, w)
+    return to.fused_moe_staged(x, d13, w["w13_bias"], d2, w["w2_bias"], tw, ids, cfg.E,
+                               activation=cfg.activation, act_quant=cfg.recipe == "fp8block")
+
+
+def cpu_worker(rank, world, port, T, result_queue):
+    """Gloo ranks on CPU: the exchange plumbing (EpAllToAll) around the oracle's
+    permutation and experts must reproduce the single-process oracle."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import torch_oracle as to
+        from oracle import workloads as wl
+        from vllm_xpu_kernels.ep_moe import EpAllToAll, owner_map
+        cfg, w, x, tw, ids = _case(rank, T + 3 * rank, "cfg1_small_bf16", dict(H=64, I=32, E=8), 5)
+        E_local = cfg.E // world
+        a2a = EpAllToAll()
+        owner = owner_map(cfg.E, world, "cpu")
+        send_rows, _, send_counts, send_pos = to.remap_hidden_states(x, None, ids, owner, world)
+        M = ids.numel()
+        send_eids = torch.empty(M, dtype=torch.int32)
+        send_eids[send_pos.reshape(-1).long()] = (ids.reshape(-1) % E_local).to(torch.int32)
+        s_spl, r_spl = a2a.exchange_counts(send_counts)
+        assert sum(s_spl) == M
+        recv_rows, none, recv_eids = a2a.dispatch((send_rows, None, send_eids), s_spl, r_spl)
+        assert none is None and recv_rows.shape[0] == sum(r_spl) == recv_eids.numel()
+        # local experts = this rank's slice of the weights, top-1 with unit weight
+        lo = rank * E_local
+        d13, d2 = wl.dequant_weights(cfg, w)
+        R = recv_rows.shape[0]
+        local_out = to.fused_moe_staged(recv_rows, d13[lo:lo + E_local], None, d2[lo:lo + E_local], None,
+                                        torch.ones(R, 1), recv_eids.view(R, 1), E_local)
+        back = a2a.combine(local_out, s_spl, r_spl)
+        out = to.moe_gather(back, tw, send_pos, x.dtype)
+        ref = _oracle_full(cfg, w, x, tw, ids)
+        err = float((out.float() - ref.float()).abs().max())
+        result_queue.put((rank, err, s_spl, r_spl))
+    finally:
+        dist.destroy_process_group()
+
+
+def gpu_worker(rank, world, port, T, cfg_name, dims, result_queue):
+    """NCCL ranks, one GPU each: EpFusedMoe against the single-process oracle."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from oracle import workloads as wl
+        from vllm_xpu_kernels.ep_moe import EpFusedMoe
+        cfg, w, x, tw, ids = _case(rank, T + 5 * rank, cfg_name, dims, 7)
+        E_local = cfg.E // world
+        sl = slice(rank * E_local, (rank + 1) * E_local)
+        wr = {k: (v[sl] if v is not None else None) for k, v in w.items()}
+        w13, s13, w2, s2 = wl.to_op_layout(cfg, wr)
+        mv = lambda t: t.to(dev) if t is not None else None
+        layer = EpFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]), cfg.K,
+                           cfg.activation, E_local)
+        out = torch.empty(x.shape, dtype=torch.bfloat16, device=dev)
+        for _ in range(2):  # twice: the second call reuses cached state
+            layer.apply(out, x.to(dev), tw.to(dev), ids.to(dev))
+        torch.cuda.synchronize()
+        ref = _oracle_full(cfg, w, x, tw, ids)
+        err = float((out.cpu().float() - ref.float()).abs().max())
+        scale = float(ref.float().abs().max())
+        result_queue.put((rank, err, scale))
+    finally:
+        dist.destroy_process_group()

@@ -131,6 +131,15 @@ def test_grouped_gemm_mxfp4(native, impl, E, M, N, K, has_bias):
                        bias.to(DEV) if has_bias else None, rows.to(DEV), N, K, impl=impl)
     n = int(rows.sum())
     torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=2e-2, atol=2e-2)
+    if not has_bias:
+        # float16 activations and scale bytes above 128 take the converter's general path
+        sc2 = torch.randint(126, 133, (E, N, K // 32), generator=g, dtype=torch.int32).to(torch.uint8)
+        for dt, scl in ((torch.float16, sc), (torch.bfloat16, sc2)):
+            wd = to.dequant_mxfp4(packed, scl).to(dt).float()
+            r2 = to.grouped_gemm(x.to(dt).float(), wd, None, rows, dt)
+            o2 = grouped_gemm(x.to(dt).to(DEV), None, packed.to(DEV).view(torch.float4_e2m1fn_x2), scl.to(DEV),
+                              None, rows.to(DEV), N, K, impl=impl, out_dtype=dt)
+            torch.testing.assert_close(o2.cpu()[:n].float(), r2[:n].float(), rtol=2e-2, atol=2e-2 * float(r2.abs().max()))
     if has_bias:  # SwigluOAI fused into the epilogue (interleaved gate / up columns)
         fused = grouped_gemm(x.to(DEV), None, packed.to(DEV).view(torch.float4_e2m1fn_x2), sc.to(DEV),
                              bias.to(DEV), rows.to(DEV), N, K, epilogue=2, impl=impl)

@@ -221,6 +221,34 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int et = q * 32 + lane;           // feature row inside the tile
     const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
     const int col0 = ((warp - 2) / 4) * kCols;   // first token column of this warp
+    // fp8 block-scale prefetch state (see the promotion loop below)
+    constexpr int kGroup = 4;
+    constexpr int kPerLane = (kCols + 31) / 32;
+    struct ScaleRegs { float a[kPerLane][kGroup]; float w[kGroup]; };
+    ScaleRegs cur, pre;
+    bool pre_valid = false;
+    const int kbs = p.k / 128;  // scale blocks along K
+    const bool vec4_ok = kFp8 && (kbs % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.a_scale) & 15) == 0);
+    auto fetch_group = [&](const TileInfo& tt, int g, ScaleRegs& r) {
+      const int kb0 = g * kGroup;
+      const int64_t wsb = ((int64_t)tt.e * (p.n / 128) + tt.n_tile) * kbs + kb0;
+#pragma unroll
+      for (int jb = 0; jb < kGroup; ++jb) r.w[jb] = (kb0 + jb < kbs) ? p.w_scale[wsb + jb] : 0.f;
+#pragma unroll
+      for (int u = 0; u < kPerLane; ++u) {
+        const int c = col0 + lane + 32 * u;
+        const int row = tt.row0 + c;
+        const bool live = (lane + 32 * u < kCols) && (c < tt.valid) && (row < p.m);
+        const float* src = p.a_scale + (int64_t)row * kbs + kb0;
+        if (live && vec4_ok) {
+          const float4 q4 = *reinterpret_cast<const float4*>(src);
+          r.a[u][0] = q4.x; r.a[u][1] = q4.y; r.a[u][2] = q4.z; r.a[u][3] = q4.w;
+        } else {
+#pragma unroll
+          for (int jb = 0; jb < kGroup; ++jb) r.a[u][jb] = (live && kb0 + jb < kbs) ? src[jb] : 0.f;
+        }
+      }
+    };
     uint32_t acc_it = 0;
     int cursor = 0;
     bool ok = true;
@@ -263,57 +291,68 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         float acc[kCols];
 #pragma unroll
         for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
-        const int kbs = p.k / 128;  // scale blocks along K
-        const int64_t ws_base = ((int64_t)ti.e * (p.n / 128) + ti.n_tile) * kbs;
-        // Each warp stages its own copy of the combined scales of its columns
-        // for a K block (lane l owns columns l, l+32, ..), so no barrier couples
+        // Scales are fetched kGroup K blocks at a time, one group ahead of their
+        // use (the first group of the next tile during the last group of this
+        // one), so the strided a_scale loads are off the critical path.  Each
+        // warp stages its own copy of the combined scales of its columns in
+        // shared memory (lane l owns columns l, l+32, ..): no barrier couples
         // the warps.
-        constexpr int kPerLane = (kCols + 31) / 32;
-        float next_sc[kPerLane];
-        auto fetch_scales = [&](int kb) {
-          const float ws = p.w_scale[ws_base + kb];
-#pragma unroll
-          for (int u = 0; u < kPerLane; ++u) {
-            const int c = col0 + lane + 32 * u;
-            const int row = ti.row0 + c;
-            next_sc[u] = (lane + 32 * u < kCols && c < ti.valid && row < p.m)
-                             ? p.a_scale[(int64_t)row * kbs + kb] * ws : 0.f;
+        if (!pre_valid) fetch_group(ti, 0, cur);
+        else cur = pre;
+        pre_valid = false;
+        const int n_groups = (p.num_kb + kGroup - 1) / kGroup;
+        for (int g = 0; g < n_groups && ok; ++g) {
+          if (g + 1 < n_groups) {
+            fetch_group(ti, g + 1, pre);
+          } else if (t + (int)gridDim.x < total_tiles) {
+            int cursor2 = cursor;
+            TileInfo tn;
+            locate_tile<BT>(tile_start, row_start, t + gridDim.x, cursor2, tn);
+            fetch_group(tn, 0, pre);
+            pre_valid = true;
           }
-        };
-        fetch_scales(0);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          float* sc = ctrl->sc[warp - 2][kb & 1];
 #pragma unroll
-          for (int u = 0; u < kPerLane; ++u)
-            if (lane + 32 * u < kCols) sc[lane + 32 * u] = next_sc[u];
-          __syncwarp();
-          if (kb + 1 < p.num_kb) fetch_scales(kb + 1);
-          const uint32_t a = acc_it % kAccStages;
-          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
-            *abort_flag = 1; ok = false; break;
-          }
-          ptx::tc_fence_after();
+          for (int jb = 0; jb < kGroup; ++jb) {
+            const int kb = g * kGroup + jb;
+            if (kb >= p.num_kb) break;
+            float* sc = ctrl->sc[warp - 2][kb & 1];
 #pragma unroll
-          for (int c0 = 0; c0 < kCols; c0 += kChunk) {
-            if (col0 + c0 < ti.valid) {
+            for (int u = 0; u < kPerLane; ++u)
+              if (lane + 32 * u < kCols) sc[lane + 32 * u] = cur.a[u][jb] * cur.w[jb];
+            __syncwarp();
+            const uint32_t a = acc_it % kAccStages;
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
+              *abort_flag = 1; ok = false; break;
+            }
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < kCols; c0 += kChunk) {
+              const bool last_chunk = (c0 + kChunk >= kCols);
               uint32_t v[kChunk];
-              if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
-              else ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
-              ptx::tmem_wait_ld();
+              if (col0 + c0 < ti.valid) {
+                if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
+                else ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
+                ptx::tmem_wait_ld();
+              }
+              if (last_chunk) {  // the stage is free as soon as its last column is in registers
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
+              }
+              if (col0 + c0 < ti.valid) {
 #pragma unroll
-              for (int i = 0; i < kChunk; i += 4) {
-                const float4 s4 = *reinterpret_cast<const float4*>(sc + c0 + i);
-                acc[c0 + i + 0] = fmaf(__uint_as_float(v[i + 0]), s4.x, acc[c0 + i + 0]);
-                acc[c0 + i + 1] = fmaf(__uint_as_float(v[i + 1]), s4.y, acc[c0 + i + 1]);
-                acc[c0 + i + 2] = fmaf(__uint_as_float(v[i + 2]), s4.z, acc[c0 + i + 2]);
-                acc[c0 + i + 3] = fmaf(__uint_as_float(v[i + 3]), s4.w, acc[c0 + i + 3]);
+                for (int i = 0; i < kChunk; i += 4) {
+                  const float4 s4 = *reinterpret_cast<const float4*>(sc + c0 + i);
+                  acc[c0 + i + 0] = fmaf(__uint_as_float(v[i + 0]), s4.x, acc[c0 + i + 0]);
+                  acc[c0 + i + 1] = fmaf(__uint_as_float(v[i + 1]), s4.y, acc[c0 + i + 1]);
+                  acc[c0 + i + 2] = fmaf(__uint_as_float(v[i + 2]), s4.z, acc[c0 + i + 2]);
+                  acc[c0 + i + 3] = fmaf(__uint_as_float(v[i + 3]), s4.w, acc[c0 + i + 3]);
+                }
               }
             }
+            ++acc_it;
           }
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
-          ++acc_it;
+          if (g + 1 < n_groups) cur = pre;
         }
         if (ok && feat_ok) {
 #pragma unroll
@@ -386,10 +425,12 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   p.out_f16 = a->d_dtype == B200MOE_F16;
 
   const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
+  // Token-tile width from the mean rows per expert (routing is never perfectly
+  // even, so leave headroom before a second token tile re-reads the weights).
   int bt;
-  if (avg <= 16) bt = 16;
-  else if (avg <= 64) bt = 64;
-  else if (avg <= 192 || a_fp8) bt = 128;
+  if (avg <= 8) bt = 16;
+  else if (avg <= 40) bt = 64;
+  else if (avg <= 160 || a_fp8) bt = 128;
   else bt = 256;
 
   const uint32_t fmt = a_fp8 ? 0u : (a->a_dtype == B200MOE_BF16 ? 1u : 0u);

@@ -31,6 +31,7 @@ constexpr int kOpBytes = 16384;   // 128 rows x 64 sixteen-bit values
 constexpr int kRawBytes = 4096;   // 128 rows x 32 packed bytes
 constexpr int kDqThreads = 320;
 constexpr int kDqMaxStages = 8;
+constexpr int kDqGroup = 8;      // K blocks per scale prefetch
 
 struct DqParams {
   const uint8_t* w_scale;  // [E, N, K/32] e8m0
@@ -187,6 +188,7 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------ converters --------------------------------
     const int r = (warp - 2) * 32 + lane;  // row of the tile
     const int kgroups = p.k / 32;           // scale bytes per weight row
+    const bool pair_aligned = (kgroups % 2 == 0) && ((reinterpret_cast<uintptr_t>(p.w_scale) & 1) == 0);
     uint32_t it = 0;
     int cursor = 0;
     bool ok = true;
@@ -196,41 +198,90 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int feat = ti.n_tile * kFeat + r;
       const bool feat_ok = feat < p.n;
       const uint8_t* srow = p.w_scale + ((int64_t)ti.e * p.n + (feat_ok ? feat : 0)) * kgroups;
-      // scale bytes of K block kb: groups 2kb and 2kb+1 (the second may lie past K)
-      auto fetch = [&](int kb, uint32_t& s0, uint32_t& s1) {
-        s0 = (feat_ok && 2 * kb < kgroups) ? srow[2 * kb] : 127u;
-        s1 = (feat_ok && 2 * kb + 1 < kgroups) ? srow[2 * kb + 1] : 127u;
-      };
-      uint32_t n0s, n1s;
-      fetch(0, n0s, n1s);
-      for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-        const uint32_t s = it % kStages, ph = (it / kStages) & 1;
-        const uint32_t c0s = n0s, c1s = n1s;
-        if (kb + 1 < p.num_kb) fetch(kb + 1, n0s, n1s);
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->full_raw[s], ph, abort_flag))) {
-          *abort_flag = 1; ok = false; break;
+      // Scale bytes of this thread's row, kDqGroup K blocks (two bytes each) at a
+      // time and one group ahead of their use, so the loads never stall a stage.
+      auto fetch = [&](int g, uint32_t (&dst)[kDqGroup]) {
+#pragma unroll
+        for (int u = 0; u < kDqGroup; ++u) {
+          const int kb = g * kDqGroup + u;
+          uint32_t v = 0x7f7fu;  // 2^0 twice
+          if (feat_ok && 2 * kb + 1 < kgroups) {
+            if (pair_aligned) v = *reinterpret_cast<const uint16_t*>(srow + 2 * kb);
+            else v = (uint32_t)srow[2 * kb] | ((uint32_t)srow[2 * kb + 1] << 8);
+          } else if (feat_ok && 2 * kb < kgroups) {
+            v = (uint32_t)srow[2 * kb] | 0x7f00u;
+          }
+          dst[u] = v;
         }
+      };
+      uint32_t cur_s[kDqGroup], nxt_s[kDqGroup];
+      fetch(0, cur_s);
+      const int n_groups = (p.num_kb + kDqGroup - 1) / kDqGroup;
+      for (int g = 0; g < n_groups && ok; ++g) {
+       if (g + 1 < n_groups) fetch(g + 1, nxt_s);
+#pragma unroll
+       for (int u = 0; u < kDqGroup; ++u) {
+        const int kb = g * kDqGroup + u;
+        if (kb < p.num_kb && ok) {
+        const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+        const uint32_t c0s = cur_s[u] & 0xffu, c1s = cur_s[u] >> 8;
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->full_raw[s], ph, abort_flag))) {
+          *abort_flag = 1; ok = false;
+        }
+        if (ok) {
         uint8_t* st = smem + s * kStageBytes;
         const uint4* raw = reinterpret_cast<const uint4*>(st + kOpBytes + BT * 128 + r * 32);
         const uint4 q0 = raw[0], q1 = raw[1];
         const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        const float sc0 = e8m0_to_f32(c0s), sc1 = e8m0_to_f32(c1s);
         uint8_t* orow = st + (r >> 3) * 1024 + (r & 7) * 128;
+        if (!p.out_f16 && c0s <= 128u && c1s <= 128u) {
+          // Integer path for bf16.  Put the code's exponent and mantissa bits
+          // where bf16 keeps them ((c & 7) << 6, sign to bit 15): read as bf16
+          // that is the code's value times 2^-126, subnormal codes included, so
+          // one exact multiply by 2^(scale - 1) yields code * 2^(scale - 127).
+          const uint32_t m0 = (c0s + 126u) << 7, m1 = (c1s + 126u) << 7;
+          const uint32_t mm0 = m0 | (m0 << 16), mm1 = m1 | (m1 << 16);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {  // 8 values = one 16-byte chunk of the row
-          const float sc = c < 4 ? sc0 : sc1;
-          const uint32_t w = words[c];
-          uint32_t o[4];
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t w = words[c];
+            const uint32_t xe = w & 0x0F0F0F0Fu;          // codes of even k in bytes 0..3
+            const uint32_t xo = (w >> 4) & 0x0F0F0F0Fu;   // codes of odd k
+            const uint32_t mm = c < 4 ? mm0 : mm1;
+            uint32_t o[4];
 #pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            const float2 f = e2m1x2_to_float2((w >> (8 * b)) & 0xffu);
-            o[b] = pack16(f.x * sc, f.y * sc, p.out_f16);
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t q = __byte_perm(xe, xo, (uint32_t)(j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12)));
+              const uint32_t bits = ((q << 6) & 0x01C001C0u) | ((q << 12) & 0x80008000u);
+              const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&bits),
+                                                  *reinterpret_cast<const __nv_bfloat162*>(&mm));
+              o[j] = *reinterpret_cast<const uint32_t*>(&prod);
+            }
+            *reinterpret_cast<uint4*>(orow + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
           }
-          *reinterpret_cast<uint4*>(orow + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        } else {
+          const float sc0 = e8m0_to_f32(c0s), sc1 = e8m0_to_f32(c1s);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {  // 8 values = one 16-byte chunk of the row
+            const float sc = c < 4 ? sc0 : sc1;
+            const uint32_t w = words[c];
+            uint32_t o[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const float2 f = e2m1x2_to_float2((w >> (8 * b)) & 0xffu);
+              o[b] = pack16(f.x * sc, f.y * sc, p.out_f16);
+            }
+            *reinterpret_cast<uint4*>(orow + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
         }
         ptx::fence_proxy_async();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&ctrl->full_op[s]);
+        }
+        ++it;
+        }
+       }
+#pragma unroll
+       for (int u = 0; u < kDqGroup; ++u) cur_s[u] = nxt_s[u];
       }
     }
   } else {
@@ -343,7 +394,7 @@ int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
   p.alpha = a->act_alpha; p.limit = a->act_limit; p.clamp_limit = a->clamp_limit;
 
   const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
-  const int bt = avg <= 16 ? 16 : (avg <= 64 ? 64 : 128);
+  const int bt = avg <= 8 ? 16 : (avg <= 40 ? 64 : 128);
   const uint32_t fmt = a->a_dtype == B200MOE_BF16 ? 1u : 0u;
   p.idesc = ptx::make_idesc(fmt, fmt, 0u, 0u, kFeat, (uint32_t)bt);
 
