@@ -148,12 +148,14 @@ def launches_per_step(M: int, quant: bool) -> int:
     return 1 + (1 if M <= 2048 else 3) + 1 + 2 + 1 + (1 if quant else 0) + 1
 
 
-def build_gpu_workload(cfg, T, dev):
+def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0):
+    """Synthetic weights on the device (this rank's experts only when the experts
+    are sharded) and the host-side inputs of one step."""
     import vllm_xpu_kernels.fused_moe_interface as fmi
     from oracle import workloads as wl
     assert fmi.FUSEDMOE_AVAILABLE, fmi.FUSEDMOE_UNAVAILABLE_REASON
-    g = torch.Generator(device=dev).manual_seed(1234)
-    E, H, I = cfg.E, cfg.H, cfg.I
+    g = torch.Generator(device=dev).manual_seed(1234 + ep_rank)
+    E, H, I = cfg.E // ep_world, cfg.H, cfg.I
     if cfg.recipe == "bf16":
         # op layout [E,K,N], drawn on the device expert by expert
         w13 = torch.empty(E, H, 2 * I, dtype=torch.bfloat16, device=dev)
@@ -179,8 +181,12 @@ def build_gpu_workload(cfg, T, dev):
         s2 = torch.randint(117, 124, (E, H, I // 32), generator=g, device=dev, dtype=torch.int32).to(torch.uint8)
         b13 = (torch.randn(E, 2 * I, generator=g, device=dev) * 0.02).to(torch.bfloat16)
         b2 = (torch.randn(E, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
-    layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
-    x_cpu, logits_cpu, bias_cpu = wl.make_inputs(cfg, T, seed=0)
+    if ep_world > 1:
+        from vllm_xpu_kernels.ep_moe import EpFusedMoe
+        layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
+    else:
+        layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
+    x_cpu, logits_cpu, bias_cpu = wl.make_inputs(cfg, T, seed=ep_rank)
     return layer, x_cpu, logits_cpu, bias_cpu
 
 
@@ -206,12 +212,23 @@ def make_step(cfg, layer, dev, T):
     return step, (tw, ids)
 
 
-def time_gemms(cfg, layer, ids, T, dev, iters):
+def time_gemms(cfg, layer, ids, T, dev, iters, ep_world=1, ep_rank=0):
     """Average duration of the two grouped-GEMM launches of a step, CUDA events
-    on the launching stream, on this step's real row distribution."""
-    E, H, I, K = cfg.E, cfg.H, cfg.I, cfg.K
-    M = T * K
-    rows = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
+    on the launching stream, on this step's real row distribution (with sharded
+    experts: the rows all ranks route to this rank's experts)."""
+    H, I, K = cfg.H, cfg.I, cfg.K
+    E = cfg.E // ep_world
+    if ep_world > 1:
+        import torch.distributed as dist
+        gathered = [torch.empty_like(ids) for _ in range(ep_world)]
+        dist.all_gather(gathered, ids)
+        flat = torch.cat([g.reshape(-1) for g in gathered]).long()
+        flat = flat[(flat >= ep_rank * E) & (flat < (ep_rank + 1) * E)] - ep_rank * E
+        layer = layer.local
+    else:
+        flat = ids.reshape(-1).long()
+    rows = torch.bincount(flat, minlength=E).to(torch.int32)
+    M = int(flat.numel())
     fp8 = cfg.recipe == "fp8block"
     adt = torch.float8_e4m3fn if fp8 else torch.bfloat16
     a1 = torch.randn(M, H, device=dev).to(adt)
@@ -237,7 +254,7 @@ def time_gemms(cfg, layer, ids, T, dev, iters):
     torch.cuda.synchronize()
     ms_pair = e0.elapsed_time(e1) / iters
     e_act = int((rows > 0).sum())
-    return ms_pair, e_act
+    return ms_pair, e_act, M
 
 
 def weight_bytes_per_expert(cfg):
@@ -261,7 +278,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     cfg = wl.CONFIGS[args.workload]
     T = args.tokens
-    layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev)
+    ep_world = world if (args.parallelism == "ep" and world > 1) else 1
+    layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev, ep_world, rank if ep_world > 1 else 0)
     step, (tw, ids) = make_step(cfg, layer, dev, T)
     x, logits = x_cpu.to(dev), logits_cpu.to(dev)
     bias = bias_cpu.to(dev) if bias_cpu is not None else None
@@ -319,10 +337,10 @@ def run_ours(args):
 
     # ---- roofline of the grouped GEMM kernel ---------------------------------------------
     peaks = _peaks()
-    ms_pair, e_act = time_gemms(cfg, layer, ids, T, dev, max(3, min(20, args.steps)))
-    flops = 6.0 * T * cfg.K * cfg.H * cfg.I
+    ms_pair, e_act, m_rows = time_gemms(cfg, layer, ids, T, dev, max(3, min(20, args.steps)), ep_world, rank)
+    flops = 6.0 * m_rows * cfg.H * cfg.I
     wbytes = e_act * weight_bytes_per_expert(cfg)
-    act_bytes = T * cfg.K * (cfg.H + 2 * cfg.I + cfg.I + cfg.H) * 2  # A and D of both launches
+    act_bytes = m_rows * (cfg.H + 2 * cfg.I + cfg.I + cfg.H) * 2  # A and D of both launches
     t_tensor = flops / (peaks["tensor"] * 1e12)
     t_hbm = (wbytes + act_bytes) / (peaks["hbm"] * 1e9)
     if t_tensor >= t_hbm:
@@ -344,7 +362,8 @@ def run_ours(args):
                                                           "mxfp4": "mxfp4"}[cfg.recipe],
         "data": "synthetic",
         "config": {"workload": f"{cfg.name} T={T} per GPU", "H": cfg.H, "I": cfg.I, "E": cfg.E, "top_k": cfg.K,
-                   "tokens_per_gpu": T, "routing": cfg.routing, "parallelism": f"replicas x{world}",
+                   "tokens_per_gpu": T, "routing": cfg.routing, "parallelism": (f"ep{world}: {cfg.E // world} experts per GPU, NCCL all-to-all dispatch/combine"
+                                   if ep_world > 1 else f"replicas x{world}"),
                    "l2": "inputs exceed L2: the weights streamed per step are larger than the 126 MB L2"
                          if e_act * weight_bytes_per_expert(cfg) > 126e6 else "inputs smaller than L2",
                    "seed": 0},
@@ -396,6 +415,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2_mixtral_bf16")
     ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
+                    help="N > 1: independent replicas (default) or experts sharded over the ranks "
+                         "with all-to-all token dispatch / combine")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -25,6 +25,8 @@
 // Every wait on an mbarrier is bounded (see sm100_ptx.cuh): on expiry the CTA
 // raises an abort flag, all roles leave their loops, tensor memory is freed and
 // *status is set to 1.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "gemm_tc_common.cuh"
@@ -49,9 +51,10 @@ struct TcParams {
   int num_kb;   // K blocks of 128 bytes
   uint32_t idesc;
   int out_f16;  // 1: D and bias are float16, 0: bfloat16
+  int debug;    // experiment switches (B200MOE_DEBUG), 0 in normal use
 };
 
-template <int BT>
+template <int BT, bool kFp8>
 struct Ctrl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -59,7 +62,8 @@ struct Ctrl {
   uint64_t acc_empty[kMaxAccStages];
   uint32_t tmem_base;
   int abort_flag;
-  alignas(16) float sc[8][2][BT];  // per epilogue warp, double buffered
+  alignas(16) float sc[kFp8 ? 8 : 1][2][kFp8 ? (BT >= 128 ? BT / 2 : BT) : 4];  // per epilogue warp, double buffered
+  alignas(16) uint16_t xpose[kFp8 && BT >= 128 ? 8 : 4][32 * 32];  // per epilogue warp: output transpose tile
   int tile_start[kMaxExperts + 1];
   int row_start[kMaxExperts + 1];
 };
@@ -71,9 +75,9 @@ __host__ __device__ constexpr int num_stages() {
   return (200 * 1024) / stage_bytes<BT>() > kMaxStages ? kMaxStages
                                                         : (200 * 1024) / stage_bytes<BT>();
 }
-template <int BT>
+template <int BT, bool kFp8>
 __host__ __device__ constexpr size_t smem_bytes() {
-  return 1024 + (size_t)num_stages<BT>() * stage_bytes<BT>() + sizeof(Ctrl<BT>);
+  return 1024 + (size_t)num_stages<BT>() * stage_bytes<BT>() + sizeof(Ctrl<BT, kFp8>);
 }
 // Accumulator stages in tensor memory.  16-bit inputs hand over one whole tile
 // per stage (two are enough); fp8 hands over every 128-wide K block, so more
@@ -109,7 +113,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  Ctrl<BT>* ctrl = reinterpret_cast<Ctrl<BT>*>(smem + kStages * kStageBytes);
+  Ctrl<BT, kFp8>* ctrl = reinterpret_cast<Ctrl<BT, kFp8>*>(smem + kStages * kStageBytes);
   volatile int* abort_flag = &ctrl->abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -184,12 +188,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         uint32_t a = acc_it % kAccStages;
-        if (!kFp8) {
+        const bool per_block = kFp8 && !(p.debug & 4);
+        if (!per_block) {
           if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) break;
           ptx::tc_fence_after();
         }
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-          if (kFp8) {
+          if (per_block) {
             a = acc_it % kAccStages;
             if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
           }
@@ -206,13 +211,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             else if (kFp8) wdesc = ptx::make_smem_desc(wbase + j * 4096, 16384, 1024);
             else wdesc = ptx::make_smem_desc(wbase + j * 2048, 8192, 1024);
             const uint64_t adesc = ptx::make_smem_desc(abase + j * 32, 16, 1024);
-            const uint32_t accumulate = kFp8 ? (j > 0) : (kb > 0 || j > 0);
+            const uint32_t accumulate = per_block ? (j > 0) : (kb > 0 || j > 0);
             ptx::umma<kFp8>(d_tmem, wdesc, adesc, p.idesc, accumulate);
           }
           ptx::umma_commit(&ctrl->empty[s]);
-          if (kFp8) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+          if (per_block) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
         }
-        if (!kFp8 && ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+        if (!per_block && ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
       }
     }
   } else {
@@ -268,18 +273,18 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < BT; c0 += kChunk) {
-          if (c0 < ti.valid) {
+          if (c0 < ti.valid && !(p.debug & 16)) {
             uint32_t v[kChunk];
             if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
             else ptx::tmem_ld_32x16(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
             ptx::tmem_wait_ld();
-            if (feat_ok) {
+            if (!(p.debug & 8)) {
+              float vals[kChunk];
 #pragma unroll
-              for (int i = 0; i < kChunk; ++i) {
-                if (c0 + i < ti.valid && ti.row0 + c0 + i < p.m)
-                  store_out(p.d, p.out_f16, (int64_t)(ti.row0 + c0 + i) * p.n + feat,
-                            __uint_as_float(v[i]) + bias_v);
-              }
+              for (int i = 0; i < kChunk; ++i) vals[i] = __uint_as_float(v[i]) + bias_v;
+              store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
+                                                 (int64_t)ti.row0 + c0, ti.valid - c0, p.m, p.n,
+                                                 ti.n_tile * kFeat + q * 32, lane);
             }
           }
         }
@@ -315,10 +320,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int jb = 0; jb < kGroup; ++jb) {
             const int kb = g * kGroup + jb;
             if (kb >= p.num_kb) break;
-            float* sc = ctrl->sc[warp - 2][kb & 1];
+            if ((p.debug & 4) && kb + 1 < p.num_kb) continue;
+            const uint32_t sc = ptx::smem_u32(ctrl->sc[warp - 2][kb & 1]);
 #pragma unroll
             for (int u = 0; u < kPerLane; ++u)
-              if (lane + 32 * u < kCols) sc[lane + 32 * u] = cur.a[u][jb] * cur.w[jb];
+              if (lane + 32 * u < kCols) ptx::sts32f(sc + (lane + 32 * u) * 4, cur.a[u][jb] * cur.w[jb]);
             __syncwarp();
             const uint32_t a = acc_it % kAccStages;
             if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
@@ -329,7 +335,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int c0 = 0; c0 < kCols; c0 += kChunk) {
               const bool last_chunk = (c0 + kChunk >= kCols);
               uint32_t v[kChunk];
-              if (col0 + c0 < ti.valid) {
+              if (col0 + c0 < ti.valid && !(p.debug & 2)) {
                 if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
                 else ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
                 ptx::tmem_wait_ld();
@@ -339,10 +345,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
               }
-              if (col0 + c0 < ti.valid) {
+              if (col0 + c0 < ti.valid && !(p.debug & 3)) {
 #pragma unroll
                 for (int i = 0; i < kChunk; i += 4) {
-                  const float4 s4 = *reinterpret_cast<const float4*>(sc + c0 + i);
+                  const float4 s4 = ptx::lds128f(sc + (c0 + i) * 4);
                   acc[c0 + i + 0] = fmaf(__uint_as_float(v[i + 0]), s4.x, acc[c0 + i + 0]);
                   acc[c0 + i + 1] = fmaf(__uint_as_float(v[i + 1]), s4.y, acc[c0 + i + 1]);
                   acc[c0 + i + 2] = fmaf(__uint_as_float(v[i + 2]), s4.z, acc[c0 + i + 2]);
@@ -354,12 +360,17 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (g + 1 < n_groups) cur = pre;
         }
-        if (ok && feat_ok) {
+        if (ok) {
 #pragma unroll
-          for (int i = 0; i < kCols; ++i) {
-            const int c = col0 + i;
-            if (c < ti.valid && ti.row0 + c < p.m)
-              store_out(p.d, p.out_f16, (int64_t)(ti.row0 + c) * p.n + feat, acc[i] + bias_v);
+          for (int c0 = 0; c0 < kCols; c0 += kChunk) {
+            if (col0 + c0 < ti.valid) {
+              float vals[kChunk];
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i) vals[i] = acc[c0 + i] + bias_v;
+              store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
+                                                 (int64_t)ti.row0 + col0 + c0, ti.valid - col0 - c0, p.m,
+                                                 p.n, ti.n_tile * kFeat + q * 32, lane);
+            }
           }
         }
       }
@@ -384,10 +395,10 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, i
   static bool configured = false;
   if (!configured) {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem_bytes<BT>()));
+                                      (int)smem_bytes<BT, kFp8>()));
     configured = true;
   }
-  kern<<<grid, num_threads<BT, kFp8>(), smem_bytes<BT>(), st>>>(ta, tw, p);
+  kern<<<grid, num_threads<BT, kFp8>(), smem_bytes<BT, kFp8>(), st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_tc_kernel");
   return B200MOE_OK;
 }
@@ -411,8 +422,8 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   const int es = a_fp8 ? 1 : 2;
   if (((int64_t)a->k * es) % 16 != 0 || ((int64_t)a->n * es) % 16 != 0)
     return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: row pitch must be a multiple of 16 bytes");
-  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15))
-    return fail(B200MOE_E_BADARG, "grouped GEMM: A and W must be 16-byte aligned");
+  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15) || ((uintptr_t)a->d & 15))
+    return fail(B200MOE_E_BADARG, "grouped GEMM: A, W and D must be 16-byte aligned");
   if (a->m == 0 || a->n == 0) return B200MOE_OK;
 
   const int kpb = a_fp8 ? 128 : 64;
@@ -423,6 +434,11 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   p.n_tiles = (a->n + kFeat - 1) / kFeat;
   p.num_kb = (a->k + kpb - 1) / kpb;
   p.out_f16 = a->d_dtype == B200MOE_F16;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("B200MOE_DEBUG"); dbg = e ? atoi(e) : 0; }
+    p.debug = dbg;
+  }
 
   const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
   // Token-tile width from the mean rows per expert (routing is never perfectly
@@ -432,6 +448,11 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   else if (avg <= 40) bt = 64;
   else if (avg <= 160 || a_fp8) bt = 128;
   else bt = 256;
+  {
+    static int force_bt = -1;
+    if (force_bt < 0) { const char* e = getenv("B200MOE_BT"); force_bt = e ? atoi(e) : 0; }
+    if (force_bt == 16 || force_bt == 64 || force_bt == 128 || (force_bt == 256 && !a_fp8)) bt = force_bt;
+  }
 
   const uint32_t fmt = a_fp8 ? 0u : (a->a_dtype == B200MOE_BF16 ? 1u : 0u);
   p.idesc = ptx::make_idesc(fmt, fmt, kn ? 1u : 0u, 0u, kFeat, (uint32_t)bt);

@@ -42,6 +42,44 @@ __device__ __forceinline__ float load_bias(const void* b, int out_f16, int64_t i
 }
 
 
+// Output path of the epilogue warps.  A warp holds a block of the result as
+// vals[i] = D(token i, feature lane) (one TMEM lane per thread), but D is
+// row-major over features, so a direct store would write 2 bytes per lane into
+// 32 different 64-byte pieces.  The block is transposed through a per-warp
+// shared-memory tile ([token][feature], 16-bit) and written as 16-byte vectors:
+// kFeat/8 lanes cover one token row, 256/kFeat rows per store instruction.
+// kFeat = 32 (one value per lane) or 16 (values on the even lanes only).
+template <int kTok, int kFeatW>
+__device__ __forceinline__ void store_block_transposed(uint16_t* xp, const float (&vals)[kTok],
+                                                       void* d, int out_f16, int64_t row0,
+                                                       int tok_valid, int64_t m_limit, int n_out,
+                                                       int feat0, int lane) {
+  const int col = (kFeatW == 32) ? lane : (lane >> 1);
+  const bool writer = (kFeatW == 32) || !(lane & 1);
+  const uint32_t xp_s = ptx::smem_u32(xp);
+#pragma unroll
+  for (int i = 0; i < kTok; ++i) {
+    uint16_t bits;
+    if (out_f16) { const __half h = __float2half_rn(vals[i]); bits = *reinterpret_cast<const uint16_t*>(&h); }
+    else { const __nv_bfloat16 h = __float2bfloat16_rn(vals[i]); bits = *reinterpret_cast<const uint16_t*>(&h); }
+    if (writer) ptx::sts16(xp_s + (i * kFeatW + col) * 2, bits);
+  }
+  __syncwarp();
+  constexpr int kLanesPerRow = kFeatW / 8;          // 16-byte pieces per token row
+  constexpr int kRowsPerIter = 32 / kLanesPerRow;
+  const int piece = lane % kLanesPerRow;
+  const int f = feat0 + piece * 8;
+#pragma unroll
+  for (int it = 0; it < kTok / kRowsPerIter; ++it) {
+    const int tok = lane / kLanesPerRow + it * kRowsPerIter;
+    if (tok < tok_valid && row0 + tok < m_limit && f < n_out) {
+      const uint4 q = ptx::lds128(xp_s + (tok * kFeatW + piece * 8) * 2);
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(d) + (row0 + tok) * (int64_t)n_out + f) = q;
+    }
+  }
+  __syncwarp();
+}
+
 // Warp-cooperative prefix sums over the experts: row_start[e], tile_start[e]
 // (tiles of expert e = ceil(rows_e / BT) * n_tiles).  Called by one full warp.
 template <int BT>

@@ -7,18 +7,19 @@
 // with one more role between the TMA producer and the MMA issuer:
 //   warp 0   : TMA producer: packed weight tile (128 rows x 32 bytes, no
 //              swizzle) and activation tile (BT rows x 128 bytes, 128B swizzle)
-//   warps 2-5: converters: thread r expands row r of the packed tile to 64
+//   warps 2-9: converters: two threads per row, each expands 32 of the row's 64
 //              16-bit values (code * 2^(scale-127), exact in bf16/fp16 range)
 //              and writes them in the 128-byte-swizzled K-major layout the MMA
 //              reads; generic-proxy writes are fenced before the hand-over
 //   warp 1   : MMA issuer (kind::f16), owns tensor memory
-//   warps 6-9: epilogue
+//   warps 10-13: epilogue
 // HBM sees only the 4-bit weights (0.53 bytes per element with scales).
 //
 // Numerics follow csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:411-419, 455-471 of
 // vllm-xpu-kernels: LUT[code] * 2^(byte-127) rounded to the activation type
 // before the multiply, fp32 accumulation, bias added in fp32.
 #include <cuda_fp4.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "gemm_tc_common.cuh"
@@ -29,7 +30,8 @@ namespace {
 
 constexpr int kOpBytes = 16384;   // 128 rows x 64 sixteen-bit values
 constexpr int kRawBytes = 4096;   // 128 rows x 32 packed bytes
-constexpr int kDqThreads = 320;
+constexpr int kDqConvWarps = 8;    // two per weight row half
+constexpr int kDqThreads = 64 + 32 * kDqConvWarps + 128;
 constexpr int kDqMaxStages = 8;
 constexpr int kDqGroup = 8;      // K blocks per scale prefetch
 
@@ -46,6 +48,7 @@ struct DqParams {
   int out_f16;
   int swiglu;      // 1: D[m, f/2] = swigluoai(acc[m,f], acc[m,f+1]) for even f
   float alpha, limit, clamp_limit;
+  int debug;  // experiment switches (B200MOE_DEBUG), 0 in normal use
 };
 
 template <int BT>
@@ -59,6 +62,7 @@ struct DqCtrl {
   int abort_flag;
   int tile_start[kMaxExperts + 1];
   int row_start[kMaxExperts + 1];
+  alignas(16) uint16_t xpose[4][32 * 32];  // per epilogue warp: output transpose tile
 };
 
 template <int BT>
@@ -116,7 +120,7 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 2 && lane == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&ctrl->full_raw[s], 1);
-      ptx::mbar_init(&ctrl->full_op[s], 4);
+      ptx::mbar_init(&ctrl->full_op[s], kDqConvWarps);
       ptx::mbar_init(&ctrl->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -149,8 +153,8 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t s = it % kStages, ph = (it / kStages) & 1;
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* st = smem + s * kStageBytes;
-          ptx::mbar_expect_tx(&ctrl->full_raw[s], kRawBytes + BT * 128);
-          ptx::tma_load_3d(st + kOpBytes + BT * 128, &tmap_w, &ctrl->full_raw[s], kb * 32, n0, ti.e);
+          ptx::mbar_expect_tx(&ctrl->full_raw[s], ((p.debug & 2) ? 0 : kRawBytes) + BT * 128);
+          if (!(p.debug & 2)) ptx::tma_load_3d(st + kOpBytes + BT * 128, &tmap_w, &ctrl->full_raw[s], kb * 32, n0, ti.e);
           ptx::tma_load_2d(st + kOpBytes, &tmap_a, &ctrl->full_raw[s], kb * 64, ti.row0);
         }
       }
@@ -184,9 +188,11 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + kDqConvWarps) {
     // ------------------------------ converters --------------------------------
-    const int r = (warp - 2) * 32 + lane;  // row of the tile
+    const int ct = (warp - 2) * 32 + lane;
+    const int r = ct & 127;                // row of the tile
+    const int half = ct >> 7;              // which 32 of the row's 64 values
     const int kgroups = p.k / 32;           // scale bytes per weight row
     const bool pair_aligned = (kgroups % 2 == 0) && ((reinterpret_cast<uintptr_t>(p.w_scale) & 1) == 0);
     uint32_t it = 0;
@@ -228,25 +234,28 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->full_raw[s], ph, abort_flag))) {
           *abort_flag = 1; ok = false;
         }
-        if (ok) {
-        uint8_t* st = smem + s * kStageBytes;
-        const uint4* raw = reinterpret_cast<const uint4*>(st + kOpBytes + BT * 128 + r * 32);
-        const uint4 q0 = raw[0], q1 = raw[1];
-        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        uint8_t* orow = st + (r >> 3) * 1024 + (r & 7) * 128;
-        if (!p.out_f16 && c0s <= 128u && c1s <= 128u) {
+        if (ok && (p.debug & 1)) {
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&ctrl->full_op[s]);
+        }
+        if (ok && !(p.debug & 1)) {
+        const uint32_t st = ptx::smem_u32(smem + s * kStageBytes);
+        const uint4 q0 = ptx::lds128(st + kOpBytes + BT * 128 + r * 32 + half * 16);
+        const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
+        const uint32_t sbyte = half ? c1s : c0s;
+        const uint32_t orow = st + (r >> 3) * 1024 + (r & 7) * 128;
+        if (!p.out_f16 && sbyte <= 128u) {
           // Integer path for bf16.  Put the code's exponent and mantissa bits
           // where bf16 keeps them ((c & 7) << 6, sign to bit 15): read as bf16
           // that is the code's value times 2^-126, subnormal codes included, so
           // one exact multiply by 2^(scale - 1) yields code * 2^(scale - 127).
-          const uint32_t m0 = (c0s + 126u) << 7, m1 = (c1s + 126u) << 7;
-          const uint32_t mm0 = m0 | (m0 << 16), mm1 = m1 | (m1 << 16);
+          const uint32_t m0 = (sbyte + 126u) << 7;
+          const uint32_t mm = m0 | (m0 << 16);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
+          for (int c = 0; c < 4; ++c) {
             const uint32_t w = words[c];
             const uint32_t xe = w & 0x0F0F0F0Fu;          // codes of even k in bytes 0..3
             const uint32_t xo = (w >> 4) & 0x0F0F0F0Fu;   // codes of odd k
-            const uint32_t mm = c < 4 ? mm0 : mm1;
             uint32_t o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -256,13 +265,12 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                   *reinterpret_cast<const __nv_bfloat162*>(&mm));
               o[j] = *reinterpret_cast<const uint32_t*>(&prod);
             }
-            *reinterpret_cast<uint4*>(orow + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            ptx::sts128(orow + (((4 * half + c) ^ (r & 7)) << 4), make_uint4(o[0], o[1], o[2], o[3]));
           }
         } else {
-          const float sc0 = e8m0_to_f32(c0s), sc1 = e8m0_to_f32(c1s);
+          const float sc = e8m0_to_f32(sbyte);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {  // 8 values = one 16-byte chunk of the row
-            const float sc = c < 4 ? sc0 : sc1;
+          for (int c = 0; c < 4; ++c) {  // 8 values = one 16-byte chunk of the row
             const uint32_t w = words[c];
             uint32_t o[4];
 #pragma unroll
@@ -270,7 +278,7 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const float2 f = e2m1x2_to_float2((w >> (8 * b)) & 0xffu);
               o[b] = pack16(f.x * sc, f.y * sc, p.out_f16);
             }
-            *reinterpret_cast<uint4*>(orow + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            ptx::sts128(orow + (((4 * half + c) ^ (r & 7)) << 4), make_uint4(o[0], o[1], o[2], o[3]));
           }
         }
         ptx::fence_proxy_async();
@@ -312,10 +320,10 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
           else ptx::tmem_ld_32x16(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
           ptx::tmem_wait_ld();
+          float vals[kChunk];
 #pragma unroll
           for (int i = 0; i < kChunk; ++i) {
             float x = __uint_as_float(v[i]) + bias_v;
-            const bool row_ok = (c0 + i < ti.valid) && (ti.row0 + c0 + i < p.m);
             if (p.swiglu) {
               // gate sits on even features, up on the next odd one: neighbours in the warp
               const float other = __shfl_xor_sync(0xffffffffu, x, 1);
@@ -328,12 +336,17 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
               gate = fminf(gate, p.limit);
               up = fminf(fmaxf(up, -p.limit), p.limit);
               x = (up + 1.0f) * gate * (1.0f / (1.0f + __expf(-gate * p.alpha)));
-              if (row_ok && feat_ok && !(lane & 1))
-                store_out(p.d, p.out_f16, (int64_t)(ti.row0 + c0 + i) * n_out + (feat >> 1), x);
-            } else if (row_ok && feat_ok) {
-              store_out(p.d, p.out_f16, (int64_t)(ti.row0 + c0 + i) * n_out + feat, x);
             }
+            vals[i] = x;
           }
+          if (p.swiglu)
+            store_block_transposed<kChunk, 16>(ctrl->xpose[warp - 2 - kDqConvWarps], vals, p.d, p.out_f16,
+                                               (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
+                                               (ti.n_tile * kFeat + q * 32) >> 1, lane);
+          else
+            store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2 - kDqConvWarps], vals, p.d, p.out_f16,
+                                               (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
+                                               ti.n_tile * kFeat + q * 32, lane);
         }
       }
       ptx::tc_fence_before();
@@ -379,8 +392,10 @@ int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
     return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM: SiLU epilogue not available");
   if (a->num_experts > kMaxExperts || a->k % 64 != 0 || (a->k / 2) % 16 != 0)
     return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM: K must be a multiple of 64");
-  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15))
-    return fail(B200MOE_E_BADARG, "grouped GEMM: A and W must be 16-byte aligned");
+  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15) || ((uintptr_t)a->d & 15))
+    return fail(B200MOE_E_BADARG, "grouped GEMM: A, W and D must be 16-byte aligned");
+  if (a->epilogue == B200MOE_EPI_SWIGLUOAI && (a->n / 2) % 8 != 0)
+    return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM: gated output width must be a multiple of 8");
   if (a->m == 0 || a->n == 0) return B200MOE_OK;
 
   DqParams p;
@@ -392,6 +407,11 @@ int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
   p.out_f16 = a->d_dtype == B200MOE_F16;
   p.swiglu = a->epilogue == B200MOE_EPI_SWIGLUOAI;
   p.alpha = a->act_alpha; p.limit = a->act_limit; p.clamp_limit = a->clamp_limit;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("B200MOE_DEBUG"); dbg = e ? atoi(e) : 0; }
+    p.debug = dbg;
+  }
 
   const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
   const int bt = avg <= 8 ? 16 : (avg <= 40 ? 64 : 128);
