@@ -34,6 +34,10 @@ sys.path.insert(0, str(ROOT / "vllm-xpu-kernels_b200"))
 
 import torch  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the two grouped-GEMM launches of one
+# step, from one ncu capture per workload (see the summaries under profiles/).
+NCU_TRAFFIC_BYTES = {("cfg2_mixtral_bf16", 4096): 3.956e9}
+
 METRIC = "fused_moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -351,7 +355,8 @@ def run_ours(args):
         ach = (wbytes + act_bytes) / (ms_pair * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm"], "unit": "GB/s",
                 "frac": round(ach / peaks["hbm"], 4)}
-    roof.update({"traffic": None, "kernel": "grouped_gemm_tc_kernel (gemm1 + gemm2 of one step)",
+    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((cfg.name, T)) if ep_world == 1 else None, "kernel": ("grouped_gemm_dq_kernel" if cfg.recipe == "mxfp4" else "grouped_gemm_tc_kernel")
+                           + " (gemm1 + gemm2 of one step)",
                  "ms_per_launch_pair": round(ms_pair, 4), "peak_source": peaks["source"] + " (sustained)",
                  "experts_active": e_act})
 
