@@ -152,7 +152,7 @@ def launches_per_step(M: int, quant: bool) -> int:
     return 1 + (1 if M <= 2048 else 3) + 1 + 2 + 1 + (1 if quant else 0) + 1
 
 
-def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0):
+def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, ep_chunks=None, ep_sm_reserve=20):
     """Synthetic weights on the device (this rank's experts only when the experts
     are sharded) and the host-side inputs of one step."""
     import vllm_xpu_kernels.fused_moe_interface as fmi
@@ -187,7 +187,8 @@ def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0):
         b2 = (torch.randn(E, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
     if ep_world > 1:
         from vllm_xpu_kernels.ep_moe import EpFusedMoe
-        layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
+        layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E,
+                           overlap_chunks=ep_chunks, sm_reserve=ep_sm_reserve)
     else:
         layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
     x_cpu, logits_cpu, bias_cpu = wl.make_inputs(cfg, T, seed=ep_rank)
@@ -201,7 +202,7 @@ def make_step(cfg, layer, dev, T):
     src = torch.empty(T, K, dtype=torch.int32, device=dev)
     out = torch.empty(T, cfg.H, dtype=torch.bfloat16, device=dev)
 
-    def step(x, logits, bias):
+    def step(x, logits, bias, out=out):
         if cfg.routing == "softmax":
             torch.ops._moe_C.topk_softmax(tw, ids, src, logits, cfg.renormalize, None)
             layer.apply(out, x, tw, ids)
@@ -283,7 +284,8 @@ def run_ours(args):
     cfg = wl.CONFIGS[args.workload]
     T = args.tokens
     ep_world = world if (args.parallelism == "ep" and world > 1) else 1
-    layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev, ep_world, rank if ep_world > 1 else 0)
+    layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev, ep_world, rank if ep_world > 1 else 0,
+                                                            args.ep_chunks, args.ep_sm_reserve)
     step, (tw, ids) = make_step(cfg, layer, dev, T)
     x, logits = x_cpu.to(dev), logits_cpu.to(dev)
     bias = bias_cpu.to(dev) if bias_cpu is not None else None
@@ -314,22 +316,47 @@ def run_ours(args):
     value = world * T * args.steps / (ms_total * 1e-3)
 
     # ---- end to end: host buffers, copies inside the timed region -----------------------
+    # Every step copies its inputs from pinned host memory and its result back; the copies of
+    # neighbouring steps overlap the compute of the current one (two buffers, three streams),
+    # as a serving loop would run it.
     x_pin, lg_pin = x_cpu.pin_memory(), logits_cpu.pin_memory()
-    out_pin = torch.empty(T, cfg.H, dtype=torch.bfloat16).pin_memory()
-    x_d, lg_d = torch.empty_like(x), torch.empty_like(logits)
+    out_pin = [torch.empty(T, cfg.H, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    x_d = [torch.empty_like(x) for _ in range(2)]
+    lg_d = [torch.empty_like(logits) for _ in range(2)]
+    out_d = [torch.empty(T, cfg.H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    s_in, s_out, cur = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.current_stream(dev)
 
-    def e2e_step():
-        x_d.copy_(x_pin, non_blocking=True)
-        lg_d.copy_(lg_pin, non_blocking=True)
-        o = step(x_d, lg_d, bias)
-        out_pin.copy_(o, non_blocking=True)
+    def e2e_loop(n):
+        comp_done = [None, None]
+        out_done = [None, None]
+        for i in range(n):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if comp_done[b] is not None:
+                    s_in.wait_event(comp_done[b])       # step i-2 has consumed this input buffer
+                x_d[b].copy_(x_pin, non_blocking=True)
+                lg_d[b].copy_(lg_pin, non_blocking=True)
+                in_ready = torch.cuda.Event()
+                in_ready.record(s_in)
+            cur.wait_event(in_ready)
+            if out_done[b] is not None:
+                cur.wait_event(out_done[b])             # step i-2's result has left this buffer
+            step(x_d[b], lg_d[b], bias, out_d[b])
+            comp_done[b] = torch.cuda.Event()
+            comp_done[b].record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(comp_done[b])
+                out_pin[b].copy_(out_d[b], non_blocking=True)
+                out_done[b] = torch.cuda.Event()
+                out_done[b].record(s_out)
+        for ev in out_done:
+            if ev is not None:
+                cur.wait_event(ev)
 
-    for _ in range(3):
-        e2e_step()
+    e2e_loop(3)
     barrier()
     e0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    e2e_loop(args.steps)
     e1.record()
     barrier()
     ms2 = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -337,7 +364,7 @@ def run_ours(args):
         dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
     e2e_value = world * T * args.steps / (float(ms2) * 1e-3)
     h2d = x_pin.numel() * 2 + lg_pin.numel() * 4
-    d2h = out_pin.numel() * 2
+    d2h = out_pin[0].numel() * 2
 
     # ---- roofline of the grouped GEMM kernel ---------------------------------------------
     peaks = _peaks()
@@ -423,6 +450,10 @@ def main():
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
                     help="N > 1: independent replicas (default) or experts sharded over the ranks "
                          "with all-to-all token dispatch / combine")
+    ap.add_argument("--ep-chunks", type=int, default=None,
+                    help="ep: token chunks whose exchange overlaps the experts (default: by batch size)")
+    ap.add_argument("--ep-sm-reserve", type=int, default=20,
+                    help="ep: SMs the GEMM kernels leave to the collective while chunks overlap")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

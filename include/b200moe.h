@@ -235,6 +235,9 @@ typedef struct {
                              up; may be NULL                                      */
   int impl;               /* 0 = auto, 1 = tensor-core kernel, 2 = plain-CUDA
                              checking kernel                                      */
+  int max_ctas;           /* >0: the persistent tensor-core kernel uses at most this
+                             many CTAs (leaves SMs to a concurrent collective);
+                             0 = one per SM                                       */
 } b200moe_gemm_args;
 
 int b200moe_grouped_gemm(const b200moe_gemm_args* args, b200moe_stream stream);

@@ -60,7 +60,7 @@ def grouped_gemm(a, a_scale, w, w_scale, bias, rows, N, K, layout=0, epilogue=0,
     n_out = N // 2 if epilogue else N
     d = torch.full((M, n_out), float("nan"), dtype=out_dtype, device=DEV)
     torch.ops._xpu_C.b200_grouped_gemm(a, a_scale, w, w_scale, bias, d, rows, N, K, E, layout,
-                                       epilogue, 1.702, 7.0, clamp, impl)
+                                       epilogue, 1.702, 7.0, clamp, impl, 0)
     return d
 
 

@@ -133,6 +133,6 @@ def test_full_size_mixtral_properties(native):
     a = torch.randn(T * K, H, generator=g, device=DEV).to(torch.bfloat16)
     d1 = torch.empty(T * K, 2 * I, dtype=torch.bfloat16, device=DEV)
     d2 = torch.empty_like(d1)
-    torch.ops._xpu_C.b200_grouped_gemm(a, None, w13, None, None, d1, rows, 2 * I, H, E, 2, 0, 1.702, 7.0, 0.0, 1)
-    torch.ops._xpu_C.b200_grouped_gemm(a, None, w13, None, None, d2, rows, 2 * I, H, E, 2, 0, 1.702, 7.0, 0.0, 2)
+    torch.ops._xpu_C.b200_grouped_gemm(a, None, w13, None, None, d1, rows, 2 * I, H, E, 2, 0, 1.702, 7.0, 0.0, 1, 0)
+    torch.ops._xpu_C.b200_grouped_gemm(a, None, w13, None, None, d2, rows, 2 * I, H, E, 2, 0, 1.702, 7.0, 0.0, 2, 0)
     torch.testing.assert_close(d1.float(), d2.float(), rtol=1e-2, atol=1e-2)

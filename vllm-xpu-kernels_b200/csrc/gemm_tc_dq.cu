@@ -437,6 +437,7 @@ int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
   }
   const int64_t tile_bound = ((a->m + bt - 1) / bt + a->num_experts) * (int64_t)p.n_tiles;
   int grid = sm_count();
+  if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if (tile_bound < grid) grid = (int)tile_bound;
   if (grid < 1) grid = 1;
   if (bt == 16) return launch_dq<16>(ta, tw, p, grid, st);

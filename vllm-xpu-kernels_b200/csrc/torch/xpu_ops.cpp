@@ -16,7 +16,7 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
                              const std::optional<at::Tensor>& ptr_bias, at::Tensor& ptr_D,
                              at::Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                              int64_t layout, int64_t epilogue, double alpha, double limit,
-                             double clamp_limit, int64_t impl) {
+                             double clamp_limit, int64_t impl, int64_t max_ctas) {
   check_cuda(ptr_A, "ptr_A");
   const auto A_dtype = ptr_A.scalar_type();
   const auto B_dtype = ptr_B.scalar_type();
@@ -127,6 +127,7 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   g.act_alpha = (float)alpha; g.act_limit = (float)limit; g.clamp_limit = (float)clamp_limit;
   g.status = nullptr;
   g.impl = (int)impl;
+  g.max_ctas = (int)max_ctas;
   const c10::cuda::CUDAGuard guard(ptr_A.device());
   check_status(b200moe_grouped_gemm(&g, current_stream()));
   return ptr_D;
@@ -139,7 +140,7 @@ at::Tensor cutlass_grouped_gemm_interface(at::Tensor ptr_A, const std::optional<
                                           int64_t num_experts) {
   // The reference accepts ptr_A_scale and ignores it for 16-bit activations.
   return grouped_gemm_impl(ptr_A, ptr_A_scale, ptr_B, ptr_B_scale, ptr_bias, ptr_D, rows_per_expert, N,
-                           K, num_experts, 0, 0, 1.702, 7.0, 0.0, 0);
+                           K, num_experts, 0, 0, 1.702, 7.0, 0.0, 0, 0);
 }
 
 at::Tensor b200_grouped_gemm(at::Tensor ptr_A, const std::optional<at::Tensor>& ptr_A_scale,
@@ -147,9 +148,9 @@ at::Tensor b200_grouped_gemm(at::Tensor ptr_A, const std::optional<at::Tensor>& 
                              const std::optional<at::Tensor>& ptr_bias, at::Tensor ptr_D,
                              at::Tensor rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                              int64_t layout, int64_t epilogue, double alpha, double limit,
-                             double clamp_limit, int64_t impl) {
+                             double clamp_limit, int64_t impl, int64_t max_ctas) {
   return grouped_gemm_impl(ptr_A, ptr_A_scale, ptr_B, ptr_B_scale, ptr_bias, ptr_D, rows_per_expert, N,
-                           K, num_experts, layout, epilogue, alpha, limit, clamp_limit, impl);
+                           K, num_experts, layout, epilogue, alpha, limit, clamp_limit, impl, max_ctas);
 }
 
 }  // namespace
@@ -163,7 +164,7 @@ TORCH_LIBRARY_FRAGMENT(_xpu_C, m) {
       "b200_grouped_gemm(Tensor ptr_A, Tensor? ptr_A_scale, Tensor ptr_B, Tensor? ptr_B_scale, "
       "Tensor? ptr_bias, Tensor(a!) ptr_D, Tensor rows_per_expert, int N, int K, int num_experts, "
       "int layout=0, int epilogue=0, float alpha=1.702, float limit=7.0, float clamp_limit=0.0, "
-      "int impl=0) -> Tensor(a!)");
+      "int impl=0, int max_ctas=0) -> Tensor(a!)");
 }
 
 TORCH_LIBRARY_IMPL(_xpu_C, CUDA, m) {

@@ -66,11 +66,35 @@ class EpAllToAll:
     def combine(self, rows, send_splits, recv_splits):
         """The way back: `rows` are in the order they were received; the result is
         in the order this rank sent its rows."""
+        back, work = self.combine_async(rows, send_splits, recv_splits)
+        work.wait()
+        return back
+
+    # Asynchronous forms: the collective is queued behind the work already on
+    # the current stream and runs beside whatever is queued after it;
+    # ``work.wait()`` makes the current stream wait for it (no host block).
+    def dispatch_async(self, tensors, send_splits, recv_splits):
+        n_recv = int(sum(recv_splits))
+        out, works = [], []
+        for t in tensors:
+            if t is None:
+                out.append(None)
+                continue
+            r = torch.empty((n_recv,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+            tv = t.view(torch.uint8) if t.element_size() == 1 else t
+            rv = r.view(torch.uint8) if r.element_size() == 1 else r
+            works.append(dist.all_to_all_single(rv, tv, output_split_sizes=recv_splits,
+                                                input_split_sizes=send_splits, group=self.group,
+                                                async_op=True))
+            out.append(r)
+        return out, works
+
+    def combine_async(self, rows, send_splits, recv_splits):
         n_send = int(sum(send_splits))
         back = torch.empty((n_send,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
-        dist.all_to_all_single(back, rows, output_split_sizes=send_splits,
-                               input_split_sizes=recv_splits, group=self.group)
-        return back
+        work = dist.all_to_all_single(back, rows, output_split_sizes=send_splits,
+                                      input_split_sizes=recv_splits, group=self.group, async_op=True)
+        return back, work
 
 
 def owner_map(num_experts_total: int, ep_size: int, device) -> torch.Tensor:
@@ -90,7 +114,8 @@ class EpFusedMoe:
     def __init__(self, w13, w13_scales, w13_bias, w2, w2_scales, w2_bias,
                  n_experts_per_token, activation, num_local_experts,
                  group: Optional[dist.ProcessGroup] = None,
-                 gemm1_clamp_limit: Optional[float] = None):
+                 gemm1_clamp_limit: Optional[float] = None,
+                 overlap_chunks: Optional[int] = None, sm_reserve: int = 20):
         from .fused_moe_interface import XpuFusedMoe
         self.a2a = EpAllToAll(group)
         self.ep_size, self.ep_rank = self.a2a.ep_size, self.a2a.ep_rank
@@ -102,8 +127,26 @@ class EpFusedMoe:
                                  num_local_experts, gemm1_clamp_limit=gemm1_clamp_limit)
         self.owner = owner_map(self.num_experts_total, self.ep_size, w13.device)
         self.quant = self.local.is_block_fp8
+        # Optional: cut the batch into `overlap_chunks` token chunks so that the
+        # exchange of one chunk runs beside the experts of another (the persistent
+        # GEMM kernels then leave `sm_reserve` SMs to the collective's kernels).
+        # Off by default: every chunk streams the local experts' weights again,
+        # which on B200 cost more than the overlap saved (DeepSeek-V3 shape,
+        # 8192 tokens per GPU, 2 GPUs: 12.0 ms unchunked, 13.7 ms with 2 chunks,
+        # 15.2 ms with 4).
+        self.overlap_chunks = overlap_chunks
+        self.sm_reserve = sm_reserve
+        self._sm_count = torch.cuda.get_device_properties(w13.device).multi_processor_count
+
+    def _num_chunks(self, T):
+        if self.overlap_chunks is None:
+            return 1
+        return max(1, min(self.overlap_chunks, T))
 
     def apply(self, output, hidden_states, topk_weights, topk_ids):
+        nc = self._num_chunks(hidden_states.shape[0])
+        if nc > 1:
+            return self._apply_chunked(output, hidden_states, topk_weights, topk_ids, nc)
         T, H = hidden_states.shape
         K = self.topk
         dev = hidden_states.device
@@ -145,3 +188,77 @@ class EpFusedMoe:
         # 4. rows travel back; weighted top-k reduction on the source rank
         back = self.a2a.combine(local_out, send_splits, recv_splits)
         ops.moe_gather(output, back, topk_weights, send_pos, self.num_experts_total)
+
+    def _permute_for_send(self, hidden_states, topk_ids):
+        """Groups one token range's routed rows by destination rank."""
+        T, H = hidden_states.shape
+        K, ep, dev = self.topk, self.ep_size, hidden_states.device
+        M = T * K
+        ops = torch.ops._moe_C
+        send_counts = torch.empty((ep,), dtype=torch.int32, device=dev)
+        send_pos = torch.empty((T, K), dtype=torch.int32, device=dev)
+        if self.quant:
+            send_rows = torch.empty((M, H), dtype=torch.float8_e4m3fn, device=dev)
+            send_scales = torch.empty((M, H // FP8_BLOCK), dtype=torch.float32, device=dev)
+            ops.b200_remap_quant_fp8(hidden_states, send_rows, send_scales, self.owner, send_counts,
+                                     send_pos, topk_ids, self.num_experts_total, ep)
+        else:
+            send_rows = torch.empty((M, H), dtype=hidden_states.dtype, device=dev)
+            send_scales = None
+            ops.remap_hidden_states(hidden_states, None, send_rows, None, self.owner, send_counts,
+                                    send_pos, topk_ids, self.num_experts_total, ep)
+        send_eids = torch.empty((M,), dtype=torch.int32, device=dev)
+        send_eids[send_pos.reshape(-1).long()] = (topk_ids.reshape(-1) % self.num_local_experts).to(torch.int32)
+        return send_rows, send_scales, send_eids, send_counts, send_pos
+
+    def _apply_chunked(self, output, hidden_states, topk_weights, topk_ids, nc):
+        T, H = hidden_states.shape
+        dev = hidden_states.device
+        ep = self.ep_size
+        bounds = [(T * c) // nc for c in range(nc + 1)]
+        # phase 1: permute every chunk, exchange all counts, read them back once
+        prep = []
+        for c in range(nc):
+            t0, t1 = bounds[c], bounds[c + 1]
+            prep.append(self._permute_for_send(hidden_states[t0:t1], topk_ids[t0:t1]))
+        counts = torch.stack([p[3] for p in prep], dim=1).contiguous()       # [ep, nc]
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=self.a2a.group)     # [ep(src), nc]
+        both = torch.stack((counts, recv_counts)).cpu()
+        send_spl = [both[0][:, c].tolist() for c in range(nc)]
+        recv_spl = [both[1][:, c].tolist() for c in range(nc)]
+
+        # phase 2: dispatch(c+1) and combine(c-1) run beside the experts of chunk c
+        self.local.gemm_max_ctas = max(1, self._sm_count - self.sm_reserve)
+        try:
+            inflight = [None] * nc
+            inflight[0] = self.a2a.dispatch_async(prep[0][:3], send_spl[0], recv_spl[0])
+            pending = None  # (chunk, back rows, work) of the previous chunk's combine
+            keep = []
+
+            def finish(c, back, work):
+                work.wait()
+                t0, t1 = bounds[c], bounds[c + 1]
+                torch.ops._moe_C.moe_gather(output[t0:t1], back, topk_weights[t0:t1], prep[c][4],
+                                            self.num_experts_total)
+
+            for c in range(nc):
+                if c + 1 < nc:
+                    inflight[c + 1] = self.a2a.dispatch_async(prep[c + 1][:3], send_spl[c + 1], recv_spl[c + 1])
+                (recv_rows, recv_scales, recv_eids), works = inflight[c]
+                for w in works:
+                    w.wait()
+                R = recv_rows.shape[0]
+                local_out = torch.empty((R, H), dtype=output.dtype, device=dev)
+                if R > 0:
+                    ones = torch.ones((R, 1), dtype=torch.float32, device=dev)
+                    self.local.apply(local_out, recv_rows, ones, recv_eids.view(R, 1),
+                                     a1q_scale=recv_scales if self.quant else None)
+                back, work = self.a2a.combine_async(local_out, send_spl[c], recv_spl[c])
+                keep.append((recv_rows, recv_scales, recv_eids, local_out, back))
+                if pending is not None:
+                    finish(*pending)
+                pending = (c, back, work)
+            finish(*pending)
+        finally:
+            self.local.gemm_max_ctas = 0

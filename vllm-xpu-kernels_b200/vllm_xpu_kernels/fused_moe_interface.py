@@ -229,6 +229,9 @@ class XpuFusedMoe:
         else:
             self.total_experts_num = self.num_experts * self.ep_size
         self.local_experts_num = self.num_experts
+        # >0: cap on the CTAs of the persistent GEMM kernels (set by callers that
+        # overlap a collective with this layer and need free SMs for it)
+        self.gemm_max_ctas = 0
 
     def apply(self, output, hidden_states, topk_weights, topk_ids,
               expert_map=None, a1q_scale=None):
@@ -287,14 +290,14 @@ class XpuFusedMoe:
             torch.ops._xpu_C.b200_grouped_gemm(
                 remapped, a_scale1, self.w13, self.gemm1_wei_scales, self.w13_bias, act_output,
                 rows_per_expert, 2 * I, hidden_size, E, 0,
-                _EPI_SILU if self._act_kind == "silu" else _EPI_SWIGLUOAI, 1.702, 7.0, clamp, 0)
+                _EPI_SILU if self._act_kind == "silu" else _EPI_SWIGLUOAI, 1.702, 7.0, clamp, 0,
+                self.gemm_max_ctas)
         else:
             gemm1_output = torch.empty((num_moe_inputs, 2 * I), dtype=output.dtype, device=dev)
-            torch.ops._xpu_C.cutlass_grouped_gemm_interface(
-                ptr_A=remapped, ptr_A_scale=a_scale1, ptr_B=self.w13,
-                ptr_B_scale=self.gemm1_wei_scales, ptr_bias=self.w13_bias,
-                ptr_D=gemm1_output, rows_per_expert=rows_per_expert, N=2 * I,
-                K=hidden_size, num_experts=E)
+            torch.ops._xpu_C.b200_grouped_gemm(
+                remapped, a_scale1, self.w13, self.gemm1_wei_scales, self.w13_bias, gemm1_output,
+                rows_per_expert, 2 * I, hidden_size, E, 0, _EPI_NONE, 1.702, 7.0, 0.0, 0,
+                self.gemm_max_ctas)
             if clamp > 0:
                 gate = gemm1_output[:, :I]
                 up = gemm1_output[:, I:]
@@ -309,11 +312,9 @@ class XpuFusedMoe:
             act_q, gemm2_act_scale = quant_act_xpu(act_output, self.recipe)
         else:
             act_q, gemm2_act_scale = act_output, None
-        torch.ops._xpu_C.cutlass_grouped_gemm_interface(
-            ptr_A=act_q, ptr_A_scale=gemm2_act_scale, ptr_B=self.w2,
-            ptr_B_scale=self.gemm2_wei_scales, ptr_bias=self.w2_bias,
-            ptr_D=gemm2_output, rows_per_expert=rows_per_expert, N=hidden_size,
-            K=I, num_experts=E)
+        torch.ops._xpu_C.b200_grouped_gemm(
+            act_q, gemm2_act_scale, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_output,
+            rows_per_expert, hidden_size, I, E, 0, _EPI_NONE, 1.702, 7.0, 0.0, 0, self.gemm_max_ctas)
 
         torch.ops._moe_C.moe_gather(output, gemm2_output, topk_weights, row_map, E)
 
