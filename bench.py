@@ -243,10 +243,22 @@ def time_gemms(cfg, layer, ids, T, dev, iters, ep_world=1, ep_rank=0):
     d1 = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=dev)
     d2 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     f = torch.ops._xpu_C.cutlass_grouped_gemm_interface
+    if getattr(layer, "mx_acts", False):
+        # block-scaled MXFP4 path: MXFP8 activations, SwigluOAI inside gemm1's epilogue
+        a1, s1 = layer._quant_mx(a1)
+        a2, s2 = layer._quant_mx(a2)
+        d1 = torch.empty(M, I, dtype=torch.bfloat16, device=dev)
+        g = torch.ops._xpu_C.b200_grouped_gemm
 
-    def both():
-        f(a1, s1, layer.w13, layer.gemm1_wei_scales, layer.w13_bias, d1, rows, 2 * I, H, E)
-        f(a2, s2, layer.w2, layer.gemm2_wei_scales, layer.w2_bias, d2, rows, H, I, E)
+        def both():
+            g(a1, s1, layer.w13, layer.gemm1_wei_scales, layer.w13_bias, d1, rows, 2 * I, H, E, 0, 2, 1.702,
+              7.0, 0.0, 0, 0)
+            g(a2, s2, layer.w2, layer.gemm2_wei_scales, layer.w2_bias, d2, rows, H, I, E, 0, 0, 1.702, 7.0,
+              0.0, 0, 0)
+    else:
+        def both():
+            f(a1, s1, layer.w13, layer.gemm1_wei_scales, layer.w13_bias, d1, rows, 2 * I, H, E)
+            f(a2, s2, layer.w2, layer.gemm2_wei_scales, layer.w2_bias, d2, rows, H, I, E)
 
     for _ in range(3):
         both()
@@ -388,6 +400,10 @@ def run_ours(args):
     flops = 6.0 * m_rows * cfg.H * cfg.I
     wbytes = e_act * weight_bytes_per_expert(cfg)
     act_bytes = m_rows * (cfg.H + 2 * cfg.I + cfg.I + cfg.H) * 2  # A and D of both launches
+    mx = getattr(layer.local if ep_world > 1 else layer, "mx_acts", False)
+    if mx:  # per plane 1-byte codes + 1/32 scale byte in, 16-bit out; gemm1 writes the activated [M, I]
+        planes = (layer.local if ep_world > 1 else layer).mx_planes
+        act_bytes = m_rows * (planes * (cfg.H + cfg.I) * 33 // 32 + (cfg.I + cfg.H) * 2)
     t_tensor = flops / (peaks["tensor"] * 1e12)
     t_hbm = (wbytes + act_bytes) / (peaks["hbm"] * 1e9)
     if t_tensor >= t_hbm:
@@ -398,7 +414,7 @@ def run_ours(args):
         ach = (wbytes + act_bytes) / (ms_pair * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm"], "unit": "GB/s",
                 "frac": round(ach / peaks["hbm"], 4)}
-    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((cfg.name, T)) if ep_world == 1 else None, "kernel": ("grouped_gemm_dq_kernel" if cfg.recipe == "mxfp4" else "grouped_gemm_tc_kernel")
+    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((cfg.name, T)) if ep_world == 1 else None, "kernel": (("grouped_gemm_mx_kernel" if mx else "grouped_gemm_dq_kernel") if cfg.recipe == "mxfp4" else "grouped_gemm_tc_kernel")
                            + " (gemm1 + gemm2 of one step)",
                  "ms_per_launch_pair": round(ms_pair, 4), "peak_source": peaks["source"] + " (sustained)",
                  "experts_active": e_act})

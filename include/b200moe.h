@@ -32,7 +32,9 @@ typedef enum {
   B200MOE_I32 = 5,
   B200MOE_I64 = 6,
   B200MOE_U32 = 7,
-  B200MOE_FP4X2 = 8 /* float4_e2m1fn_x2: two e2m1 codes per byte, low nibble first */
+  B200MOE_FP4X2 = 8, /* float4_e2m1fn_x2: two e2m1 codes per byte, low nibble first */
+  B200MOE_FP8_E4M3_X2 = 9 /* two float8_e4m3fn planes [2][rows][cols]: value =
+                             plane 0 + plane 1 (MXFP8 activations + residual) */
 } b200moe_dtype;
 
 /* Status codes. */
@@ -217,7 +219,11 @@ typedef enum {
 typedef struct {
   const void* a;          /* [M,K] a_dtype, row-major, 16-byte aligned            */
   b200moe_dtype a_dtype;  /* BF16, F16, or FP8_E4M3 (with a_scale)                */
-  const float* a_scale;   /* fp8 activations: [M,K/128] fp32 row-major, else NULL */
+  const void* a_scale;    /* fp8 activations: block-fp8 weights: fp32 [M,K/128];
+                             MXFP4 weights (MXFP8 activations, a_dtype FP8_E4M3
+                             or FP8_E4M3_X2): e8m0 bytes as 32-bit words
+                             [planes][ceil(K/128)][M], the output of
+                             b200moe_quant_mxfp8; else NULL                  */
   const void* w;          /* weights, layout per w_format                         */
   b200moe_weight_format w_format;
   const void* w_scale;    /* per w_format, else NULL                              */
@@ -267,6 +273,22 @@ int b200moe_per_token_group_fp8_quant(const void* x, b200moe_dtype dtype,
                                       int scale_ue8m0, int64_t s_stride_row,
                                       int64_t s_stride_col,
                                       b200moe_stream stream);
+
+/* MX-format activation quantisation for the block-scaled MXFP4 GEMM: per 32
+ * consecutive values of a row one e8m0 scale byte b (2^(b-127) is the smallest
+ * power of two with amax / scale <= 448, floor 1e-10) and e4m3 codes of
+ * x / scale.  With terms == 2 a second plane holds the residual
+ * x - code * scale quantised the same way (activation = plane 0 + plane 1).
+ * x [rows,cols] bf16/f16 -> q [terms][rows,cols] e4m3, s: 32-bit words
+ * [terms][ceil(cols/128)][rows]; byte (g & 3) of word [g >> 2][row] is the
+ * scale of group g, bytes of groups past the row end are 0x7f.
+ * No reference counterpart as an op: the reference's device kernel for MXFP4
+ * keeps 16-bit activations (csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:411-471);
+ * the one-plane math is `per_token_group_fp8_quant` with group 32 and
+ * scale_ue8m0 (csrc/quantization/fp8/fp8_quant.cpp:340-387). */
+int b200moe_quant_mxfp8(const void* x, b200moe_dtype dtype, void* q, void* s,
+                        int64_t rows, int cols, int terms,
+                        b200moe_stream stream);
 
 /* Replaces `moe_gather` (csrc/moe/moe_gather.cpp:161-204; schema
  * csrc/moe/torch_bindings.cpp:78-82).

@@ -191,6 +191,37 @@ def per_token_group_fp8_quant(x, group=128, eps=1e-10, ue8m0=False):
     return q.reshape(shape), s.reshape(*shape[:-1], shape[-1] // group)
 
 
+def quant_mxfp8(x, terms=1):
+    """MX-format activation quantisation used by the block-scaled MXFP4 GEMM (the
+    OCP microscaling recipe; the reference op with the same one-plane math is
+    per_token_group_fp8_quant with group 32 and scale_ue8m0,
+    csrc/quantization/fp8/fp8_quant.cpp:340-387): per 32 values the smallest
+    power-of-two scale with amax / scale <= 448 (floor 1e-10), e4m3 codes of
+    x / scale.  With terms == 2 a second plane quantises the residual
+    x - code * scale the same way.  Returns (codes e4m3 [terms, rows, cols],
+    scale bytes uint8 [terms, rows, cols/32])."""
+    rows, cols = x.shape
+    v = x.float().reshape(rows, cols // 32, 32)
+    qs, ss = [], []
+    for _ in range(terms):
+        amax = v.abs().amax(dim=-1)
+        m, e = torch.frexp((amax / FP8_MAX).clamp(min=1e-10))   # = m * 2^e, m in [0.5, 1)
+        exp = torch.where(m == 0.5, e - 1, e)                    # ceil(log2(.)), exactly
+        sc = torch.exp2(exp.float()).unsqueeze(-1)
+        q = (v * (1.0 / sc)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+        v = v - q.float() * sc
+        qs.append(q.reshape(rows, cols))
+        ss.append((exp + 127).to(torch.uint8))
+    return torch.stack(qs), torch.stack(ss)
+
+
+def dequant_mxfp8(q, scale_u8):
+    """Sum of the planes of quant_mxfp8: q [terms, rows, cols], scale_u8 [terms, rows, cols/32]."""
+    terms, rows, cols = q.shape
+    sc = torch.exp2(scale_u8.float() - 127.0)
+    return (q.float().reshape(terms, rows, cols // 32, 32) * sc.unsqueeze(-1)).sum(dim=0).reshape(rows, cols)
+
+
 def dequant_fp8_block_act(q, s):
     """vllm_xpu_kernels/moe_utils.py:143-148."""
     shape = q.shape
@@ -293,13 +324,16 @@ def fused_moe_staged(x, w13_deq, w13_bias, w2_deq, w2_bias, topk_weights, topk_i
     (vllm_xpu_kernels/fused_moe_interface.py:328-419 with the qdq semantics of
     vllm_xpu_kernels/moe_utils.py:236-403): permute -> GEMM1 (fp32 accumulate,
     rounded to x.dtype) -> gated activation -> [per-1x128 e4m3 quant-dequant of
-    the activations when act_quant] -> GEMM2 -> weighted gather in fp32.
+    the activations when act_quant; per-32 MX quant-dequant with one or two
+    planes when act_quant is "mxfp8" / "mxfp8x2"] -> GEMM2 -> weighted gather in fp32.
     w13_deq [E,2I,H] / w2_deq [E,H,I] are the dequantised weights in fp32."""
     T, H = x.shape
     dt = x.dtype
     remapped, _, rows, row_map = remap_hidden_states(x, None, topk_ids, expert_map, num_experts)
     a1 = remapped.float()
-    if act_quant:
+    if act_quant in ("mxfp8", "mxfp8x2"):
+        a1 = dequant_mxfp8(*quant_mxfp8(remapped, 2 if act_quant == "mxfp8x2" else 1))
+    elif act_quant:
         q, s = per_token_group_fp8_quant(remapped)
         a1 = dequant_fp8_block_act(q, s)
     g1 = grouped_gemm(a1, w13_deq, w13_bias, rows, dt)
@@ -313,7 +347,9 @@ def fused_moe_staged(x, w13_deq, w13_bias, w2_deq, w2_bias, topk_weights, topk_i
     else:
         act = swigluoai_and_mul(g1.float(), alpha, limit).to(dt)
     a2 = act.float()
-    if act_quant:
+    if act_quant in ("mxfp8", "mxfp8x2"):
+        a2 = dequant_mxfp8(*quant_mxfp8(act, 2 if act_quant == "mxfp8x2" else 1))
+    elif act_quant:
         q, s = per_token_group_fp8_quant(act)
         a2 = dequant_fp8_block_act(q, s)
     g2 = grouped_gemm(a2, w2_deq, w2_bias, rows, dt)

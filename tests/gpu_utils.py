@@ -54,8 +54,8 @@ def remap(hidden, scales, topk_ids, expert_map, total_experts, local_experts):
 
 
 def grouped_gemm(a, a_scale, w, w_scale, bias, rows, N, K, layout=0, epilogue=0, impl=0,
-                 out_dtype=torch.bfloat16, clamp=0.0):
-    M = a.shape[0]
+                 out_dtype=torch.bfloat16, clamp=0.0, rows_out=None):
+    M = a.shape[0] if rows_out is None else rows_out
     E = rows.numel()
     n_out = N // 2 if epilogue else N
     d = torch.full((M, n_out), float("nan"), dtype=out_dtype, device=DEV)
@@ -73,3 +73,19 @@ def random_rows(E, total, gen, zero_frac=0.25):
     r = torch.floor(w / w.sum() * total).long()
     r[int(torch.argmax(w))] += total - int(r.sum())
     return r.to(torch.int32)
+
+
+def quant_mxfp8(x, terms=1):
+    """x [rows, cols] bf16/f16 -> (e4m3 codes [terms * rows, cols], int32 scale words
+    [terms, ceil(cols/128), rows]) as the block-scaled GEMM takes them."""
+    rows, cols = x.shape
+    q = torch.empty(terms * rows, cols, dtype=torch.float8_e4m3fn, device=DEV)
+    s = torch.full((terms, (cols + 127) // 128, rows), -1, dtype=torch.int32, device=DEV)
+    torch.ops._C.b200_quant_mxfp8(x, q, s)
+    return q, s
+
+
+def mx_scale_bytes(s, cols):
+    """int32 scale words [terms, nkb, rows] -> uint8 [terms, rows, 4 * nkb] (group order)."""
+    terms, nkb, rows = s.shape
+    return s.cpu().view(torch.uint8).reshape(terms, nkb, rows, 4).permute(0, 2, 1, 3).reshape(terms, rows, 4 * nkb)

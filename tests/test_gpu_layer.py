@@ -15,12 +15,13 @@ pytestmark = pytest.mark.gpu
 TOL = {"bf16": 2e-2, "fp8block": 5e-2, "mxfp4": 1e-1}
 
 
-def _run_layer(native, cfg, w, x, tw, ids, E_local=None, ep_rank=0, ep_size=1, fuse=False, clamp=None):
+def _run_layer(native, cfg, w, x, tw, ids, E_local=None, ep_rank=0, ep_size=1, fuse=False, clamp=None,
+               mx=None):
     w13, s13, w2, s2 = wl.to_op_layout(cfg, w)
     mv = lambda t: t.to(DEV) if t is not None else None
     layer = native.XpuFusedMoe(mv(w13), mv(s13), mv(w["w13_bias"]), mv(w2), mv(s2), mv(w["w2_bias"]),
                                cfg.K, cfg.activation, E_local or cfg.E, ep_rank=ep_rank, ep_size=ep_size,
-                               gemm1_clamp_limit=clamp, fuse_activation=fuse)
+                               gemm1_clamp_limit=clamp, fuse_activation=fuse, mxfp4_activations=mx)
     out = torch.empty(x.shape, dtype=torch.bfloat16, device=DEV)
     layer.apply(out, x.to(DEV), tw.to(DEV), ids.to(DEV))
     return out.cpu()
@@ -73,6 +74,33 @@ def test_layer_against_oracle(native, name, dims, T):
     # the fused-activation path computes the same layer
     out_f = _run_layer(native, cfg, w, x, tw, ids, fuse=True)
     torch.testing.assert_close(out_f.float(), ref.float(), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("T", [1, 20, 300])
+def test_layer_mxfp4_activation_modes(native, T):
+    """MXFP4 weights: the 16-bit-activation path (the reference's w4a16) and the
+    two-plane block-scaled path against the w4a16 oracle at the bf16 tolerance
+    (absolute part relative to the largest output);
+    the one-plane path against an oracle that quantises the activations the
+    same way, and against the w4a16 oracle at the MXFP4 tolerance relative to
+    the largest output."""
+    cfg = wl.scaled(wl.CONFIGS["cfg5_gptoss_mxfp4"], H=576, I=704, E=16)
+    w = wl.make_weights(cfg, seed=3)
+    x, logits, bias = wl.make_inputs(cfg, T, seed=3)
+    tw, ids = wl.route_cpu(cfg, logits, bias)
+    d13, d2 = wl.dequant_weights(cfg, w)
+    ref16 = to.fused_moe_staged(x, d13, w["w13_bias"], d2, w["w2_bias"], tw, ids, cfg.E, activation=cfg.activation)
+    ref_mx = to.fused_moe_staged(x, d13, w["w13_bias"], d2, w["w2_bias"], tw, ids, cfg.E,
+                                 activation=cfg.activation, act_quant="mxfp8")
+    scale = float(ref16.float().abs().max())
+    for fuse in (False, True):
+        o16 = _run_layer(native, cfg, w, x, tw, ids, fuse=fuse, mx="bf16")
+        torch.testing.assert_close(o16.float(), ref16.float(), rtol=2e-2, atol=2e-2 * max(1.0, scale))
+        ox2 = _run_layer(native, cfg, w, x, tw, ids, fuse=fuse, mx="mxfp8x2")
+        torch.testing.assert_close(ox2.float(), ref16.float(), rtol=2e-2, atol=2e-2 * max(1.0, scale))
+        omx = _run_layer(native, cfg, w, x, tw, ids, fuse=fuse, mx="mxfp8")
+        torch.testing.assert_close(omx.float(), ref_mx.float(), rtol=3e-2, atol=3e-2 * max(1.0, scale))
+        torch.testing.assert_close(omx.float(), ref16.float(), rtol=1e-1, atol=1e-1 * scale)
 
 
 def test_layer_expert_parallel_masks_sum_to_the_full_layer(native):

@@ -163,6 +163,68 @@ group_quant_fp8_scalar_kernel(const T* __restrict__ x, uint8_t* __restrict__ q,
     q[g * group + i] = f32_to_e4m3(fminf(fmaxf(__fmul_rn(to_f32<T>(xg[i]), inv), -448.f), 448.f));
 }
 
+// MX-format activation quantisation: per 32 consecutive values one power-of-two
+// scale 2^(b-127) (stored as the e8m0 byte b, the smallest power of two with
+// amax / scale <= 448) and e4m3 codes of x / scale.  With terms == 2 a second
+// plane holds the residual x - code * scale quantised the same way, so that the
+// two planes together carry about 8 significant bits.
+// Layouts: codes [terms][rows][cols]; scales as 32-bit words [terms][ceil(cols/128)]
+// [rows], byte (g & 3) of word [g >> 2][row] for group g (so the GEMM reads one
+// coalesced word per row and 128-wide K block); bytes of groups past the row end
+// are 0x7f (2^0).  A lane owns 8 values, four lanes one group; one block per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_mxfp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ s,
+                   int64_t rows, int cols, int terms) {
+  const int64_t r = blockIdx.x;
+  const T* xr = x + r * (int64_t)cols;
+  const int nvec = cols / 8;
+  const int num_kb = (cols + 127) / 128;
+  const int64_t q_plane = rows * (int64_t)cols;
+  const int64_t s_plane = (int64_t)num_kb * rows * 4;
+  for (int j0 = (threadIdx.x & ~31); j0 < nvec; j0 += blockDim.x) {
+    const int j = j0 + (threadIdx.x & 31);
+    const bool active = j < nvec;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (active) {
+      const vec16 in = ld16(xr + (int64_t)j * 8);
+      const T* e = reinterpret_cast<const T*>(&in);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = to_f32<T>(e[i]);
+    }
+    const int64_t s_off = (((int64_t)(j >> 4)) * rows + r) * 4 + ((j >> 2) & 3);
+    for (int term = 0; term < terms; ++term) {
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      // smallest power of two >= amax / 448 (floor 1e-10)
+      const float sc = ceil_pow2(__fdiv_rn(amax, 448.f));
+      const uint32_t sbyte = (__float_as_uint(sc) >> 23) & 0xffu;
+      if (active) {
+        if ((j & 3) == 0) s[term * s_plane + s_off] = (uint8_t)sbyte;
+        const float inv = __fdiv_rn(1.0f, sc);
+        alignas(8) uint8_t o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          o[i] = f32_to_e4m3(fminf(fmaxf(__fmul_rn(v[i], inv), -448.f), 448.f));
+          v[i] = __fsub_rn(v[i], __fmul_rn(e4m3_to_f32(o[i]), sc));  // residual for the next plane
+        }
+        *reinterpret_cast<uint2*>(q + term * q_plane + r * (int64_t)cols + (int64_t)j * 8) =
+            *reinterpret_cast<uint2*>(o);
+      }
+    }
+  }
+  const int pad = 4 * num_kb - cols / 32;
+  if ((int)threadIdx.x < pad * terms) {
+    const int term = threadIdx.x / pad, g = cols / 32 + threadIdx.x % pad;
+    s[term * s_plane + (((int64_t)(g >> 2)) * rows + r) * 4 + (g & 3)] = 0x7f;
+  }
+}
+
 // out[t, :] = sum_k w[t,k] * moe_out[row_map[t,k], :], fp32, k ascending.
 // kWeighted = false is moe_sum: slot (t,k) reads row t*K+k of src and is skipped
 // when its id is negative or maps to a negative entry of `map`.
@@ -353,5 +415,23 @@ extern "C" int b200moe_moe_sum(void* out, const void* in, b200moe_dtype dtype, i
             expert_map, hidden, topk, vec_ok);
   });
   B200_LAUNCH_OK("topk_reduce_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_quant_mxfp8(const void* x, b200moe_dtype dtype, void* q, void* s, int64_t rows,
+                                   int cols, int terms, b200moe_stream stream) {
+  B200_CHECK_ARG(dtype == B200MOE_BF16 || dtype == B200MOE_F16, "quant_mxfp8: input must be bfloat16 or float16");
+  B200_CHECK_ARG(rows >= 0 && cols >= 0 && cols % 32 == 0, "quant_mxfp8: the row length must be a multiple of 32");
+  B200_CHECK_ARG(terms == 1 || terms == 2, "quant_mxfp8: terms must be 1 or 2");
+  if (rows == 0 || cols == 0) return B200MOE_OK;
+  B200_CHECK_ARG(x && q && s, "quant_mxfp8: null pointer");
+  B200_CHECK_ARG(aligned16(x) && (((uintptr_t)q & 7) == 0), "quant_mxfp8: buffers must be 16-byte aligned");
+  if (dtype == B200MOE_BF16)
+    quant_mxfp8_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, as_stream(stream)>>>(
+        (const __nv_bfloat16*)x, (uint8_t*)q, (uint8_t*)s, rows, cols, terms);
+  else
+    quant_mxfp8_kernel<__half><<<(unsigned)rows, 256, 0, as_stream(stream)>>>(
+        (const __half*)x, (uint8_t*)q, (uint8_t*)s, rows, cols, terms);
+  B200_LAUNCH_OK("quant_mxfp8_kernel");
   return B200MOE_OK;
 }

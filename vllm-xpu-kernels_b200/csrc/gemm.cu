@@ -7,6 +7,7 @@
 namespace b200moe {
 int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st);
 int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st);
+int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st);
 int grouped_gemm_check(const b200moe_gemm_args* a, cudaStream_t st);
 }  // namespace b200moe
 
@@ -20,7 +21,8 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
                  a->k, a->num_experts);
   B200_CHECK_ARG(a->d_dtype == B200MOE_BF16 || a->d_dtype == B200MOE_F16,
                  "grouped_gemm: ptr_D must be bfloat16 or float16");
-  const bool a_fp8 = a->a_dtype == B200MOE_FP8_E4M3;
+  const bool a_x2 = a->a_dtype == B200MOE_FP8_E4M3_X2;
+  const bool a_fp8 = a->a_dtype == B200MOE_FP8_E4M3 || a_x2;
   B200_CHECK_ARG(a_fp8 || a->a_dtype == a->d_dtype,
                  "grouped_gemm: ptr_A must be fp8 (with scales) or have ptr_D's dtype");
   switch (a->w_format) {
@@ -44,16 +46,22 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
     case B200MOE_W_MXFP4_NK:
       B200_CHECK_ARG(a->w_scale != nullptr, "w8a16 grouped gemm must have scales");
       B200_CHECK_ARG(a->k % 32 == 0, "group_size must be 32, 64, 128 or 256");
-      B200_CHECK_ARG(!a_fp8, "grouped_gemm: fp8 activations need block-scaled fp8 weights");
+      B200_CHECK_ARG(!a_fp8 || a->a_scale != nullptr,
+                     "grouped_gemm: fp8 activations with MXFP4 weights need the e8m0 scale words "
+                     "[planes][ceil(K / 128)][M] of b200moe_quant_mxfp8");
       break;
     default:
       return fail(B200MOE_E_BADARG, "grouped_gemm: unknown weight format %d", (int)a->w_format);
   }
+  B200_CHECK_ARG(!a_x2 || a->w_format == B200MOE_W_MXFP4_NK,
+                 "grouped_gemm: two-plane fp8 activations need MXFP4 weights");
   B200_CHECK_ARG(a->epilogue == B200MOE_EPI_NONE || a->n % 2 == 0,
                  "grouped_gemm: a gated epilogue needs an even N");
   if (a->m == 0 || a->n == 0) return B200MOE_OK;
   B200_CHECK_ARG(a->a && a->w && a->d && a->rows_per_expert, "grouped_gemm: null pointer");
   cudaStream_t st = as_stream(stream);
+  // MXFP8 activations exist on the block-scaled tensor-core path only.
+  if (a->w_format == B200MOE_W_MXFP4_NK && a_fp8) return grouped_gemm_tc_mx(a, st);
   if (a->impl == 2) return grouped_gemm_check(a, st);
   int rc = (a->w_format == B200MOE_W_MXFP4_NK) ? grouped_gemm_tc_dq(a, st) : grouped_gemm_tc(a, st);
   if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) return grouped_gemm_check(a, st);

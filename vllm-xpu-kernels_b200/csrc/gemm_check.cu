@@ -221,7 +221,7 @@ gemm_check_kernel(CheckArgs g, bool a_fp8) {
 
 int grouped_gemm_check(const b200moe_gemm_args* a, cudaStream_t st) {
   CheckArgs g;
-  g.a = a->a; g.a_scale = a->a_scale; g.w = a->w; g.w_scale = a->w_scale; g.bias = a->bias;
+  g.a = a->a; g.a_scale = reinterpret_cast<const float*>(a->a_scale); g.w = a->w; g.w_scale = a->w_scale; g.bias = a->bias;
   g.d = a->d; g.rows_per_expert = a->rows_per_expert; g.m = a->m; g.n = a->n; g.k = a->k;
   g.num_experts = a->num_experts; g.fmt = a->w_format; g.epi = a->epilogue;
   g.alpha = a->act_alpha; g.limit = a->act_limit; g.clamp_limit = a->clamp_limit;

@@ -428,7 +428,7 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
 
   const int kpb = a_fp8 ? 128 : 64;
   TcParams p;
-  p.a_scale = a->a_scale; p.w_scale = reinterpret_cast<const float*>(a->w_scale);
+  p.a_scale = reinterpret_cast<const float*>(a->a_scale); p.w_scale = reinterpret_cast<const float*>(a->w_scale);
   p.bias = a->bias; p.d = a->d; p.rows_per_expert = a->rows_per_expert; p.status = a->status;
   p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
   p.n_tiles = (a->n + kFeat - 1) / kFeat;

@@ -48,8 +48,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // `kWaitBudgetCycles` clock cycles or until `*abort_flag` becomes non-zero.
 // Returns false (and raises the flag) when it gave up.
 constexpr long long kWaitBudgetCycles = 2000000000LL;  // roughly one second
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag, bool spin = false) {
+  if (spin) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_test_wait(bar, parity)) {
+      if ((++spins & 0xfff) == 0) {
+        if (*abort_flag != 0) return false;
+        if (clock64() - t0 > kWaitBudgetCycles) {
+          *abort_flag = 1;
+          return false;
+        }
+      }
+    }
+    return true;
+  }
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -63,6 +89,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     }
   }
   return true;
+}
+
+// Warp-level wait: lane 0 polls (sleeping `sleep_ns` between polls when non-zero),
+// the other lanes wait at the warp barrier, which also orders their later reads
+// after the barrier's completion.  Keeps the polling traffic of long waits off
+// the shared-memory pipeline that other warps need.  Same budget and abort rules
+// as mbar_wait; every lane gets the result.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,
+                                               volatile int* abort_flag, uint32_t sleep_ns) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0 && !mbar_try_wait(bar, parity)) {
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+      if (sleep_ns) __nanosleep(sleep_ns);
+      if ((++spins & 0x3f) == 0) {
+        if (*abort_flag != 0) { ok = false; break; }
+        if (clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1; ok = false; break; }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();
+  return ok;
 }
 
 // ---- TMA ---------------------------------------------------------------------
@@ -136,6 +186,25 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 
+// 32 lanes x N consecutive 32-bit columns written from registers: thread i
+// writes lane (base lane + i).
+__device__ __forceinline__ void tmem_st_32x1(uint32_t taddr, uint32_t r0) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(r0) : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x2(uint32_t taddr, uint32_t r0, uint32_t r1) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(r0), "r"(r1)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2,
+                                             uint32_t r3) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0),
+               "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // ---- UMMA ------------------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version bit set.
 // lbo / sbo in bytes (16-byte units once encoded).
@@ -176,6 +245,26 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
         : "memory");
   }
 }
+// Instruction descriptor of tcgen05.mma kind::mxf8f6f4.block_scale with e8m0
+// scales: a_fmt / b_fmt 0 = e4m3, 1 = e5m2, 3 = e2m3, 4 = e3m2, 5 = e2m1; both
+// operands K-major; fp32 accumulate.  The scale byte (0..3) of the 32-bit scale
+// column each operand uses is OR-ed in per instruction: a at bit 29, b at bit 4.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_fmt, uint32_t b_fmt, uint32_t M,
+                                                     uint32_t N) {
+  return (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24);
+}
+// D[tmem_d] (+)= (A * 2^(sfa-127)) * (B * 2^(sfb-127)) over K = 32; sfa / sfb are
+// tensor-memory addresses of the scale columns (one byte per row, replicated in
+// the four lane quarters).
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                        uint32_t idesc, uint32_t accumulate, uint32_t sfa,
+                                        uint32_t sfb) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
 // Makes `bar` receive one arrival when all MMAs issued so far by this thread
 // have completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -197,6 +286,9 @@ __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+  asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
 __device__ __forceinline__ void sts16(uint32_t addr, uint16_t v) {
   asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
 }
@@ -208,6 +300,37 @@ __device__ __forceinline__ float4 lds128f(uint32_t addr) {
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// 16-byte asynchronous copy global -> shared; only the first `src_bytes` are read,
+// the rest of the 16 bytes is zero-filled.  Both addresses 16-byte aligned.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+// One arrival on `bar` once all cp.async copies this thread issued so far have
+// landed (the arrival is part of the barrier's expected count).
+__device__ __forceinline__ void cp_async_mbar_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {

@@ -59,9 +59,28 @@ void per_token_group_fp8_quant(const at::Tensor& input, at::Tensor& output_q, at
       output_s.stride(0), output_s.stride(1), current_stream()));
 }
 
+// x [rows, cols] bf16/f16 -> q e4m3 [planes * rows, cols], s int32 [planes, ceil(cols/128), rows]
+// (four e8m0 bytes per word); planes = 1, or 2 with the residual plane.
+void b200_quant_mxfp8(const at::Tensor& input, at::Tensor& output_q, at::Tensor& output_s) {
+  check_cuda(input, "input");
+  TORCH_CHECK(input.is_contiguous() && output_q.is_contiguous() && output_s.is_contiguous());
+  TORCH_CHECK(input.dim() == 2 && output_q.dim() == 2 && output_s.dim() == 3);
+  const int64_t rows = input.size(0), cols = input.size(1), planes = output_s.size(0);
+  TORCH_CHECK(planes == 1 || planes == 2, "b200_quant_mxfp8: one or two planes");
+  TORCH_CHECK(output_q.scalar_type() == at::kFloat8_e4m3fn && output_q.size(0) == planes * rows &&
+              output_q.size(1) == cols, "b200_quant_mxfp8: output_q must be float8_e4m3fn [planes * rows, cols]");
+  TORCH_CHECK(output_s.scalar_type() == at::kInt && output_s.size(1) == (cols + 127) / 128 &&
+              output_s.size(2) == rows, "b200_quant_mxfp8: output_s must be int32 [planes, ceil(cols / 128), rows]");
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(b200moe_quant_mxfp8(input.data_ptr(), float_dtype(input, "b200_quant_mxfp8"),
+                                   output_q.data_ptr(), output_s.data_ptr(), rows, (int)cols, (int)planes,
+                                   current_stream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(_C, m) {
+  m.def("b200_quant_mxfp8(Tensor input, Tensor! output_q, Tensor! output_s) -> ()");
   m.def("silu_and_mul(Tensor! result, Tensor input) -> ()");
   m.def("swigluoai_and_mul(Tensor! out, Tensor input, float alpha=1.702, float limit=7.0) -> ()");
   m.def(
@@ -76,6 +95,7 @@ TORCH_LIBRARY_IMPL(_C, CUDA, m) {
   m.impl("silu_and_mul", &silu_and_mul);
   m.impl("swigluoai_and_mul", &swigluoai_and_mul);
   m.impl("per_token_group_fp8_quant", &per_token_group_fp8_quant);
+  m.impl("b200_quant_mxfp8", &b200_quant_mxfp8);
 }
 
 B200_REGISTER_EXTENSION(_C)

@@ -64,7 +64,8 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   TORCH_CHECK(B_E == num_experts, "ptr_B.size(0) must match num_experts");
   TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
               rows_per_expert.numel() == num_experts, "rows_per_expert must be int32 [num_experts]");
-  TORCH_CHECK(A_total_M == D_total_M, "ptr_A.size(0) must match ptr_D.size(0)");
+  TORCH_CHECK(A_total_M == D_total_M || (is_B_mxfp4 && A_dtype == at::kFloat8_e4m3fn && A_total_M == 2 * D_total_M),
+              "ptr_A.size(0) must match ptr_D.size(0)");
   TORCH_CHECK(A_K == B_K && B_K == K, "ptr_A K dimension must match ptr_B logical K dimension and K");
   TORCH_CHECK(B_N == N && D_N == n_out, "ptr_B logical N dimension must match ptr_D N dimension and N");
   if (ptr_bias.has_value()) {
@@ -101,13 +102,26 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   b200moe_gemm_args g = {};
   g.a = ptr_A.data_ptr();
   if (A_dtype == at::kFloat8_e4m3fn) {
-    TORCH_CHECK(is_B_fp8_block && ptr_A_scale.has_value(),
-                "fp8 activations need block-scaled fp8 weights and ptr_A_scale");
-    TORCH_CHECK(ptr_A_scale->scalar_type() == at::kFloat && ptr_A_scale->is_contiguous() &&
-                ptr_A_scale->dim() == 2 && ptr_A_scale->size(0) == A_total_M &&
-                ptr_A_scale->size(1) == K / 128, "ptr_A_scale must be float32 [Total_M, K / 128]");
+    TORCH_CHECK((is_B_fp8_block || is_B_mxfp4) && ptr_A_scale.has_value(),
+                "fp8 activations need block-scaled fp8 or mxfp4 weights and ptr_A_scale");
     g.a_dtype = B200MOE_FP8_E4M3;
-    g.a_scale = ptr_A_scale->data_ptr<float>();
+    if (is_B_mxfp4) {
+      // ptr_A [planes * Total_M, K] (planes = 1 or 2, the second the residual), scales
+      // int32 [planes, ceil(K / 128), Total_M]: the outputs of _C::b200_quant_mxfp8.
+      const int64_t planes = A_total_M / D_total_M;
+      TORCH_CHECK((planes == 1 || planes == 2) && planes * D_total_M == A_total_M,
+                  "ptr_A must hold one or two planes of ptr_D.size(0) rows");
+      TORCH_CHECK(ptr_A_scale->scalar_type() == at::kInt && ptr_A_scale->is_contiguous() &&
+                  ptr_A_scale->dim() == 3 && ptr_A_scale->size(0) == planes &&
+                  ptr_A_scale->size(1) == (K + 127) / 128 && ptr_A_scale->size(2) == D_total_M,
+                  "ptr_A_scale must be int32 [planes, ceil(K / 128), Total_M]");
+      if (planes == 2) g.a_dtype = B200MOE_FP8_E4M3_X2;
+    } else {
+      TORCH_CHECK(ptr_A_scale->scalar_type() == at::kFloat && ptr_A_scale->is_contiguous() &&
+                  ptr_A_scale->dim() == 2 && ptr_A_scale->size(0) == A_total_M &&
+                  ptr_A_scale->size(1) == K / 128, "ptr_A_scale must be float32 [Total_M, K / 128]");
+    }
+    g.a_scale = ptr_A_scale->data_ptr();
   } else {
     TORCH_CHECK(A_dtype == at::kBFloat16 || A_dtype == at::kHalf, "ptr_A must be bfloat16, float16 or float8_e4m3fn");
     TORCH_CHECK(A_dtype == ptr_D.scalar_type(), "ptr_A and ptr_D must have the same dtype");
@@ -122,7 +136,7 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   g.d = ptr_D.data_ptr();
   g.d_dtype = ptr_D.scalar_type() == at::kBFloat16 ? B200MOE_BF16 : B200MOE_F16;
   g.rows_per_expert = rows_per_expert.data_ptr<int32_t>();
-  g.m = A_total_M; g.n = (int)N; g.k = (int)K; g.num_experts = (int)num_experts;
+  g.m = D_total_M; g.n = (int)N; g.k = (int)K; g.num_experts = (int)num_experts;
   g.epilogue = (b200moe_epilogue)epilogue;
   g.act_alpha = (float)alpha; g.act_limit = (float)limit; g.clamp_limit = (float)clamp_limit;
   g.status = nullptr;

@@ -146,6 +146,19 @@ class XpuFusedMoe:
     activation inside the first grouped GEMM's epilogue instead of a separate
     pass over ``[T*K, 2I]``; the default picks it where the tensor-core kernel
     of the recipe has that epilogue (MXFP4 with SwigluOAI).
+
+    ``mxfp4_activations`` (not in the reference; keyword only) chooses what the
+    MXFP4 grouped GEMMs multiply the 4-bit weights with:
+    ``"mxfp8x2"`` (default where the shapes allow it: hidden and intermediate
+    sizes multiples of 64) quantises the activations to two MXFP8 planes (e4m3
+    codes with one power-of-two scale per 32 values, plus the residual
+    quantised the same way) and runs the block-scaled tensor-core instruction
+    on both: 16-bit-like activation accuracy with nothing dequantised by CUDA
+    cores; ``"mxfp8"`` uses one plane (about 3 % activation rounding error, like
+    the reference's ``VLLM_XPU_FUSED_MOE_USE_MXFP4_FP8`` recipe, which also
+    selects it); ``"bf16"`` keeps 16-bit activations exactly as the reference's
+    device kernel does (w4a16) and dequantises the weights on the way into the
+    tensor cores.
     """
 
     def __init__(
@@ -165,6 +178,7 @@ class XpuFusedMoe:
         gemm1_clamp_limit: Optional[float] = None,
         *,
         fuse_activation: Optional[bool] = None,
+        mxfp4_activations: Optional[str] = None,
     ):
         assert w13.is_contiguous() and w2.is_contiguous()
         _require_native()
@@ -213,6 +227,18 @@ class XpuFusedMoe:
             # fused where the tensor-core kernel of this recipe has the epilogue
             fuse_activation = self.is_mxfp4 and self._act_kind == "swigluoai"
         self.fuse_activation = fuse_activation
+        if mxfp4_activations is None:
+            mxfp4_activations = "mxfp8" if self.recipe == "mxfp4_fp8" else "mxfp8x2"
+        if mxfp4_activations not in ("mxfp8x2", "mxfp8", "bf16"):
+            raise ValueError("mxfp4_activations must be 'mxfp8x2', 'mxfp8' or 'bf16', "
+                             f"got {mxfp4_activations!r}")
+        self.mx_planes = 2 if mxfp4_activations == "mxfp8x2" else 1
+        hidden = w2.shape[-2] if is_mxfp4 else 0
+        self.mx_acts = bool(is_mxfp4 and mxfp4_activations != "bf16"
+                            and hidden % 64 == 0 and self.inter_size % 64 == 0
+                            and hidden >= 128 and self.inter_size >= 128)
+        if self.mx_acts and self._act_kind == "silu" and fuse_activation:
+            raise ValueError("the block-scaled MXFP4 GEMM has no fused SiLU epilogue")
         if self._act_kind == "silu":
             self.act_func = torch.ops._C.silu_and_mul
         else:
@@ -237,6 +263,16 @@ class XpuFusedMoe:
               expert_map=None, a1q_scale=None):
         self._apply_kernel(output, hidden_states, topk_weights, topk_ids,
                            expert_map, a1q_scale)
+
+    def _quant_mx(self, x):
+        """[rows, cols] 16-bit -> (e4m3 codes [planes * rows, cols], int32 scale words
+        [planes, ceil(cols / 128), rows]); planes = 2 adds the residual plane."""
+        rows, cols = x.shape
+        planes = self.mx_planes
+        q = torch.empty((planes * rows, cols), dtype=torch.float8_e4m3fn, device=x.device)
+        s = torch.empty((planes, (cols + 127) // 128, rows), dtype=torch.int32, device=x.device)
+        torch.ops._C.b200_quant_mxfp8(x, q, s)
+        return q, s
 
     # The stages below are the reference's eight steps (:328-419); what differs
     # is inside the ops and, for block fp8, that activations really are
@@ -281,6 +317,8 @@ class XpuFusedMoe:
                 local_experts_num=self.local_experts_num)
 
         a_scale1 = remapped_scales if quant_acts else None
+        if self.mx_acts:
+            remapped, a_scale1 = self._quant_mx(remapped)
         clamp = float(self.gemm1_clamp_limit) if (self.gemm1_clamp_limit is not None
                                                    and self.gemm1_clamp_limit > 0) else 0.0
 
@@ -310,6 +348,8 @@ class XpuFusedMoe:
         gemm2_output = torch.empty((num_moe_inputs, hidden_size), dtype=output.dtype, device=dev)
         if quant_acts:
             act_q, gemm2_act_scale = quant_act_xpu(act_output, self.recipe)
+        elif self.mx_acts:
+            act_q, gemm2_act_scale = self._quant_mx(act_output)
         else:
             act_q, gemm2_act_scale = act_output, None
         torch.ops._xpu_C.b200_grouped_gemm(
