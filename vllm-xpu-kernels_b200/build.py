@@ -33,6 +33,8 @@ SHIMS = {"_C": "c_ops.cpp", "_moe_C": "moe_ops.cpp", "_xpu_C": "xpu_ops.cpp"}
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
               "-std=c++17", "-Xcompiler", "-fPIC", "--threads", "2"]
+# extra nvcc flags for experiments (e.g. -DB200_MX_PROF); a change needs a clean rebuild
+NVCC_FLAGS += os.environ.get("B200MOE_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

@@ -37,6 +37,21 @@
 #include "gemm_tc_common.cuh"
 #include "sm100_ptx.cuh"
 
+// Cycle accounting of the roles of CTA 0 (printed at kernel end); compiled in
+// only with -DB200_MX_PROF, for experiments.
+#ifdef B200_MX_PROF
+#include <stdio.h>
+#define MX_PROF_DECL(...) long long __VA_ARGS__
+#define MX_PROF_T(var) const long long var = clock64()
+#define MX_PROF_ADD(acc, t0) acc += clock64() - (t0)
+#define MX_PROF_PRINT(...) if (blockIdx.x == 0) printf(__VA_ARGS__)
+#else
+#define MX_PROF_DECL(...)
+#define MX_PROF_T(var)
+#define MX_PROF_ADD(acc, t0)
+#define MX_PROF_PRINT(...)
+#endif
+
 namespace b200moe {
 namespace {
 
@@ -62,12 +77,12 @@ struct MxParams {
   int tail;        // 1: the last K block is partial and comes through the byte map
   int stages, stage_bytes;
   int sfw_bytes;   // bytes of one staged weight-scale buffer
+  int raw_shared;  // 1: one buffer for the partial K block after the staging buffers, 0: one per stage
   uint32_t tmem_cols;
   uint32_t idesc;
   int out_f16;
   int swiglu;      // 1: D[m, f/2] = swigluoai(acc[m,f], acc[m,f+1]) for even f
   float alpha, limit, clamp_limit;
-  int debug;       // experiment switches (B200MOE_DEBUG), 0 in normal use
 };
 
 struct MxCtrl {
@@ -80,10 +95,12 @@ struct MxCtrl {
   uint64_t sfw_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int tile_start[kMaxExperts + 1];
-  int row_start[kMaxExperts + 1];
   alignas(16) uint16_t xpose[4][32 * 32];
 };
+// Shared memory after the pipeline stages: one buffer for the partial K block
+// (when the stages do not carry their own), MxCtrl, the tile walk's prefix arrays
+// (2 x (experts + 1) ints) and two weight-scale staging buffers.
+__host__ __device__ inline int mx_prefix_bytes(int num_experts) { return ((num_experts + 1) * 4 + 15) & ~15; }
 
 // Weight scales of a tile's rows: one contiguous piece of the scale tensor,
 // copied to staging buffer (seq & 1) asynchronously by the 128 feeder threads
@@ -128,14 +145,18 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
   const int stage_bytes = p.stage_bytes;
-  MxCtrl* ctrl = reinterpret_cast<MxCtrl*>(smem + stages * stage_bytes);
-  uint8_t* sfw = smem + stages * stage_bytes + ((sizeof(MxCtrl) + 15) & ~(size_t)15);
+  uint8_t* raw_one = smem + stages * stage_bytes;   // used when p.raw_shared (1024-byte aligned)
+  uint8_t* ctrl_at = raw_one + (p.raw_shared ? kMxRawBytes : 0);
+  MxCtrl* ctrl = reinterpret_cast<MxCtrl*>(ctrl_at);
+  uint8_t* after = ctrl_at + ((sizeof(MxCtrl) + 15) & ~(size_t)15);
+  int* tile_start_w = reinterpret_cast<int*>(after);
+  int* row_start_w = reinterpret_cast<int*>(after + mx_prefix_bytes(p.num_experts));
+  uint8_t* sfw = after + 2 * mx_prefix_bytes(p.num_experts);
   volatile int* abort_flag = &ctrl->abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (warp == 0) {
-    build_tile_prefix<BT>(p.rows_per_expert, p.num_experts, p.n_tiles, ctrl->row_start,
-                          ctrl->tile_start);
+    build_tile_prefix<BT>(p.rows_per_expert, p.num_experts, p.n_tiles, row_start_w, tile_start_w);
     if (lane == 0) {
       ptx::prefetch_tensormap(&tmap_a);
       ptx::prefetch_tensormap(&tmap_w);
@@ -164,9 +185,9 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
   ptx::tc_fence_after();
 
   const uint32_t tmem_base = ctrl->tmem_base;
-  const int total_tiles = ctrl->tile_start[p.num_experts];
-  const int* tile_start = ctrl->tile_start;
-  const int* row_start = ctrl->row_start;
+  const int* tile_start = tile_start_w;
+  const int* row_start = row_start_w;
+  const int total_tiles = tile_start[p.num_experts];
   const int tail_kb = p.tail ? p.num_kb - 1 : -1;
   const int num_st = (p.num_kb + kSub - 1) / kSub;   // stages per tile
 
@@ -176,12 +197,15 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t s = 0, ph = 0;
       int cursor = 0;
       bool ok = true;
+      MX_PROF_DECL(pw = 0, pt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         const int n0 = ti.n_tile * kFeat;
         for (int si = 0; si < num_st; ++si) {
+          MX_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          MX_PROF_ADD(pw, w0);
           uint8_t* st = smem + s * stage_bytes;
           const int kb0 = si * kSub;
           const int nsub = (p.num_kb - kb0) < kSub ? (p.num_kb - kb0) : kSub;
@@ -191,7 +215,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int kb = kb0 + sub;
             if (sub < nsub) {
               if (kb == tail_kb)
-                ptx::tma_load_3d(st + kRawOff, &tmap_raw, &ctrl->full[s], kb * 64, n0, ti.e);
+                ptx::tma_load_3d(p.raw_shared ? raw_one : st + kRawOff, &tmap_raw, &ctrl->full[s], kb * 64, n0, ti.e);
               else
                 ptx::tma_load_3d(st + sub * kMxWBytes, &tmap_w, &ctrl->full[s], kb * 128, n0, ti.e);
 #pragma unroll
@@ -203,6 +227,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (++s == (uint32_t)stages) { s = 0; ph ^= 1; }
         }
       }
+      MX_PROF_PRINT("producer: total %lld wait_empty %lld\n", clock64() - pt0, pw);
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
@@ -210,41 +235,58 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t s = 0, ph = 0, acc_it = 0;
       int cursor = 0;
       bool ok = true;
+      const uint32_t smem_base = ptx::smem_u32(smem);
+      uint32_t idesc_j[4];
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) idesc_j[j] = p.idesc | (j << 29) | (j << 4);
+      MX_PROF_DECL(mf = 0, ms = 0, ma = 0, mi = 0, mc = 0, mt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         const uint32_t a = acc_it & 1;
+        MX_PROF_T(wa0);
         if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) break;
+        MX_PROF_ADD(ma, wa0);
         ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * kNT;
         for (int si = 0; si < num_st; ++si) {
-          if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag) ||
-              !ptx::mbar_wait(&ctrl->sf_full[s], ph, abort_flag)) { ok = false; break; }
+          MX_PROF_T(w0);
+          if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
+          MX_PROF_ADD(mf, w0);
+          MX_PROF_T(w1);
+          if (!ptx::mbar_wait(&ctrl->sf_full[s], ph, abort_flag)) { ok = false; break; }
+          MX_PROF_ADD(ms, w1);
+          MX_PROF_T(w2);
           ptx::tc_fence_after();
-          const uint32_t wbase = ptx::smem_u32(smem + s * stage_bytes);
+          // Every operand descriptor of the stage is the first weight block's plus a
+          // compile-time offset (the address field counts 16-byte units).
+          const uint64_t desc0 = ptx::make_smem_desc(smem_base + s * stage_bytes, 16, 1024);
           const uint32_t sf0 = tmem_base + kSfBase + s * kSfCols;
           const int kb0 = si * kSub;
 #pragma unroll
           for (int sub = 0; sub < kSub; ++sub) {
-            if (kb0 + sub < p.num_kb && !(p.debug & 2)) {
+            if (kb0 + sub < p.num_kb) {
               // The planes' activation tiles are adjacent in the stage: one K-major
               // operand of kNT rows; their results land in adjacent column blocks.
-              const uint32_t wb = wbase + sub * kMxWBytes;
-              const uint32_t ab = wbase + kAOff + sub * kABytes;
               const uint32_t sfa = sf0 + 8 * sub;
 #pragma unroll
               for (uint32_t j = 0; j < 4; ++j) {
-                const uint64_t wdesc = ptx::make_smem_desc(wb + j * 32, 16, 1024);
-                const uint64_t adesc = ptx::make_smem_desc(ab + j * 32, 16, 1024);
-                ptx::umma_mx(tmem_base + a * kNT, wdesc, adesc, p.idesc | (j << 29) | (j << 4),
-                             (kb0 + sub > 0 || j > 0) ? 1u : 0u, sfa, sfa + 4);
+                const uint64_t wdesc = desc0 + (uint64_t)((sub * kMxWBytes + j * 32) >> 4);
+                const uint64_t adesc = desc0 + (uint64_t)((kAOff + sub * kABytes + j * 32) >> 4);
+                ptx::umma_mx(d_tmem, wdesc, adesc, idesc_j[j], (kb0 + sub > 0 || j > 0) ? 1u : 0u, sfa, sfa + 4);
               }
             }
           }
+          MX_PROF_ADD(mi, w2);
+          MX_PROF_T(w3);
           ptx::umma_commit(&ctrl->empty[s]);
+          MX_PROF_ADD(mc, w3);
           if (++s == (uint32_t)stages) { s = 0; ph ^= 1; }
         }
         if (ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
       }
+      MX_PROF_PRINT("mma: total %lld wait_full %lld wait_sf %lld wait_acc %lld issue %lld commit %lld\n",
+                    clock64() - mt0, mf, ms, ma, mi, mc);
     }
   } else if (warp < 6) {
     // ------------------------------ scale feeders ------------------------------
@@ -258,6 +300,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t s = 0, ph = 0;
     int cursor = 0, cursor_next = 0, cursor_la = 0;
     bool ok = true;
+    MX_PROF_DECL(fw = 0, fl = 0, fs = 0, ff = 0, fsw = 0, fq = 0, ft0 = clock64());
 
     // Token scales of kMxGroup K blocks: word [plane][kb][row], coalesced over the
     // lanes.  They are read two groups ahead of their use (cur <- nxt <- nx2), by a
@@ -316,7 +359,9 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t sfw_s = ptx::smem_u32(sfw + b * p.sfw_bytes);
       const int n0 = ti.n_tile * kFeat;
       for (int g = 0; g < n_groups && ok; ++g) {
+        MX_PROF_T(q0);
         if (la_valid) { fetch_b(la_ti, la_g, nx2_b); B200_MX_LA_ADVANCE(); }
+        MX_PROF_ADD(fq, q0);
 #pragma unroll
         for (int u = 0; u < kMxGroup; ++u) {
           const int kb = g * kMxGroup + u;
@@ -325,6 +370,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // Four scale bytes per row from the staged piece: two aligned words and a
             // funnel shift (rows are K/32 bytes apart, any alignment); bytes of groups
             // past the row end become 0x7f.
+            MX_PROF_T(l0);
             uint32_t wa[4];
             const int left = kgroups - 4 * kb;
             const uint32_t keep = left >= 4 ? 0xffffffffu : ((1u << (8 * left)) - 1u);
@@ -336,20 +382,24 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const uint32_t v = __funnelshift_r(lo, hi, (addr & 3u) * 8);
               wa[j] = (n0 + row < p.n) ? ((v & keep) | (0x7f7f7f7fu & ~keep)) : 0x7f7f7f7fu;
             }
+            MX_PROF_ADD(fl, l0);
             if (sub == 0) {   // the stage's scale columns and weight buffer are free again
+              MX_PROF_T(w0);
               if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag))) {
                 *abort_flag = 1; ok = false;
               }
               ptx::tc_fence_after();
+              MX_PROF_ADD(fw, w0);
             }
+            MX_PROF_T(s0);
             if (ok) {
               const uint32_t col = tmem_base + kSfBase + s * kSfCols + 8 * sub + lane_sel;
-              if (!(p.debug & 1)) {
-                ptx::tmem_st_32x4(col, wa[0], wa[1], wa[2], wa[3]);
-                if (kW == 1) ptx::tmem_st_32x1(col + 4, cur_b[u][0]);
-                else if (kW == 2) ptx::tmem_st_32x2(col + 4, cur_b[u][0], cur_b[u][kW > 1 ? 1 : 0]);
-                else ptx::tmem_st_32x4(col + 4, cur_b[u][0], cur_b[u][kW > 1 ? 1 : 0], cur_b[u][kW > 2 ? 2 : 0],
-                                       cur_b[u][kW > 3 ? 3 : 0]);
+              {
+                // eight columns at once: the weight rows' four, then the tokens' (unused ones 2^0)
+                uint32_t r8[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { r8[j] = wa[j]; r8[4 + j] = j < kW ? cur_b[u][j < kW ? j : 0] : 0x7f7f7f7fu; }
+                ptx::tmem_st_32x8(col, r8);
               }
               if (kb == tail_kb) {
                 // Spread the partial block: row ft, 64 packed bytes -> eight 16-byte
@@ -358,7 +408,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   *abort_flag = 1; ok = false;
                 } else {
                   const uint32_t st = ptx::smem_u32(smem + s * stage_bytes);
-                  const uint32_t src = st + kRawOff + ft * 64;
+                  const uint32_t src = (p.raw_shared ? ptx::smem_u32(raw_one) : st + kRawOff) + ft * 64;
                   const uint32_t dst = st + sub * kMxWBytes + (ft >> 3) * 1024 + (ft & 7) * 128;
 #pragma unroll
                   for (int c = 0; c < 4; ++c) {
@@ -369,6 +419,8 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   ptx::fence_proxy_async();
                 }
               }
+              MX_PROF_ADD(fs, s0);
+              MX_PROF_T(f0);
               if (sub == kSub - 1 || kb == p.num_kb - 1) {   // last K block of the stage
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before();
@@ -376,18 +428,24 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (lane == 0) ptx::mbar_arrive(&ctrl->sf_full[s]);
                 if (++s == (uint32_t)stages) { s = 0; ph ^= 1; }
               }
+              MX_PROF_ADD(ff, f0);
             }
           }
         }
+        MX_PROF_T(r0);
 #pragma unroll
         for (int u = 0; u < kMxGroup; ++u)
 #pragma unroll
           for (int j = 0; j < kW; ++j) { cur_b[u][j] = nxt_b[u][j]; nxt_b[u][j] = nx2_b[u][j]; }
+        MX_PROF_ADD(fsw, r0);
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&ctrl->sfw_empty[b]);
     }
 #undef B200_MX_LA_ADVANCE
+    if (warp == 2 && lane == 0)
+      MX_PROF_PRINT("feeder: total %lld wait_empty %lld lds %lld st %lld finish %lld rotate %lld fetch %lld\n",
+                    clock64() - ft0, fw, fl, fs, ff, fsw, fq);
     ptx::cp_async_wait_all();
   } else {
     // ------------------------------ epilogue ----------------------------------
@@ -478,13 +536,25 @@ int launch_mx(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& t
   auto kern = grouped_gemm_mx_kernel<BT, kTerms, kSub>;
   const uint32_t need = 2 * kTerms * BT + kMxMaxStages * 8 * kSub;
   p.tmem_cols = need <= 128 ? 128u : (need <= 256 ? 256u : 512u);
-  p.stage_bytes = kSub * (kMxWBytes + kTerms * BT * 128) + (p.tail ? kMxRawBytes : 0);
-  const int ctrl_bytes = (int)((sizeof(MxCtrl) + 15) & ~(size_t)15);
-  const int budget = 226 * 1024 - 1024 - ctrl_bytes - 2 * p.sfw_bytes;
+  // The partial K block's packed bytes get one buffer for the whole CTA when a tile
+  // has at least as many stages as the pipeline (its next use then comes after
+  // the previous one was consumed), else one per stage.
+  const int body = kSub * (kMxWBytes + kTerms * BT * 128);
+  const int fixed = 1024 + (int)((sizeof(MxCtrl) + 15) & ~(size_t)15) + 2 * mx_prefix_bytes(p.num_experts) +
+                    2 * p.sfw_bytes;
+  const int budget = 227 * 1024 - fixed;
+  const int num_st = (p.num_kb + kSub - 1) / kSub;
+  p.raw_shared = 0;
+  p.stage_bytes = body + (p.tail ? kMxRawBytes : 0);
   p.stages = budget / p.stage_bytes;
+  if (p.tail) {
+    int st_shared = (budget - kMxRawBytes) / body;
+    if (st_shared > kMxMaxStages) st_shared = kMxMaxStages;
+    if (st_shared > p.stages && num_st >= st_shared) { p.raw_shared = 1; p.stage_bytes = body; p.stages = st_shared; }
+  }
   if (p.stages > kMxMaxStages) p.stages = kMxMaxStages;
   if (p.stages < 2) return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM: tile does not fit shared memory");
-  const size_t smem = 1024 + (size_t)p.stages * p.stage_bytes + ctrl_bytes + 2 * (size_t)p.sfw_bytes;
+  const size_t smem = (size_t)fixed + (size_t)p.stages * p.stage_bytes + (p.raw_shared ? kMxRawBytes : 0);
   static size_t configured = 0;
   if (configured < smem) {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -539,11 +609,6 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
   p.swiglu = a->epilogue == B200MOE_EPI_SWIGLUOAI;
   p.alpha = a->act_alpha; p.limit = a->act_limit; p.clamp_limit = a->clamp_limit;
 
-  {
-    static int dbg = -1;
-    if (dbg < 0) { const char* e = getenv("B200MOE_DEBUG"); dbg = e ? atoi(e) : 0; }
-    p.debug = dbg;
-  }
   const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
   int bt = avg <= 8 ? 16 : (avg <= 40 ? 64 : 128);
   {
