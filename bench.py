@@ -449,6 +449,60 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_ops(args):
+    """`--workload ops`: the standalone activation / quantisation / routing-side ops of the
+    layer's neighbourhood, one JSON line each: CUDA-event time at a DeepSeek-sized
+    activation (rows x 2*2048 gate|up, larger than L2 in total), algorithmic bytes,
+    achieved GB/s against the measured copy bandwidth.  Not the headline: the
+    default run reports the layer."""
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    import vllm_xpu_kernels.fused_moe_interface  # noqa: F401  (registers the ops)
+    peaks = _peaks()
+    rows, H = 65536, 2048
+    g = torch.Generator(device=dev).manual_seed(0)
+    x2 = torch.randn(rows, 2 * H, generator=g, device=dev).to(torch.bfloat16)
+    x1 = torch.randn(rows, H, generator=g, device=dev).to(torch.bfloat16)
+    q8 = torch.empty(rows, H, dtype=torch.float8_e4m3fn, device=dev)
+    q4 = torch.empty(rows, H // 2, dtype=torch.uint8, device=dev)
+    s128 = torch.empty(rows, H // 128, dtype=torch.float32, device=dev)
+    s32 = torch.empty(rows, H // 32, dtype=torch.float32, device=dev)
+    o16 = torch.empty(rows, H, dtype=torch.bfloat16, device=dev)
+    qmx = torch.empty(2 * rows, H, dtype=torch.float8_e4m3fn, device=dev)
+    smx = torch.empty(2, (H + 127) // 128, rows, dtype=torch.int32, device=dev)
+    one = torch.tensor([0.5], device=dev)
+    C = torch.ops._C
+    cases = [
+        ("silu_and_mul", lambda: C.silu_and_mul(o16, x2), rows * H * 6),
+        ("swigluoai_and_mul", lambda: C.swigluoai_and_mul(o16, x2, 1.702, 7.0), rows * H * 6),
+        ("per_token_group_fp8_quant", lambda: C.per_token_group_fp8_quant(x1, q8, s128, 128, 1e-10, -448., 448., False, False, False),
+         rows * H * 3 + s128.numel() * 4),
+        ("silu_and_mul_per_block_quant", lambda: C.silu_and_mul_per_block_quant(q8, x2, s128, 128, None, False, False),
+         rows * H * 5 + s128.numel() * 4),
+        ("silu_and_mul_quant", lambda: C.silu_and_mul_quant(q8, x2, one), rows * H * 5),
+        ("silu_and_mul_mxfp4_quant", lambda: C.silu_and_mul_mxfp4_quant(q4, x2, s32, 32, 1e-10),
+         rows * H * 4 + rows * H // 2 + s32.numel() * 4),
+        ("per_token_group_quant_mxfp4", lambda: C.per_token_group_quant_mxfp4(x1, q4, s32, 32, 1e-10),
+         rows * H * 2 + rows * H // 2 + s32.numel() * 4),
+        ("b200_quant_mxfp8 (2 planes)", lambda: C.b200_quant_mxfp8(x1, qmx, smx), rows * H * 4 + smx.numel() * 4),
+    ]
+    for name, fn, nbytes in cases:
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        print(json.dumps({"op": name, "rows": rows, "hidden": H, "ms": round(ms, 4), "algorithmic_bytes": nbytes,
+                          "achieved_GBps": round(gbs, 1), "peak_GBps": peaks["hbm"],
+                          "frac": round(gbs / peaks["hbm"], 3), "peak_source": peaks["source"]}), flush=True)
+
+
 def run_reference(args):
     """The reference's own CPU path for this layer (its pure-torch test
     reference, restated in oracle/), timed on the host cores of this box."""
@@ -491,7 +545,9 @@ def main():
                     help="device-resident loop replays the step from a CUDA graph instead of eager ops")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "ops":
+        run_ops(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

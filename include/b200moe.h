@@ -33,8 +33,9 @@ typedef enum {
   B200MOE_I64 = 6,
   B200MOE_U32 = 7,
   B200MOE_FP4X2 = 8, /* float4_e2m1fn_x2: two e2m1 codes per byte, low nibble first */
-  B200MOE_FP8_E4M3_X2 = 9 /* two float8_e4m3fn planes [2][rows][cols]: value =
-                             plane 0 + plane 1 (MXFP8 activations + residual) */
+  B200MOE_FP8_E4M3_X2 = 9, /* two float8_e4m3fn planes [2][rows][cols]: value =
+                              plane 0 + plane 1 (MXFP8 activations + residual) */
+  B200MOE_I8 = 10 /* int8 */
 } b200moe_dtype;
 
 /* Status codes. */
@@ -273,6 +274,53 @@ int b200moe_per_token_group_fp8_quant(const void* x, b200moe_dtype dtype,
                                       int scale_ue8m0, int64_t s_stride_row,
                                       int64_t s_stride_col,
                                       b200moe_stream stream);
+
+/* Replaces `silu_and_mul_per_block_quant`
+ * (csrc/quantization/fused_kernels/fused_silu_mul_block_quant.cpp:141-239, kernel
+ * :14-128; schema csrc/torch_bindings.cpp:89-101).  in [rows, 2*hidden] (gate |
+ * up) -> out [rows, hidden] e4m3 or int8 of silu(gate)*up (fp32) divided by a
+ * per-group scale = max(amax/448, 1/(448*512)) (int8: max(amax/127, FLT_EPSILON)),
+ * optionally capped by *scale_ub and rounded up to a power of two; scales
+ * fp32 at [row*s_stride_row + group*s_stride_group]. */
+int b200moe_silu_and_mul_per_block_quant(void* out, b200moe_dtype out_dtype,
+                                         float* scales, const void* in,
+                                         b200moe_dtype dtype, int64_t rows,
+                                         int hidden, int group_size,
+                                         const float* scale_ub,
+                                         int64_t s_stride_row,
+                                         int64_t s_stride_group,
+                                         int scale_ue8m0, b200moe_stream stream);
+
+/* Replaces `silu_and_mul_mxfp4_quant`
+ * (csrc/quantization/fused_kernels/fused_silu_mul_mxfp4_quant.cpp:134-210, kernel
+ * :19-131; schema csrc/torch_bindings.cpp:103-107).  in [rows, 2*hidden] ->
+ * out [rows, hidden/2] packed e2m1 (low nibble = even element) of
+ * silu(gate)*up, scales fp32 powers of two = ceil_pow2(max(amax/6, eps)) per 32. */
+int b200moe_silu_and_mul_mxfp4_quant(void* out, float* scales, const void* in,
+                                     b200moe_dtype dtype, int64_t rows,
+                                     int hidden, float eps,
+                                     int64_t s_stride_row,
+                                     int64_t s_stride_group,
+                                     b200moe_stream stream);
+
+/* Replaces `per_token_group_quant_mxfp4` (csrc/quantization/fp4/mxfp4_quant.cpp:24-126,
+ * kernel mxfp4_quant.h:133-245; schema csrc/torch_bindings.cpp:180-184).
+ * in [rows, hidden] f32/f16/bf16 -> out_q [rows, hidden/2], out_s as above.
+ * Rows must be a multiple of 32 values long (the reference's scalar path for
+ * groups that straddle rows is not built). */
+int b200moe_per_token_group_quant_mxfp4(const void* in, b200moe_dtype dtype,
+                                        void* out_q, float* out_s, int64_t rows,
+                                        int hidden, float eps,
+                                        int64_t s_stride_row,
+                                        int64_t s_stride_group,
+                                        b200moe_stream stream);
+
+/* Replaces `silu_and_mul_quant` (csrc/activation.cpp:552-566, kernel :191-234;
+ * schema csrc/torch_bindings.cpp:84-86): out [rows,d] e4m3 =
+ * clamp(float(T(silu(x)) *_T y) * (1 / *scale)), static per-tensor scale. */
+int b200moe_silu_and_mul_quant(void* out, const void* in, b200moe_dtype dtype,
+                               const float* scale, int64_t rows, int d,
+                               b200moe_stream stream);
 
 /* MX-format activation quantisation for the block-scaled MXFP4 GEMM: per 32
  * consecutive values of a row one e8m0 scale byte b (2^(b-127) is the smallest

@@ -222,6 +222,79 @@ def dequant_mxfp8(q, scale_u8):
     return (q.float().reshape(terms, rows, cols // 32, 32) * sc.unsqueeze(-1)).sum(dim=0).reshape(rows, cols)
 
 
+def _ceil_pow2(v, eps):
+    """exp2(ceil(log2(max(|v|, eps)))) computed exactly."""
+    m, e = torch.frexp(v.abs().clamp(min=eps))
+    return torch.exp2(torch.where(m == 0.5, e - 1, e).float())
+
+
+_E2M1_MID = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+
+
+def f32_to_e2m1(x):
+    """csrc/quantization/fp4/mxfp4_quant.h:17-30: code = number of midpoints strictly
+    below |x| (ties go down), sign in bit 3 (x < 0)."""
+    code = (x.abs().unsqueeze(-1) > _E2M1_MID).sum(-1).to(torch.uint8)
+    return code | ((x < 0).to(torch.uint8) << 3)
+
+
+def _pack_e2m1(codes):
+    return (codes[..., 0::2] | (codes[..., 1::2] << 4)).to(torch.uint8)
+
+
+def _silu_mul_f32(x):
+    d = x.shape[-1] // 2
+    g, u = x[..., :d].float(), x[..., d:].float()
+    return (g / (1.0 + torch.exp(-g))) * u
+
+
+def silu_and_mul_per_block_quant(x, group, out_dtype=torch.float8_e4m3fn, scale_ub=None, ue8m0=False):
+    """csrc/quantization/fused_kernels/fused_silu_mul_block_quant.cpp:62-116: fp32
+    silu(g)*u, per-group amax, scale = max(amax/448, 1/(448*512)) (int8:
+    max(amax/127, FLT_EPSILON)), optional cap and power-of-two rounding, x / scale."""
+    r = _silu_mul_f32(x)
+    T, H = r.shape
+    v = r.reshape(T, H // group, group)
+    amax = v.abs().amax(-1)
+    if out_dtype == torch.int8:
+        sc = (amax / 127.0).clamp(min=torch.finfo(torch.float32).eps)
+        q = torch.round(v / sc.unsqueeze(-1)).clamp(-128, 127).to(torch.int8)
+    else:
+        floor_s = 1.0 / (FP8_MAX * 512.0)
+        sc = (amax / FP8_MAX).clamp(min=floor_s)
+        if scale_ub is not None:
+            sc = torch.minimum(sc, scale_ub.float()).clamp(min=floor_s)
+        if ue8m0:
+            sc = _ceil_pow2(sc, 1e-10)
+        q = (v / sc.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q.reshape(T, H), sc
+
+
+def per_token_group_quant_mxfp4(x, eps=1e-10):
+    """csrc/quantization/fp4/mxfp4_quant.h:186-240: scale = ceil_pow2(max(amax/6, eps))
+    per 32 values, codes of clamp(x * (1/scale), -6, 6), low nibble = even element."""
+    T, H = x.shape
+    v = x.float().reshape(T, H // 32, 32)
+    sc = _ceil_pow2(v.abs().amax(-1) / 6.0, eps)
+    codes = f32_to_e2m1((v * (1.0 / sc).unsqueeze(-1)).clamp(-6.0, 6.0)).reshape(T, H)
+    return _pack_e2m1(codes), sc
+
+
+def silu_and_mul_mxfp4_quant(x, eps=1e-10):
+    """csrc/quantization/fused_kernels/fused_silu_mul_mxfp4_quant.cpp:62-118."""
+    return per_token_group_quant_mxfp4(_silu_mul_f32(x), eps)
+
+
+def silu_and_mul_quant(x, scale):
+    """csrc/activation.cpp:216-226: float(T(silu(x)) *_T y) * (1/scale), clamp, e4m3."""
+    d = x.shape[-1] // 2
+    g = x[..., :d].float()
+    s = (g / (1.0 + torch.exp(-g))).to(x.dtype)
+    prod = (s.float() * x[..., d:].float()).to(x.dtype)
+    inv = 1.0 / scale.float()
+    return (prod.float() * inv).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+
+
 def dequant_fp8_block_act(q, s):
     """vllm_xpu_kernels/moe_utils.py:143-148."""
     shape = q.shape

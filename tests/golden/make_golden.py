@@ -43,7 +43,11 @@ def load_reference(root: str):
     import tests.ops.swigluoai_and_mul_op as swi_op
     import tests.test_fp8_quant as fp8_t
     import vllm_xpu_kernels.moe_utils as mu
-    return dict(topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
+    import tests.test_fused_silu_mul_block_quant as sbq_t
+    import tests.test_fused_silu_mul_mxfp4_quant as smx_t
+    import tests.test_fused_quant_activation as sq_t
+    import tests.ops.mx_utils as mx_utils
+    return dict(sbq=sbq_t, smx=smx_t, sq=sq_t, mxu=mx_utils, topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
                 layer=layer_t, act=act_op, swi=swi_op, fp8=fp8_t, mu=mu)
 
 
@@ -183,6 +187,29 @@ def main():
     cases.append(dict(x=a, w13=w13, w2=w2, w13_bias=None, w2_bias=None, topk_weights=tw, topk_ids=tid,
                       num_experts=4, ep_rank=1, ep_size=2, clamp=None, output=out))
     torch.save(cases, OUT / "layer_bf16.pt")
+
+    # ---- fused activation + quantisation ops (own generator: earlier files stay as they are) --------
+    g2 = torch.Generator().manual_seed(1)
+    fq = dict(per_block=[], silu_mxfp4=[], mxfp4=[], static=[])
+    for (T, hidden, group, dt, qdt) in [(3, 256, 128, torch.bfloat16, torch.float8_e4m3fn),
+                                        (5, 384, 64, torch.float16, torch.float8_e4m3fn),
+                                        (4, 256, 128, torch.bfloat16, torch.int8)]:
+        x = (torch.randn(T, 2 * hidden, generator=g2) * 2).to(dt)
+        q, sc = ref["sbq"].ref_silu_and_mul_per_block_quant(x, qdt, group)
+        fq["per_block"].append(dict(x=x, group=group, q=q, scales=sc))
+    for (T, hidden, dt) in [(3, 128, torch.bfloat16), (7, 256, torch.float16)]:
+        x = (torch.randn(T, 2 * hidden, generator=g2) * 2).to(dt)
+        packed, sc, silu_out = ref["smx"]._ref_silu_and_mul_mxfp4_quant(x)
+        fq["silu_mxfp4"].append(dict(x=x, packed=packed, scales=sc, silu_out=silu_out))
+    for (T, hidden, dt) in [(4, 128, torch.bfloat16), (2, 320, torch.float32)]:
+        x = (torch.rand(T, hidden, generator=g2) + 1e-6).to(dt)
+        sc, packed = ref["mxu"].to_mxfp(x, block_size=32, format="mxfp4")
+        fq["mxfp4"].append(dict(x=x, packed=packed.view(torch.uint8), scale_e8m0=sc.view(torch.uint8)))
+    for (T, d, dt) in [(3, 64, torch.bfloat16), (5, 24, torch.float16)]:
+        x = torch.randn(T, 2 * d, generator=g2).to(dt)
+        scale = torch.tensor([0.5])
+        fq["static"].append(dict(x=x, scale=scale, q=ref["sq"].ref_silu_and_mul_quant(x, scale, torch.float8_e4m3fn)))
+    torch.save(fq, OUT / "fused_quant.pt")
     print("wrote", sorted(p.name for p in OUT.glob("*.pt")))
 
 

@@ -27,7 +27,7 @@ PKG = HERE / "vllm_xpu_kernels"
 OBJ = HERE / "build"
 INCLUDE = HERE.parent / "include"
 
-CU_SOURCES = ["abi.cu", "routing.cu", "permute.cu", "elementwise.cu", "gemm.cu",
+CU_SOURCES = ["abi.cu", "routing.cu", "permute.cu", "elementwise.cu", "fused_quant.cu", "gemm.cu",
               "gemm_check.cu", "gemm_tc.cu", "gemm_tc_dq.cu", "gemm_tc_mx.cu"]
 SHIMS = {"_C": "c_ops.cpp", "_moe_C": "moe_ops.cpp", "_xpu_C": "xpu_ops.cpp"}
 

@@ -31,6 +31,21 @@
 #include "sm100_ptx.cuh"
 #include "gemm_tc_common.cuh"
 
+// Cycle accounting of the roles of CTA 0 (printed at kernel end); compiled in
+// only with -DB200_TC_PROF, for experiments.
+#ifdef B200_TC_PROF
+#include <stdio.h>
+#define TC_PROF_DECL(...) long long __VA_ARGS__
+#define TC_PROF_T(var) const long long var = clock64()
+#define TC_PROF_ADD(acc, t0) acc += clock64() - (t0)
+#define TC_PROF_PRINT(...) if (blockIdx.x == 0) printf(__VA_ARGS__)
+#else
+#define TC_PROF_DECL(...)
+#define TC_PROF_T(var)
+#define TC_PROF_ADD(acc, t0)
+#define TC_PROF_PRINT(...)
+#endif
+
 namespace b200moe {
 namespace {
 
@@ -155,13 +170,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t it = 0;
       int cursor = 0;
       bool ok = true;
+      TC_PROF_DECL(pw = 0, pt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         const int n0 = ti.n_tile * kFeat;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          TC_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          TC_PROF_ADD(pw, w0);
           uint8_t* wdst = smem + s * kStageBytes;
           uint8_t* adst = wdst + kWTileBytes;
           ptx::mbar_expect_tx(&ctrl->full[s], kStageBytes);
@@ -177,6 +195,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ptx::tma_load_2d(adst, &tmap_a, &ctrl->full[s], k0, ti.row0);
         }
       }
+      TC_PROF_PRINT("producer: total %lld wait_empty %lld blocks %u\n", clock64() - pt0, pw, it);
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
@@ -184,22 +203,30 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t it = 0, acc_it = 0;
       int cursor = 0;
       bool ok = true;
+      TC_PROF_DECL(mf = 0, ma = 0, mi = 0, mc = 0, mt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         uint32_t a = acc_it % kAccStages;
         const bool per_block = kFp8 && !(p.debug & 4);
         if (!per_block) {
+          TC_PROF_T(wa0);
           if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) break;
+          TC_PROF_ADD(ma, wa0);
           ptx::tc_fence_after();
         }
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           if (per_block) {
             a = acc_it % kAccStages;
+            TC_PROF_T(wa1);
             if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            TC_PROF_ADD(ma, wa1);
           }
           const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          TC_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
+          TC_PROF_ADD(mf, w0);
+          TC_PROF_T(w2);
           ptx::tc_fence_after();
           const uint32_t wbase = ptx::smem_u32(smem + s * kStageBytes);
           const uint32_t abase = wbase + kWTileBytes;
@@ -214,11 +241,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t accumulate = per_block ? (j > 0) : (kb > 0 || j > 0);
             ptx::umma<kFp8>(d_tmem, wdesc, adesc, p.idesc, accumulate);
           }
+          TC_PROF_ADD(mi, w2);
+          TC_PROF_T(w3);
           ptx::umma_commit(&ctrl->empty[s]);
           if (per_block) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+          TC_PROF_ADD(mc, w3);
         }
         if (!per_block && ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
       }
+      TC_PROF_PRINT("mma: total %lld wait_full %lld wait_acc %lld issue %lld commit %lld\n", clock64() - mt0, mf, ma,
+                    mi, mc);
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
@@ -257,6 +289,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_it = 0;
     int cursor = 0;
     bool ok = true;
+    TC_PROF_DECL(ew = 0, et0 = clock64());
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       TileInfo ti;
       locate_tile<BT>(tile_start, row_start, t, cursor, ti);
@@ -267,9 +300,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       if (!kFp8) {
         const uint32_t a = acc_it % kAccStages;
+        TC_PROF_T(e0);
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
           *abort_flag = 1; ok = false; break;
         }
+        TC_PROF_ADD(ew, e0);
         ptx::tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < BT; c0 += kChunk) {
@@ -327,9 +362,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               if (lane + 32 * u < kCols) ptx::sts32f(sc + (lane + 32 * u) * 4, cur.a[u][jb] * cur.w[jb]);
             __syncwarp();
             const uint32_t a = acc_it % kAccStages;
+            TC_PROF_T(e1);
             if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
               *abort_flag = 1; ok = false; break;
             }
+            TC_PROF_ADD(ew, e1);
             ptx::tc_fence_after();
 #pragma unroll
             for (int c0 = 0; c0 < kCols; c0 += kChunk) {
@@ -375,6 +412,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    if (warp == 2 && lane == 0) TC_PROF_PRINT("epilogue: total %lld wait_acc_full %lld\n", clock64() - et0, ew);
   }
 
   // Teardown: everyone meets here, also after an aborted wait.

@@ -77,9 +77,129 @@ void b200_quant_mxfp8(const at::Tensor& input, at::Tensor& output_q, at::Tensor&
                                    current_stream()));
 }
 
+// csrc/quantization/fused_kernels/fused_silu_mul_block_quant.cpp:141-195 of the reference.
+void silu_and_mul_per_block_quant(at::Tensor& out, const at::Tensor& input, at::Tensor& scales,
+                                  int64_t group_size, const std::optional<at::Tensor>& scale_ub,
+                                  bool is_scale_transposed, bool scale_ue8m0) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == at::kFloat8_e4m3fn || out.scalar_type() == at::kFloat8_e5m2 ||
+                  out.scalar_type() == at::kChar,
+              "out must be float8_e4m3fn, float8_e5m2, or int8");
+  TORCH_CHECK(out.scalar_type() != at::kFloat8_e5m2, "float8_e5m2 output is not available in this build");
+  TORCH_CHECK(input.scalar_type() == at::kHalf || input.scalar_type() == at::kBFloat16,
+              "input must be float16 or bfloat16");
+  TORCH_CHECK(out.is_contiguous(), "out must be contiguous");
+  TORCH_CHECK(input.is_contiguous(), "input must be contiguous");
+  TORCH_CHECK(scales.scalar_type() == at::kFloat, "scales must be float32");
+  TORCH_CHECK(group_size == 32 || group_size == 64 || group_size == 128,
+              "group_size must be 32, 64, or 128, got ", group_size);
+  if (scale_ub.has_value())
+    TORCH_CHECK(out.scalar_type() == at::kFloat8_e4m3fn, "scale_ub is only supported for FP8 output");
+  TORCH_CHECK(input.dim() == 2, "input must be 2-dimensional");
+  TORCH_CHECK(out.dim() == 2, "out must be 2-dimensional");
+  const int64_t num_tokens = input.size(0), hidden = out.size(-1);
+  TORCH_CHECK(input.size(-1) == hidden * 2, "input last dim must be 2 * hidden_size");
+  TORCH_CHECK(hidden % group_size == 0, "hidden_size must be divisible by group_size");
+  TORCH_CHECK(out.size(0) == num_tokens, "out.size(0) must equal num_tokens (input.size(0))");
+  const int64_t num_groups = hidden / group_size;
+  TORCH_CHECK(scales.size(0) == num_tokens && scales.size(1) == num_groups,
+              "scales must have logical shape [num_tokens, num_groups]");
+  if (num_tokens == 0) return;
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(b200moe_silu_and_mul_per_block_quant(
+      out.data_ptr(), out.scalar_type() == at::kChar ? B200MOE_I8 : B200MOE_FP8_E4M3, scales.data_ptr<float>(),
+      input.data_ptr(), float_dtype(input, "silu_and_mul_per_block_quant"), num_tokens, (int)hidden,
+      (int)group_size, scale_ub.has_value() ? scale_ub->data_ptr<float>() : nullptr,
+      is_scale_transposed ? 1 : num_groups, is_scale_transposed ? num_tokens : 1, scale_ue8m0, current_stream()));
+}
+
+// csrc/quantization/fused_kernels/fused_silu_mul_mxfp4_quant.cpp:134-185 of the reference.
+void silu_and_mul_mxfp4_quant(at::Tensor& out, const at::Tensor& input, at::Tensor& scales, int64_t group_size,
+                              double eps) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == at::kByte, "out must be uint8");
+  TORCH_CHECK(input.scalar_type() == at::kHalf || input.scalar_type() == at::kBFloat16,
+              "input must be float16 or bfloat16");
+  TORCH_CHECK(out.is_contiguous() && input.is_contiguous(), "out and input must be contiguous");
+  TORCH_CHECK(scales.scalar_type() == at::kFloat, "scales must be float32");
+  TORCH_CHECK(group_size == 32, "MXFP4 requires group_size == 32, got ", group_size);
+  TORCH_CHECK(input.dim() == 2 && out.dim() == 2 && scales.dim() == 2, "input, out and scales must be 2-dimensional");
+  const int64_t num_tokens = input.size(0), hidden = input.size(-1) / 2;
+  TORCH_CHECK(input.size(-1) % 2 == 0 && hidden % group_size == 0, "hidden_size must be divisible by group_size");
+  TORCH_CHECK(out.size(0) == num_tokens && out.size(1) == hidden / 2, "out must be [num_tokens, hidden_size / 2]");
+  TORCH_CHECK(scales.size(0) == num_tokens && scales.size(1) == hidden / group_size,
+              "scales must have logical shape [num_tokens, num_groups]");
+  if (num_tokens == 0) return;
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(b200moe_silu_and_mul_mxfp4_quant(out.data_ptr(), scales.data_ptr<float>(), input.data_ptr(),
+                                                float_dtype(input, "silu_and_mul_mxfp4_quant"), num_tokens,
+                                                (int)hidden, (float)eps, scales.stride(0), scales.stride(1),
+                                                current_stream()));
+}
+
+// csrc/quantization/fp4/mxfp4_quant.cpp:24-86 of the reference.
+void per_token_group_quant_mxfp4(const at::Tensor& input, at::Tensor& output_q, at::Tensor& output_s,
+                                 int64_t group_size, double eps) {
+  check_cuda(input, "input");
+  TORCH_CHECK(input.is_contiguous(), "input must be contiguous");
+  TORCH_CHECK(output_q.is_contiguous(), "output_q must be contiguous");
+  TORCH_CHECK(group_size == 32, "MXFP4 requires group_size == 32, got ", group_size);
+  TORCH_CHECK(input.numel() % group_size == 0, "input numel must be divisible by group_size");
+  TORCH_CHECK(output_s.dim() == 2, "output_s must be 2-D");
+  TORCH_CHECK(output_q.scalar_type() == at::kByte, "output_q must be uint8");
+  TORCH_CHECK(output_s.scalar_type() == at::kFloat, "output_s must be float32");
+  if (input.numel() == 0) {
+    TORCH_CHECK(output_q.numel() == 0, "output_q must be empty when input is empty");
+    TORCH_CHECK(output_s.numel() == 0, "output_s must be empty when input is empty");
+    return;
+  }
+  const int64_t hidden = input.size(-1), rows = input.numel() / hidden;
+  TORCH_CHECK(hidden % group_size == 0,
+              "per_token_group_quant_mxfp4: rows that are not a multiple of 32 long are not available in this build");
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(b200moe_per_token_group_quant_mxfp4(input.data_ptr(), float_dtype(input, "per_token_group_quant_mxfp4"),
+                                                   output_q.data_ptr(), output_s.data_ptr<float>(), rows, (int)hidden,
+                                                   (float)eps, output_s.stride(0), output_s.stride(1),
+                                                   current_stream()));
+}
+
+// csrc/activation.cpp:552-566 of the reference.
+void silu_and_mul_quant(at::Tensor& out, at::Tensor& input, at::Tensor& scale) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == at::kFloat8_e4m3fn || out.scalar_type() == at::kFloat8_e5m2);
+  TORCH_CHECK(out.scalar_type() == at::kFloat8_e4m3fn, "float8_e5m2 output is not available in this build");
+  TORCH_CHECK(input.scalar_type() == at::kHalf || input.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(input.size(-1) % 2 == 0);
+  TORCH_CHECK(input.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(scale.scalar_type() == at::kFloat && scale.numel() >= 1);
+  const int64_t d = input.size(-1) / 2;
+  const int64_t rows = input.numel() / input.size(-1);
+  if (rows == 0) return;
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(b200moe_silu_and_mul_quant(out.data_ptr(), input.data_ptr(), float_dtype(input, "silu_and_mul_quant"),
+                                          scale.data_ptr<float>(), rows, (int)d, current_stream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(_C, m) {
+  m.def("silu_and_mul_quant(Tensor! result, Tensor input, Tensor scale) -> ()");
+  m.def(
+      "silu_and_mul_per_block_quant("
+      "Tensor! out, "
+      "Tensor input, "
+      "Tensor! scales, "
+      "int group_size, "
+      "Tensor? scale_ub=None, "
+      "bool is_scale_transposed=False, "
+      "bool scale_ue8m0=False) -> ()");
+  m.def(
+      "silu_and_mul_mxfp4_quant("
+      "Tensor! out, Tensor input, Tensor! scales, "
+      "int group_size, float eps=1e-10) -> ()");
+  m.def(
+      "per_token_group_quant_mxfp4(Tensor input, Tensor! output_q, Tensor! "
+      "output_s, int group_size, float eps) -> ()");
   m.def("b200_quant_mxfp8(Tensor input, Tensor! output_q, Tensor! output_s) -> ()");
   m.def("silu_and_mul(Tensor! result, Tensor input) -> ()");
   m.def("swigluoai_and_mul(Tensor! out, Tensor input, float alpha=1.702, float limit=7.0) -> ()");
@@ -96,6 +216,10 @@ TORCH_LIBRARY_IMPL(_C, CUDA, m) {
   m.impl("swigluoai_and_mul", &swigluoai_and_mul);
   m.impl("per_token_group_fp8_quant", &per_token_group_fp8_quant);
   m.impl("b200_quant_mxfp8", &b200_quant_mxfp8);
+  m.impl("silu_and_mul_quant", &silu_and_mul_quant);
+  m.impl("silu_and_mul_per_block_quant", &silu_and_mul_per_block_quant);
+  m.impl("silu_and_mul_mxfp4_quant", &silu_and_mul_mxfp4_quant);
+  m.impl("per_token_group_quant_mxfp4", &per_token_group_quant_mxfp4);
 }
 
 B200_REGISTER_EXTENSION(_C)

@@ -341,12 +341,23 @@ class XpuFusedMoe:
                 up = gemm1_output[:, I:]
                 gate.clamp_(max=clamp)
                 up.clamp_(min=-clamp, max=clamp)
-            act_output = torch.empty((num_moe_inputs, I), dtype=output.dtype, device=dev)
-            self.act_func(act_output, gemm1_output)
+            if quant_acts and self._act_kind == "silu" and I % FP8_BLOCK_SIZE == 0:
+                # SiLU, multiply and the 1x128 e4m3 quantisation of gemm2's input in one pass
+                act_output = None
+                act_q = torch.empty((num_moe_inputs, I), dtype=torch.float8_e4m3fn, device=dev)
+                gemm2_act_scale = torch.empty((num_moe_inputs, I // FP8_BLOCK_SIZE), dtype=torch.float32,
+                                              device=dev)
+                torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_output, gemm2_act_scale,
+                                                          FP8_BLOCK_SIZE, None, False, False)
+            else:
+                act_output = torch.empty((num_moe_inputs, I), dtype=output.dtype, device=dev)
+                self.act_func(act_output, gemm1_output)
 
         # ---- gemm2 ----
         gemm2_output = torch.empty((num_moe_inputs, hidden_size), dtype=output.dtype, device=dev)
-        if quant_acts:
+        if quant_acts and act_output is None:
+            pass   # already quantised together with the activation
+        elif quant_acts:
             act_q, gemm2_act_scale = quant_act_xpu(act_output, self.recipe)
         elif self.mx_acts:
             act_q, gemm2_act_scale = self._quant_mx(act_output)
