@@ -264,6 +264,26 @@ int b200moe_swigluoai_and_mul(void* out, const void* in, b200moe_dtype dtype,
                               int64_t rows, int d, float alpha, float limit,
                               b200moe_stream stream);
 
+/* Replace `gelu_and_mul`, `gelu_tanh_and_mul` (csrc/activation.cpp:53-75, 576-592;
+ * schema csrc/torch_bindings.cpp:112-116): in [rows,2d] -> out [rows,d] =
+ * T(gelu(x)) *_T y, erf form / tanh form. */
+int b200moe_gelu_and_mul(void* out, const void* in, b200moe_dtype dtype,
+                         int64_t rows, int d, b200moe_stream stream);
+int b200moe_gelu_tanh_and_mul(void* out, const void* in, b200moe_dtype dtype,
+                              int64_t rows, int d, b200moe_stream stream);
+
+/* Replaces `swiglustep_and_mul` (csrc/activation.cpp:299-312, 351-378, 711-716;
+ * schema csrc/torch_bindings.cpp:197-201): gate = first half, up = second;
+ * out = T(min(silu(gate), limit) * clamp(up, -limit, limit)) in fp32. */
+int b200moe_swiglustep_and_mul(void* out, const void* in, b200moe_dtype dtype,
+                               int64_t rows, int d, float limit,
+                               b200moe_stream stream);
+
+/* Replaces `relu2_no_mul` (csrc/activation.cpp:45-50, 674-681; schema
+ * csrc/torch_bindings.cpp:193-195): out [rows,d] = T(max(x,0)^2), no gating. */
+int b200moe_relu2_no_mul(void* out, const void* in, b200moe_dtype dtype,
+                         int64_t rows, int d, b200moe_stream stream);
+
 /* Replaces `per_token_group_fp8_quant` (csrc/quantization/fp8/fp8_quant.cpp:724-840,
  * kernel :278-390; schema csrc/torch_bindings.cpp:170-177).
  * x [rows,cols] -> q [rows,cols] e4m3, s [rows,cols/group] fp32 with element

@@ -177,6 +177,26 @@ def swigluoai_and_mul(x, alpha=1.702, limit=7.0):
     return (up + 1) * (gate * torch.sigmoid(gate * alpha))
 
 
+def gelu_and_mul(x, approximate="none"):
+    """tests/ops/activation_op.py:86-90 (csrc/activation.cpp:53-75): T(gelu(x)) *_T y."""
+    d = x.shape[-1] // 2
+    return torch.nn.functional.gelu(x[..., :d].float(), approximate=approximate).to(x.dtype) * x[..., d:]
+
+
+def swiglustep_and_mul(x, limit=7.0):
+    """csrc/activation.cpp:299-312: min(silu(gate), limit) * clamp(up, +-limit) in fp32,
+    gate = first half (tests/ops/swiglustep_and_mul_op.py:27-33)."""
+    d = x.shape[-1] // 2
+    g, u = x[..., :d].float(), x[..., d:].float()
+    return ((g / (1.0 + torch.exp(-g))).clamp(max=limit) * u.clamp(min=-limit, max=limit)).to(x.dtype)
+
+
+def relu2_no_mul(x):
+    """csrc/activation.cpp:45-50: max(x, 0)^2 in fp32, no gating."""
+    r = x.float().clamp(min=0)
+    return (r * r).to(x.dtype)
+
+
 # --------------------------------------------------------------------------- quantisation
 def per_token_group_fp8_quant(x, group=128, eps=1e-10, ue8m0=False):
     """Order of csrc/quantization/fp8/fp8_quant.cpp:340-387: amax floor eps,
@@ -417,6 +437,14 @@ def fused_moe_staged(x, w13_deq, w13_bias, w2_deq, w2_bias, topk_weights, topk_i
     if activation == "silu":
         d = g1.shape[1] // 2
         act = (torch.nn.functional.silu(g1[:, :d].float()).to(dt).float() * g1[:, d:].float()).to(dt)
+    elif activation == "gelu":
+        act = gelu_and_mul(g1)
+    elif activation == "gelu_tanh":
+        act = gelu_and_mul(g1, "tanh")
+    elif activation == "swiglustep":
+        act = swiglustep_and_mul(g1, 7.0)
+    elif activation == "relu2_no_mul":
+        act = relu2_no_mul(g1)
     else:
         act = swigluoai_and_mul(g1.float(), alpha, limit).to(dt)
     a2 = act.float()

@@ -47,7 +47,8 @@ def load_reference(root: str):
     import tests.test_fused_silu_mul_mxfp4_quant as smx_t
     import tests.test_fused_quant_activation as sq_t
     import tests.ops.mx_utils as mx_utils
-    return dict(sbq=sbq_t, smx=smx_t, sq=sq_t, mxu=mx_utils, topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
+    import tests.ops.swiglustep_and_mul_op as step_op
+    return dict(step=step_op, sbq=sbq_t, smx=smx_t, sq=sq_t, mxu=mx_utils, topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
                 layer=layer_t, act=act_op, swi=swi_op, fp8=fp8_t, mu=mu)
 
 
@@ -210,6 +211,18 @@ def main():
         scale = torch.tensor([0.5])
         fq["static"].append(dict(x=x, scale=scale, q=ref["sq"].ref_silu_and_mul_quant(x, scale, torch.float8_e4m3fn)))
     torch.save(fq, OUT / "fused_quant.pt")
+
+    # ---- the other gated activations ---------------------------------------------------------------
+    g3 = torch.Generator().manual_seed(2)
+    x = (torch.randn(6, 2 * 96, generator=g3) * 3).to(torch.bfloat16)
+    xh = (torch.randn(5, 2 * 40, generator=g3) * 3).to(torch.float16)
+    acts = {}
+    for name, t in (("bf16", x), ("f16", xh)):
+        acts[name] = dict(x=t,
+                          gelu=ref["act"].GeluAndMul.forward_native(ref["act"].GeluAndMul("none"), t),
+                          gelu_tanh=ref["act"].GeluAndMul.forward_native(ref["act"].GeluAndMul("tanh"), t),
+                          swiglustep=ref["step"].SwigluStepAndMul.forward_native(ref["step"].SwigluStepAndMul(7.0), t))
+    torch.save(acts, OUT / "activations2.pt")
     print("wrote", sorted(p.name for p in OUT.glob("*.pt")))
 
 

@@ -180,3 +180,14 @@ def test_fused_quant_ops_against_reference_vectors():
     for c in fq["static"]:
         q = to.silu_and_mul_quant(c["x"], c["scale"])
         torch.testing.assert_close(q.float(), c["q"].float())
+
+
+def test_other_activations_against_reference_vectors():
+    """gelu / gelu_tanh / swiglustep restatements against the reference's native
+    forward functions (tests/ops/activation_op.py:86-90, swiglustep_and_mul_op.py:27-33)."""
+    for c in load_golden("activations2.pt").values():
+        x = c["x"]
+        tol = dict(rtol=2e-2, atol=1e-3) if x.dtype == torch.bfloat16 else dict(rtol=2e-3, atol=1e-3)
+        torch.testing.assert_close(to.gelu_and_mul(x), c["gelu"], **tol)
+        torch.testing.assert_close(to.gelu_and_mul(x, "tanh"), c["gelu_tanh"], **tol)
+        torch.testing.assert_close(to.swiglustep_and_mul(x), c["swiglustep"], **tol)

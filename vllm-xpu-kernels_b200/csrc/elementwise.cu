@@ -48,6 +48,58 @@ silu_and_mul_kernel(T* __restrict__ out, const T* __restrict__ in, int d, bool v
   }
 }
 
+// Other gated activations of the layer (csrc/activation.cpp:45-75, 299-312 of the
+// reference).  kKind 1: gelu (erf), 2: gelu (tanh form): out = T(act(x)) *_T y as
+// in silu_and_mul; 3: swiglustep: out = T(min(silu(g), limit) * clamp(u, +-limit))
+// in fp32; 4: relu2_no_mul: out = T(max(x, 0)^2), no second half.
+template <typename T, int kKind>
+__device__ __forceinline__ T gated_act(T gv, T uv, float limit) {
+  const float f = to_f32<T>(gv);
+  if (kKind == 1) {
+    const T a = from_f32<T>(f * 0.5f * (1.0f + erff(f * 0.70710678118654752440f)));
+    return from_f32<T>(to_f32<T>(a) * to_f32<T>(uv));
+  } else if (kKind == 2) {
+    const float inner = 0.79788456080286535588f * (f + 0.044715f * (f * f * f));
+    const T a = from_f32<T>(0.5f * f * (1.0f + tanhf(inner)));
+    return from_f32<T>(to_f32<T>(a) * to_f32<T>(uv));
+  } else if (kKind == 3) {
+    const float sg = fminf(silu_f32(f), limit);
+    const float u = fminf(fmaxf(to_f32<T>(uv), -limit), limit);
+    return from_f32<T>(sg * u);
+  } else {
+    const float r = fmaxf(f, 0.0f);
+    return from_f32<T>(r * r);
+  }
+}
+
+// Rows of [x(d) | y(d)] -> d outputs (kKind 4: rows of d inputs -> d outputs).
+template <typename T, int kKind>
+__global__ void __launch_bounds__(256)
+gated_act_kernel(T* __restrict__ out, const T* __restrict__ in, int d, float limit, bool vec_ok) {
+  constexpr int N = Vec<T>::N;
+  constexpr bool kGated = kKind != 4;
+  const int64_t r = blockIdx.x;
+  const T* g = in + r * (kGated ? 2 : 1) * (int64_t)d;
+  const T* u = kGated ? g + d : g;
+  T* o = out + r * (int64_t)d;
+  if (vec_ok) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < d / N; j += gridDim.y * blockDim.x) {
+      const vec16 gv = ld16(g + (int64_t)j * N);
+      const vec16 uv = kGated ? ld16(u + (int64_t)j * N) : gv;
+      const T* ge = reinterpret_cast<const T*>(&gv);
+      const T* ue = reinterpret_cast<const T*>(&uv);
+      vec16 ov;
+      T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+      for (int i = 0; i < N; ++i) oe[i] = gated_act<T, kKind>(ge[i], ue[i], limit);
+      st16(o + (int64_t)j * N, ov);
+    }
+  } else {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < d; j += gridDim.y * blockDim.x)
+      o[j] = gated_act<T, kKind>(g[j], u[j], limit);
+  }
+}
+
 __device__ __forceinline__ float swigluoai_f32(float g, float u, float alpha, float limit) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
@@ -434,4 +486,39 @@ extern "C" int b200moe_quant_mxfp8(const void* x, b200moe_dtype dtype, void* q, 
         (const __half*)x, (uint8_t*)q, (uint8_t*)s, rows, cols, terms);
   B200_LAUNCH_OK("quant_mxfp8_kernel");
   return B200MOE_OK;
+}
+
+namespace {
+template <int kKind>
+int launch_gated_act(void* out, const void* in, b200moe_dtype dtype, int64_t rows, int d, float limit,
+                     b200moe_stream stream, const char* name) {
+  B200_CHECK_ARG(rows >= 0 && d >= 0, "%s: negative size", name);
+  if (rows == 0 || d == 0) return B200MOE_OK;
+  B200_CHECK_ARG(out && in, "%s: null pointer", name);
+  B200_DISPATCH_FLOAT(dtype, name, {
+    constexpr int N = 16 / sizeof(scalar_t);
+    const bool vec_ok = (d % N == 0) && aligned16(out) && aligned16(in);
+    gated_act_kernel<scalar_t, kKind><<<row_grid(rows, vec_ok ? d / N : d), 256, 0, as_stream(stream)>>>(
+        (scalar_t*)out, (const scalar_t*)in, d, limit, vec_ok);
+  });
+  B200_LAUNCH_OK(name);
+  return B200MOE_OK;
+}
+}  // namespace
+
+extern "C" int b200moe_gelu_and_mul(void* out, const void* in, b200moe_dtype dtype, int64_t rows, int d,
+                                    b200moe_stream stream) {
+  return launch_gated_act<1>(out, in, dtype, rows, d, 0.f, stream, "gelu_and_mul");
+}
+extern "C" int b200moe_gelu_tanh_and_mul(void* out, const void* in, b200moe_dtype dtype, int64_t rows, int d,
+                                         b200moe_stream stream) {
+  return launch_gated_act<2>(out, in, dtype, rows, d, 0.f, stream, "gelu_tanh_and_mul");
+}
+extern "C" int b200moe_swiglustep_and_mul(void* out, const void* in, b200moe_dtype dtype, int64_t rows, int d,
+                                          float limit, b200moe_stream stream) {
+  return launch_gated_act<3>(out, in, dtype, rows, d, limit, stream, "swiglustep_and_mul");
+}
+extern "C" int b200moe_relu2_no_mul(void* out, const void* in, b200moe_dtype dtype, int64_t rows, int d,
+                                    b200moe_stream stream) {
+  return launch_gated_act<4>(out, in, dtype, rows, d, 0.f, stream, "relu2_no_mul");
 }

@@ -77,6 +77,45 @@ void b200_quant_mxfp8(const at::Tensor& input, at::Tensor& output_q, at::Tensor&
                                    current_stream()));
 }
 
+// gelu_and_mul / gelu_tanh_and_mul / swiglustep_and_mul: [..., 2d] -> [..., d]
+// (csrc/activation.cpp:576-592, 711-716 of the reference).
+template <typename F>
+void gated_act_op(at::Tensor& out, at::Tensor& input, const char* name, F call) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == input.scalar_type(), name, ": dtype mismatch");
+  TORCH_CHECK(input.is_contiguous() && out.is_contiguous(), name, " expects contiguous tensors");
+  const int d = input.size(-1) / 2;
+  const int64_t rows = d ? input.numel() / input.size(-1) : 0;
+  TORCH_CHECK(out.numel() == rows * d, name, ": out must be [..., d]");
+  if (input.numel() == 0) return;
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(call(out.data_ptr(), input.data_ptr(), float_dtype(input, name), rows, d, current_stream()));
+}
+void gelu_and_mul(at::Tensor& out, at::Tensor& input) {
+  gated_act_op(out, input, "gelu_and_mul", b200moe_gelu_and_mul);
+}
+void gelu_tanh_and_mul(at::Tensor& out, at::Tensor& input) {
+  gated_act_op(out, input, "gelu_tanh_and_mul", b200moe_gelu_tanh_and_mul);
+}
+void swiglustep_and_mul(at::Tensor& out, at::Tensor& input, double limit) {
+  gated_act_op(out, input, "swiglustep_and_mul",
+               [limit](void* o, const void* i, b200moe_dtype dt, int64_t rows, int d, b200moe_stream st) {
+                 return b200moe_swiglustep_and_mul(o, i, dt, rows, d, (float)limit, st);
+               });
+}
+// relu2_no_mul: out and input have the same shape (csrc/activation.cpp:674-681).
+void relu2_no_mul(at::Tensor& out, at::Tensor& input) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == input.scalar_type(), "relu2_no_mul: dtype mismatch");
+  TORCH_CHECK(input.is_contiguous() && out.is_contiguous(), "relu2_no_mul expects contiguous tensors");
+  TORCH_CHECK(out.numel() == input.numel(), "relu2_no_mul: out must have the input's shape");
+  if (input.numel() == 0) return;
+  const int d = input.size(-1);
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(b200moe_relu2_no_mul(out.data_ptr(), input.data_ptr(), float_dtype(input, "relu2_no_mul"),
+                                    input.numel() / d, d, current_stream()));
+}
+
 // csrc/quantization/fused_kernels/fused_silu_mul_block_quant.cpp:141-195 of the reference.
 void silu_and_mul_per_block_quant(at::Tensor& out, const at::Tensor& input, at::Tensor& scales,
                                   int64_t group_size, const std::optional<at::Tensor>& scale_ub,
@@ -183,6 +222,12 @@ void silu_and_mul_quant(at::Tensor& out, at::Tensor& input, at::Tensor& scale) {
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(_C, m) {
+  m.def("gelu_and_mul(Tensor! out, Tensor input) -> ()");
+  m.def("gelu_tanh_and_mul(Tensor! out, Tensor input) -> ()");
+  m.def("relu2_no_mul(Tensor! out, Tensor! input) -> ()");
+  m.def(
+      "swiglustep_and_mul(Tensor! out, Tensor input, float limit=7.0) "
+      "-> ()");
   m.def("silu_and_mul_quant(Tensor! result, Tensor input, Tensor scale) -> ()");
   m.def(
       "silu_and_mul_per_block_quant("
@@ -216,6 +261,10 @@ TORCH_LIBRARY_IMPL(_C, CUDA, m) {
   m.impl("swigluoai_and_mul", &swigluoai_and_mul);
   m.impl("per_token_group_fp8_quant", &per_token_group_fp8_quant);
   m.impl("b200_quant_mxfp8", &b200_quant_mxfp8);
+  m.impl("gelu_and_mul", &gelu_and_mul);
+  m.impl("gelu_tanh_and_mul", &gelu_tanh_and_mul);
+  m.impl("relu2_no_mul", &relu2_no_mul);
+  m.impl("swiglustep_and_mul", &swiglustep_and_mul);
   m.impl("silu_and_mul_quant", &silu_and_mul_quant);
   m.impl("silu_and_mul_per_block_quant", &silu_and_mul_per_block_quant);
   m.impl("silu_and_mul_mxfp4_quant", &silu_and_mul_mxfp4_quant);

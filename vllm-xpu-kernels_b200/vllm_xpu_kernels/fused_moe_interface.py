@@ -124,19 +124,28 @@ def compute_num_tokens_per_block(num_tokens, num_experts_per_node):
 
 def _activation_kind(activation):
     """Maps the reference's activation names (:119-133, :239-254) to an op."""
-    if activation == "silu":
-        return "silu"
+    if activation in ("silu", "gelu", "gelu_tanh", "relu2_no_mul", "swiglustep"):
+        return activation
     if activation == "swigluoai" or ("SWIGLUOAI" in str(activation)):
         return "swigluoai"
     raise ValueError(f"Unsupported FusedMoe activation: {activation}.")
 
 
+def _activation_op(kind):
+    """The op ``act(out, gemm1_output)`` of an activation kind."""
+    C = torch.ops._C
+    return {
+        "silu": C.silu_and_mul,
+        "gelu": C.gelu_and_mul,
+        "gelu_tanh": C.gelu_tanh_and_mul,
+        "swigluoai": lambda out, x: C.swigluoai_and_mul(out, x, 1.702, 7.0),
+        "relu2_no_mul": C.relu2_no_mul,
+        "swiglustep": lambda out, x: C.swiglustep_and_mul(out, x, 7.0),
+    }[kind]
+
+
 def fused_moe_activation(act_output, gemm1_output, activation):
-    kind = _activation_kind(activation)
-    if kind == "silu":
-        torch.ops._C.silu_and_mul(act_output, gemm1_output)
-    else:
-        torch.ops._C.swigluoai_and_mul(act_output, gemm1_output, 1.702, 7.0)
+    _activation_op(_activation_kind(activation))(act_output, gemm1_output)
 
 
 class XpuFusedMoe:
@@ -211,7 +220,8 @@ class XpuFusedMoe:
         self.n_experts_per_token = n_experts_per_token
         self.activation = activation
         self._act_kind = _activation_kind(activation)
-        self.inter_size_scale = 1
+        # relu2_no_mul keeps both halves of gemm1's output (reference :226)
+        self.inter_size_scale = 2 if self._act_kind == "relu2_no_mul" else 1
         self.num_experts = num_experts
         self.ep_rank = ep_rank
         self.ep_size = ep_size
@@ -239,10 +249,9 @@ class XpuFusedMoe:
                             and hidden >= 128 and self.inter_size >= 128)
         if self.mx_acts and self._act_kind == "silu" and fuse_activation:
             raise ValueError("the block-scaled MXFP4 GEMM has no fused SiLU epilogue")
-        if self._act_kind == "silu":
-            self.act_func = torch.ops._C.silu_and_mul
-        else:
-            self.act_func = torch.ops._C.swigluoai_and_mul
+        if fuse_activation and self._act_kind not in ("silu", "swigluoai"):
+            raise ValueError(f"no fused epilogue for the {self._act_kind} activation")
+        self.act_func = _activation_op(self._act_kind)
 
         self.expert_map = expert_map
         if self.expert_map is None and self.ep_size > 1:
@@ -350,7 +359,8 @@ class XpuFusedMoe:
                 torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_output, gemm2_act_scale,
                                                           FP8_BLOCK_SIZE, None, False, False)
             else:
-                act_output = torch.empty((num_moe_inputs, I), dtype=output.dtype, device=dev)
+                act_output = torch.empty((num_moe_inputs, I * self.inter_size_scale), dtype=output.dtype,
+                                         device=dev)
                 self.act_func(act_output, gemm1_output)
 
         # ---- gemm2 ----
@@ -365,7 +375,8 @@ class XpuFusedMoe:
             act_q, gemm2_act_scale = act_output, None
         torch.ops._xpu_C.b200_grouped_gemm(
             act_q, gemm2_act_scale, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_output,
-            rows_per_expert, hidden_size, I, E, 0, _EPI_NONE, 1.702, 7.0, 0.0, 0, self.gemm_max_ctas)
+            rows_per_expert, hidden_size, I * self.inter_size_scale, E, 0, _EPI_NONE, 1.702, 7.0, 0.0, 0,
+            self.gemm_max_ctas)
 
         torch.ops._moe_C.moe_gather(output, gemm2_output, topk_weights, row_map, E)
 
