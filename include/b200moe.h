@@ -201,7 +201,8 @@ typedef enum {
   B200MOE_W_FP8_TENSOR_KN = 2, /* fp8 e4m3 [E,K,N] + fp32 scale [E]                 */
   B200MOE_W_FP8_BLOCK_NK = 3,  /* fp8 e4m3 [E,N,K] + fp32 scales [E,N/128,K/128]    */
   B200MOE_W_FP8_BLOCK_KN = 4,  /* fp8 e4m3 [E,K,N] + same scales                    */
-  B200MOE_W_MXFP4_NK = 5  /* e2m1 pairs [E,N,K/2] + e8m0 bytes [E,N,K/32]           */
+  B200MOE_W_MXFP4_NK = 5, /* e2m1 pairs [E,N,K/2] + e8m0 bytes [E,N,K/32]           */
+  B200MOE_W_FP8E5M2_TENSOR_KN = 6 /* fp8 e5m2 [E,K,N] + fp32 scale [E]                */
 } b200moe_weight_format;
 
 typedef enum {

@@ -74,3 +74,36 @@ def test_grouped_gemm_mxfp4_block_scaled(native, E, M, N, K, has_bias, terms):
         full = to.grouped_gemm(xdq, wdeq, bias, rows, torch.float32)
         expect = to.swigluoai_and_mul(full)
         torch.testing.assert_close(fused.cpu()[:n].float(), expect[:n], rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("E,M,N,K", [(4, 30, 256, 128), (4, 50, 256, 160), (8, 130, 720, 576), (3, 700, 2816, 2048),
+                                     (2, 3, 128, 256), (5, 64, 208, 320)])
+@pytest.mark.parametrize("w_dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("has_bias", [False, True])
+@pytest.mark.parametrize("terms", [1, 2])
+def test_grouped_gemm_per_tensor_fp8_block_scaled(native, E, M, N, K, w_dtype, has_bias, terms):
+    """Per-tensor-scaled fp8 weights [E,K,N] (the reference's w8a16 recipe) against
+    MXFP8 activation planes on the block-scaled instruction: fp8 values are exact
+    operands, the expert's scale multiplies the accumulator."""
+    g = torch.Generator().manual_seed(N + K + M)
+    rows = random_rows(E, M, g)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, K, N, generator=g) * K ** -0.5 * 4).to(w_dtype)
+    sc = torch.exp2(torch.randint(-3, 4, (E,), generator=g).float()) * 0.25
+    bias = (torch.randn(E, N, generator=g) * 0.05).to(torch.bfloat16) if has_bias else None
+    wdeq = w.float().transpose(1, 2) * sc.view(E, 1, 1)          # [E, N, K]
+    xq, xs = quant_mxfp8(x.to(DEV), terms)
+    xdq = to.dequant_mxfp8(xq.cpu().reshape(terms, M, K), mx_scale_bytes(xs, K)[:, :, :K // 32])
+    ref = to.grouped_gemm(xdq, wdeq, bias, rows, torch.bfloat16)
+    out = grouped_gemm(xq, xs, w.to(DEV), sc.to(DEV), bias.to(DEV) if has_bias else None, rows.to(DEV), N, K,
+                       rows_out=M)
+    n = int(rows.sum())
+    torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=2e-2, atol=2e-2)
+    assert bool(torch.isnan(out[n:].float()).all())
+    if terms == 2:   # as good as 16-bit activations
+        ref16 = to.grouped_gemm(x.float(), wdeq, bias, rows, torch.bfloat16)
+        torch.testing.assert_close(out.cpu()[:n].float(), ref16[:n].float(), rtol=2e-2, atol=2e-2)
+        # and the checking kernel with 16-bit activations agrees
+        chk = grouped_gemm(x.to(DEV), None, w.to(DEV), sc.to(DEV), bias.to(DEV) if has_bias else None,
+                           rows.to(DEV), N, K, impl=2)
+        torch.testing.assert_close(out.cpu()[:n].float(), chk.cpu()[:n].float(), rtol=2e-2, atol=2e-2)

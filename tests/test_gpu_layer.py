@@ -103,6 +103,41 @@ def test_layer_mxfp4_activation_modes(native, T):
         torch.testing.assert_close(omx.float(), ref16.float(), rtol=1e-1, atol=1e-1 * scale)
 
 
+@pytest.mark.parametrize("w_dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("has_bias", [False, True])
+@pytest.mark.parametrize("mode", ["mxfp8x2", "bf16"])
+def test_layer_per_tensor_fp8(native, w_dtype, dtype, has_bias, mode):
+    """tests/fused_moe/test_fused_moe.py:179-296 of the reference: per-tensor fp8 weights
+    (e4m3 / e5m2) with power-of-two expert scales, weights handed over as [E,K,N],
+    tolerance 2e-2 (bf16) / 1e-2 (fp16); on the block-scaled tensor-core path
+    (default) and on the 16-bit-activation path."""
+    T, H, I, E, K = 48, 256, 192, 8, 2
+    g = torch.Generator().manual_seed(7)
+    a = (torch.randn(T, H, generator=g) / 16).to(dtype)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) / 16).to(dtype)
+    w2 = (torch.randn(E, H, I, generator=g) / 16).to(dtype)
+    b13 = (torch.randn(E, 2 * I, generator=g) / 16).to(dtype) if has_bias else None
+    b2 = (torch.randn(E, H, generator=g) / 16).to(dtype) if has_bias else None
+    s13 = torch.exp2(torch.randint(-3, 4, (E,), generator=g).float())
+    s2 = torch.exp2(torch.randint(-3, 4, (E,), generator=g).float())
+    q13 = (w13.float() / s13.view(E, 1, 1)).to(w_dtype)
+    q2 = (w2.float() / s2.view(E, 1, 1)).to(w_dtype)
+    ref13 = (q13.to(dtype) * s13.view(E, 1, 1).to(dtype))
+    ref2 = (q2.to(dtype) * s2.view(E, 1, 1).to(dtype))
+    tw, ids = torch.topk(torch.randn(T, E, generator=g), k=K, dim=-1, sorted=False)
+    ref = to.fused_moe_bf16(a, ref13, b13, ref2, b2, tw, ids.int(), E)
+    mv = lambda t: t.to(DEV) if t is not None else None
+    layer = native.XpuFusedMoe(mv(q13.transpose(-1, -2).contiguous()), mv(s13), mv(b13),
+                               mv(q2.transpose(-1, -2).contiguous()), mv(s2), mv(b2), K, "silu", E,
+                               mxfp4_activations=mode)
+    assert layer.mx_acts == (mode != "bf16")
+    out = torch.empty_like(a, device=DEV)
+    layer.apply(out, a.to(DEV), tw.to(DEV), ids.int().to(DEV))
+    tol = 1e-2 if dtype == torch.float16 else 2e-2
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=tol, atol=tol)
+
+
 def test_layer_expert_parallel_masks_sum_to_the_full_layer(native):
     """ep_size ranks, each holding E/ep experts and masking the others
     (tests/fused_moe/test_fused_moe.py:531-657): the partial outputs add up."""

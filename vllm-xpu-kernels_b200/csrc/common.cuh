@@ -68,6 +68,13 @@ __device__ __forceinline__ float e4m3_to_f32(uint8_t v) {
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
+// e5m2 is the upper byte of an IEEE half.
+__device__ __forceinline__ float e5m2_to_f32(uint8_t v) {
+  __half_raw h;
+  h.x = (unsigned short)((unsigned short)v << 8);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
 // e2m1 code (4 bits) -> float: {0,.5,1,1.5,2,3,4,6} with sign bit 3.
 __device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
   const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};

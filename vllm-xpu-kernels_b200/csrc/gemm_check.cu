@@ -42,6 +42,8 @@ __device__ __forceinline__ float load_w(const CheckArgs& g, int e, int n, int k)
       return to_f32<T>(reinterpret_cast<const T*>(g.w)[((int64_t)e * N + n) * K + k]);
     case B200MOE_W_FP8_TENSOR_KN:
       return round_to<T>(e4m3_to_f32(reinterpret_cast<const uint8_t*>(g.w)[((int64_t)e * K + k) * N + n]));
+    case B200MOE_W_FP8E5M2_TENSOR_KN:
+      return round_to<T>(e5m2_to_f32(reinterpret_cast<const uint8_t*>(g.w)[((int64_t)e * K + k) * N + n]));
     case B200MOE_W_FP8_BLOCK_NK:
     case B200MOE_W_FP8_BLOCK_KN: {
       const uint8_t q = (g.fmt == B200MOE_W_FP8_BLOCK_NK)
@@ -124,7 +126,8 @@ gemm_check_kernel(CheckArgs g, bool a_fp8) {
     for (int p = 0; p < kPlanes; ++p) {
       for (int idx = threadIdx.x; idx < TN * TK; idx += 256) {
         int kk, nn;
-        if (g.fmt == B200MOE_W_BF16_KN || g.fmt == B200MOE_W_FP8_TENSOR_KN || g.fmt == B200MOE_W_FP8_BLOCK_KN) {
+        if (g.fmt == B200MOE_W_BF16_KN || g.fmt == B200MOE_W_FP8_TENSOR_KN || g.fmt == B200MOE_W_FP8E5M2_TENSOR_KN ||
+            g.fmt == B200MOE_W_FP8_BLOCK_KN) {
           nn = idx % TN; kk = idx / TN;
         } else {
           kk = idx % TK; nn = idx / TK;
@@ -192,7 +195,8 @@ gemm_check_kernel(CheckArgs g, bool a_fp8) {
       for (int p = 0; p < kPlanes; ++p) {
         v[p] = acc[p][i][j];
         const int wr = w_row(c, p);
-        if (g.fmt == B200MOE_W_FP8_TENSOR_KN) v[p] *= reinterpret_cast<const float*>(g.w_scale)[e];
+        if (g.fmt == B200MOE_W_FP8_TENSOR_KN || g.fmt == B200MOE_W_FP8E5M2_TENSOR_KN)
+          v[p] *= reinterpret_cast<const float*>(g.w_scale)[e];
         if (bias != nullptr) v[p] += to_f32<T>(bias[(int64_t)e * g.n + wr]);
       }
       float out;

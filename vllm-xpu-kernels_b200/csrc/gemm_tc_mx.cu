@@ -27,6 +27,13 @@
 //               through a plain byte tensor map.
 //   warps 6-9 : epilogue
 //
+// The same kernel (kW8) multiplies per-tensor-scaled fp8 weights ([E,K,N], e4m3 or
+// e5m2, one fp32 scale per expert: the reference's w8a16 recipe,
+// csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:322-360) with the same
+// two-plane activations: the weight tile then is a plain byte tile read as an
+// MN-major operand, its scale factors are 2^0, and the expert's scale
+// multiplies the accumulator in the epilogue.
+//
 // Numerics: products of e2m1 and e4m3 codes are exact, scaling by powers of two is
 // exact, accumulation is fp32; the difference from the reference's w4a16 path
 // (csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:411-471 of vllm-xpu-kernels) is the
@@ -64,7 +71,8 @@ constexpr int kMxGroup = 2;         // K blocks per token-scale prefetch group (
 constexpr int kMxSfwCap = 24576;    // largest weight-scale piece (128 rows x K/32 bytes) staged in shared memory
 
 struct MxParams {
-  const uint8_t* w_scale;   // [E, N, K/32] e8m0
+  const uint8_t* w_scale;   // [E, N, K/32] e8m0 (kW8: unused)
+  const float* w_tensor_scale;  // kW8: [E] fp32, multiplies the result
   const uint32_t* a_scale;  // [terms][num_kb][M] words of four e8m0 bytes
   const void* bias;
   void* d;
@@ -126,7 +134,7 @@ __device__ __forceinline__ bool stage_w_scales(const MxParams& p, MxCtrl* ctrl, 
 // BT tokens per tile, kTerms activation planes, kSub 128-wide K blocks per
 // pipeline stage (one barrier hand-over per stage: with small token tiles the
 // roles' fixed cost per hand-over, not the data, bounds the rate).
-template <int BT, int kTerms, int kSub>
+template <int BT, int kTerms, int kSub, bool kW8>
 __global__ void __launch_bounds__(kMxThreads, 1)
 grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_w,
@@ -188,7 +196,8 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int* tile_start = tile_start_w;
   const int* row_start = row_start_w;
   const int total_tiles = tile_start[p.num_experts];
-  const int tail_kb = p.tail ? p.num_kb - 1 : -1;
+  const int tail_kb = (!kW8 && p.tail) ? p.num_kb - 1 : -1;
+  constexpr int kWTx = kW8 ? kMxWBytes : kMxWTx;   // bytes a weight-tile load reports
   const int num_st = (p.num_kb + kSub - 1) / kSub;   // stages per tile
 
   if (warp == 0) {
@@ -209,12 +218,14 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* st = smem + s * stage_bytes;
           const int kb0 = si * kSub;
           const int nsub = (p.num_kb - kb0) < kSub ? (p.num_kb - kb0) : kSub;
-          ptx::mbar_expect_tx(&ctrl->full[s], nsub * (kMxWTx + kABytes));
+          ptx::mbar_expect_tx(&ctrl->full[s], nsub * (kWTx + kABytes));
 #pragma unroll
           for (int sub = 0; sub < kSub; ++sub) {
             const int kb = kb0 + sub;
             if (sub < nsub) {
-              if (kb == tail_kb)
+              if (kW8)   // 128 K rows x 128 features, one byte each; rows past K are zero-filled
+                ptx::tma_load_3d(st + sub * kMxWBytes, &tmap_w, &ctrl->full[s], n0, kb * 128, ti.e);
+              else if (kb == tail_kb)
                 ptx::tma_load_3d(p.raw_shared ? raw_one : st + kRawOff, &tmap_raw, &ctrl->full[s], kb * 64, n0, ti.e);
               else
                 ptx::tma_load_3d(st + sub * kMxWBytes, &tmap_w, &ctrl->full[s], kb * 128, n0, ti.e);
@@ -261,6 +272,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // Every operand descriptor of the stage is the first weight block's plus a
           // compile-time offset (the address field counts 16-byte units).
           const uint64_t desc0 = ptx::make_smem_desc(smem_base + s * stage_bytes, 16, 1024);
+          const uint64_t desc0w = kW8 ? ptx::make_smem_desc(smem_base + s * stage_bytes, 16384, 1024) : desc0;
           const uint32_t sf0 = tmem_base + kSfBase + s * kSfCols;
           const int kb0 = si * kSub;
 #pragma unroll
@@ -271,7 +283,8 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const uint32_t sfa = sf0 + 8 * sub;
 #pragma unroll
               for (uint32_t j = 0; j < 4; ++j) {
-                const uint64_t wdesc = desc0 + (uint64_t)((sub * kMxWBytes + j * 32) >> 4);
+                // K-major e2m1 tile: 32 codes further is 32 bytes; MN-major byte tile: 32 K rows
+                const uint64_t wdesc = desc0w + (uint64_t)((sub * kMxWBytes + j * (kW8 ? 4096 : 32)) >> 4);
                 const uint64_t adesc = desc0 + (uint64_t)((kAOff + sub * kABytes + j * 32) >> 4);
                 ptx::umma_mx(d_tmem, wdesc, adesc, idesc_j[j], (kb0 + sub > 0 || j > 0) ? 1u : 0u, sfa, sfa + 4);
               }
@@ -339,21 +352,21 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     uint32_t tile_seq = 0;
     TileInfo ti, ti_next;
-    if ((int)blockIdx.x < total_tiles) {
+    if (!kW8 && (int)blockIdx.x < total_tiles) {
       locate_tile<BT>(tile_start, row_start, blockIdx.x, cursor_next, ti_next);
       if (!stage_w_scales(p, ctrl, sfw, ti_next, 0u, ft, kgroups, abort_flag)) { *abort_flag = 1; ok = false; }
     }
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_seq) {
       locate_tile<BT>(tile_start, row_start, t, cursor, ti);
       const int t_next = t + gridDim.x;
-      if (t_next < total_tiles) {
+      if (!kW8 && t_next < total_tiles) {
         locate_tile<BT>(tile_start, row_start, t_next, cursor_next, ti_next);
         if (!stage_w_scales(p, ctrl, sfw, ti_next, tile_seq + 1, ft, kgroups, abort_flag)) {
           *abort_flag = 1; ok = false; break;
         }
       }
       const uint32_t b = tile_seq & 1;
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->sfw_full[b], (tile_seq >> 1) & 1, abort_flag))) {
+      if (!kW8 && !__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->sfw_full[b], (tile_seq >> 1) & 1, abort_flag))) {
         *abort_flag = 1; ok = false; break;
       }
       const uint32_t sfw_s = ptx::smem_u32(sfw + b * p.sfw_bytes);
@@ -381,6 +394,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const uint32_t lo = ptx::lds32(addr & ~3u), hi = ptx::lds32((addr & ~3u) + 4);
               const uint32_t v = __funnelshift_r(lo, hi, (addr & 3u) * 8);
               wa[j] = (n0 + row < p.n) ? ((v & keep) | (0x7f7f7f7fu & ~keep)) : 0x7f7f7f7fu;
+              if (kW8) wa[j] = 0x7f7f7f7fu;   // per-tensor scale: applied in the epilogue
             }
             MX_PROF_ADD(fl, l0);
             if (sub == 0) {   // the stage's scale columns and weight buffer are free again
@@ -439,8 +453,10 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < kW; ++j) { cur_b[u][j] = nxt_b[u][j]; nxt_b[u][j] = nx2_b[u][j]; }
         MX_PROF_ADD(fsw, r0);
       }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&ctrl->sfw_empty[b]);
+      if (!kW8) {
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctrl->sfw_empty[b]);
+      }
     }
 #undef B200_MX_LA_ADVANCE
     if (warp == 2 && lane == 0)
@@ -463,6 +479,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool feat_ok = feat < p.n;
       float bias_v = 0.f;
       if (p.bias != nullptr && feat_ok) bias_v = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat);
+      const float w_mul = kW8 ? p.w_tensor_scale[ti.e] : 1.0f;
       const uint32_t a = acc_it & 1;
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
         *abort_flag = 1; ok = false; break;
@@ -474,7 +491,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint32_t v[kChunk];
           float acc[kChunk];
 #pragma unroll
-          for (int i = 0; i < kChunk; ++i) acc[i] = bias_v;
+          for (int i = 0; i < kChunk; ++i) acc[i] = 0.f;
 #pragma unroll
           for (int term = 0; term < kTerms; ++term) {   // the planes' partial results add up
             const uint32_t col = tmem_base + a * kNT + term * BT + c0 + lane_sel;
@@ -487,7 +504,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           float vals[kChunk];
 #pragma unroll
           for (int i = 0; i < kChunk; ++i) {
-            float x = acc[i];
+            float x = kW8 ? fmaf(acc[i], w_mul, bias_v) : acc[i] + bias_v;
             if (p.swiglu) {
               // gate sits on even features, up on the next odd one: neighbours in the warp
               const float other = __shfl_xor_sync(0xffffffffu, x, 1);
@@ -530,10 +547,10 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
 }
 
-template <int BT, int kTerms, int kSub>
+template <int BT, int kTerms, int kSub, bool kW8>
 int launch_mx(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& traw, MxParams& p,
               int grid, cudaStream_t st) {
-  auto kern = grouped_gemm_mx_kernel<BT, kTerms, kSub>;
+  auto kern = grouped_gemm_mx_kernel<BT, kTerms, kSub, kW8>;
   const uint32_t need = 2 * kTerms * BT + kMxMaxStages * 8 * kSub;
   p.tmem_cols = need <= 128 ? 128u : (need <= 256 ? 256u : 512u);
   // The partial K block's packed bytes get one buffer for the whole CTA when a tile
@@ -573,12 +590,17 @@ int launch_mx(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& t
 // Returns B200MOE_E_UNSUPPORTED (no launch) for anything else.
 int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
   const bool x2 = a->a_dtype == B200MOE_FP8_E4M3_X2;
-  if (a->w_format != B200MOE_W_MXFP4_NK || !(a->a_dtype == B200MOE_FP8_E4M3 || x2) || a->a_scale == nullptr)
-    return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM takes MXFP4 weights and MXFP8 activations");
+  const bool w4 = a->w_format == B200MOE_W_MXFP4_NK;
+  const bool w8 = a->w_format == B200MOE_W_FP8_TENSOR_KN || a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN;
+  if (!(w4 || w8) || !(a->a_dtype == B200MOE_FP8_E4M3 || x2) || a->a_scale == nullptr)
+    return fail(B200MOE_E_UNSUPPORTED,
+                "block-scaled GEMM takes MXFP4 or per-tensor fp8 weights and MXFP8 activations");
   if (a->epilogue == B200MOE_EPI_SILU_MUL)
     return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM: SiLU epilogue not available");
-  if (a->num_experts > kMaxExperts || a->k % 64 != 0 || a->k < 128)
-    return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM: K must be a multiple of 64, at least 128");
+  if (a->num_experts > kMaxExperts || a->k % 32 != 0 || a->k < 128 || (w4 && a->k % 64 != 0))
+    return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM: K must be a multiple of 64 (fp8 weights: 32), at least 128");
+  if (w8 && a->n % 16 != 0)
+    return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM: N must be a multiple of 16 for [E,K,N] fp8 weights");
   if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 31) || ((uintptr_t)a->d & 15) || ((uintptr_t)a->a_scale & 3))
     return fail(B200MOE_E_BADARG, "block-scaled GEMM: A and D must be 16-byte, W 32-byte, A scales 4-byte aligned");
   if (a->epilogue == B200MOE_EPI_SWIGLUOAI && (a->n / 2) % 8 != 0)
@@ -589,22 +611,26 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
 
   MxParams p;
   p.w_scale = reinterpret_cast<const uint8_t*>(a->w_scale);
+  p.w_tensor_scale = reinterpret_cast<const float*>(a->w_scale);
   p.a_scale = reinterpret_cast<const uint32_t*>(a->a_scale);
   p.bias = a->bias; p.d = a->d; p.rows_per_expert = a->rows_per_expert; p.status = a->status;
   p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
   p.n_tiles = (a->n + kFeat - 1) / kFeat;
   p.num_kb = (a->k + 127) / 128;
   p.terms = x2 ? 2 : 1;
-  p.tail = (a->k % 128) != 0;
-  const int kgroups = a->k / 32;
-  // The weight scales of a tile (128 rows x K/32 bytes, contiguous in the scale
-  // tensor) are staged in shared memory: every tile's piece must start on a
-  // 16-byte boundary and two pieces must fit.
-  const int piece = ((128 * kgroups + 15) & ~15) + 16;
-  if (((uintptr_t)a->w_scale & 15) != 0 || ((int64_t)a->n * kgroups) % 16 != 0 || piece > kMxSfwCap)
-    return fail(B200MOE_E_UNSUPPORTED,
-                "block-scaled GEMM: N * K / 32 must be a multiple of 16, K at most 6144, scales 16-byte aligned");
-  p.sfw_bytes = piece;
+  p.tail = w4 && (a->k % 128) != 0;
+  p.sfw_bytes = 0;
+  if (w4) {
+    // The weight scales of a tile (128 rows x K/32 bytes, contiguous in the scale
+    // tensor) are staged in shared memory: every tile's piece must start on a
+    // 16-byte boundary and two pieces must fit.
+    const int kgroups = a->k / 32;
+    const int piece = ((128 * kgroups + 15) & ~15) + 16;
+    if (((uintptr_t)a->w_scale & 15) != 0 || ((int64_t)a->n * kgroups) % 16 != 0 || piece > kMxSfwCap)
+      return fail(B200MOE_E_UNSUPPORTED,
+                  "block-scaled GEMM: N * K / 32 must be a multiple of 16, K at most 6144, scales 16-byte aligned");
+    p.sfw_bytes = piece;
+  }
   p.out_f16 = a->d_dtype == B200MOE_F16;
   p.swiglu = a->epilogue == B200MOE_EPI_SWIGLUOAI;
   p.alpha = a->act_alpha; p.limit = a->act_limit; p.clamp_limit = a->clamp_limit;
@@ -617,7 +643,9 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
     if (force == 16 || force == 64 || force == 128) bt = force;
   }
   if (x2 && bt > 64) bt = 64;   // both planes' accumulators share tensor memory
-  p.idesc = ptx::make_idesc_mx(5u, 0u, kFeat, (uint32_t)(bt * p.terms));
+  // weights: e2m1 K-major, or e4m3 / e5m2 MN-major; activations e4m3 K-major
+  const uint32_t a_fmt = w4 ? 5u : (a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN ? 1u : 0u);
+  p.idesc = ptx::make_idesc_mx(a_fmt, 0u, kFeat, (uint32_t)(bt * p.terms)) | (w8 ? (1u << 15) : 0u);
 
   CUtensorMap ta, tw, traw;
   {
@@ -627,22 +655,31 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
     int rc = encode_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->a, dims, strides, box);
     if (rc) return rc;
   }
-  {
-    // Whole 128-code blocks only: this tensor-map type wants the inner extent to be
-    // a multiple of 128 codes; the row pitch stays K/2 bytes.
-    cuuint64_t dims[3] = {(cuuint64_t)(a->k - a->k % 128), (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
-    cuuint64_t strides[2] = {(cuuint64_t)(a->k / 2), (cuuint64_t)(a->k / 2) * a->n};
-    cuuint32_t box[3] = {128, (cuuint32_t)kFeat, 1};
-    int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, a->w, dims, strides, box);
+  if (w8) {
+    cuuint64_t dims[3] = {(cuuint64_t)a->n, (cuuint64_t)a->k, (cuuint64_t)a->num_experts};
+    cuuint64_t strides[2] = {(cuuint64_t)a->n, (cuuint64_t)a->k * a->n};
+    cuuint32_t box[3] = {128, 128, 1};
+    int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box);
     if (rc) return rc;
-  }
-  {
-    cuuint64_t dims[3] = {(cuuint64_t)(a->k / 2), (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
-    cuuint64_t strides[2] = {(cuuint64_t)(a->k / 2), (cuuint64_t)(a->k / 2) * a->n};
-    cuuint32_t box[3] = {64, (cuuint32_t)kFeat, 1};
-    int rc = encode_map(&traw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc) return rc;
+    traw = tw;
+  } else {
+    {
+      // Whole 128-code blocks only: this tensor-map type wants the inner extent to be
+      // a multiple of 128 codes; the row pitch stays K/2 bytes.
+      cuuint64_t dims[3] = {(cuuint64_t)(a->k - a->k % 128), (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
+      cuuint64_t strides[2] = {(cuuint64_t)(a->k / 2), (cuuint64_t)(a->k / 2) * a->n};
+      cuuint32_t box[3] = {128, (cuuint32_t)kFeat, 1};
+      int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, a->w, dims, strides, box);
+      if (rc) return rc;
+    }
+    {
+      cuuint64_t dims[3] = {(cuuint64_t)(a->k / 2), (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
+      cuuint64_t strides[2] = {(cuuint64_t)(a->k / 2), (cuuint64_t)(a->k / 2) * a->n};
+      cuuint32_t box[3] = {64, (cuuint32_t)kFeat, 1};
+      int rc = encode_map(&traw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    }
   }
   const int64_t tile_bound = ((a->m + bt - 1) / bt + a->num_experts) * (int64_t)p.n_tiles;
   int grid = sm_count();
@@ -650,13 +687,17 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
   if (tile_bound < grid) grid = (int)tile_bound;
   if (grid < 1) grid = 1;
   // Small token tiles move two K blocks per pipeline stage.
-  if (x2) {
-    if (bt == 16) return launch_mx<16, 2, 2>(ta, tw, traw, p, grid, st);
-    return launch_mx<64, 2, 1>(ta, tw, traw, p, grid, st);
-  }
-  if (bt == 16) return launch_mx<16, 1, 2>(ta, tw, traw, p, grid, st);
-  if (bt == 64) return launch_mx<64, 1, 2>(ta, tw, traw, p, grid, st);
-  return launch_mx<128, 1, 1>(ta, tw, traw, p, grid, st);
+#define B200_MX_CASES(W8)                                                              \
+  if (x2) {                                                                            \
+    if (bt == 16) return launch_mx<16, 2, 2, W8>(ta, tw, traw, p, grid, st);           \
+    return launch_mx<64, 2, 1, W8>(ta, tw, traw, p, grid, st);                         \
+  }                                                                                    \
+  if (bt == 16) return launch_mx<16, 1, 2, W8>(ta, tw, traw, p, grid, st);             \
+  if (bt == 64) return launch_mx<64, 1, 2, W8>(ta, tw, traw, p, grid, st);             \
+  return launch_mx<128, 1, 1, W8>(ta, tw, traw, p, grid, st);
+  if (w8) { B200_MX_CASES(true) }
+  B200_MX_CASES(false)
+#undef B200_MX_CASES
 }
 
 }  // namespace b200moe

@@ -35,7 +35,6 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   TORCH_CHECK(ptr_D.is_contiguous(), "ptr_D must be contiguous");
   if (ptr_bias.has_value()) TORCH_CHECK(ptr_bias->is_contiguous(), "ptr_bias must be contiguous");
   TORCH_CHECK(!is_B_int4, "int4 grouped GEMM is not available in this build");
-  TORCH_CHECK(B_dtype != at::kFloat8_e5m2, "float8_e5m2 weights are not available in this build");
 
   const int64_t A_total_M = ptr_A.size(0), A_K = ptr_A.size(1);
   const int64_t B_E = ptr_B.size(0);
@@ -54,7 +53,7 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
     if (layout == 1) fmt = B200MOE_W_FP8_BLOCK_NK;
     if (layout == 2) fmt = B200MOE_W_FP8_BLOCK_KN;
   } else if (is_weight_fp8) {
-    fmt = B200MOE_W_FP8_TENSOR_KN;
+    fmt = B_dtype == at::kFloat8_e5m2 ? B200MOE_W_FP8E5M2_TENSOR_KN : B200MOE_W_FP8_TENSOR_KN;
   } else {
     fmt = B200MOE_W_BF16_KN;
     if (layout == 1) { fmt = B200MOE_W_BF16_NK; B_K = ptr_B.size(2); B_N = ptr_B.size(1); }
@@ -64,7 +63,7 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   TORCH_CHECK(B_E == num_experts, "ptr_B.size(0) must match num_experts");
   TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
               rows_per_expert.numel() == num_experts, "rows_per_expert must be int32 [num_experts]");
-  TORCH_CHECK(A_total_M == D_total_M || (is_B_mxfp4 && A_dtype == at::kFloat8_e4m3fn && A_total_M == 2 * D_total_M),
+  TORCH_CHECK(A_total_M == D_total_M || ((is_B_mxfp4 || (is_weight_fp8 && !is_B_fp8_block)) && A_dtype == at::kFloat8_e4m3fn && A_total_M == 2 * D_total_M),
               "ptr_A.size(0) must match ptr_D.size(0)");
   TORCH_CHECK(A_K == B_K && B_K == K, "ptr_A K dimension must match ptr_B logical K dimension and K");
   TORCH_CHECK(B_N == N && D_N == n_out, "ptr_B logical N dimension must match ptr_D N dimension and N");
@@ -102,10 +101,10 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   b200moe_gemm_args g = {};
   g.a = ptr_A.data_ptr();
   if (A_dtype == at::kFloat8_e4m3fn) {
-    TORCH_CHECK((is_B_fp8_block || is_B_mxfp4) && ptr_A_scale.has_value(),
-                "fp8 activations need block-scaled fp8 or mxfp4 weights and ptr_A_scale");
+    TORCH_CHECK((is_weight_fp8 || is_B_mxfp4) && ptr_A_scale.has_value(),
+                "fp8 activations need fp8 or mxfp4 weights and ptr_A_scale");
     g.a_dtype = B200MOE_FP8_E4M3;
-    if (is_B_mxfp4) {
+    if (is_B_mxfp4 || !is_B_fp8_block) {
       // ptr_A [planes * Total_M, K] (planes = 1 or 2, the second the residual), scales
       // int32 [planes, ceil(K / 128), Total_M]: the outputs of _C::b200_quant_mxfp8.
       const int64_t planes = A_total_M / D_total_M;

@@ -157,7 +157,7 @@ class XpuFusedMoe:
     of the recipe has that epilogue (MXFP4 with SwigluOAI).
 
     ``mxfp4_activations`` (not in the reference; keyword only) chooses what the
-    MXFP4 grouped GEMMs multiply the 4-bit weights with:
+    MXFP4 (and per-tensor fp8) grouped GEMMs multiply the quantised weights with:
     ``"mxfp8x2"`` (default where the shapes allow it: hidden and intermediate
     sizes multiples of 64) quantises the activations to two MXFP8 planes (e4m3
     codes with one power-of-two scale per 32 values, plus the residual
@@ -198,8 +198,8 @@ class XpuFusedMoe:
             raise NotImplementedError("int4 (w4a16) weights are not built for sm_100a yet")
         if is_mxfp8:
             raise NotImplementedError("mxfp8 weights are not built for sm_100a yet")
-        if w13.dtype == torch.float8_e5m2:
-            raise NotImplementedError("float8_e5m2 weights are not built for sm_100a yet")
+        if w13.dtype == torch.float8_e5m2 and is_block_fp8:
+            raise NotImplementedError("block-scaled float8_e5m2 weights are not built for sm_100a yet")
         if _is_env_enabled(REF_FUSED_MOE_ENV):
             raise NotImplementedError(
                 f"{REF_FUSED_MOE_ENV} selects the reference's eager qdq simulation, "
@@ -243,10 +243,19 @@ class XpuFusedMoe:
             raise ValueError("mxfp4_activations must be 'mxfp8x2', 'mxfp8' or 'bf16', "
                              f"got {mxfp4_activations!r}")
         self.mx_planes = 2 if mxfp4_activations == "mxfp8x2" else 1
-        hidden = w2.shape[-2] if is_mxfp4 else 0
-        self.mx_acts = bool(is_mxfp4 and mxfp4_activations != "bf16"
-                            and hidden % 64 == 0 and self.inter_size % 64 == 0
-                            and hidden >= 128 and self.inter_size >= 128)
+        # MXFP4 and per-tensor fp8 weights both run on the block-scaled tensor-core
+        # instruction against MXFP8 activation planes where the shapes allow it
+        # ([E,N,K/2] resp. [E,K,N] weights; K of both GEMMs a multiple of 64, N of 16)
+        if is_mxfp4:
+            hidden, gran = w2.shape[-2], 64
+        elif is_fp8:
+            hidden, gran = w2.shape[-1], 32
+        else:
+            hidden, gran = 0, 1
+        k2 = self.inter_size * self.inter_size_scale
+        self.mx_acts = bool((is_mxfp4 or is_fp8) and mxfp4_activations != "bf16"
+                            and hidden % gran == 0 and k2 % gran == 0 and hidden >= 128 and k2 >= 128
+                            and hidden % 16 == 0 and self.inter_size % 8 == 0)
         if self.mx_acts and self._act_kind == "silu" and fuse_activation:
             raise ValueError("the block-scaled MXFP4 GEMM has no fused SiLU epilogue")
         if fuse_activation and self._act_kind not in ("silu", "swigluoai"):
