@@ -82,6 +82,24 @@ int b200moe_topk_sigmoid(float* topk_weights, void* topk_indices,
                          const float* bias, double routed_scaling_factor,
                          b200moe_stream stream);
 
+/* sqrt(softplus) top-k gating (DeepSeek-V4 style).  Replaces `topk_softplus_sqrt`
+ * (csrc/moe/topk_softplus_sqrt_kernels.cpp:701-772, kernel :205-400; schema
+ * csrc/moe/torch_bindings.cpp:70-76).  score = sqrt(softplus(x)) (softplus(x) = x
+ * above 20); selection on score + correction_bias, ties to the lower index;
+ * weight = (score + bias) - bias; with `renormalize` divided by their sum (if
+ * positive), times routed_scaling_factor.  With `tid2eid` ([vocab, topk], same
+ * integer type as topk_indices) the ids of token t are row input_ids[t] of the
+ * table and the weights their scores (non-finite -> 0). */
+int b200moe_topk_softplus_sqrt(float* topk_weights, void* topk_indices,
+                               b200moe_dtype index_dtype,
+                               int32_t* token_expert_indices, const void* gating,
+                               b200moe_dtype gating_dtype, int64_t num_tokens,
+                               int num_experts, int topk, int renormalize,
+                               double routed_scaling_factor,
+                               const float* correction_bias,
+                               const void* input_ids, const void* tid2eid,
+                               b200moe_stream stream);
+
 /* Group-limited top-k on already activated scores.  Replaces `grouped_topk`
  * (csrc/moe/grouped_topk.cpp:782-876, kernels :404-695; schema
  * csrc/moe/torch_bindings.cpp:53-57).

@@ -53,6 +53,23 @@ def topk_gating(gating: torch.Tensor, topk: int, renormalize: bool, bias=None, s
     return w, idx, src
 
 
+def topk_softplus_sqrt(gating: torch.Tensor, topk: int, renormalize: bool, routed_scaling_factor: float = 1.0,
+                       bias=None, input_ids=None, tid2eid=None):
+    """-> (weights f32 [T,K], ids i32 [T,K], token_expert_indices i32 [T,K])"""
+    T, E = gating.shape
+    g = gating.float().contiguous()
+    w = torch.empty(T, topk, dtype=torch.float32)
+    idx = torch.empty(T, topk, dtype=torch.int32)
+    src = torch.empty(T, topk, dtype=torch.int32)
+    b = bias.float().contiguous() if bias is not None else None
+    ids = input_ids.long().contiguous() if input_ids is not None else None
+    tab = tid2eid.long().contiguous() if tid2eid is not None else None
+    lib().orc_topk_softplus_sqrt(_p(g), ctypes.c_int64(T), E, topk, int(renormalize),
+                                 ctypes.c_double(routed_scaling_factor), _p(b), _p(ids), _p(tab),
+                                 _p(w), _p(idx), _p(src))
+    return w, idx, src
+
+
 def grouped_topk(scores, scores_with_bias, n_group, topk_group, topk, renormalize,
                  routed_scaling_factor):
     """-> (values in scores.dtype [T,K], ids i32 [T,K]); descending biased score."""

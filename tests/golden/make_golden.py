@@ -48,7 +48,8 @@ def load_reference(root: str):
     import tests.test_fused_quant_activation as sq_t
     import tests.ops.mx_utils as mx_utils
     import tests.ops.swiglustep_and_mul_op as step_op
-    return dict(step=step_op, sbq=sbq_t, smx=smx_t, sq=sq_t, mxu=mx_utils, topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
+    import tests.test_topk_softplus_sqrt as sps_t
+    return dict(sps=sps_t, step=step_op, sbq=sbq_t, smx=smx_t, sq=sq_t, mxu=mx_utils, topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
                 layer=layer_t, act=act_op, swi=swi_op, fp8=fp8_t, mu=mu)
 
 
@@ -223,6 +224,25 @@ def main():
                           gelu_tanh=ref["act"].GeluAndMul.forward_native(ref["act"].GeluAndMul("tanh"), t),
                           swiglustep=ref["step"].SwigluStepAndMul.forward_native(ref["step"].SwigluStepAndMul(7.0), t))
     torch.save(acts, OUT / "activations2.pt")
+
+    # ---- sqrt(softplus) routing (tests/test_topk_softplus_sqrt.py:19-47) ------------------------------
+    g4 = torch.Generator().manual_seed(3)
+    cases = []
+    for (T, E, K, renorm, rsf, dt, use_hash) in [(33, 256, 8, True, 1.5, torch.float32, False),
+                                                 (17, 384, 6, False, 1.0, torch.bfloat16, False),
+                                                 (9, 128, 16, True, 2.5, torch.float16, False),
+                                                 (21, 256, 8, True, 2.5, torch.float32, True)]:
+        gating = torch.randn(T, E, generator=g4).to(dt)
+        bias = torch.randn(E, generator=g4)
+        ids = table = None
+        if use_hash:
+            table = torch.stack([torch.randperm(E, generator=g4)[:K] for _ in range(64)]).to(torch.int32)
+            ids = torch.randint(0, 64, (T,), generator=g4, dtype=torch.int32)
+            bias = None
+        w, i = ref["sps"]._torch_topk_softplus_sqrt(gating, K, renorm, rsf, bias, ids, table)
+        cases.append(dict(gating=gating, bias=bias, topk=K, renormalize=renorm, routed_scaling_factor=rsf,
+                          input_ids=ids, tid2eid=table, weights=w, ids=i))
+    torch.save(cases, OUT / "routing_softplus_sqrt.pt")
     print("wrote", sorted(p.name for p in OUT.glob("*.pt")))
 
 

@@ -102,3 +102,57 @@ def test_grouped_topk_reference_vectors_ties_and_errors(native):
         torch.ops._moe_C.grouped_topk(s, s, 7, 2, 4, True, 1.0)
     with pytest.raises(RuntimeError, match="n_group should be smaller than or equal to 32"):
         torch.ops._moe_C.grouped_topk(s, s, 64, 2, 4, True, 1.0)
+
+
+def _softplus_sqrt(gating, K, renorm, rsf, bias=None, input_ids=None, table=None, index_dtype=torch.int32):
+    T = gating.shape[0]
+    w = torch.empty(T, K, dtype=torch.float32, device=DEV)
+    ids = torch.empty(T, K, dtype=index_dtype, device=DEV)
+    src = torch.empty(T, K, dtype=torch.int32, device=DEV)
+    mv = lambda t: t.to(DEV) if t is not None else None
+    torch.ops._moe_C.topk_softplus_sqrt(w, ids, src, gating.to(DEV), renorm, rsf, mv(bias), mv(input_ids), mv(table))
+    return w.cpu(), ids.cpu(), src.cpu()
+
+
+@pytest.mark.parametrize("T", [1, 33, 128, 1024])
+@pytest.mark.parametrize("E", [128, 256, 384, 512, 60])
+@pytest.mark.parametrize("K", [6, 8, 16])
+@pytest.mark.parametrize("renorm,rsf", [(True, 1.0), (False, 1.5)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_topk_softplus_sqrt_bit_exact(native, T, E, K, renorm, rsf, dtype):
+    """Parameters of tests/test_topk_softplus_sqrt.py:243-256 of the reference; ids,
+    weights and source indices equal to the C oracle bit for bit."""
+    g = torch.Generator().manual_seed(T + E + K)
+    gating = (torch.randn(T, E, generator=g) * 3).to(dtype)
+    bias = torch.randn(E, generator=g)
+    for b in (bias, None):
+        w, ids, src = _softplus_sqrt(gating, K, renorm, rsf, b)
+        ow, oi, osrc = co.topk_softplus_sqrt(gating, K, renorm, rsf, b)
+        assert torch.equal(ids, oi) and torch.equal(src, osrc)
+        assert torch.equal(w, ow), f"max diff {(w - ow).abs().max()}"
+
+
+@pytest.mark.parametrize("index_dtype", [torch.int32, torch.int64])
+def test_topk_softplus_sqrt_hash_and_reference_vectors(native, index_dtype):
+    g = torch.Generator().manual_seed(5)
+    T, E, K = 100, 256, 8
+    gating = torch.randn(T, E, generator=g)
+    gating[0, :4] = torch.tensor([float("inf"), float("nan"), 25.0, -50.0])
+    table = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(64)]).to(index_dtype)
+    table[0, :4] = torch.tensor([0, 1, 2, 3])
+    input_ids = torch.randint(0, 64, (T,), generator=g).to(index_dtype)
+    input_ids[0] = 0
+    w, ids, src = _softplus_sqrt(gating, K, True, 2.5, None, input_ids, table, index_dtype)
+    ow, oi, osrc = co.topk_softplus_sqrt(gating, K, True, 2.5, None, input_ids, table)
+    assert torch.equal(ids.long(), oi.long()) and torch.equal(src, osrc) and torch.equal(w, ow)
+    assert torch.equal(ids.long(), table[input_ids.long()].long())
+    with pytest.raises(RuntimeError, match="input_ids is required for hash MoE"):
+        _softplus_sqrt(gating, K, True, 1.0, None, None, table, index_dtype)
+    if index_dtype == torch.int32:
+        for c in load_golden("routing_softplus_sqrt.pt"):
+            w, ids, _ = _softplus_sqrt(c["gating"], c["topk"], c["renormalize"], c["routed_scaling_factor"],
+                                       c["bias"], c["input_ids"], c["tid2eid"])
+            s_ref, i_ref = c["ids"].sort(dim=-1)
+            s_our, i_our = ids.sort(dim=-1)
+            assert torch.equal(s_ref, s_our)
+            torch.testing.assert_close(c["weights"].gather(1, i_ref), w.gather(1, i_our), atol=2e-2, rtol=1e-2)

@@ -191,3 +191,17 @@ def test_other_activations_against_reference_vectors():
         torch.testing.assert_close(to.gelu_and_mul(x), c["gelu"], **tol)
         torch.testing.assert_close(to.gelu_and_mul(x, "tanh"), c["gelu_tanh"], **tol)
         torch.testing.assert_close(to.swiglustep_and_mul(x), c["swiglustep"], **tol)
+
+
+def test_topk_softplus_sqrt_against_reference_vectors():
+    """tests/test_topk_softplus_sqrt.py:283-289 of the reference: ids equal as sorted
+    sets, weights within atol 2e-2 / rtol 1e-2 after the same sort."""
+    for c in load_golden("routing_softplus_sqrt.pt"):
+        w, ids, src = co.topk_softplus_sqrt(c["gating"], c["topk"], c["renormalize"], c["routed_scaling_factor"],
+                                            c["bias"], c["input_ids"], c["tid2eid"])
+        s_ref, i_ref = c["ids"].sort(dim=-1)
+        s_our, i_our = ids.sort(dim=-1)
+        assert torch.equal(s_ref, s_our)
+        torch.testing.assert_close(c["weights"].gather(1, i_ref), w.gather(1, i_our), atol=2e-2, rtol=1e-2)
+        T, K = ids.shape
+        assert torch.equal(src, (torch.arange(K).view(1, K) * T + torch.arange(T).view(T, 1)).int())

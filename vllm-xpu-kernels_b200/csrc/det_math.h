@@ -73,3 +73,58 @@ DM_HD float dm_sigmoidf(float x) {
   float e = dm_expf(-x);
   return DM_DIV(1.0f, DM_ADD(1.0f, e));
 }
+
+// log(x) for positive normal x: x = m * 2^e with m in [sqrt(1/2), sqrt(2)),
+// degree-9 polynomial in m - 1 (the Cephes logf scheme), every step a
+// correctly rounded IEEE operation.  About 1 ulp.  NaN and +inf are returned as is.
+DM_HD float dm_logf(float x) {
+  if (!(x < INFINITY)) return x;   // NaN and +inf pass through
+  uint32_t bits;
+#if defined(__CUDA_ARCH__)
+  bits = __float_as_uint(x);
+#else
+  memcpy(&bits, &x, sizeof(bits));
+#endif
+  int e = (int)(bits >> 23) - 126;
+  const uint32_t mb = (bits & 0x007fffffu) | 0x3f000000u;   // m in [0.5, 1)
+  float m;
+#if defined(__CUDA_ARCH__)
+  m = __uint_as_float(mb);
+#else
+  memcpy(&m, &mb, sizeof(m));
+#endif
+  if (m < 0.70710678118654752f) {
+    e -= 1;
+    m = DM_ADD(DM_ADD(m, m), -1.0f);
+  } else {
+    m = DM_ADD(m, -1.0f);
+  }
+  const float z = DM_MUL(m, m);
+  float p = 7.0376836292e-2f;
+  p = DM_FMA(p, m, -1.1514610310e-1f);
+  p = DM_FMA(p, m, 1.1676998740e-1f);
+  p = DM_FMA(p, m, -1.2420140846e-1f);
+  p = DM_FMA(p, m, 1.4249322787e-1f);
+  p = DM_FMA(p, m, -1.6668057665e-1f);
+  p = DM_FMA(p, m, 2.0000714765e-1f);
+  p = DM_FMA(p, m, -2.4999993993e-1f);
+  p = DM_FMA(p, m, 3.3333331174e-1f);
+  float y = DM_MUL(DM_MUL(p, m), z);
+  const float fe = (float)e;
+  y = DM_FMA(-2.12194440e-4f, fe, y);
+  y = DM_FMA(-0.5f, z, y);
+  float r = DM_ADD(m, y);
+  r = DM_FMA(0.693359375f, fe, r);
+  return r;
+}
+
+// sqrt(softplus(x)) with softplus(x) = x for x > 20, else log(1 + exp(x))
+// (csrc/moe/topk_softplus_sqrt_kernels.cpp:233-261, 303-309 of vllm-xpu-kernels).
+DM_HD float dm_softplus_sqrtf(float x) {
+  const float sp = (x > 20.0f) ? x : dm_logf(DM_ADD(1.0f, dm_expf(x)));
+#if defined(__CUDA_ARCH__)
+  return __fsqrt_rn(sp);
+#else
+  return sqrtf(sp);
+#endif
+}

@@ -481,9 +481,9 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (p.bias != nullptr && feat_ok) bias_v = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat);
       const float w_mul = kW8 ? p.w_tensor_scale[ti.e] : 1.0f;
       const uint32_t a = acc_it & 1;
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
-        *abort_flag = 1; ok = false; break;
-      }
+      // a whole tile's MMAs away: poll from one lane, sleeping in between, so that the
+      // wait does not take issue slots from the feeder warp on the same scheduler
+      if (!ptx::mbar_wait_warp(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag, 128)) { ok = false; break; }
       ptx::tc_fence_after();
 #pragma unroll
       for (int c0 = 0; c0 < BT; c0 += kChunk) {

@@ -1,4 +1,4 @@
-// Router kernels: softmax / sigmoid top-k gating and group-limited top-k.
+// Router kernels: softmax / sigmoid / sqrt(softplus) top-k gating and group-limited top-k.
 //
 // One row (token) is handled by a power-of-two group of R <= 32 lanes; lane j
 // owns the expert columns j, j+R, j+2R, ... so that global loads coalesce.  All
@@ -8,7 +8,8 @@
 // exp() and sigmoid() come from det_math.h, so the weights can be reproduced
 // bit-for-bit on a CPU.
 //
-// Behaviour follows csrc/moe/topk.cpp:395-583 (gating) and
+// Behaviour follows csrc/moe/topk.cpp:395-583 (gating),
+// csrc/moe/topk_softplus_sqrt_kernels.cpp:205-400 (sqrt-softplus gating) and
 // csrc/moe/grouped_topk.cpp:404-447, 525-678 (grouped) of vllm-xpu-kernels.
 #include "common.cuh"
 #include "det_math.h"
@@ -28,7 +29,9 @@ __device__ __forceinline__ void store_index(void* base, b200moe_dtype dt,
 }
 
 // R lanes per row, VPT columns per lane.  E <= R * VPT.
-template <typename T, int R, int VPT, bool kSoftmax>
+// kMode 0: softmax, 1: sigmoid, 2: sqrt(softplus) (its weight is the biased
+// score minus the bias again, as the reference computes it).
+template <typename T, int R, int VPT, int kMode>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 topk_gating_kernel(const T* __restrict__ gating, float* __restrict__ out_w,
                    void* __restrict__ out_idx, b200moe_dtype idx_dtype,
@@ -51,7 +54,7 @@ topk_gating_kernel(const T* __restrict__ gating, float* __restrict__ out_w,
     p[i] = (c < E) ? to_f32<T>(src[c]) : -INFINITY;
   }
 
-  if (kSoftmax) {
+  if (kMode == 0) {
     float m = p[0];
 #pragma unroll
     for (int i = 1; i < VPT; ++i) m = fmaxf(m, p[i]);
@@ -71,12 +74,18 @@ topk_gating_kernel(const T* __restrict__ gating, float* __restrict__ out_w,
     const float rs = __fdiv_rn(1.f, s);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) p[i] = __fmul_rn(p[i], rs);
-  } else {
+  } else if (kMode == 1) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = sub + i * R;
       // The sigmoid is rounded through the input type, as the reference does.
       p[i] = (c < E) ? to_f32<T>(from_f32<T>(dm_sigmoidf(p[i]))) : 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = sub + i * R;
+      p[i] = (c < E) ? dm_softplus_sqrtf(p[i]) : 0.f;
     }
   }
 
@@ -109,6 +118,7 @@ topk_gating_kernel(const T* __restrict__ gating, float* __restrict__ out_w,
       const int oe = __shfl_xor_sync(0xffffffffu, e, mask);
       if (ov > best_v || (ov == best_v && oe < e)) { best_v = ov; best_p = op; e = oe; }
     }
+    if (kMode == 2 && bias != nullptr) best_p = __fsub_rn(best_v, bias[e]);
     sum_val = __fadd_rn(sum_val, best_p);
     if (live && sub == 0) {
       const int64_t pos = row * K + k;
@@ -132,7 +142,7 @@ topk_gating_kernel(const T* __restrict__ gating, float* __restrict__ out_w,
   }
 }
 
-template <typename T, bool kSoftmax>
+template <typename T, int kMode>
 int launch_gating(const T* gating, float* w, void* idx, b200moe_dtype idx_dtype,
                   int32_t* src, const float* bias, int64_t T_, int E, int K,
                   bool renorm, float rsf, cudaStream_t st) {
@@ -140,7 +150,7 @@ int launch_gating(const T* gating, float* w, void* idx, b200moe_dtype idx_dtype,
   {                                                                             \
     constexpr int rows_per_block = kWarpsPerBlock * (32 / R_);                  \
     const unsigned grid = (unsigned)((T_ + rows_per_block - 1) / rows_per_block); \
-    topk_gating_kernel<T, R_, VPT_, kSoftmax>                                   \
+    topk_gating_kernel<T, R_, VPT_, kMode>                                      \
         <<<grid, kWarpsPerBlock * 32, 0, st>>>(gating, w, idx, idx_dtype, src,  \
                                                bias, T_, E, K, renorm, rsf);    \
   }
@@ -160,12 +170,12 @@ int launch_gating(const T* gating, float* w, void* idx, b200moe_dtype idx_dtype,
   return B200MOE_OK;
 }
 
-int gating_entry(bool softmax, float* topk_weights, void* topk_indices,
+int gating_entry(int mode, float* topk_weights, void* topk_indices,
                  b200moe_dtype index_dtype, int32_t* token_expert_indices,
                  const void* gating, b200moe_dtype gating_dtype,
                  int64_t num_tokens, int num_experts, int topk, int renormalize,
                  const float* bias, double rsf, b200moe_stream stream) {
-  const char* name = softmax ? "topk_softmax" : "topk_sigmoid";
+  const char* name = mode == 0 ? "topk_softmax" : (mode == 1 ? "topk_sigmoid" : "topk_softplus_sqrt");
   B200_CHECK_ARG(index_dtype == B200MOE_I32 || index_dtype == B200MOE_U32 ||
                      index_dtype == B200MOE_I64,
                  "%s: topk_indices must be int32, uint32 or int64", name);
@@ -179,12 +189,17 @@ int gating_entry(bool softmax, float* topk_weights, void* topk_indices,
                  "%s: null pointer", name);
   cudaStream_t st = as_stream(stream);
   B200_DISPATCH_FLOAT(gating_dtype, name, {
-    if (softmax)
-      return launch_gating<scalar_t, true>(
+    if (mode == 0)
+      return launch_gating<scalar_t, 0>(
           (const scalar_t*)gating, topk_weights, topk_indices, index_dtype,
           token_expert_indices, bias, num_tokens, num_experts, topk,
           renormalize != 0, (float)rsf, st);
-    return launch_gating<scalar_t, false>(
+    if (mode == 2)
+      return launch_gating<scalar_t, 2>(
+          (const scalar_t*)gating, topk_weights, topk_indices, index_dtype,
+          token_expert_indices, bias, num_tokens, num_experts, topk,
+          renormalize != 0, (float)rsf, st);
+    return launch_gating<scalar_t, 1>(
         (const scalar_t*)gating, topk_weights, topk_indices, index_dtype,
         token_expert_indices, bias, num_tokens, num_experts, topk,
         renormalize != 0, (float)rsf, st);
@@ -346,7 +361,7 @@ extern "C" int b200moe_topk_softmax(float* topk_weights, void* topk_indices,
                                     int64_t num_tokens, int num_experts, int topk,
                                     int renormalize, const float* bias,
                                     b200moe_stream stream) {
-  return gating_entry(true, topk_weights, topk_indices, index_dtype,
+  return gating_entry(0, topk_weights, topk_indices, index_dtype,
                       token_expert_indices, gating, gating_dtype, num_tokens,
                       num_experts, topk, renormalize, bias, 1.0, stream);
 }
@@ -360,7 +375,7 @@ extern "C" int b200moe_topk_sigmoid(float* topk_weights, void* topk_indices,
                                     int renormalize, const float* bias,
                                     double routed_scaling_factor,
                                     b200moe_stream stream) {
-  return gating_entry(false, topk_weights, topk_indices, index_dtype,
+  return gating_entry(1, topk_weights, topk_indices, index_dtype,
                       token_expert_indices, gating, gating_dtype, num_tokens,
                       num_experts, topk, renormalize, bias,
                       routed_scaling_factor, stream);
@@ -411,5 +426,75 @@ extern "C" int b200moe_grouped_topk(void* topk_values, int32_t* topk_indices,
   });
 #undef B200_GT_CASE
   B200_LAUNCH_OK("grouped_topk_kernel");
+  return B200MOE_OK;
+}
+
+namespace b200moe {
+namespace {
+__device__ __forceinline__ int64_t load_index(const void* base, b200moe_dtype dt, int64_t pos) {
+  if (dt == B200MOE_I64) return reinterpret_cast<const int64_t*>(base)[pos];
+  if (dt == B200MOE_U32) return reinterpret_cast<const uint32_t*>(base)[pos];
+  return reinterpret_cast<const int32_t*>(base)[pos];
+}
+
+// Hash routing (csrc/moe/topk_softplus_sqrt_kernels.cpp:238-301): the expert ids of
+// a token come from row input_ids[t] of the table tid2eid [vocab, K]; weights
+// are sqrt(softplus(logit)) of those experts (non-finite -> 0), renormalised
+// in k order.  One thread per token.
+template <typename T>
+__global__ void __launch_bounds__(128)
+softplus_sqrt_hash_kernel(const T* __restrict__ gating, float* __restrict__ out_w,
+                          void* __restrict__ out_idx, b200moe_dtype idx_dtype,
+                          int32_t* __restrict__ out_src, const void* __restrict__ input_ids,
+                          const void* __restrict__ tid2eid, int64_t num_rows, int E, int K,
+                          bool renorm, float rsf) {
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= num_rows) return;
+  const int64_t tok = load_index(input_ids, idx_dtype, row);
+  float sum = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int e = (int)load_index(tid2eid, idx_dtype, tok * K + k);
+    float w = 0.f;
+    if (e >= 0 && e < E) {
+      w = dm_softplus_sqrtf(to_f32<T>(gating[row * (int64_t)E + e]));
+      if (!isfinite(w)) w = 0.f;
+    }
+    const int64_t pos = row * K + k;
+    out_w[pos] = w;
+    store_index(out_idx, idx_dtype, pos, (e >= 0 && e < E) ? e : E);
+    out_src[pos] = (int32_t)((int64_t)k * num_rows + row);
+    if (renorm) sum = __fadd_rn(sum, w);
+  }
+  float scale = rsf;
+  if (renorm) scale = __fdiv_rn(scale, sum > 0.f ? sum : 1.f);
+  for (int k = 0; k < K; ++k) out_w[row * K + k] = __fmul_rn(out_w[row * K + k], scale);
+}
+}  // namespace
+}  // namespace b200moe
+
+extern "C" int b200moe_topk_softplus_sqrt(float* topk_weights, void* topk_indices,
+                                          b200moe_dtype index_dtype, int32_t* token_expert_indices,
+                                          const void* gating, b200moe_dtype gating_dtype,
+                                          int64_t num_tokens, int num_experts, int topk, int renormalize,
+                                          double routed_scaling_factor, const float* correction_bias,
+                                          const void* input_ids, const void* tid2eid,
+                                          b200moe_stream stream) {
+  if (tid2eid == nullptr)
+    return gating_entry(2, topk_weights, topk_indices, index_dtype, token_expert_indices, gating,
+                        gating_dtype, num_tokens, num_experts, topk, renormalize, correction_bias,
+                        routed_scaling_factor, stream);
+  B200_CHECK_ARG(input_ids != nullptr, "input_ids is required for hash MoE");
+  B200_CHECK_ARG(index_dtype == B200MOE_I32 || index_dtype == B200MOE_U32 || index_dtype == B200MOE_I64,
+                 "topk_softplus_sqrt: topk_indices must be int32, uint32 or int64");
+  B200_CHECK_ARG(num_experts >= 1 && topk >= 1 && num_tokens >= 0, "topk_softplus_sqrt: bad sizes");
+  if (num_tokens == 0) return B200MOE_OK;
+  B200_CHECK_ARG(topk_weights && topk_indices && token_expert_indices && gating, "topk_softplus_sqrt: null pointer");
+  const unsigned grid = (unsigned)((num_tokens + 127) / 128);
+  B200_DISPATCH_FLOAT(gating_dtype, "topk_softplus_sqrt", {
+    b200moe::softplus_sqrt_hash_kernel<scalar_t><<<grid, 128, 0, b200moe::as_stream(stream)>>>(
+        (const scalar_t*)gating, topk_weights, topk_indices, index_dtype, token_expert_indices, input_ids,
+        tid2eid, num_tokens, num_experts, topk, renormalize != 0, (float)routed_scaling_factor);
+  });
+  B200_LAUNCH_OK("softplus_sqrt_hash_kernel");
   return B200MOE_OK;
 }

@@ -55,6 +55,50 @@ void topk_sigmoid(at::Tensor& topk_weights, at::Tensor& topk_indices,
       current_stream()));
 }
 
+// csrc/moe/topk_softplus_sqrt_kernels.cpp:596-772 of the reference.
+void topk_softplus_sqrt(at::Tensor& topk_weights, at::Tensor& topk_indices,
+                        at::Tensor& token_expert_indices, at::Tensor& gating_output, bool renormalize,
+                        double routed_scaling_factor, const std::optional<at::Tensor>& correction_bias,
+                        const std::optional<at::Tensor>& input_ids, const std::optional<at::Tensor>& tid2eid) {
+  check_cuda(gating_output, "gating_output");
+  const int num_experts = gating_output.size(-1);
+  const int64_t num_tokens = num_experts ? gating_output.numel() / num_experts : 0;
+  const int topk = topk_weights.size(-1);
+  TORCH_CHECK(topk_indices.scalar_type() == at::kInt || topk_indices.scalar_type() == at::kUInt32 ||
+              topk_indices.scalar_type() == at::kLong,
+              "topk_indices must be int32, uint32 or int64");
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, "topk_weights must be float32");
+  TORCH_CHECK(gating_output.scalar_type() == at::kFloat || gating_output.scalar_type() == at::kHalf ||
+              gating_output.scalar_type() == at::kBFloat16,
+              "Unsupported gating_output data type: ", gating_output.scalar_type());
+  TORCH_CHECK(gating_output.is_contiguous() && topk_weights.is_contiguous() &&
+              topk_indices.is_contiguous() && token_expert_indices.is_contiguous(),
+              "topk_softplus_sqrt expects contiguous tensors");
+  if (correction_bias.has_value())
+    TORCH_CHECK(correction_bias->scalar_type() == at::kFloat && correction_bias->is_contiguous(),
+                "correction_bias must be contiguous float32");
+  const void* ids_ptr = nullptr;
+  const void* table_ptr = nullptr;
+  if (tid2eid.has_value()) {
+    TORCH_CHECK(input_ids.has_value(), "input_ids is required for hash MoE");
+    TORCH_CHECK(input_ids->scalar_type() == topk_indices.scalar_type(),
+                "input_ids dtype must match topk_indices dtype");
+    TORCH_CHECK(tid2eid->scalar_type() == topk_indices.scalar_type(),
+                "tid2eid dtype must match topk_indices dtype");
+    TORCH_CHECK(input_ids->is_contiguous() && tid2eid->is_contiguous() && input_ids->numel() == num_tokens &&
+                tid2eid->size(-1) == topk, "input_ids must be [num_tokens] and tid2eid [vocab, topk]");
+    ids_ptr = input_ids->data_ptr();
+    table_ptr = tid2eid->data_ptr();
+  }
+  const c10::cuda::CUDAGuard guard(gating_output.device());
+  check_status(b200moe_topk_softplus_sqrt(
+      topk_weights.data_ptr<float>(), topk_indices.data_ptr(), index_dtype(topk_indices),
+      token_expert_indices.data_ptr<int32_t>(), gating_output.data_ptr(),
+      float_dtype(gating_output, "topk_softplus_sqrt"), num_tokens, num_experts, topk, renormalize,
+      routed_scaling_factor, correction_bias.has_value() ? correction_bias->data_ptr<float>() : nullptr, ids_ptr,
+      table_ptr, current_stream()));
+}
+
 std::tuple<at::Tensor, at::Tensor> grouped_topk(const at::Tensor& scores,
                                                 const at::Tensor& scores_with_bias,
                                                 int64_t n_group, int64_t topk_group, int64_t topk,
@@ -305,6 +349,11 @@ TORCH_LIBRARY_FRAGMENT(_moe_C, m) {
       "token_expert_indices, Tensor gating_output, bool renormalize, Tensor? "
       "bias, float routed_scaling_factor) -> ()");
   m.def(
+      "topk_softplus_sqrt(Tensor! topk_weights, Tensor! topk_indices, "
+      "Tensor! token_expert_indices, Tensor gating_output, bool renormalize, "
+      "float routed_scaling_factor, Tensor? correction_bias=None, Tensor? "
+      "input_ids=None, Tensor? tid2eid=None) -> ()");
+  m.def(
       "moe_gather(Tensor! output, Tensor moe_output, Tensor topk_weights, "
       "Tensor unpermuted_row_to_permuted_row, int num_experts) -> ()");
   m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
@@ -327,6 +376,7 @@ TORCH_LIBRARY_IMPL(_moe_C, CUDA, m) {
   m.impl("moe_sum", &moe_sum);
   m.impl("moe_align_block_size", &moe_align_block_size);
   m.impl("grouped_topk", &grouped_topk);
+  m.impl("topk_softplus_sqrt", &topk_softplus_sqrt);
   m.impl("topk_softmax", &topk_softmax);
   m.impl("topk_sigmoid", &topk_sigmoid);
   m.impl("moe_gather", &moe_gather);
