@@ -168,6 +168,19 @@ int b200moe_moe_align_block_size_noalloc(const void* topk_ids,
                                          b200moe_stream stream);
 size_t b200moe_noalloc_scratch_capacity(void);
 
+/* Replaces `batched_moe_align_block_size` (csrc/moe/moe_align_sum_kernels.cpp:1183-1222,
+ * kernel :25-133; schema csrc/moe/torch_bindings.cpp:24-33).  Batch b owns token
+ * slots [b*max_tokens, (b+1)*max_tokens) and has batch_num_tokens[b] of them in
+ * use; sorted_ids [B * ceil(max_tokens/block) * block] lists them batch by batch,
+ * each batch padded to whole blocks with the sentinel B*max_tokens; batch_ids holds
+ * the batch of every block (-1 for unused blocks). */
+int b200moe_batched_moe_align_block_size(int max_tokens_per_batch, int block_size,
+                                         const int32_t* batch_num_tokens,
+                                         int num_batches, int32_t* sorted_ids,
+                                         int32_t* batch_ids,
+                                         int32_t* num_tokens_post_pad,
+                                         b200moe_stream stream);
+
 /* Replaces `init_expert_map` (csrc/moe/init_expert_map.cpp:78-95; schema
  * csrc/moe/torch_bindings.cpp:93-98). expert_map has num_local*ep_size ints. */
 int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,

@@ -116,3 +116,15 @@ def init_expert_map(n_local, ep_rank, ep_size):
 
 def expf(x: float) -> float:
     return lib().orc_expf_export(ctypes.c_float(x))
+
+
+def batched_moe_align_block_size(max_tokens_per_batch: int, block_size: int, counts: torch.Tensor):
+    """-> (sorted_ids i32, block_ids i32, num_tokens_post_pad i32 [1])"""
+    B = counts.numel()
+    n = (max_tokens_per_batch + block_size - 1) // block_size * block_size * B
+    sorted_ids = torch.empty(n, dtype=torch.int32)
+    block_ids = torch.empty(n // block_size, dtype=torch.int32)
+    post = torch.empty(1, dtype=torch.int32)
+    c = counts.int().contiguous()
+    lib().orc_batched_align(_p(c), B, max_tokens_per_batch, block_size, _p(sorted_ids), _p(block_ids), _p(post))
+    return sorted_ids, block_ids, post

@@ -53,6 +53,42 @@ def load_reference(root: str):
                 layer=layer_t, act=act_op, swi=swi_op, fp8=fp8_t, mu=mu)
 
 
+def capture_batched_align(align_t, max_tokens, num_experts, block, empty):
+    """The reference's expected outputs for batched_moe_align_block_size live in a
+    function nested in its test (tests/test_moe_align_block_size.py:340-417); run
+    that test on CPU with the op replaced by a recorder and keep what it compares."""
+    rec = {}
+    real_to, real_close = torch.Tensor.to, torch.testing.assert_close
+
+    def fake_to(self, *a, **k):
+        if a and a[0] == "xpu":
+            return self
+        return real_to(self, *a, **k)
+
+    def fake_op(mt, bs, counts):
+        rec["counts"] = counts.clone()
+        n = (mt + bs - 1) // bs * bs * counts.numel()
+        return (torch.zeros(n, dtype=torch.int32), torch.zeros(n // bs, dtype=torch.int32),
+                torch.zeros(1, dtype=torch.int32))
+
+    def fake_close(expected, actual, **k):
+        rec.setdefault("expected", []).append(expected.clone())
+
+    torch.Tensor.to, torch.testing.assert_close = fake_to, fake_close
+    old_op = align_t.batched_moe_align_block_size
+    align_t.batched_moe_align_block_size = fake_op
+    try:
+        align_t.test_batched_moe_align_block_size.__wrapped__(max_tokens, num_experts, block, empty) \
+            if hasattr(align_t.test_batched_moe_align_block_size, "__wrapped__") \
+            else align_t.test_batched_moe_align_block_size(max_tokens, num_experts, block, empty)
+    finally:
+        torch.Tensor.to, torch.testing.assert_close = real_to, real_close
+        align_t.batched_moe_align_block_size = old_op
+    s_ids, b_ids, post = rec["expected"]
+    return dict(max_tokens=max_tokens, block=block, counts=rec["counts"], sorted_ids=s_ids, block_ids=b_ids,
+                num_post_pad=post)
+
+
 def main():
     root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     ref = load_reference(root)
@@ -243,6 +279,12 @@ def main():
         cases.append(dict(gating=gating, bias=bias, topk=K, renormalize=renorm, routed_scaling_factor=rsf,
                           input_ids=ids, tid2eid=table, weights=w, ids=i))
     torch.save(cases, OUT / "routing_softplus_sqrt.pt")
+
+    # ---- batched align (expected values recorded from the reference's own test) -----------------------
+    torch.manual_seed(4)
+    cases = [capture_batched_align(ref["align"], mt, ne, bs, empty)
+             for (mt, ne, bs, empty) in [(13, 8, 8, False), (16, 16, 16, True), (512, 64, 32, False), (13, 32, 64, True)]]
+    torch.save(cases, OUT / "batched_align.pt")
     print("wrote", sorted(p.name for p in OUT.glob("*.pt")))
 
 

@@ -136,3 +136,33 @@ def test_init_expert_map(native):
         assert torch.equal(m.cpu(), co.init_expert_map(n, r, s))
     with pytest.raises(RuntimeError, match="expert_map must be int32"):
         torch.ops._moe_C.init_expert_map(torch.empty(8, dtype=torch.int64, device=DEV), 4, 0, 2)
+
+
+@pytest.mark.parametrize("max_tokens", [13, 16, 512])
+@pytest.mark.parametrize("num_batches", [1, 8, 64, 1000])
+@pytest.mark.parametrize("block", [8, 16, 64])
+@pytest.mark.parametrize("empty", [False, True])
+def test_batched_moe_align_block_size_exact(native, max_tokens, num_batches, block, empty):
+    """Parameters of tests/test_moe_align_block_size.py:336-339 of the reference (plus a
+    1000-batch case); exact against the C oracle and the recorded reference values."""
+    g = torch.Generator().manual_seed(max_tokens + num_batches + block)
+    counts = torch.randint(0, max_tokens + 1, (num_batches,), generator=g, dtype=torch.int32)
+    if empty:
+        counts[torch.randperm(num_batches, generator=g)[:num_batches // 2]] = 0
+    n = (max_tokens + block - 1) // block * block * num_batches
+    s = torch.empty(n, dtype=torch.int32, device=DEV)
+    b = torch.empty(n // block, dtype=torch.int32, device=DEV)
+    p = torch.empty(1, dtype=torch.int32, device=DEV)
+    torch.ops._moe_C.batched_moe_align_block_size(max_tokens, block, counts.to(DEV), s, b, p)
+    os_, ob, op = co.batched_moe_align_block_size(max_tokens, block, counts)
+    assert torch.equal(s.cpu(), os_) and torch.equal(b.cpu(), ob) and torch.equal(p.cpu(), op)
+
+
+def test_batched_moe_align_reference_vectors(native):
+    for c in load_golden("batched_align.pt"):
+        s = torch.empty_like(c["sorted_ids"], device=DEV)
+        b = torch.empty_like(c["block_ids"], device=DEV)
+        p = torch.empty(1, dtype=torch.int32, device=DEV)
+        torch.ops._moe_C.batched_moe_align_block_size(c["max_tokens"], c["block"], c["counts"].to(DEV), s, b, p)
+        assert torch.equal(s.cpu(), c["sorted_ids"]) and torch.equal(b.cpu(), c["block_ids"])
+        assert torch.equal(p.cpu(), c["num_post_pad"])

@@ -205,3 +205,11 @@ def test_topk_softplus_sqrt_against_reference_vectors():
         torch.testing.assert_close(c["weights"].gather(1, i_ref), w.gather(1, i_our), atol=2e-2, rtol=1e-2)
         T, K = ids.shape
         assert torch.equal(src, (torch.arange(K).view(1, K) * T + torch.arange(T).view(T, 1)).int())
+
+
+def test_batched_align_against_reference_vectors():
+    """Expected values recorded from the reference's own test
+    (tests/test_moe_align_block_size.py:340-417), compared exactly."""
+    for c in load_golden("batched_align.pt"):
+        s, b, p = co.batched_moe_align_block_size(c["max_tokens"], c["block"], c["counts"])
+        assert torch.equal(s, c["sorted_ids"]) and torch.equal(b, c["block_ids"]) and torch.equal(p, c["num_post_pad"])

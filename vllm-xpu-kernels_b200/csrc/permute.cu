@@ -511,6 +511,65 @@ extern "C" int b200moe_moe_align_block_size(
   return run_sort<0>(p, ao, ro, workspace, workspace_bytes, as_stream(stream));
 }
 
+namespace b200moe {
+namespace {
+// One block; thread b owns batch b (csrc/moe/moe_align_sum_kernels.cpp:61-130 of the
+// reference): exclusive scan of the block-padded counts, then each thread
+// writes its batch's token slots and block ids.
+__global__ void __launch_bounds__(1024)
+batched_align_kernel(const int32_t* __restrict__ counts, int B, int max_tokens, int block,
+                     int32_t* __restrict__ sorted_ids, int32_t* __restrict__ block_ids,
+                     int32_t* __restrict__ num_post_pad) {
+  __shared__ int warp_sums[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int blocks_per_batch = (max_tokens + block - 1) / block;
+  const int n_sorted = blocks_per_batch * B * block;
+  for (int i = tid; i < n_sorted; i += blockDim.x) sorted_ids[i] = B * max_tokens;
+  for (int i = tid; i < n_sorted / block; i += blockDim.x) block_ids[i] = -1;
+  const int n = tid < B ? counts[tid] : 0;
+  const int ceil_n = (n + block - 1) / block * block;
+  int incl = ceil_n;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += o;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();   // also orders the fills above before the writes below
+  if (warp == 0) {
+    int w = warp_sums[lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, w, d);
+      if (lane >= d) w += o;
+    }
+    warp_sums[lane] = w;
+  }
+  __syncthreads();
+  const int start = incl - ceil_n + (warp > 0 ? warp_sums[warp - 1] : 0);
+  if (tid == B - 1) *num_post_pad = start + ceil_n;
+  if (tid < B) {
+    for (int i = 0; i < n; ++i) sorted_ids[start + i] = tid * max_tokens + i;
+    for (int i = 0; i < ceil_n / block; ++i) block_ids[start / block + i] = tid;
+  }
+}
+}  // namespace
+}  // namespace b200moe
+
+extern "C" int b200moe_batched_moe_align_block_size(int max_tokens_per_batch, int block_size,
+                                                    const int32_t* batch_num_tokens, int num_batches,
+                                                    int32_t* sorted_ids, int32_t* batch_ids,
+                                                    int32_t* num_tokens_post_pad, b200moe_stream stream) {
+  B200_CHECK_ARG(num_batches >= 1 && num_batches <= 1024, "batched_moe_align_block_size: at most 1024 batches");
+  B200_CHECK_ARG(block_size >= 1 && max_tokens_per_batch >= 0, "batched_moe_align_block_size: bad sizes");
+  B200_CHECK_ARG(batch_num_tokens && sorted_ids && batch_ids && num_tokens_post_pad,
+                 "batched_moe_align_block_size: null pointer");
+  batched_align_kernel<<<1, 1024, 0, as_stream(stream)>>>(batch_num_tokens, num_batches, max_tokens_per_batch,
+                                                          block_size, sorted_ids, batch_ids, num_tokens_post_pad);
+  B200_LAUNCH_OK("batched_align_kernel");
+  return B200MOE_OK;
+}
+
 extern "C" int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,
                                        int ep_rank, int ep_size, b200moe_stream stream) {
   B200_CHECK_ARG(expert_map, "init_expert_map: null pointer");

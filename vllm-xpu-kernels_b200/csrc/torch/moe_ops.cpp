@@ -55,6 +55,29 @@ void topk_sigmoid(at::Tensor& topk_weights, at::Tensor& topk_indices,
       current_stream()));
 }
 
+// csrc/moe/moe_align_sum_kernels.cpp:1183-1222 of the reference.
+void batched_moe_align_block_size(int64_t max_tokens_per_batch, int64_t block_size,
+                                  const at::Tensor& batch_num_tokens, at::Tensor sorted_ids,
+                                  at::Tensor batch_ids, at::Tensor num_tokens_post_pad) {
+  check_cuda(batch_num_tokens, "expert_num_tokens");
+  const int64_t B = batch_num_tokens.size(0);
+  const int64_t sorted_size = (max_tokens_per_batch + block_size - 1) / block_size * block_size * B;
+  TORCH_CHECK(sorted_ids.size(0) == sorted_size);
+  TORCH_CHECK(batch_ids.size(0) == sorted_size / block_size);
+  TORCH_CHECK(num_tokens_post_pad.size(0) == 1);
+  TORCH_CHECK(B <= 1024);
+  TORCH_CHECK(batch_num_tokens.scalar_type() == at::kInt && sorted_ids.scalar_type() == at::kInt &&
+              batch_ids.scalar_type() == at::kInt && num_tokens_post_pad.scalar_type() == at::kInt,
+              "batched_moe_align_block_size expects int32 tensors");
+  TORCH_CHECK(batch_num_tokens.is_contiguous() && sorted_ids.is_contiguous() && batch_ids.is_contiguous());
+  if (B == 0) return;
+  const c10::cuda::CUDAGuard guard(batch_num_tokens.device());
+  check_status(b200moe_batched_moe_align_block_size(
+      (int)max_tokens_per_batch, (int)block_size, batch_num_tokens.data_ptr<int32_t>(), (int)B,
+      sorted_ids.data_ptr<int32_t>(), batch_ids.data_ptr<int32_t>(), num_tokens_post_pad.data_ptr<int32_t>(),
+      current_stream()));
+}
+
 // csrc/moe/topk_softplus_sqrt_kernels.cpp:596-772 of the reference.
 void topk_softplus_sqrt(at::Tensor& topk_weights, at::Tensor& topk_indices,
                         at::Tensor& token_expert_indices, at::Tensor& gating_output, bool renormalize,
@@ -349,6 +372,12 @@ TORCH_LIBRARY_FRAGMENT(_moe_C, m) {
       "token_expert_indices, Tensor gating_output, bool renormalize, Tensor? "
       "bias, float routed_scaling_factor) -> ()");
   m.def(
+      "batched_moe_align_block_size(int max_tokens_per_batch,"
+      "                     int block_size, Tensor expert_num_tokens,"
+      "                     Tensor! sorted_token_ids,"
+      "                     Tensor! experts_ids,"
+      "                     Tensor! num_tokens_post_pad) -> ()");
+  m.def(
       "topk_softplus_sqrt(Tensor! topk_weights, Tensor! topk_indices, "
       "Tensor! token_expert_indices, Tensor gating_output, bool renormalize, "
       "float routed_scaling_factor, Tensor? correction_bias=None, Tensor? "
@@ -377,6 +406,7 @@ TORCH_LIBRARY_IMPL(_moe_C, CUDA, m) {
   m.impl("moe_align_block_size", &moe_align_block_size);
   m.impl("grouped_topk", &grouped_topk);
   m.impl("topk_softplus_sqrt", &topk_softplus_sqrt);
+  m.impl("batched_moe_align_block_size", &batched_moe_align_block_size);
   m.impl("topk_softmax", &topk_softmax);
   m.impl("topk_sigmoid", &topk_sigmoid);
   m.impl("moe_gather", &moe_gather);
