@@ -233,7 +233,9 @@ typedef enum {
   B200MOE_W_FP8_BLOCK_NK = 3,  /* fp8 e4m3 [E,N,K] + fp32 scales [E,N/128,K/128]    */
   B200MOE_W_FP8_BLOCK_KN = 4,  /* fp8 e4m3 [E,K,N] + same scales                    */
   B200MOE_W_MXFP4_NK = 5, /* e2m1 pairs [E,N,K/2] + e8m0 bytes [E,N,K/32]           */
-  B200MOE_W_FP8E5M2_TENSOR_KN = 6 /* fp8 e5m2 [E,K,N] + fp32 scale [E]                */
+  B200MOE_W_FP8E5M2_TENSOR_KN = 6, /* fp8 e5m2 [E,K,N] + fp32 scale [E]               */
+  B200MOE_W_INT4_NK = 7   /* two's-complement 4-bit pairs [E,N,K/2] (low nibble = even k)
+                             + scales [E,N,K/group_size] in the activation dtype   */
 } b200moe_weight_format;
 
 typedef enum {
@@ -277,6 +279,8 @@ typedef struct {
   int max_ctas;           /* >0: the persistent tensor-core kernel uses at most this
                              many CTAs (leaves SMs to a concurrent collective);
                              0 = one per SM                                       */
+  int group_size;         /* INT4 weights: K elements per scale (32, 64, 128 or 256);
+                             ignored otherwise                                    */
 } b200moe_gemm_args;
 
 int b200moe_grouped_gemm(const b200moe_gemm_args* args, b200moe_stream stream);

@@ -349,6 +349,18 @@ def dequant_mxfp4(packed, scale_u8):
     return (vals.reshape(-1, 32) * sc.reshape(-1, 1)).reshape(vals.shape)
 
 
+def dequant_int4(packed_u4, scales, group_size):
+    """tests/fused_moe/test_fused_moe.py:63-76 of the reference: uint4 pairs (low nibble =
+    even k) with zero point 8, value = (q - 8) * scale[n, k // group] rounded to the
+    scales' dtype.  packed_u4 [..., N, K/2] uint8, scales [..., N, K/group]."""
+    u8 = packed_u4.view(torch.uint8)
+    lo = (u8 & 0xF).to(torch.int32) - 8
+    hi = (u8 >> 4).to(torch.int32) - 8
+    q = torch.stack((lo, hi), dim=-1).reshape(*u8.shape[:-1], u8.shape[-1] * 2).float()
+    sc = scales.float().repeat_interleave(group_size, dim=-1)
+    return (q * sc).to(scales.dtype)
+
+
 # --------------------------------------------------------------------------- grouped GEMM
 def grouped_gemm(a, w_deq, bias, rows_per_expert, out_dtype):
     """Per-expert fp32 matmul over the ragged segments (semantics of

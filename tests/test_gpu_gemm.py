@@ -198,3 +198,26 @@ def test_grouped_gemm_argument_checks(native):
           torch.zeros(4, 128, dtype=torch.bfloat16, device=DEV), rows, 128, 128, 2)
     out = f(a, None, w, None, None, d, rows, 32, 64, 2)
     assert out.data_ptr() == d.data_ptr()
+
+
+@pytest.mark.parametrize("E,M,N,K,group", [(4, 37, 256, 256, 128), (8, 130, 320, 512, 64), (3, 5, 128, 1024, 256),
+                                           (6, 64, 72, 128, 32)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("has_bias", [False, True])
+def test_grouped_gemm_int4(native, E, M, N, K, group, dtype, has_bias):
+    """w4a16 with group scales: two's-complement nibbles at the op boundary (what the
+    reference's layer hands its kernel after implement_zp)."""
+    g = torch.Generator().manual_seed(N + K)
+    rows = random_rows(E, M, g)
+    x = (torch.randn(M, K, generator=g) / 4).to(dtype)
+    u4 = torch.randint(0, 256, (E, N, K // 2), generator=g, dtype=torch.int32).to(torch.uint8)
+    sc = (torch.exp2(torch.randint(-6, -3, (E, N, K // group), generator=g).float()) *
+          (1 + torch.rand(E, N, K // group, generator=g) * 0.5)).to(dtype)
+    bias = (torch.randn(E, N, generator=g) * 0.05).to(dtype) if has_bias else None
+    wdeq = to.dequant_int4(u4, sc, group).float()
+    ref = to.grouped_gemm(x.float(), wdeq, bias, rows, dtype)
+    s4 = (u4 ^ 0x88).view(torch.int8)
+    out = grouped_gemm(x.to(DEV), None, s4.to(DEV), sc.to(DEV), bias.to(DEV) if has_bias else None, rows.to(DEV),
+                       N, K, out_dtype=dtype)
+    n = int(rows.sum())
+    torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=2e-2, atol=2e-2)

@@ -138,6 +138,32 @@ def test_layer_per_tensor_fp8(native, w_dtype, dtype, has_bias, mode):
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=tol, atol=tol)
 
 
+@pytest.mark.parametrize("has_bias", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_layer_int4(native, has_bias, dtype):
+    """tests/fused_moe/test_fused_moe.py:299-410 of the reference: uint4 weights [E,N,K/2]
+    with zero point 8 and power-of-two group scales (group 128), handed over as uint8."""
+    T, H, I, E, K, group = 40, 256, 128, 8, 2, 128
+    g = torch.Generator().manual_seed(7)
+    a = (torch.randn(T, H, generator=g) / 16).to(dtype)
+    w13 = torch.randint(0, 255, (E, 2 * I, H // 2), generator=g, dtype=torch.int32).to(torch.uint8)
+    w2 = torch.randint(0, 255, (E, H, I // 2), generator=g, dtype=torch.int32).to(torch.uint8)
+    s13 = torch.exp2(torch.randint(-5, -4, (E, 2 * I, H // group), generator=g).float()).to(dtype)
+    s2 = torch.exp2(torch.randint(-5, -4, (E, H, I // group), generator=g).float()).to(dtype)
+    b13 = (torch.randn(E, 2 * I, generator=g) / 16).to(dtype) if has_bias else None
+    b2 = (torch.randn(E, H, generator=g) / 16).to(dtype) if has_bias else None
+    tw, ids = torch.topk(torch.randn(T, E, generator=g), k=K, dim=-1, sorted=False)
+    ref = to.fused_moe_bf16(a, to.dequant_int4(w13, s13, group), b13, to.dequant_int4(w2, s2, group), b2, tw,
+                            ids.int(), E)
+    mv = lambda t: t.to(DEV) if t is not None else None
+    w13_dev = mv(w13)
+    layer = native.XpuFusedMoe(w13_dev, mv(s13), mv(b13), mv(w2), mv(s2), mv(b2), K, "silu", E)
+    assert layer.is_int4 and torch.equal(w13_dev.cpu(), w13)        # caller's weights untouched
+    out = torch.empty_like(a, device=DEV)
+    layer.apply(out, a.to(DEV), tw.to(DEV), ids.int().to(DEV))
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
 def test_layer_expert_parallel_masks_sum_to_the_full_layer(native):
     """ep_size ranks, each holding E/ep experts and masking the others
     (tests/fused_moe/test_fused_moe.py:531-657): the partial outputs add up."""

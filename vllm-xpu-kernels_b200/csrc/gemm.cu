@@ -53,6 +53,13 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
                      "grouped_gemm: fp8 activations with MXFP4 weights need the e8m0 scale words "
                      "[planes][ceil(K / 128)][M] of b200moe_quant_mxfp8");
       break;
+    case B200MOE_W_INT4_NK:
+      B200_CHECK_ARG(a->w_scale != nullptr, "w8a16 grouped gemm must have scales");
+      B200_CHECK_ARG(a->group_size == 32 || a->group_size == 64 || a->group_size == 128 || a->group_size == 256,
+                     "group_size must be 32, 64, 128 or 256");
+      B200_CHECK_ARG(a->k % a->group_size == 0, "ptr_scales.size(2) of int4 must be divisible by K");
+      B200_CHECK_ARG(!a_fp8, "grouped_gemm: int4 weights take 16-bit activations");
+      break;
     default:
       return fail(B200MOE_E_BADARG, "grouped_gemm: unknown weight format %d", (int)a->w_format);
   }
@@ -66,7 +73,7 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
   cudaStream_t st = as_stream(stream);
   // MXFP8 activations exist on the block-scaled tensor-core path only.
   if ((a->w_format == B200MOE_W_MXFP4_NK || w_tensor8) && a_fp8) return grouped_gemm_tc_mx(a, st);
-  if (a->impl == 2) return grouped_gemm_check(a, st);
+  if (a->impl == 2 || a->w_format == B200MOE_W_INT4_NK) return grouped_gemm_check(a, st);
   int rc = (a->w_format == B200MOE_W_MXFP4_NK) ? grouped_gemm_tc_dq(a, st) : grouped_gemm_tc(a, st);
   if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) return grouped_gemm_check(a, st);
   return rc;

@@ -26,6 +26,7 @@ struct CheckArgs {
   int64_t m; int n, k, num_experts;
   int fmt, epi; float alpha, limit, clamp_limit;
   int n_out;  // columns of D
+  int group;  // INT4: K elements per scale
 };
 
 template <typename T>
@@ -52,6 +53,14 @@ __device__ __forceinline__ float load_w(const CheckArgs& g, int e, int n, int k)
       if (g.a_scale != nullptr) return e4m3_to_f32(q);  // scales applied per block
       const float s = reinterpret_cast<const float*>(g.w_scale)[((int64_t)e * (N / 128) + n / 128) * (K / 128) + k / 128];
       return round_to<T>(e4m3_to_f32(q) * s);
+    }
+    case B200MOE_W_INT4_NK: {
+      // two's-complement nibble times the group's scale, rounded to the activation type
+      // (csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:400-410, 455-471 of the reference)
+      const uint8_t b = reinterpret_cast<const uint8_t*>(g.w)[((int64_t)e * N + n) * (K / 2) + k / 2];
+      const int q = (int)(((k & 1) ? (b >> 4) : (b & 15)) ^ 8) - 8;
+      const float sc = to_f32<T>(reinterpret_cast<const T*>(g.w_scale)[((int64_t)e * N + n) * (K / g.group) + k / g.group]);
+      return round_to<T>((float)q * sc);
     }
     case B200MOE_W_MXFP4_NK: {
       const uint8_t b = reinterpret_cast<const uint8_t*>(g.w)[((int64_t)e * N + n) * (K / 2) + k / 2];
@@ -229,6 +238,7 @@ int grouped_gemm_check(const b200moe_gemm_args* a, cudaStream_t st) {
   g.d = a->d; g.rows_per_expert = a->rows_per_expert; g.m = a->m; g.n = a->n; g.k = a->k;
   g.num_experts = a->num_experts; g.fmt = a->w_format; g.epi = a->epilogue;
   g.alpha = a->act_alpha; g.limit = a->act_limit; g.clamp_limit = a->clamp_limit;
+  g.group = a->group_size > 0 ? a->group_size : 32;
   const bool gated = a->epilogue != B200MOE_EPI_NONE;
   g.n_out = gated ? a->n / 2 : a->n;
   const bool a_fp8 = a->a_dtype == B200MOE_FP8_E4M3;

@@ -34,13 +34,15 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   TORCH_CHECK(ptr_B.is_contiguous(), "ptr_B must be contiguous");
   TORCH_CHECK(ptr_D.is_contiguous(), "ptr_D must be contiguous");
   if (ptr_bias.has_value()) TORCH_CHECK(ptr_bias->is_contiguous(), "ptr_bias must be contiguous");
-  TORCH_CHECK(!is_B_int4, "int4 grouped GEMM is not available in this build");
 
   const int64_t A_total_M = ptr_A.size(0), A_K = ptr_A.size(1);
   const int64_t B_E = ptr_B.size(0);
   int64_t B_K = ptr_B.size(1), B_N = ptr_B.size(2);
   b200moe_weight_format fmt;
-  if (is_B_mxfp4) {
+  if (is_B_int4) {
+    B_K = ptr_B.size(2) * 2; B_N = ptr_B.size(1);
+    fmt = B200MOE_W_INT4_NK;
+  } else if (is_B_mxfp4) {
     B_K = ptr_B.size(2) * 2; B_N = ptr_B.size(1);
     fmt = B200MOE_W_MXFP4_NK;
   } else if (is_B_fp8_block) {
@@ -72,7 +74,18 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
     TORCH_CHECK(ptr_bias->size(1) == N, "ptr_bias.size(1) must match N");
     TORCH_CHECK(ptr_bias->scalar_type() == ptr_D.scalar_type(), "ptr_bias must have ptr_D's dtype");
   }
-  if (is_B_mxfp4) {
+  int64_t group_size = 0;
+  if (is_B_int4) {
+    TORCH_CHECK(ptr_B_scale->is_contiguous(), "ptr_scales must be contiguous");
+    TORCH_CHECK(ptr_B_scale->dim() == 3, "ptr_scales of int4 must be 3D [num_experts, group_num, N]");
+    TORCH_CHECK(ptr_B_scale->size(0) == num_experts, "ptr_scales.size(0) of int4 must match num_experts");
+    TORCH_CHECK(K % ptr_B_scale->size(2) == 0, "ptr_scales.size(2) of int4 must be divisible by K");
+    TORCH_CHECK(ptr_B_scale->size(1) == N, "ptr_scales.size(1) of int4 must match N");
+    group_size = K / ptr_B_scale->size(2);
+    TORCH_CHECK(group_size == 32 || group_size == 64 || group_size == 128 || group_size == 256,
+                "group_size must be 32, 64, 128 or 256");
+    TORCH_CHECK(ptr_B_scale->scalar_type() == A_dtype, "int4 scales must have the activation dtype");
+  } else if (is_B_mxfp4) {
     TORCH_CHECK(ptr_B_scale->is_contiguous(), "ptr_scales must be contiguous");
     TORCH_CHECK(ptr_B_scale->dim() == 3, "ptr_scales of int4 must be 3D [num_experts, group_num, N]");
     TORCH_CHECK(ptr_B_scale->size(0) == num_experts, "ptr_scales.size(0) of int4 must match num_experts");
@@ -141,6 +154,7 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   g.status = nullptr;
   g.impl = (int)impl;
   g.max_ctas = (int)max_ctas;
+  g.group_size = (int)group_size;
   const c10::cuda::CUDAGuard guard(ptr_A.device());
   check_status(b200moe_grouped_gemm(&g, current_stream()));
   return ptr_D;

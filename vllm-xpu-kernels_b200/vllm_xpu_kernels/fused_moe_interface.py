@@ -194,8 +194,6 @@ class XpuFusedMoe:
 
         (is_fp8, is_int4, is_mxfp4, is_mxfp8,
          is_block_fp8) = _get_weights_dtype(w13, w13_scales)
-        if is_int4:
-            raise NotImplementedError("int4 (w4a16) weights are not built for sm_100a yet")
         if is_mxfp8:
             raise NotImplementedError("mxfp8 weights are not built for sm_100a yet")
         if w13.dtype == torch.float8_e5m2 and is_block_fp8:
@@ -206,9 +204,15 @@ class XpuFusedMoe:
                 "which this build does not ship: only the CUDA kernels run")
 
         self.inter_size = _get_inter_size(w13, w13_scales, is_int4, is_mxfp4, is_block_fp8)
+        if is_int4 and not getattr(w13, "xpu_fused_moe", False):
+            # uint4 with the default zero point 8 -> two's-complement int4 (reference
+            # implement_zp, :135-162: u4 - 8 re-encoded per nibble, i.e. bit 3 flipped);
+            # the caller's tensors are left as they are
+            w13 = (w13 ^ 0x88).view(torch.int8)
+            w2 = (w2 ^ 0x88).view(torch.int8)
         self.w13 = w13
         self.w2 = w2
-        if not (is_fp8 or is_mxfp4 or is_block_fp8):
+        if not (is_fp8 or is_mxfp4 or is_block_fp8 or is_int4):
             self.gemm1_wei_scales = None
             self.gemm2_wei_scales = None
         else:
