@@ -201,10 +201,11 @@ def test_grouped_gemm_argument_checks(native):
 
 
 @pytest.mark.parametrize("E,M,N,K,group", [(4, 37, 256, 256, 128), (8, 130, 320, 512, 64), (3, 5, 128, 1024, 256),
-                                           (6, 64, 72, 128, 32)])
+                                           (6, 64, 72, 128, 32), (2, 900, 384, 2048, 128)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("has_bias", [False, True])
-def test_grouped_gemm_int4(native, E, M, N, K, group, dtype, has_bias):
+@pytest.mark.parametrize("impl", [CHECK, TC])
+def test_grouped_gemm_int4(native, E, M, N, K, group, dtype, has_bias, impl):
     """w4a16 with group scales: two's-complement nibbles at the op boundary (what the
     reference's layer hands its kernel after implement_zp)."""
     g = torch.Generator().manual_seed(N + K)
@@ -218,6 +219,6 @@ def test_grouped_gemm_int4(native, E, M, N, K, group, dtype, has_bias):
     ref = to.grouped_gemm(x.float(), wdeq, bias, rows, dtype)
     s4 = (u4 ^ 0x88).view(torch.int8)
     out = grouped_gemm(x.to(DEV), None, s4.to(DEV), sc.to(DEV), bias.to(DEV) if has_bias else None, rows.to(DEV),
-                       N, K, out_dtype=dtype)
+                       N, K, out_dtype=dtype, impl=impl)
     n = int(rows.sum())
     torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=2e-2, atol=2e-2)

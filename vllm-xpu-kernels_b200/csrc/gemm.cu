@@ -73,8 +73,9 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
   cudaStream_t st = as_stream(stream);
   // MXFP8 activations exist on the block-scaled tensor-core path only.
   if ((a->w_format == B200MOE_W_MXFP4_NK || w_tensor8) && a_fp8) return grouped_gemm_tc_mx(a, st);
-  if (a->impl == 2 || a->w_format == B200MOE_W_INT4_NK) return grouped_gemm_check(a, st);
-  int rc = (a->w_format == B200MOE_W_MXFP4_NK) ? grouped_gemm_tc_dq(a, st) : grouped_gemm_tc(a, st);
+  if (a->impl == 2) return grouped_gemm_check(a, st);
+  int rc = (a->w_format == B200MOE_W_MXFP4_NK || a->w_format == B200MOE_W_INT4_NK) ? grouped_gemm_tc_dq(a, st)
+                                                                                    : grouped_gemm_tc(a, st);
   if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) return grouped_gemm_check(a, st);
   return rc;
 }

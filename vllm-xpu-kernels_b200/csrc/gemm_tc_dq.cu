@@ -1,6 +1,7 @@
 // Tensor-core grouped GEMM for weights that are dequantised on the way in:
 // MXFP4 (two e2m1 codes per byte, [E,N,K/2], one e8m0 scale per 32 elements,
-// [E,N,K/32]) times 16-bit activations.
+// [E,N,K/32]) or INT4 (two's-complement nibbles, [E,N,K/2], one 16-bit scale per
+// group of 32..256 elements, [E,N,K/group]) times 16-bit activations.
 //
 // Same orientation, tile walk and epilogue as grouped_gemm_tc_kernel (weights'
 // output features on the 128-row M side of tcgen05.mma, tokens on the N side),
@@ -15,9 +16,9 @@
 //   warps 10-13: epilogue
 // HBM sees only the 4-bit weights (0.53 bytes per element with scales).
 //
-// Numerics follow csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:411-419, 455-471 of
-// vllm-xpu-kernels: LUT[code] * 2^(byte-127) rounded to the activation type
-// before the multiply, fp32 accumulation, bias added in fp32.
+// Numerics follow csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:400-419, 455-471 of
+// vllm-xpu-kernels: LUT[code] * 2^(byte-127) (INT4: nibble * scale) rounded to
+// the activation type before the multiply, fp32 accumulation, bias added in fp32.
 #include <cuda_fp4.h>
 #include <stdlib.h>
 
@@ -36,7 +37,8 @@ constexpr int kDqMaxStages = 8;
 constexpr int kDqGroup = 8;      // K blocks per scale prefetch
 
 struct DqParams {
-  const uint8_t* w_scale;  // [E, N, K/32] e8m0
+  const uint8_t* w_scale;  // [E, N, K/32] e8m0; INT4: [E, N, K/group] 16-bit values
+  int group;               // INT4: K elements per scale
   const void* bias;
   void* d;
   const int32_t* rows_per_expert;
@@ -93,7 +95,7 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int out_f16) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int BT>
+template <int BT, bool kInt4>
 __global__ void __launch_bounds__(kDqThreads, 1)
 grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_w, const DqParams p) {
@@ -210,6 +212,17 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int u = 0; u < kDqGroup; ++u) {
           const int kb = g * kDqGroup + u;
+          if (kInt4) {
+            // the 16-bit scale of this thread's 32 values, duplicated into both halves
+            uint32_t v = 0;
+            if (feat_ok && kb < p.num_kb) {
+              const uint16_t* s16 = reinterpret_cast<const uint16_t*>(p.w_scale) +
+                                    ((int64_t)ti.e * p.n + feat) * (p.k / p.group);
+              v = s16[(kb * 64 + half * 32) / p.group];
+            }
+            dst[u] = v | (v << 16);
+            continue;
+          }
           uint32_t v = 0x7f7fu;  // 2^0 twice
           if (feat_ok && 2 * kb + 1 < kgroups) {
             if (pair_aligned) v = *reinterpret_cast<const uint16_t*>(srow + 2 * kb);
@@ -244,7 +257,38 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t words[4] = {q0.x, q0.y, q0.z, q0.w};
         const uint32_t sbyte = half ? c1s : c0s;
         const uint32_t orow = st + (r >> 3) * 1024 + (r & 7) * 128;
-        if (!p.out_f16 && sbyte <= 128u) {
+        if (kInt4) {
+          // nibble n (two's complement) -> 128 + (n ^ 8) (bf16 0x4300 | .; fp16: 1024 +,
+          // 0x6400 | .) exactly, minus 136 (1032) = n as a signed value, times the scale:
+          // one rounding, as the reference's product in the activation type.
+          const uint32_t magic = p.out_f16 ? 0x64006400u : 0x43004300u;
+          const uint32_t offs = p.out_f16 ? 0x64086408u : 0x43084308u;   // 1032.0 / 136.0
+          const uint32_t sc2 = cur_s[u];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t w = words[c];
+            const uint32_t xe = (w & 0x0F0F0F0Fu) ^ 0x08080808u;
+            const uint32_t xo = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t q = __byte_perm(xe, xo, (uint32_t)(j | (4 << 4) | ((4 + j) << 8) | (4 << 12))) & 0x00ff00ffu;
+              const uint32_t bits = magic | q;
+              if (p.out_f16) {
+                const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&bits),
+                                                  *reinterpret_cast<const __half2*>(&offs)),
+                                          *reinterpret_cast<const __half2*>(&sc2));
+                o[j] = *reinterpret_cast<const uint32_t*>(&v);
+              } else {
+                const __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&bits),
+                                                         *reinterpret_cast<const __nv_bfloat162*>(&offs)),
+                                                 *reinterpret_cast<const __nv_bfloat162*>(&sc2));
+                o[j] = *reinterpret_cast<const uint32_t*>(&v);
+              }
+            }
+            ptx::sts128(orow + (((4 * half + c) ^ (r & 7)) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+          }
+        } else if (!p.out_f16 && sbyte <= 128u) {
           // Integer path for bf16.  Put the code's exponent and mantissa bits
           // where bf16 keeps them ((c & 7) << 6, sign to bit 15): read as bf16
           // that is the code's value times 2^-126, subnormal codes included, so
@@ -366,10 +410,10 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
 }
 
-template <int BT>
+template <int BT, bool kInt4>
 int launch_dq(const CUtensorMap& ta, const CUtensorMap& tw, const DqParams& p, int grid,
               cudaStream_t st) {
-  auto kern = grouped_gemm_dq_kernel<BT>;
+  auto kern = grouped_gemm_dq_kernel<BT, kInt4>;
   static bool configured = false;
   if (!configured) {
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -383,11 +427,14 @@ int launch_dq(const CUtensorMap& ta, const CUtensorMap& tw, const DqParams& p, i
 
 }  // namespace
 
-// MXFP4 weights x 16-bit activations on the tensor cores.  Returns
+// MXFP4 or INT4 weights x 16-bit activations on the tensor cores.  Returns
 // B200MOE_E_UNSUPPORTED (no launch) for anything else.
 int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
-  if (a->w_format != B200MOE_W_MXFP4_NK || a->a_dtype == B200MOE_FP8_E4M3)
-    return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM takes MXFP4 weights only");
+  const bool int4 = a->w_format == B200MOE_W_INT4_NK;
+  if (!(a->w_format == B200MOE_W_MXFP4_NK || int4) || a->a_dtype == B200MOE_FP8_E4M3)
+    return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM takes MXFP4 or INT4 weights only");
+  if (int4 && ((uintptr_t)a->w_scale & 1))
+    return fail(B200MOE_E_BADARG, "grouped GEMM: INT4 scales must be 2-byte aligned");
   if (a->epilogue == B200MOE_EPI_SILU_MUL)
     return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM: SiLU epilogue not available");
   if (a->num_experts > kMaxExperts || a->k % 64 != 0 || (a->k / 2) % 16 != 0)
@@ -400,6 +447,7 @@ int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
 
   DqParams p;
   p.w_scale = reinterpret_cast<const uint8_t*>(a->w_scale);
+  p.group = int4 ? a->group_size : 32;
   p.bias = a->bias; p.d = a->d; p.rows_per_expert = a->rows_per_expert; p.status = a->status;
   p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
   p.n_tiles = (a->n + kFeat - 1) / kFeat;
@@ -440,9 +488,14 @@ int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if (tile_bound < grid) grid = (int)tile_bound;
   if (grid < 1) grid = 1;
-  if (bt == 16) return launch_dq<16>(ta, tw, p, grid, st);
-  if (bt == 64) return launch_dq<64>(ta, tw, p, grid, st);
-  return launch_dq<128>(ta, tw, p, grid, st);
+  if (int4) {
+    if (bt == 16) return launch_dq<16, true>(ta, tw, p, grid, st);
+    if (bt == 64) return launch_dq<64, true>(ta, tw, p, grid, st);
+    return launch_dq<128, true>(ta, tw, p, grid, st);
+  }
+  if (bt == 16) return launch_dq<16, false>(ta, tw, p, grid, st);
+  if (bt == 64) return launch_dq<64, false>(ta, tw, p, grid, st);
+  return launch_dq<128, false>(ta, tw, p, grid, st);
 }
 
 }  // namespace b200moe
