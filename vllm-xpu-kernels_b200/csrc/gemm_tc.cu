@@ -259,7 +259,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
     const int col0 = ((warp - 2) / 4) * kCols;   // first token column of this warp
     // fp8 block-scale prefetch state (see the promotion loop below)
-    constexpr int kGroup = 4;
+    // (the software-pipelined promotion keeps two chunks of TMEM data in registers: smaller groups)
+    constexpr bool kPipe = kFp8 && BT == 128 && (kCols == 2 * kChunk) && (kChunk == 32);
+    constexpr int kGroup = kPipe ? 2 : 4;
     constexpr int kPerLane = (kCols + 31) / 32;
     struct ScaleRegs { float a[kPerLane][kGroup]; float w[kGroup]; };
     ScaleRegs cur, pre;
@@ -277,9 +279,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int row = tt.row0 + c;
         const bool live = (lane + 32 * u < kCols) && (c < tt.valid) && (row < p.m);
         const float* src = p.a_scale + (int64_t)row * kbs + kb0;
-        if (live && vec4_ok) {
+        if (live && vec4_ok && kGroup == 4) {
           const float4 q4 = *reinterpret_cast<const float4*>(src);
-          r.a[u][0] = q4.x; r.a[u][1] = q4.y; r.a[u][2] = q4.z; r.a[u][3] = q4.w;
+          r.a[u][0] = q4.x; r.a[u][1] = q4.y; r.a[u][2 % kGroup] = q4.z; r.a[u][3 % kGroup] = q4.w;
+        } else if (live && vec4_ok && kGroup == 2) {   // kbs % 4 == 0 and a 16-byte base: 8-byte aligned pairs
+          const float2 q2 = *reinterpret_cast<const float2*>(src);
+          r.a[u][0] = q2.x; r.a[u][1] = q2.y;
         } else {
 #pragma unroll
           for (int jb = 0; jb < kGroup; ++jb) r.a[u][jb] = (live && kb0 + jb < kbs) ? src[jb] : 0.f;
@@ -331,6 +336,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         float acc[kCols];
 #pragma unroll
         for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
+        uint32_t va[16], vb[16];   // kPipe: TMEM data of the chunk in work / in flight
         // Scales are fetched kGroup K blocks at a time, one group ahead of their
         // use (the first group of the next tile during the last group of this
         // one), so the strided a_scale loads are off the critical path.  Each
@@ -351,6 +357,86 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             fetch_group(tn, 0, pre);
             pre_valid = true;
           }
+          if (kPipe) {
+            // Four 16-column chunks per K block, two register buffers.  The TMEM load of
+            // the next chunk (or of the next block's first chunk) is in flight while the
+            // current one is promoted: tcgen05.wait::ld waits for every load issued so
+            // far, so each wait sits after the arithmetic that does not need the newest
+            // load.  A buffer is not touched between its load and its wait.
+#pragma unroll
+            for (int jb = 0; jb < kGroup; ++jb) {
+              const int kb = g * kGroup + jb;
+              if (kb >= p.num_kb) break;
+              const uint32_t sc = ptx::smem_u32(ctrl->sc[warp - 2][kb & 1]);
+              uint32_t a = acc_it % kAccStages;
+              if (kb == 0) {   // first block of the tile: nothing was loaded ahead
+#pragma unroll
+                for (int u = 0; u < kPerLane; ++u)
+                  if (lane + 32 * u < kCols) ptx::sts32f(sc + (lane + 32 * u) * 4, cur.a[u][jb] * cur.w[jb]);
+                __syncwarp();
+                TC_PROF_T(e1);
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
+                  *abort_flag = 1; ok = false; break;
+                }
+                TC_PROF_ADD(ew, e1);
+                ptx::tc_fence_after();
+                ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + lane_sel, va);
+                ptx::tmem_wait_ld_tied(va);
+              }
+              const bool more = kb + 1 < p.num_kb;
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                // chunk c of this block sits in (c even ? va : vb); start the load after it
+                if (c < 3) {
+                  if (c & 1) ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + 16 * (c + 1) + lane_sel, va);
+                  else ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + 16 * (c + 1) + lane_sel, vb);
+                } else {
+                  // all of this block is in registers (chunk 3 was waited for): free its stage
+                  ptx::tc_fence_before();
+                  __syncwarp();
+                  if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
+                  ++acc_it;
+                  if (more) {   // next block of the tile: stage its scales, start its chunk 0
+                    const uint32_t scn = ptx::smem_u32(ctrl->sc[warp - 2][(kb + 1) & 1]);
+#pragma unroll
+                    for (int u = 0; u < kPerLane; ++u) {
+                      if (lane + 32 * u < kCols) {
+                        const float sv = (jb + 1 < kGroup) ? cur.a[u][(jb + 1) % kGroup] * cur.w[(jb + 1) % kGroup]
+                                                           : pre.a[u][0] * pre.w[0];
+                        ptx::sts32f(scn + (lane + 32 * u) * 4, sv);
+                      }
+                    }
+                    __syncwarp();
+                    a = acc_it % kAccStages;
+                    TC_PROF_T(e2);
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
+                      *abort_flag = 1; ok = false;
+                    }
+                    TC_PROF_ADD(ew, e2);
+                    ptx::tc_fence_after();
+                    if (ok) ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + lane_sel, va);
+                  }
+                }
+                if (col0 + 16 * c < ti.valid) {
+#pragma unroll
+                  for (int i = 0; i < 16; i += 4) {
+                    const float4 s4 = ptx::lds128f(sc + (16 * c + i) * 4);
+                    const uint32_t* v = (c & 1) ? vb : va;
+                    acc[16 * c + i + 0] = fmaf(__uint_as_float(v[i + 0]), s4.x, acc[16 * c + i + 0]);
+                    acc[16 * c + i + 1] = fmaf(__uint_as_float(v[i + 1]), s4.y, acc[16 * c + i + 1]);
+                    acc[16 * c + i + 2] = fmaf(__uint_as_float(v[i + 2]), s4.z, acc[16 * c + i + 2]);
+                    acc[16 * c + i + 3] = fmaf(__uint_as_float(v[i + 3]), s4.w, acc[16 * c + i + 3]);
+                  }
+                }
+                if (c < 3) {
+                  if (c & 1) ptx::tmem_wait_ld_tied(va); else ptx::tmem_wait_ld_tied(vb);
+                } else if (more && ok) {
+                  ptx::tmem_wait_ld_tied(va);
+                }
+              }
+              if (!ok) break;
+            }
+          } else {
 #pragma unroll
           for (int jb = 0; jb < kGroup; ++jb) {
             const int kb = g * kGroup + jb;
@@ -394,6 +480,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
             ++acc_it;
+          }
           }
           if (g + 1 < n_groups) cur = pre;
         }

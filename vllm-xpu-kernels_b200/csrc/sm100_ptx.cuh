@@ -186,6 +186,17 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 
+// tcgen05.wait::ld for loads that were issued earlier and whose destination
+// registers the code in between did not touch: the registers are operands of the
+// wait, so that no later use of them can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_wait_ld_tied(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15])
+               :
+               : "memory");
+}
 // 32 lanes x N consecutive 32-bit columns written from registers: thread i
 // writes lane (base lane + i).
 __device__ __forceinline__ void tmem_st_32x1(uint32_t taddr, uint32_t r0) {
