@@ -208,6 +208,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         uint32_t a = acc_it % kAccStages;
+        // A partly filled token tile multiplies only its valid columns (UMMA N in steps of 16).
+        const uint32_t n_eff = (uint32_t)((ti.valid + 15) & ~15);
+        const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((n_eff >> 3) << 17);
         const bool per_block = kFp8 && !(p.debug & 4);
         if (!per_block) {
           TC_PROF_T(wa0);
@@ -239,7 +242,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             else wdesc = ptx::make_smem_desc(wbase + j * 2048, 8192, 1024);
             const uint64_t adesc = ptx::make_smem_desc(abase + j * 32, 16, 1024);
             const uint32_t accumulate = per_block ? (j > 0) : (kb > 0 || j > 0);
-            ptx::umma<kFp8>(d_tmem, wdesc, adesc, p.idesc, accumulate);
+            ptx::umma<kFp8>(d_tmem, wdesc, adesc, idesc, accumulate);
           }
           TC_PROF_ADD(mi, w2);
           TC_PROF_T(w3);

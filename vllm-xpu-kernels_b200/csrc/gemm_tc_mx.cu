@@ -249,7 +249,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t smem_base = ptx::smem_u32(smem);
       uint32_t idesc_j[4];
 #pragma unroll
-      for (uint32_t j = 0; j < 4; ++j) idesc_j[j] = p.idesc | (j << 29) | (j << 4);
+      for (uint32_t j = 0; j < 4; ++j) idesc_j[j] = (p.idesc & ~(0x3fu << 17)) | (j << 29) | (j << 4);
       MX_PROF_DECL(mf = 0, ms = 0, ma = 0, mi = 0, mc = 0, mt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
@@ -260,6 +260,10 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
         MX_PROF_ADD(ma, wa0);
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * kNT;
+        // A partly filled token tile multiplies only up to its last valid column (UMMA N in
+        // steps of 16; with two planes the second one's columns follow the first one's BT).
+        const uint32_t n_eff = (uint32_t)((kTerms - 1) * BT + ((ti.valid + 15) & ~15));
+        const uint32_t n_bits = (n_eff >> 3) << 17;
         for (int si = 0; si < num_st; ++si) {
           MX_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
@@ -286,7 +290,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 // K-major e2m1 tile: 32 codes further is 32 bytes; MN-major byte tile: 32 K rows
                 const uint64_t wdesc = desc0w + (uint64_t)((sub * kMxWBytes + j * (kW8 ? 4096 : 32)) >> 4);
                 const uint64_t adesc = desc0 + (uint64_t)((kAOff + sub * kABytes + j * 32) >> 4);
-                ptx::umma_mx(d_tmem, wdesc, adesc, idesc_j[j], (kb0 + sub > 0 || j > 0) ? 1u : 0u, sfa, sfa + 4);
+                ptx::umma_mx(d_tmem, wdesc, adesc, idesc_j[j] | n_bits, (kb0 + sub > 0 || j > 0) ? 1u : 0u, sfa, sfa + 4);
               }
             }
           }
