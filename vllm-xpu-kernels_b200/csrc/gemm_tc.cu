@@ -167,7 +167,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, s = 0, ph = 0;
       int cursor = 0;
       bool ok = true;
       TC_PROF_DECL(pw = 0, pt0 = clock64());
@@ -176,7 +176,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         const int n0 = ti.n_tile * kFeat;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
           TC_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           TC_PROF_ADD(pw, w0);
@@ -193,6 +192,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tma_load_3d(wdst + kWTileBytes / 2, &tmap_w, &ctrl->full[s], n0 + 64, k0, ti.e);
           }
           ptx::tma_load_2d(adst, &tmap_a, &ctrl->full[s], k0, ti.row0);
+          if (++s == (uint32_t)kStages) { s = 0; ph ^= 1; }
         }
       }
       TC_PROF_PRINT("producer: total %lld wait_empty %lld blocks %u\n", clock64() - pt0, pw, it);
@@ -200,9 +200,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      uint32_t it = 0, acc_it = 0;
+      uint32_t s = 0, ph = 0, acc_it = 0;
       int cursor = 0;
       bool ok = true;
+      const uint32_t smem_base = ptx::smem_u32(smem);
+      // leading-dimension byte offset of the weight operand: K-major 16, MN-major 8192 (16-bit) / 16384 (fp8)
+      constexpr uint32_t kWLbo = !kWKn ? 16u : (kFp8 ? 16384u : 8192u);
+      constexpr uint32_t kWStep = !kWKn ? 32u : (kFp8 ? 4096u : 2048u);   // bytes per 32-byte K step
       TC_PROF_DECL(mf = 0, ma = 0, mi = 0, mc = 0, mt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
@@ -218,37 +222,36 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           TC_PROF_ADD(ma, wa0);
           ptx::tc_fence_after();
         }
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        for (int kb = 0; kb < p.num_kb; ++kb) {
           if (per_block) {
             a = acc_it % kAccStages;
             TC_PROF_T(wa1);
             if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
             TC_PROF_ADD(ma, wa1);
           }
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
           TC_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
           TC_PROF_ADD(mf, w0);
           TC_PROF_T(w2);
           ptx::tc_fence_after();
-          const uint32_t wbase = ptx::smem_u32(smem + s * kStageBytes);
-          const uint32_t abase = wbase + kWTileBytes;
+          // every operand descriptor of the stage = one base descriptor + a compile-time
+          // offset (the address field counts 16-byte units), so the issue loop is adds only
+          const uint32_t st_addr = smem_base + s * kStageBytes;
+          const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
+          const uint64_t adesc0 = ptx::make_smem_desc(st_addr + kWTileBytes, 16, 1024);
           const uint32_t d_tmem = tmem_base + a * BT;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            uint64_t wdesc;
-            if (!kWKn) wdesc = ptx::make_smem_desc(wbase + j * 32, 16, 1024);
-            else if (kFp8) wdesc = ptx::make_smem_desc(wbase + j * 4096, 16384, 1024);
-            else wdesc = ptx::make_smem_desc(wbase + j * 2048, 8192, 1024);
-            const uint64_t adesc = ptx::make_smem_desc(abase + j * 32, 16, 1024);
             const uint32_t accumulate = per_block ? (j > 0) : (kb > 0 || j > 0);
-            ptx::umma<kFp8>(d_tmem, wdesc, adesc, idesc, accumulate);
+            ptx::umma<kFp8>(d_tmem, wdesc0 + (uint64_t)((j * kWStep) >> 4), adesc0 + (uint64_t)((j * 32) >> 4), idesc,
+                            accumulate);
           }
           TC_PROF_ADD(mi, w2);
           TC_PROF_T(w3);
           ptx::umma_commit(&ctrl->empty[s]);
           if (per_block) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
           TC_PROF_ADD(mc, w3);
+          if (++s == (uint32_t)kStages) { s = 0; ph ^= 1; }
         }
         if (!per_block && ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
       }
