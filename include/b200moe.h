@@ -181,6 +181,57 @@ int b200moe_batched_moe_align_block_size(int max_tokens_per_batch, int block_siz
                                          int32_t* num_tokens_post_pad,
                                          b200moe_stream stream);
 
+/* Replaces `moe_lora_align_block_size` (csrc/moe/moe_align_sum_kernels.cpp:1374-1549,
+ * kernels :732-1027; schema csrc/moe/torch_bindings.cpp:36-50).  For every entry
+ * l = lora_ids[i], i in [0, max_loras], that is a valid enabled adapter
+ * (0 <= l < max_loras, adapter_enabled[l] != 0) the slots whose token has
+ * token_lora_mapping[token] == l are aligned like moe_align_block_size into
+ * segment l of the outputs: sorted_token_ids[l*max_num_tokens_padded ...] (padding
+ * = numel), expert_ids[l*max_num_m_blocks ...] (unused blocks = -1) and
+ * num_tokens_post_pad[l].  Segments of other adapters are not written.  Slots of
+ * one expert appear in ascending order (the reference leaves it unspecified). */
+int b200moe_moe_lora_align_block_size(const void* topk_ids, b200moe_dtype ids_dtype,
+                                      int64_t numel, int topk,
+                                      const int32_t* token_lora_mapping,
+                                      int num_experts, int block_size, int max_loras,
+                                      int max_num_tokens_padded, int max_num_m_blocks,
+                                      int32_t* sorted_token_ids, int32_t* expert_ids,
+                                      int32_t* num_tokens_post_pad,
+                                      const int32_t* adapter_enabled,
+                                      const int32_t* lora_ids,
+                                      const int32_t* expert_map, b200moe_stream stream);
+
+/* Replaces `fused_moe_prologue` (csrc/moe/fused_moe_prologue.cpp:5-216, kernels
+ * csrc/moe/fused_moe_prologue.hpp:153-709; schema csrc/moe/torch_bindings.cpp:83-92):
+ * the routed rows that belong to this rank's experts
+ * [ep_rank*num_experts_on_rank, (ep_rank+1)*num_experts_on_rank) are sorted by expert,
+ * ascending token inside an expert, and written into the packed workspace whose ten
+ * 256-byte aligned regions b200moe_fused_moe_prologue_layout returns, in this order:
+ *   0 permuted_row_to_unpermuted_row i32 [T*K]  (unpermuted row = k*T + token)
+ *   1 permuted_token_selected_experts i32 [T*K] (local expert id)
+ *   2 unpermuted_row_to_permuted_row i32 [T*K]  (only cells of rows kept are written)
+ *   3,4,5 scratch of the reference's three-step sort (sized as there, not written here)
+ *   6 expert_first_token_offset i64 [E_local+1]
+ *   7 permuted_token_final_scales f32 [T*K]
+ *   8 permuted rows [T*K, hidden_size] of elem_bytes each
+ *   9 permuted scale rows [T*K, hidden_size/block_k] of scale_elem_bytes each.
+ * Rows and scales are moved as opaque bytes (bf16/fp16 2, fp8 and packed fp4 1; scales
+ * f32 4 or e8m0 1; hidden_size counts storage elements).  `scratch` is caller memory of
+ * b200moe_fused_moe_prologue_scratch_bytes bytes that the call may overwrite. */
+int b200moe_fused_moe_prologue_layout(int64_t num_rows, int topk, int num_experts_on_rank,
+                                      int64_t hidden_size, int block_k, int elem_bytes,
+                                      int scale_elem_bytes, size_t offsets[10],
+                                      size_t* total_bytes);
+size_t b200moe_fused_moe_prologue_scratch_bytes(int64_t num_rows, int topk,
+                                                int num_experts_on_rank);
+int b200moe_fused_moe_prologue(const void* input, int elem_bytes, const void* input_scales,
+                               int scale_elem_bytes, const int64_t* token_selected_experts,
+                               const float* token_final_scales, void* workspace,
+                               size_t workspace_bytes, int64_t num_rows, int64_t hidden_size,
+                               int block_k, int topk, int ep_rank, int ep_size,
+                               int num_experts_on_rank, void* scratch, size_t scratch_bytes,
+                               b200moe_stream stream);
+
 /* Replaces `init_expert_map` (csrc/moe/init_expert_map.cpp:78-95; schema
  * csrc/moe/torch_bindings.cpp:93-98). expert_map has num_local*ep_size ints. */
 int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,

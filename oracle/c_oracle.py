@@ -97,6 +97,53 @@ def moe_align_block_size(topk_ids, num_experts, block_size, sorted_len, expert_i
     return sorted_ids, expert_ids, post
 
 
+def moe_lora_align_block_size(topk_ids, token_lora_mapping, num_experts, block_size, max_loras,
+                              max_num_tokens_padded, max_num_m_blocks, sorted_token_ids, expert_ids,
+                              num_tokens_post_pad, adapter_enabled, lora_ids, expert_map=None):
+    """Writes the three int32 CPU output tensors in place, like the op."""
+    ids = topk_ids.reshape(-1).to(torch.int64).contiguous()
+    m = expert_map.to(torch.int32).contiguous() if expert_map is not None else None
+    for t in (sorted_token_ids, expert_ids, num_tokens_post_pad):
+        assert t.dtype == torch.int32 and t.is_contiguous() and t.device.type == "cpu"
+    tl = token_lora_mapping.int().contiguous()
+    ae = adapter_enabled.int().contiguous()
+    li = lora_ids.int().contiguous()
+    lib().orc_moe_lora_align(_p(ids), ctypes.c_int64(ids.numel()), int(topk_ids.shape[1]), _p(tl),
+                             num_experts, block_size, max_loras, max_num_tokens_padded,
+                             max_num_m_blocks, _p(m), _p(ae), _p(li), _p(sorted_token_ids),
+                             _p(expert_ids), _p(num_tokens_post_pad))
+
+
+PROLOGUE_REGIONS = ("permuted_row_to_unpermuted_row", "permuted_token_selected_experts",
+                    "unpermuted_row_to_permuted_row", "blocked_expert_counts",
+                    "blocked_expert_counts_cumsum", "blocked_row_to_unpermuted_row",
+                    "expert_first_token_offset", "permuted_token_final_scales",
+                    "overlapped_gemm1_gemm2_inputs", "permuted_act_scales")
+
+
+def prologue_layout(num_rows, topk, experts, hidden, block_k, elem_bytes, scale_bytes):
+    """-> ({region name: byte offset}, total bytes) of the packed prologue workspace."""
+    off = (ctypes.c_int64 * 10)()
+    total = ctypes.c_int64()
+    lib().orc_prologue_layout(ctypes.c_int64(num_rows), topk, experts, ctypes.c_int64(hidden), block_k,
+                              elem_bytes, scale_bytes, off, ctypes.byref(total))
+    return dict(zip(PROLOGUE_REGIONS, list(off))), total.value
+
+
+def fused_moe_prologue(x, scales, topk_ids, topk_weights, workspace, hidden_size, block_k, ep_rank,
+                       num_experts_on_rank):
+    """Fills the uint8 CPU `workspace` in place; x / scales are taken as raw storage."""
+    xb = x.contiguous().view(torch.uint8)
+    sb = scales.contiguous().view(torch.uint8) if scales is not None else None
+    ids = topk_ids.long().contiguous()
+    w = topk_weights.float().contiguous()
+    assert workspace.dtype == torch.uint8 and workspace.is_contiguous()
+    lib().orc_fused_moe_prologue(_p(xb), x.element_size(), _p(sb), scales.element_size() if scales is not None else 0,
+                                 _p(ids), _p(w), _p(workspace), ctypes.c_int64(x.shape[0]),
+                                 ctypes.c_int64(hidden_size), block_k, int(topk_ids.shape[1]), ep_rank,
+                                 num_experts_on_rank)
+
+
 def remap_bookkeeping(topk_ids, expert_map, total_experts, local_experts):
     """-> (rows_per_expert i32 [E_local], row_map i32 [T,K])"""
     ids = topk_ids.reshape(-1).to(torch.int64).contiguous()

@@ -49,7 +49,8 @@ def load_reference(root: str):
     import tests.ops.mx_utils as mx_utils
     import tests.ops.swiglustep_and_mul_op as step_op
     import tests.test_topk_softplus_sqrt as sps_t
-    return dict(sps=sps_t, step=step_op, sbq=sbq_t, smx=smx_t, sq=sq_t, mxu=mx_utils, topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
+    import tests.fused_moe.test_moe_prologue as pro_t
+    return dict(pro=pro_t, sps=sps_t, step=step_op, sbq=sbq_t, smx=smx_t, sq=sq_t, mxu=mx_utils, topk=topk_op, grouped=grouped_op, align=align_t, remap=remap_t, gather=gather_t,
                 layer=layer_t, act=act_op, swi=swi_op, fp8=fp8_t, mu=mu)
 
 
@@ -285,6 +286,49 @@ def main():
     cases = [capture_batched_align(ref["align"], mt, ne, bs, empty)
              for (mt, ne, bs, empty) in [(13, 8, 8, False), (16, 16, 16, True), (512, 64, 32, False), (13, 32, 64, True)]]
     torch.save(cases, OUT / "batched_align.pt")
+    # ---- legacy prologue (tests/fused_moe/test_moe_prologue.py:52-97, 104-152) ------------------------
+    cases = []
+    for (m, k, e, topk, recipe) in [(1, 256, 16, 1, "bf16"), (4, 256, 16, 2, "fp16"), (16, 512, 16, 2, "mxfp8"),
+                                    (300, 256, 16, 2, "fp8block"), (300, 256, 16, 1, "mxfp4"),
+                                    (700, 128, 16, 2, "bf16"), (64, 256, 8, 2, "mxfp4")]:
+        torch.manual_seed(7)
+        data_dtype, scale_dtype = ref["pro"].RECIPE_TO_DTYPE[recipe]
+        scales, block_k = None, 1
+        if data_dtype in (torch.bfloat16, torch.float16):
+            hidden = torch.randn(m, k, dtype=data_dtype) / 16
+            ref_a = hidden.clone()
+        elif data_dtype is torch.float8_e4m3fn:
+            f32 = torch.randn(m, k)
+            hidden, ref_a = f32.to(torch.float8_e4m3fn), f32
+            if recipe == "fp8block":
+                block_k = 128
+                scales = torch.randn(m, k // block_k)
+            else:
+                block_k = 32
+                scales = torch.randint(1, 256, (m, k // block_k), dtype=torch.uint8).view(torch.float8_e8m0fnu)
+        else:
+            block_k = 16
+            ref_a = torch.randint(0, 256, (m, k // 2)).to(torch.bfloat16)   # byte values, as the test's cast makes them
+            hidden = ref_a.to(torch.uint8).view(torch.float4_e2m1fn_x2)
+            scales = torch.randint(1, 256, (m, k // 2 // block_k), dtype=torch.uint8).view(torch.float8_e8m0fnu)
+        scores = torch.randn(m, e)
+        topk_weights, topk_ids = torch.topk(scores, k=topk, dim=-1, sorted=False)
+        # ref_prologue orders rows with Tensor.argsort(); the op's order inside an expert is
+        # ascending token by construction (fused_moe_prologue.hpp:153-210, 423-462), which that
+        # call only reproduces when the sort is stable - not the case for the CPU default.
+        plain_argsort = torch.Tensor.argsort
+        torch.Tensor.argsort = lambda self, *a, **kw: plain_argsort(self, *a, **{**kw, "stable": True})
+        try:
+            off, xin, xsc = ref["pro"].ref_prologue(ref_a, scales, topk_ids.view(-1), topk, e, recipe)
+        finally:
+            torch.Tensor.argsort = plain_argsort
+        cases.append(dict(recipe=recipe, num_experts=e, topk=topk, block_k=block_k,
+                          hidden_states=hidden.view(torch.uint8) if hidden.element_size() == 1 else hidden,
+                          scales=None if scales is None else (scales.view(torch.uint8) if scales.element_size() == 1 else scales),
+                          topk_ids=topk_ids, topk_weights=topk_weights, expert_offset=off,
+                          expand_input=xin.view(torch.uint8) if xin.element_size() == 1 else xin,
+                          expand_scales=None if xsc is None else (xsc.view(torch.uint8) if xsc.element_size() == 1 else xsc)))
+    torch.save(cases, OUT / "prologue.pt")
     print("wrote", sorted(p.name for p in OUT.glob("*.pt")))
 
 

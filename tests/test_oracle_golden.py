@@ -213,3 +213,30 @@ def test_batched_align_against_reference_vectors():
     for c in load_golden("batched_align.pt"):
         s, b, p = co.batched_moe_align_block_size(c["max_tokens"], c["block"], c["counts"])
         assert torch.equal(s, c["sorted_ids"]) and torch.equal(b, c["block_ids"]) and torch.equal(p, c["num_post_pad"])
+
+
+def test_prologue_against_reference_vectors():
+    """Legacy fused_moe_prologue: the restatement reproduces what the reference's pure-torch
+    ref_prologue gives (tests/fused_moe/test_moe_prologue.py:52-97), byte for byte."""
+    from prologue_cases import check_against_reference_vectors, regions, workspace_for
+    for c in load_golden("prologue.pt"):
+        layout, total = workspace_for(c)
+        ws = torch.zeros(total, dtype=torch.uint8)
+        x = c["hidden_states"]
+        co.fused_moe_prologue(x, c["scales"], c["topk_ids"], c["topk_weights"], ws, x.shape[1], c["block_k"], 0,
+                              c["num_experts"])
+        check_against_reference_vectors(c, regions(c, ws, layout))
+    # expert parallel: rank 1 of 2 keeps experts 8..15 as local 0..7; a repeated expert counts once
+    ids = torch.tensor([[3, 9], [9, 9], [15, 8], [0, 1]])
+    w = torch.arange(8, dtype=torch.float32).view(4, 2)
+    x = torch.arange(4 * 16, dtype=torch.float32).view(4, 16).bfloat16()
+    c = dict(hidden_states=x, scales=None, topk=2, num_experts=8, block_k=1, topk_ids=ids, topk_weights=w)
+    layout, total = workspace_for(c)
+    ws = torch.full((total,), 0xEE, dtype=torch.uint8)
+    co.fused_moe_prologue(x, None, ids, w, ws, 16, 1, 1, 8)
+    r = regions(c, ws, layout)
+    assert r["first"].tolist() == [0, 1, 3, 3, 3, 3, 3, 3, 4]
+    assert r["p2u"][:4].tolist() == [1 * 4 + 2, 1 * 4 + 0, 0 * 4 + 1, 0 * 4 + 2]
+    assert r["pexp"][:4].tolist() == [0, 1, 1, 7]
+    assert r["pscale"][:4].tolist() == [5.0, 1.0, 2.0, 4.0]
+    assert torch.equal(r["rows"][:4], x[[2, 0, 1, 2]])

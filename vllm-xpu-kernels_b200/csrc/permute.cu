@@ -36,16 +36,33 @@ struct SortParams {
   int id_limit;        // ids >= id_limit (or < 0) are dropped
   int n_buckets;
   int block_size;      // align: pad every bucket to a multiple of this; remap: 1
+  // LoRA variant: a slot counts only if its token is mapped to `lora_id`
+  const int32_t* token_lora = nullptr;  // [numel / topk] or null
+  int lora_id = 0;
+  int topk = 1;
+  // prologue variant: ids are global expert ids, bucket = id - id_offset; a
+  // token that names the same expert twice keeps only the first slot
+  int id_offset = 0;
+  bool first_match_only = false;
 };
 
-__device__ __forceinline__ int bucket_of(const SortParams& p, int64_t i) {
-  int64_t e;
+__device__ __forceinline__ int64_t raw_id(const SortParams& p, int64_t i) {
   switch (p.ids_dtype) {
-    case B200MOE_I64: e = reinterpret_cast<const int64_t*>(p.ids)[i]; break;
-    case B200MOE_U32: e = reinterpret_cast<const uint32_t*>(p.ids)[i]; break;
-    default: e = reinterpret_cast<const int32_t*>(p.ids)[i]; break;
+    case B200MOE_I64: return reinterpret_cast<const int64_t*>(p.ids)[i];
+    case B200MOE_U32: return reinterpret_cast<const uint32_t*>(p.ids)[i];
+    default: return reinterpret_cast<const int32_t*>(p.ids)[i];
   }
+}
+
+__device__ __forceinline__ int bucket_of(const SortParams& p, int64_t i) {
+  const int64_t raw = raw_id(p, i);
+  const int64_t e = raw - p.id_offset;
   if (e < 0 || e >= p.id_limit) return -1;
+  if (p.first_match_only) {
+    for (int64_t j = i - i % p.topk; j < i; ++j)
+      if (raw_id(p, j) == raw) return -1;
+  }
+  if (p.token_lora != nullptr && p.token_lora[i / p.topk] != p.lora_id) return -1;
   int b = (int)e;
   if (p.map != nullptr) b = p.map[b];
   if (b < 0 || b >= p.n_buckets) return -1;
@@ -193,6 +210,103 @@ sort_single_block_kernel(SortParams p, AlignOut ao, RemapOut ro) {
                 ro.row_map[i] = pos;  // -1 when the slot has no local expert
               }
             });
+}
+
+// ------------------------- LoRA variant ---------------------------------------
+// One block per entry of lora_ids (csrc/moe/moe_align_sum_kernels.cpp:732-847,
+// 926-1027 of the reference): the block aligns the slots whose token is mapped
+// to its adapter into that adapter's segment of the outputs.  Entries that are
+// -1, out of range or disabled return without writing anything.  The slots are
+// walked in rounds of kBlockSlots with the same stable ranking as above, so the
+// order inside an expert is ascending slot index.
+struct LoraAlignArgs {
+  const int32_t* adapter_enabled;
+  const int32_t* lora_ids;
+  int max_loras;
+  int max_num_tokens_padded;
+  int max_num_m_blocks;
+  int32_t* sorted;
+  int32_t* expert_ids;
+  int32_t* post_pad;
+};
+
+__global__ void __launch_bounds__(kBlockThreads)
+lora_align_kernel(SortParams p, LoraAlignArgs a) {
+  extern __shared__ int smem[];
+  const int nb = p.n_buckets;
+  int* hist = smem;                        // [kWarps][nb]
+  int* base = hist + kWarps * nb;          // [nb + 1]
+  int* warp_tot = base + nb + 1;           // [kWarps]
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int lora_id = a.lora_ids[blockIdx.x];
+  if (lora_id < 0 || lora_id >= a.max_loras || a.adapter_enabled[lora_id] == 0) return;
+  p.lora_id = lora_id;
+  int32_t* sorted = a.sorted + (int64_t)lora_id * a.max_num_tokens_padded;
+  int32_t* eids = a.expert_ids + (int64_t)lora_id * a.max_num_m_blocks;
+
+  for (int e = t; e <= nb; e += kBlockThreads) base[e] = 0;
+  for (int i = t; i < a.max_num_tokens_padded; i += kBlockThreads) sorted[i] = (int32_t)p.numel;
+  __syncthreads();
+  for (int64_t i = t; i < p.numel; i += kBlockThreads) {
+    const int b = bucket_of(p, i);
+    if (b >= 0) atomicAdd(&base[b], 1);
+  }
+  __syncthreads();
+  int padded[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = 4 * t + j;
+    padded[j] = (e < nb) ? ((base[e] + p.block_size - 1) / p.block_size) * p.block_size : 0;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (4 * t + j < nb) base[4 * t + j] = padded[j];
+  __syncthreads();
+  block_exclusive_scan(base, nb, warp_tot);
+  const int total = base[nb];
+  if (t == 0) a.post_pad[lora_id] = total;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = 4 * t + j;
+    if (e < nb) {
+      for (int o = 0; o < padded[j]; o += p.block_size) {
+        const int blk = (base[e] + o) / p.block_size;
+        if (blk < a.max_num_m_blocks) eids[blk] = e;
+      }
+    }
+  }
+  for (int blk = total / p.block_size + t; blk < a.max_num_m_blocks; blk += kBlockThreads) eids[blk] = -1;
+
+  // base[e] is from here on the next free position of expert e
+  for (int64_t r0 = 0; r0 < p.numel; r0 += kBlockSlots) {
+    for (int i = t; i < kWarps * nb; i += kBlockThreads) hist[i] = 0;
+    __syncthreads();
+    const int64_t begin = r0 + (int64_t)warp * kChunk;
+    for (int s = 0; s < kChunk / 32; ++s) {
+      const int64_t i = begin + s * 32 + lane;
+      if (i < p.numel) {
+        const int b = bucket_of(p, i);
+        if (b >= 0) atomicAdd(&hist[warp * nb + b], 1);
+      }
+    }
+    __syncthreads();
+    for (int e = t; e < nb; e += kBlockThreads) {
+      int run = base[e];
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const int c = hist[w * nb + e];
+        hist[w * nb + e] = run;
+        run += c;
+      }
+      base[e] = run;
+    }
+    __syncthreads();
+    rank_walk(p, begin, hist + warp * nb, [&](int64_t i, int b, int pos) {
+      if (b >= 0 && pos < a.max_num_tokens_padded) sorted[pos] = (int32_t)i;
+    });
+    __syncthreads();
+  }
 }
 
 // ------------------------- multi-block path ---------------------------------
@@ -509,6 +623,213 @@ extern "C" int b200moe_moe_align_block_size(
   AlignOut ao = {sorted_token_ids, sorted_len, expert_ids, expert_ids_len, num_tokens_post_pad};
   RemapOut ro = {};
   return run_sort<0>(p, ao, ro, workspace, workspace_bytes, as_stream(stream));
+}
+
+// ------------------------- legacy prologue ------------------------------------
+namespace b200moe {
+namespace {
+
+// Tokens per block of the reference's three-step sort; it only enters the size
+// of two scratch regions of the packed workspace
+// (csrc/moe/fused_moe_prologue.hpp:43-60 of the reference).
+int64_t prologue_tokens_per_block(int64_t num_tokens, int64_t experts) {
+  for (int64_t n = 32; n <= 1024; n *= 2)
+    if ((num_tokens + n - 1) / n * experts <= n) return n;
+  return 1024;
+}
+
+struct PrologueArgs {
+  const unsigned char* input;  unsigned char* permuted;  int64_t row_bytes;
+  const unsigned char* scales; unsigned char* permuted_scales; int64_t scale_row_bytes;
+  const float* final_scales;   float* permuted_final_scales;
+  const int32_t* rows_per_expert;  // [experts]
+  const int32_t* row_map;          // [tokens * topk], -1 = not on this rank
+  const void* ids; int id_offset;
+  int32_t* permuted_to_unpermuted; int32_t* permuted_experts; int32_t* unpermuted_to_permuted;
+  int64_t* first_token_offset;     // [experts + 1]
+  int64_t num_tokens; int topk; int experts;
+};
+
+__device__ __forceinline__ void copy_bytes(unsigned char* dst, const unsigned char* src, int64_t n) {
+  if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src) | (uintptr_t)n) & 15) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int64_t i = threadIdx.x; i < n / 16; i += blockDim.x) d4[i] = __ldg(s4 + i);
+  } else {
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// One block per routed slot (grid-stride): copies the token's row, its scale row
+// and its routing weight to the slot's permuted position and writes the three
+// index maps.  Block 0 first turns the per-expert counts into the int64 offsets.
+__global__ void __launch_bounds__(kBlockThreads)
+prologue_expand_kernel(PrologueArgs a) {
+  __shared__ int scan[kMaxBuckets + 1];
+  __shared__ int warp_tot[kWarps];
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < a.experts; e += kBlockThreads) scan[e] = a.rows_per_expert[e];
+    __syncthreads();
+    block_exclusive_scan(scan, a.experts, warp_tot);
+    for (int e = threadIdx.x; e <= a.experts; e += kBlockThreads) a.first_token_offset[e] = scan[e];
+  }
+  const int64_t n = a.num_tokens * a.topk;
+  for (int64_t i = blockIdx.x; i < n; i += gridDim.x) {
+    const int pos = a.row_map[i];
+    if (pos < 0) continue;
+    const int64_t token = i / a.topk;
+    const int k = (int)(i - token * a.topk);
+    if (threadIdx.x == 0) {
+      const int32_t u = (int32_t)(k * a.num_tokens + token);
+      a.permuted_to_unpermuted[pos] = u;
+      a.unpermuted_to_permuted[u] = pos;
+      a.permuted_experts[pos] = (int32_t)(reinterpret_cast<const int64_t*>(a.ids)[i] - a.id_offset);
+      a.permuted_final_scales[pos] = a.final_scales ? a.final_scales[i] : 1.0f;
+    }
+    copy_bytes(a.permuted + (int64_t)pos * a.row_bytes, a.input + token * a.row_bytes, a.row_bytes);
+    if (a.scales != nullptr)
+      copy_bytes(a.permuted_scales + (int64_t)pos * a.scale_row_bytes,
+                 a.scales + token * a.scale_row_bytes, a.scale_row_bytes);
+  }
+}
+
+}  // namespace
+}  // namespace b200moe
+
+extern "C" int b200moe_fused_moe_prologue_layout(int64_t num_rows, int topk, int num_experts_on_rank,
+                                                 int64_t hidden_size, int block_k, int elem_bytes,
+                                                 int scale_elem_bytes, size_t offsets[10],
+                                                 size_t* total_bytes) {
+  B200_CHECK_ARG(num_rows >= 0 && topk >= 1 && num_experts_on_rank >= 1 && hidden_size >= 0 &&
+                     block_k >= 1 && elem_bytes >= 1 && scale_elem_bytes >= 0 && offsets && total_bytes,
+                 "fused_moe_prologue_layout: bad arguments");
+  const size_t n = (size_t)num_rows * topk;
+  const int64_t tpb = prologue_tokens_per_block(num_rows, num_experts_on_rank);
+  const size_t blocks_per_seq = (size_t)((num_rows + tpb - 1) / tpb);
+  const size_t counts = (size_t)num_experts_on_rank * blocks_per_seq * sizeof(int);
+  const size_t sizes[10] = {
+      n * sizeof(int),                                     // permuted_row_to_unpermuted_row
+      n * sizeof(int),                                     // permuted_token_selected_experts
+      n * sizeof(int),                                     // unpermuted_row_to_permuted_row
+      counts,                                              // blocked_expert_counts (scratch)
+      counts,                                              // blocked_expert_counts_cumsum (scratch)
+      (size_t)num_experts_on_rank * num_rows * sizeof(int),  // blocked_row_to_unpermuted_row (scratch)
+      (size_t)(num_experts_on_rank + 1) * sizeof(int64_t), // expert_first_token_offset
+      n * sizeof(float),                                   // permuted_token_final_scales
+      n * (size_t)hidden_size * elem_bytes,                // permuted rows
+      n * (size_t)hidden_size / block_k * scale_elem_bytes // permuted scale rows
+  };
+  size_t off = 0;
+  for (int i = 0; i < 10; ++i) {
+    offsets[i] = off;
+    off += (sizes[i] + 255) & ~(size_t)255;
+  }
+  *total_bytes = off;
+  return B200MOE_OK;
+}
+
+extern "C" size_t b200moe_fused_moe_prologue_scratch_bytes(int64_t num_rows, int topk,
+                                                           int num_experts_on_rank) {
+  const size_t n = (size_t)num_rows * topk;
+  const size_t maps = ((n + num_experts_on_rank) * sizeof(int32_t) + 255) & ~(size_t)255;
+  return maps + b200moe_sort_workspace_bytes((int64_t)n, num_experts_on_rank);
+}
+
+extern "C" int b200moe_fused_moe_prologue(
+    const void* input, int elem_bytes, const void* input_scales, int scale_elem_bytes,
+    const int64_t* token_selected_experts, const float* token_final_scales, void* workspace,
+    size_t workspace_bytes, int64_t num_rows, int64_t hidden_size, int block_k, int topk,
+    int ep_rank, int ep_size, int num_experts_on_rank, void* scratch, size_t scratch_bytes,
+    b200moe_stream stream) {
+  B200_CHECK_ARG(ep_size >= 1 && ep_rank >= 0 && ep_rank < ep_size, "fused_moe_prologue: bad ep_rank/ep_size");
+  B200_CHECK_ARG(num_experts_on_rank >= 1 && num_experts_on_rank <= kMaxBuckets,
+                 "fused_moe_prologue: at most 1024 experts per rank");
+  B200_CHECK_ARG(topk >= 1 && topk <= 32 && num_rows >= 0 && hidden_size >= 1 && block_k >= 1,
+                 "fused_moe_prologue: bad sizes");
+  B200_CHECK_ARG((int64_t)num_rows * topk < (int64_t)1 << 31, "fused_moe_prologue: too many routed rows");
+  B200_CHECK_ARG(workspace && (num_rows == 0 || (input && token_selected_experts)),
+                 "fused_moe_prologue: null pointer");
+  B200_CHECK_ARG(input_scales == nullptr || scale_elem_bytes >= 1, "fused_moe_prologue: scale element size");
+  size_t off[10], total = 0;
+  if (int rc = b200moe_fused_moe_prologue_layout(num_rows, topk, num_experts_on_rank, hidden_size, block_k,
+                                                 elem_bytes, input_scales ? scale_elem_bytes : 0, off, &total))
+    return rc;
+  if (workspace_bytes < total)
+    return fail(B200MOE_E_WORKSPACE, "fused_moe_prologue: workspace of %zu bytes needed, got %zu", total,
+                workspace_bytes);
+  const size_t need = b200moe_fused_moe_prologue_scratch_bytes(num_rows, topk, num_experts_on_rank);
+  if (scratch == nullptr || scratch_bytes < need)
+    return fail(B200MOE_E_WORKSPACE, "fused_moe_prologue: scratch of %zu bytes needed, got %zu", need,
+                scratch_bytes);
+  const size_t n = (size_t)num_rows * topk;
+  unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+  int32_t* rows = reinterpret_cast<int32_t*>(scratch);
+  int32_t* row_map = rows + num_experts_on_rank;
+  const size_t maps = ((n + num_experts_on_rank) * sizeof(int32_t) + 255) & ~(size_t)255;
+  cudaStream_t st = as_stream(stream);
+
+  SortParams p;
+  p.ids = token_selected_experts; p.ids_dtype = B200MOE_I64; p.map = nullptr;
+  p.numel = (int64_t)n; p.id_limit = num_experts_on_rank; p.n_buckets = num_experts_on_rank;
+  p.block_size = 1; p.topk = topk;
+  p.id_offset = num_experts_on_rank * ep_rank; p.first_match_only = true;
+  AlignOut ao = {};
+  RemapOut ro = {rows, row_map};
+  if (int rc = run_sort<1>(p, ao, ro, reinterpret_cast<unsigned char*>(scratch) + maps, scratch_bytes - maps, st))
+    return rc;
+
+  PrologueArgs a;
+  a.input = reinterpret_cast<const unsigned char*>(input);
+  a.permuted = ws + off[8];
+  a.row_bytes = hidden_size * elem_bytes;
+  a.scales = reinterpret_cast<const unsigned char*>(input_scales);
+  a.permuted_scales = ws + off[9];
+  a.scale_row_bytes = input_scales ? (hidden_size / block_k) * scale_elem_bytes : 0;
+  a.final_scales = token_final_scales;
+  a.permuted_final_scales = reinterpret_cast<float*>(ws + off[7]);
+  a.rows_per_expert = rows; a.row_map = row_map;
+  a.ids = token_selected_experts; a.id_offset = p.id_offset;
+  a.permuted_to_unpermuted = reinterpret_cast<int32_t*>(ws + off[0]);
+  a.permuted_experts = reinterpret_cast<int32_t*>(ws + off[1]);
+  a.unpermuted_to_permuted = reinterpret_cast<int32_t*>(ws + off[2]);
+  a.first_token_offset = reinterpret_cast<int64_t*>(ws + off[6]);
+  a.num_tokens = num_rows; a.topk = topk; a.experts = num_experts_on_rank;
+  const int64_t want = (int64_t)n < 1 ? 1 : (int64_t)n;
+  const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+  prologue_expand_kernel<<<grid, kBlockThreads, 0, st>>>(a);
+  B200_LAUNCH_OK("prologue_expand_kernel");
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_moe_lora_align_block_size(
+    const void* topk_ids, b200moe_dtype ids_dtype, int64_t numel, int topk,
+    const int32_t* token_lora_mapping, int num_experts, int block_size, int max_loras,
+    int max_num_tokens_padded, int max_num_m_blocks, int32_t* sorted_token_ids,
+    int32_t* expert_ids, int32_t* num_tokens_post_pad, const int32_t* adapter_enabled,
+    const int32_t* lora_ids, const int32_t* expert_map, b200moe_stream stream) {
+  B200_CHECK_ARG(ids_dtype == B200MOE_I32 || ids_dtype == B200MOE_I64 || ids_dtype == B200MOE_U32,
+                 "moe_lora_align_block_size: topk_ids must be an integer tensor");
+  B200_CHECK_ARG(block_size > 0, "block_size should be greater than 0. ");
+  B200_CHECK_ARG(num_experts >= 1 && ((num_experts + 31) / 32) * 32 < 1024,
+                 "padded_num_experts must be less than 1024");
+  B200_CHECK_ARG(topk >= 1 && numel >= 0 && numel % topk == 0 && max_loras >= 0 &&
+                     max_num_tokens_padded >= 0 && max_num_m_blocks >= 0,
+                 "moe_lora_align_block_size: bad sizes");
+  B200_CHECK_ARG(token_lora_mapping && sorted_token_ids && expert_ids && num_tokens_post_pad &&
+                     adapter_enabled && lora_ids && (numel == 0 || topk_ids),
+                 "moe_lora_align_block_size: null pointer");
+  SortParams p;
+  p.ids = topk_ids; p.ids_dtype = ids_dtype; p.map = expert_map;
+  p.numel = numel; p.id_limit = num_experts; p.n_buckets = num_experts;
+  p.block_size = block_size;
+  p.token_lora = token_lora_mapping; p.topk = topk;
+  LoraAlignArgs a = {adapter_enabled, lora_ids, max_loras, max_num_tokens_padded, max_num_m_blocks,
+                     sorted_token_ids, expert_ids, num_tokens_post_pad};
+  const size_t smem = (size_t)(kWarps * num_experts + num_experts + 1 + kWarps) * sizeof(int);
+  // lora_ids has max_loras + 1 entries: every adapter slot plus a possible -1
+  lora_align_kernel<<<max_loras + 1, kBlockThreads, smem, as_stream(stream)>>>(p, a);
+  B200_LAUNCH_OK("lora_align_kernel");
+  return B200MOE_OK;
 }
 
 namespace b200moe {

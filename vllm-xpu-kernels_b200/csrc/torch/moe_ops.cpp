@@ -78,6 +78,86 @@ void batched_moe_align_block_size(int64_t max_tokens_per_batch, int64_t block_si
       current_stream()));
 }
 
+// csrc/moe/fused_moe_prologue.cpp:170-216 of the reference.  Rows and scales are moved
+// as opaque storage elements, so every dtype the reference dispatches on (bf16, fp16,
+// fp8 e4m3 with f32 or e8m0 scales, packed fp4 with e8m0 scales) is covered by its
+// element size.
+void fused_moe_prologue(at::Tensor input, const std::optional<at::Tensor>& input_scales,
+                        at::Tensor token_selected_experts, at::Tensor token_final_scales,
+                        at::Tensor workspace, int64_t hidden_size, int64_t inter_size, int64_t block_k,
+                        int64_t ep_rank, int64_t ep_size, int64_t num_experts_on_rank) {
+  (void)inter_size;
+  check_cuda(input, "input");
+  check_cuda(workspace, "workspace");
+  TORCH_CHECK(token_selected_experts.scalar_type() == at::kLong, "token_selected_experts must be int64");
+  TORCH_CHECK(token_final_scales.scalar_type() == at::kFloat, "token_final_scales must be float32");
+  TORCH_CHECK(input.dim() == 2 && input.is_contiguous() && token_selected_experts.dim() == 2 &&
+              token_selected_experts.is_contiguous() && token_final_scales.is_contiguous() &&
+              workspace.is_contiguous(),
+              "fused_moe_prologue expects contiguous tensors");
+  TORCH_CHECK(input.size(1) == hidden_size, "hidden_size does not match the input rows");
+  TORCH_CHECK(ep_rank >= 0 && ep_rank < ep_size, "ep_rank out of range");
+  const int64_t num_rows = input.size(0);
+  const int topk = (int)token_selected_experts.size(1);
+  TORCH_CHECK(token_selected_experts.size(0) == num_rows && token_final_scales.numel() == num_rows * topk,
+              "routing tensors do not match the input rows");
+  int scale_bytes = 0;
+  const void* scales = nullptr;
+  if (input_scales.has_value()) {
+    TORCH_CHECK(input_scales->is_contiguous() && input_scales->is_cuda(), "input_scales must be contiguous CUDA");
+    TORCH_CHECK(input_scales->numel() == num_rows * (hidden_size / block_k),
+                "input_scales must hold hidden_size / block_k entries per row");
+    scale_bytes = (int)input_scales->element_size();
+    scales = input_scales->data_ptr();
+  }
+  const c10::cuda::CUDAGuard guard(input.device());
+  const size_t scratch_bytes =
+      b200moe_fused_moe_prologue_scratch_bytes(num_rows, topk, (int)num_experts_on_rank);
+  at::Tensor scratch = at::empty({(int64_t)scratch_bytes}, input.options().dtype(at::kByte));
+  check_status(b200moe_fused_moe_prologue(
+      input.data_ptr(), (int)input.element_size(), scales, scale_bytes,
+      token_selected_experts.data_ptr<int64_t>(), token_final_scales.data_ptr<float>(),
+      workspace.data_ptr(), (size_t)workspace.nbytes(), num_rows, hidden_size, (int)block_k, topk,
+      (int)ep_rank, (int)ep_size, (int)num_experts_on_rank, scratch.data_ptr(), scratch_bytes,
+      current_stream()));
+}
+
+// csrc/moe/moe_align_sum_kernels.cpp:1374-1549 of the reference.
+void moe_lora_align_block_size(at::Tensor topk_ids, at::Tensor token_lora_mapping, int64_t num_experts,
+                               int64_t block_size, int64_t max_loras, int64_t max_num_tokens_padded,
+                               int64_t max_num_m_blocks, at::Tensor sorted_token_ids,
+                               at::Tensor expert_ids, at::Tensor num_tokens_post_pad,
+                               at::Tensor adapter_enabled, at::Tensor lora_ids,
+                               std::optional<at::Tensor> maybe_expert_map) {
+  check_cuda(topk_ids, "topk_ids");
+  TORCH_CHECK(block_size > 0, "block_size should be greater than 0. ");
+  TORCH_CHECK((num_experts + 31) / 32 * 32 < 1024, "padded_num_experts must be less than 1024");
+  TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous(), "topk_ids must be a contiguous [tokens, topk] tensor");
+  for (const at::Tensor* t : {&token_lora_mapping, &sorted_token_ids, &expert_ids, &num_tokens_post_pad,
+                              &adapter_enabled, &lora_ids})
+    TORCH_CHECK(t->scalar_type() == at::kInt && t->is_contiguous() && t->is_cuda(),
+                "moe_lora_align_block_size expects contiguous int32 CUDA tensors");
+  TORCH_CHECK(token_lora_mapping.numel() >= topk_ids.size(0), "token_lora_mapping is shorter than the token count");
+  TORCH_CHECK(sorted_token_ids.numel() >= max_loras * max_num_tokens_padded, "sorted_token_ids is too small");
+  TORCH_CHECK(expert_ids.numel() >= max_loras * max_num_m_blocks, "experts_ids is too small");
+  TORCH_CHECK(num_tokens_post_pad.numel() >= max_loras, "num_tokens_post_pad is too small");
+  TORCH_CHECK(lora_ids.numel() >= max_loras + 1 && adapter_enabled.numel() >= max_loras,
+              "lora_ids needs max_loras + 1 entries and adapter_enabled max_loras");
+  const int32_t* map = nullptr;
+  if (maybe_expert_map.has_value()) {
+    TORCH_CHECK(maybe_expert_map->scalar_type() == at::kInt && maybe_expert_map->is_contiguous(),
+                "expert_map must be contiguous int32");
+    map = maybe_expert_map->data_ptr<int32_t>();
+  }
+  const c10::cuda::CUDAGuard guard(topk_ids.device());
+  check_status(b200moe_moe_lora_align_block_size(
+      topk_ids.data_ptr(), index_dtype(topk_ids), topk_ids.numel(), (int)topk_ids.size(1),
+      token_lora_mapping.data_ptr<int32_t>(), (int)num_experts, (int)block_size, (int)max_loras,
+      (int)max_num_tokens_padded, (int)max_num_m_blocks, sorted_token_ids.data_ptr<int32_t>(),
+      expert_ids.data_ptr<int32_t>(), num_tokens_post_pad.data_ptr<int32_t>(),
+      adapter_enabled.data_ptr<int32_t>(), lora_ids.data_ptr<int32_t>(), map, current_stream()));
+}
+
 // csrc/moe/topk_softplus_sqrt_kernels.cpp:596-772 of the reference.
 void topk_softplus_sqrt(at::Tensor& topk_weights, at::Tensor& topk_indices,
                         at::Tensor& token_expert_indices, at::Tensor& gating_output, bool renormalize,
@@ -378,6 +458,19 @@ TORCH_LIBRARY_FRAGMENT(_moe_C, m) {
       "                     Tensor! experts_ids,"
       "                     Tensor! num_tokens_post_pad) -> ()");
   m.def(
+      "moe_lora_align_block_size(Tensor topk_ids,"
+      "                     Tensor token_lora_mapping,"
+      "                     int num_experts,"
+      "                     int block_size, int max_loras, "
+      "                     int max_num_tokens_padded, "
+      "                     int max_num_m_blocks, "
+      "                     Tensor! sorted_token_ids,"
+      "                     Tensor! experts_ids,"
+      "                     Tensor! num_tokens_post_pad,"
+      "                     Tensor! adapter_enabled,"
+      "                     Tensor! lora_ids,"
+      "                     Tensor? maybe_expert_map) -> () ");
+  m.def(
       "topk_softplus_sqrt(Tensor! topk_weights, Tensor! topk_indices, "
       "Tensor! token_expert_indices, Tensor gating_output, bool renormalize, "
       "float routed_scaling_factor, Tensor? correction_bias=None, Tensor? "
@@ -385,6 +478,15 @@ TORCH_LIBRARY_FRAGMENT(_moe_C, m) {
   m.def(
       "moe_gather(Tensor! output, Tensor moe_output, Tensor topk_weights, "
       "Tensor unpermuted_row_to_permuted_row, int num_experts) -> ()");
+  m.def(
+      "fused_moe_prologue(Tensor input, Tensor? input_scales, Tensor "
+      "token_selected_experts, "
+      "Tensor "
+      "token_final_scales, Tensor workspace, int hidden_size, int inter_size, "
+      "int block_k, "
+      "int ep_rank, int ep_size,"
+      "int num_experts_on_rank) -> "
+      "()");
   m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
   m.def(
       "remap_hidden_states(Tensor hidden_states, Tensor? hidden_states_scales, "
@@ -407,6 +509,8 @@ TORCH_LIBRARY_IMPL(_moe_C, CUDA, m) {
   m.impl("grouped_topk", &grouped_topk);
   m.impl("topk_softplus_sqrt", &topk_softplus_sqrt);
   m.impl("batched_moe_align_block_size", &batched_moe_align_block_size);
+  m.impl("moe_lora_align_block_size", &moe_lora_align_block_size);
+  m.impl("fused_moe_prologue", &fused_moe_prologue);
   m.impl("topk_softmax", &topk_softmax);
   m.impl("topk_sigmoid", &topk_sigmoid);
   m.impl("moe_gather", &moe_gather);
