@@ -285,8 +285,9 @@ typedef enum {
   B200MOE_W_FP8_BLOCK_KN = 4,  /* fp8 e4m3 [E,K,N] + same scales                    */
   B200MOE_W_MXFP4_NK = 5, /* e2m1 pairs [E,N,K/2] + e8m0 bytes [E,N,K/32]           */
   B200MOE_W_FP8E5M2_TENSOR_KN = 6, /* fp8 e5m2 [E,K,N] + fp32 scale [E]               */
-  B200MOE_W_INT4_NK = 7   /* two's-complement 4-bit pairs [E,N,K/2] (low nibble = even k)
+  B200MOE_W_INT4_NK = 7,  /* two's-complement 4-bit pairs [E,N,K/2] (low nibble = even k)
                              + scales [E,N,K/group_size] in the activation dtype   */
+  B200MOE_W_MXFP8_KN = 8  /* fp8 e4m3 [E,K,N] + e8m0 bytes [E,K/32,N] (one per 32 K rows) */
 } b200moe_weight_format;
 
 typedef enum {

@@ -242,6 +242,22 @@ def dequant_mxfp8(q, scale_u8):
     return (q.float().reshape(terms, rows, cols // 32, 32) * sc.unsqueeze(-1)).sum(dim=0).reshape(rows, cols)
 
 
+def dequant_mxfp8_wei(w, scale_u8):
+    """vllm_xpu_kernels/moe_utils.py:76-78: w [K,N] e4m3, scale_u8 [K/32,N] e8m0 bytes,
+    one per 32 K rows -> fp32 [K,N]."""
+    return w.float() * torch.exp2(scale_u8.float() - 127.0).repeat_interleave(32, dim=0)
+
+
+def quant_mxfp8_wei(w):
+    """Synthetic-weight helper: w [K,N] -> (e4m3 [K,N], e8m0 bytes [K/32,N]) with the
+    smallest power-of-two scale per 32 K rows that keeps amax / scale <= 448."""
+    K, N = w.shape
+    v = w.float().reshape(K // 32, 32, N)
+    sc = _ceil_pow2(v.abs().amax(dim=1) / FP8_MAX, 2.0 ** -100)
+    q = (v / sc.unsqueeze(1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).reshape(K, N)
+    return q, (torch.log2(sc) + 127).to(torch.uint8)
+
+
 def _ceil_pow2(v, eps):
     """exp2(ceil(log2(max(|v|, eps)))) computed exactly."""
     m, e = torch.frexp(v.abs().clamp(min=eps))
@@ -362,10 +378,13 @@ def dequant_int4(packed_u4, scales, group_size):
 
 
 # --------------------------------------------------------------------------- grouped GEMM
-def grouped_gemm(a, w_deq, bias, rows_per_expert, out_dtype):
+def grouped_gemm(a, w_deq, bias, rows_per_expert, out_dtype, bias_after_rounding=False):
     """Per-expert fp32 matmul over the ragged segments (semantics of
     csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2.hpp:125-251): a [M,K] fp32,
-    w_deq [E,N,K] fp32 (already dequantised), bias [E,N] or None."""
+    w_deq [E,N,K] fp32 (already dequantised), bias [E,N] or None.  The kernels add the
+    bias to the fp32 accumulator; bias_after_rounding restates the reference's eager
+    simulation instead, which rounds the product to out_dtype first and adds the bias in
+    that type (vllm_xpu_kernels/moe_utils.py:345-351)."""
     M = a.shape[0]
     N = w_deq.shape[1]
     out = torch.zeros(M, N, dtype=torch.float32)
@@ -375,7 +394,7 @@ def grouped_gemm(a, w_deq, bias, rows_per_expert, out_dtype):
             continue
         o = a[off:off + r].float() @ w_deq[e].float().T
         if bias is not None:
-            o = o + bias[e].float()
+            o = (o.to(out_dtype) + bias[e].to(out_dtype)).float() if bias_after_rounding else o + bias[e].float()
         out[off:off + r] = o
         off += r
     return out.to(out_dtype)
@@ -424,7 +443,7 @@ def fused_moe_bf16(x, w13, w13_bias, w2, w2_bias, topk_weights, topk_ids, num_ex
 
 def fused_moe_staged(x, w13_deq, w13_bias, w2_deq, w2_bias, topk_weights, topk_ids, num_experts,
                      activation="silu", act_quant=False, expert_map=None, alpha=1.702, limit=7.0,
-                     gemm1_clamp_limit=None):
+                     gemm1_clamp_limit=None, bias_after_rounding=False):
     """The layer as the reference's kernel path stages it
     (vllm_xpu_kernels/fused_moe_interface.py:328-419 with the qdq semantics of
     vllm_xpu_kernels/moe_utils.py:236-403): permute -> GEMM1 (fp32 accumulate,
@@ -441,7 +460,7 @@ def fused_moe_staged(x, w13_deq, w13_bias, w2_deq, w2_bias, topk_weights, topk_i
     elif act_quant:
         q, s = per_token_group_fp8_quant(remapped)
         a1 = dequant_fp8_block_act(q, s)
-    g1 = grouped_gemm(a1, w13_deq, w13_bias, rows, dt)
+    g1 = grouped_gemm(a1, w13_deq, w13_bias, rows, dt, bias_after_rounding)
     if gemm1_clamp_limit is not None and gemm1_clamp_limit > 0:
         I = g1.shape[1] // 2
         g1[:, :I] = g1[:, :I].clamp(max=gemm1_clamp_limit)
@@ -465,5 +484,5 @@ def fused_moe_staged(x, w13_deq, w13_bias, w2_deq, w2_bias, topk_weights, topk_i
     elif act_quant:
         q, s = per_token_group_fp8_quant(act)
         a2 = dequant_fp8_block_act(q, s)
-    g2 = grouped_gemm(a2, w2_deq, w2_bias, rows, dt)
+    g2 = grouped_gemm(a2, w2_deq, w2_bias, rows, dt, bias_after_rounding)
     return moe_gather(g2, topk_weights, row_map, dt)

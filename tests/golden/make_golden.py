@@ -54,6 +54,52 @@ def load_reference(root: str):
                 layer=layer_t, act=act_op, swi=swi_op, fp8=fp8_t, mu=mu)
 
 
+def install_cpu_ops():
+    """CPU implementations of the few registered ops the reference's eager simulation
+    ref_fused_moe (vllm_xpu_kernels/moe_utils.py:236-403) calls around its own torch code.
+    They are this repository's restatements of those ops, each checked separately against
+    reference-made vectors; everything recipe-specific (MX quantise / dequantise, the matmuls,
+    their order and dtypes) stays the reference's own Python."""
+    sys.path.insert(0, str(OUT.parents[1]))
+    from oracle import torch_oracle as to
+    moe = torch.library.Library("_moe_C", "DEF")
+    moe.define("remap_hidden_states(Tensor hidden_states, Tensor? hidden_states_scales, "
+               "Tensor(a!) remapped_hidden_states, Tensor? remapped_hidden_states_scales, Tensor? expert_map, "
+               "Tensor(b!) rows_per_expert, Tensor(c!) unpermuted_row_to_permuted_row, Tensor topk_ids, "
+               "int total_experts_num, int local_experts_num) -> ()")
+    moe.define("moe_gather(Tensor(a!) output, Tensor moe_output, Tensor topk_weights, "
+               "Tensor unpermuted_row_to_permuted_row, int num_experts) -> ()")
+    c = torch.library.Library("_C", "DEF")
+    c.define("per_token_group_fp8_quant(Tensor input, Tensor(a!) output_q, Tensor(b!) output_s, int group_size, "
+             "float eps, float fp8_min, float fp8_max, bool scale_ue8m0, bool a, bool b) -> ()")
+    c.define("silu_and_mul(Tensor(a!) out, Tensor input) -> ()")
+
+    def remap(hidden_states, hidden_states_scales, remapped_hidden_states, remapped_hidden_states_scales,
+              expert_map, rows_per_expert, unpermuted_row_to_permuted_row, topk_ids, total_experts_num,
+              local_experts_num):
+        r, _, rows, row_map = to.remap_hidden_states(hidden_states, None, topk_ids, expert_map, local_experts_num)
+        remapped_hidden_states.copy_(r)
+        rows_per_expert.copy_(rows)
+        unpermuted_row_to_permuted_row.copy_(row_map)
+
+    def gather(output, moe_output, topk_weights, unpermuted_row_to_permuted_row, num_experts):
+        output.copy_(to.moe_gather(moe_output, topk_weights, unpermuted_row_to_permuted_row, output.dtype))
+
+    def group_quant(input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0, a, b):
+        q, sc = to.per_token_group_fp8_quant(input, group_size, eps, scale_ue8m0)
+        output_q.copy_(q)
+        output_s.copy_(sc)
+
+    def silu(out, input):
+        out.copy_(to.silu_and_mul(input))
+
+    moe.impl("remap_hidden_states", remap, "CPU")
+    moe.impl("moe_gather", gather, "CPU")
+    c.impl("per_token_group_fp8_quant", group_quant, "CPU")
+    c.impl("silu_and_mul", silu, "CPU")
+    return moe, c, to
+
+
 def capture_batched_align(align_t, max_tokens, num_experts, block, empty):
     """The reference's expected outputs for batched_moe_align_block_size live in a
     function nested in its test (tests/test_moe_align_block_size.py:340-417); run
@@ -329,6 +375,32 @@ def main():
                           expand_input=xin.view(torch.uint8) if xin.element_size() == 1 else xin,
                           expand_scales=None if xsc is None else (xsc.view(torch.uint8) if xsc.element_size() == 1 else xsc)))
     torch.save(cases, OUT / "prologue.pt")
+
+    # ---- mxfp8 recipe: the reference's eager simulation is its only implementation ---------------------
+    # (vllm_xpu_kernels/fused_moe_interface.py:27-31 routes mxfp8 weights to ref_fused_moe)
+    _libs = install_cpu_ops()
+    to = _libs[2]
+    cases = []
+    for (m, H, I, E, topk, dtype, bias) in [(1, 128, 128, 4, 2, torch.bfloat16, False),
+                                            (33, 256, 160, 8, 2, torch.bfloat16, True),
+                                            (40, 160, 128, 8, 4, torch.float16, False)]:
+        torch.manual_seed(11 + m)
+        x = (torch.randn(m, H) / 2).to(dtype)
+        w13_q, w13_s, w2_q, w2_s = [], [], [], []
+        for _ in range(E):
+            q, sc = to.quant_mxfp8_wei(torch.randn(H, 2 * I) / H ** 0.5)
+            w13_q.append(q); w13_s.append(sc)
+            q, sc = to.quant_mxfp8_wei(torch.randn(I, H) / I ** 0.5)
+            w2_q.append(q); w2_s.append(sc)
+        w13, w13_s, w2, w2_s = torch.stack(w13_q), torch.stack(w13_s), torch.stack(w2_q), torch.stack(w2_s)
+        b13 = (torch.randn(E, 2 * I) / 10).to(dtype) if bias else None
+        b2 = (torch.randn(E, H) / 10).to(dtype) if bias else None
+        tw, ti = torch.topk(torch.softmax(torch.randn(m, E), dim=-1), topk, dim=-1)
+        out = torch.empty_like(x)
+        ref["mu"].ref_fused_moe("mxfp8", out, x, w13, w13_s, b13, w2, w2_s, b2, tw, ti.int(), topk, "silu", E)
+        cases.append(dict(x=x, w13=w13.view(torch.uint8), w13_scales=w13_s, w13_bias=b13, w2=w2.view(torch.uint8),
+                          w2_scales=w2_s, w2_bias=b2, topk_weights=tw, topk_ids=ti.int(), num_experts=E, out=out))
+    torch.save(cases, OUT / "layer_mxfp8.pt")
     print("wrote", sorted(p.name for p in OUT.glob("*.pt")))
 
 

@@ -107,3 +107,36 @@ def test_grouped_gemm_per_tensor_fp8_block_scaled(native, E, M, N, K, w_dtype, h
         chk = grouped_gemm(x.to(DEV), None, w.to(DEV), sc.to(DEV), bias.to(DEV) if has_bias else None,
                            rows.to(DEV), N, K, impl=2)
         torch.testing.assert_close(out.cpu()[:n].float(), chk.cpu()[:n].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("E,M,N,K", [(4, 30, 256, 128), (4, 50, 256, 160), (8, 130, 720, 576), (3, 700, 2816, 2048),
+                                     (2, 3, 128, 256), (5, 64, 208, 320), (2, 40, 144, 6144)])
+@pytest.mark.parametrize("has_bias", [False, True])
+@pytest.mark.parametrize("terms", [1, 2])
+def test_grouped_gemm_mxfp8_weights_block_scaled(native, E, M, N, K, has_bias, terms):
+    """MXFP8 weights ([E,K,N] e4m3, e8m0 scales [E,K/32,N]; the reference's "mxfp8" recipe,
+    vllm_xpu_kernels/moe_utils.py:76-78) against MXFP8 activation planes: both operands'
+    scales are applied inside the block-scaled instruction."""
+    g = torch.Generator().manual_seed(N + K + M + 5)
+    rows = random_rows(E, M, g)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    wq, ws = zip(*[to.quant_mxfp8_wei(torch.randn(K, N, generator=g) * K ** -0.5 *
+                                      torch.exp2(torch.randint(-6, 7, (1, N), generator=g).float())) for _ in range(E)])
+    wq, ws = torch.stack(wq), torch.stack(ws)
+    bias = (torch.randn(E, N, generator=g) * 0.05).to(torch.bfloat16) if has_bias else None
+    wdeq = torch.stack([to.dequant_mxfp8_wei(wq[e], ws[e]).t() for e in range(E)])   # [E, N, K]
+    xq, xs = quant_mxfp8(x.to(DEV), terms)
+    xdq = to.dequant_mxfp8(xq.cpu().reshape(terms, M, K), mx_scale_bytes(xs, K)[:, :, :K // 32])
+    ref = to.grouped_gemm(xdq, wdeq, bias, rows, torch.bfloat16)
+    out = grouped_gemm(xq, xs, wq.to(DEV), ws.to(DEV), bias.to(DEV) if has_bias else None, rows.to(DEV), N, K,
+                       rows_out=M)
+    n = int(rows.sum())
+    tol = 2e-2 * float(ref[:n].float().abs().max()) if n else 0
+    torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=2e-2, atol=tol)
+    assert bool(torch.isnan(out[n:].float()).all())
+    # products and power-of-two scalings are exact: only the summation order differs
+    assert (out.cpu()[:n].float() - ref[:n].float()).abs().max() <= 2 ** -7 * float(ref[:n].float().abs().max() if n else 0)
+    if terms == 2:   # the checking kernel with 16-bit activations agrees
+        chk = grouped_gemm(x.to(DEV), None, wq.to(DEV), ws.to(DEV), bias.to(DEV) if has_bias else None,
+                           rows.to(DEV), N, K)
+        torch.testing.assert_close(out.cpu()[:n].float(), chk.cpu()[:n].float(), rtol=2e-2, atol=tol)

@@ -46,6 +46,37 @@ def test_layer_reference_vectors_bf16(native):
         torch.testing.assert_close(out.cpu(), c["output"], rtol=2e-2, atol=2e-2)
 
 
+def _mxfp8_layer(native, c, mode=None, dev_dtype=None):
+    E = c["num_experts"]
+    mv = lambda t: t.to(DEV) if t is not None else None
+    layer = native.XpuFusedMoe(mv(c["w13"].view(torch.float8_e4m3fn)), mv(c["w13_scales"]), mv(c["w13_bias"]),
+                               mv(c["w2"].view(torch.float8_e4m3fn)), mv(c["w2_scales"]), mv(c["w2_bias"]),
+                               c["topk_ids"].shape[1], "silu", E, mxfp4_activations=mode)
+    out = torch.empty_like(c["x"], device=DEV)
+    layer.apply(out, c["x"].to(DEV), c["topk_weights"].to(DEV), c["topk_ids"].to(DEV))
+    return layer, out.cpu()
+
+
+def test_layer_mxfp8_reference_vectors_and_oracle(native):
+    """mxfp8 weights: against the outputs of the reference's own eager simulation (its only
+    implementation of this recipe, vllm_xpu_kernels/fused_moe_interface.py:27-31) and against
+    the staged oracle, which differs from the kernels in summation order only."""
+    for c in load_golden("layer_mxfp8.pt"):
+        layer, out = _mxfp8_layer(native, c)
+        assert layer.recipe == "mxfp8" and layer.mx_acts and layer.mx_planes == 1
+        top = float(c["out"].float().abs().max())
+        torch.testing.assert_close(out.float(), c["out"].float(), rtol=2e-2, atol=4e-2 * top)
+        E = c["num_experts"]
+        w13, w2 = c["w13"].view(torch.float8_e4m3fn), c["w2"].view(torch.float8_e4m3fn)
+        w13d = torch.stack([to.dequant_mxfp8_wei(w13[e], c["w13_scales"][e]).t() for e in range(E)])
+        w2d = torch.stack([to.dequant_mxfp8_wei(w2[e], c["w2_scales"][e]).t() for e in range(E)])
+        for mode in ("mxfp8", "mxfp8x2", "bf16"):
+            _, o = _mxfp8_layer(native, c, mode)
+            ref = to.fused_moe_staged(c["x"], w13d, c["w13_bias"], w2d, c["w2_bias"], c["topk_weights"], c["topk_ids"],
+                                      E, activation="silu", act_quant=False if mode == "bf16" else mode)
+            torch.testing.assert_close(o.float(), ref.float(), rtol=2e-2, atol=2e-2 * top)
+
+
 SMALL = [
     ("cfg1_small_bf16", dict(H=2048, I=1408, E=8), 64),     # the CPU-runnable config at full size
     ("cfg2_mixtral_bf16", dict(H=512, I=1792, E=8), 33),

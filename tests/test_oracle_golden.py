@@ -240,3 +240,24 @@ def test_prologue_against_reference_vectors():
     assert r["pexp"][:4].tolist() == [0, 1, 1, 7]
     assert r["pscale"][:4].tolist() == [5.0, 1.0, 2.0, 4.0]
     assert torch.equal(r["rows"][:4], x[[2, 0, 1, 2]])
+
+
+def test_layer_mxfp8_against_reference_vectors():
+    """The staged oracle with the mxfp8 recipe (MXFP8 activations, [E,K,N] e4m3 weights with one
+    e8m0 scale per 32 K rows) against outputs of the reference's ref_fused_moe("mxfp8")
+    (vllm_xpu_kernels/moe_utils.py:236-403).  The simulation rounds the GEMM result to the
+    16-bit type before it adds the bias, the kernels add it in fp32; both forms are checked."""
+    for c in load_golden("layer_mxfp8.pt"):
+        E = c["num_experts"]
+        w13, w2 = c["w13"].view(torch.float8_e4m3fn), c["w2"].view(torch.float8_e4m3fn)
+        w13d = torch.stack([to.dequant_mxfp8_wei(w13[e], c["w13_scales"][e]).t() for e in range(E)])
+        w2d = torch.stack([to.dequant_mxfp8_wei(w2[e], c["w2_scales"][e]).t() for e in range(E)])
+        top = float(c["out"].float().abs().max())
+        # restated exactly as the simulation does it: agreement to the last bit or two
+        sim = to.fused_moe_staged(c["x"], w13d, c["w13_bias"], w2d, c["w2_bias"], c["topk_weights"], c["topk_ids"], E,
+                                  activation="silu", act_quant="mxfp8", bias_after_rounding=True)
+        assert (sim.float() - c["out"].float()).abs().max() <= 2 ** -7 * top
+        # as the kernels do it (bias added in fp32): the reference's own layer tolerance
+        out = to.fused_moe_staged(c["x"], w13d, c["w13_bias"], w2d, c["w2_bias"], c["topk_weights"], c["topk_ids"], E,
+                                  activation="silu", act_quant="mxfp8")
+        torch.testing.assert_close(out.float(), c["out"].float(), rtol=2e-2, atol=4e-2 * top)

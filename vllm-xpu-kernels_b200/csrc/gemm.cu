@@ -53,6 +53,13 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
                      "grouped_gemm: fp8 activations with MXFP4 weights need the e8m0 scale words "
                      "[planes][ceil(K / 128)][M] of b200moe_quant_mxfp8");
       break;
+    case B200MOE_W_MXFP8_KN:
+      B200_CHECK_ARG(a->w_scale != nullptr, "w8a16 grouped gemm must have scales");
+      B200_CHECK_ARG(a->k % 32 == 0, "mxfp8 grouped gemm requires K divisible by 32");
+      B200_CHECK_ARG(!a_fp8 || a->a_scale != nullptr,
+                     "grouped_gemm: fp8 activations with MXFP8 weights need the e8m0 scale words "
+                     "[planes][ceil(K / 128)][M] of b200moe_quant_mxfp8");
+      break;
     case B200MOE_W_INT4_NK:
       B200_CHECK_ARG(a->w_scale != nullptr, "w8a16 grouped gemm must have scales");
       B200_CHECK_ARG(a->group_size == 32 || a->group_size == 64 || a->group_size == 128 || a->group_size == 256,
@@ -63,9 +70,10 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
     default:
       return fail(B200MOE_E_BADARG, "grouped_gemm: unknown weight format %d", (int)a->w_format);
   }
-  const bool w_tensor8 = a->w_format == B200MOE_W_FP8_TENSOR_KN || a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN;
+  const bool w_tensor8 = a->w_format == B200MOE_W_FP8_TENSOR_KN || a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN ||
+                         a->w_format == B200MOE_W_MXFP8_KN;
   B200_CHECK_ARG(!a_x2 || a->w_format == B200MOE_W_MXFP4_NK || w_tensor8,
-                 "grouped_gemm: two-plane fp8 activations need MXFP4 or per-tensor fp8 weights");
+                 "grouped_gemm: two-plane fp8 activations need MXFP4, MXFP8 or per-tensor fp8 weights");
   B200_CHECK_ARG(a->epilogue == B200MOE_EPI_NONE || a->n % 2 == 0,
                  "grouped_gemm: a gated epilogue needs an even N");
   if (a->m == 0 || a->n == 0) return B200MOE_OK;
@@ -73,7 +81,7 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
   cudaStream_t st = as_stream(stream);
   // MXFP8 activations exist on the block-scaled tensor-core path only.
   if ((a->w_format == B200MOE_W_MXFP4_NK || w_tensor8) && a_fp8) return grouped_gemm_tc_mx(a, st);
-  if (a->impl == 2) return grouped_gemm_check(a, st);
+  if (a->impl == 2 || a->w_format == B200MOE_W_MXFP8_KN) return grouped_gemm_check(a, st);   // 16-bit activations
   int rc = (a->w_format == B200MOE_W_MXFP4_NK || a->w_format == B200MOE_W_INT4_NK) ? grouped_gemm_tc_dq(a, st)
                                                                                     : grouped_gemm_tc(a, st);
   if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) return grouped_gemm_check(a, st);

@@ -45,6 +45,11 @@ __device__ __forceinline__ float load_w(const CheckArgs& g, int e, int n, int k)
       return round_to<T>(e4m3_to_f32(reinterpret_cast<const uint8_t*>(g.w)[((int64_t)e * K + k) * N + n]));
     case B200MOE_W_FP8E5M2_TENSOR_KN:
       return round_to<T>(e5m2_to_f32(reinterpret_cast<const uint8_t*>(g.w)[((int64_t)e * K + k) * N + n]));
+    case B200MOE_W_MXFP8_KN: {
+      const uint8_t q = reinterpret_cast<const uint8_t*>(g.w)[((int64_t)e * K + k) * N + n];
+      const uint8_t sb = reinterpret_cast<const uint8_t*>(g.w_scale)[((int64_t)e * (K / 32) + k / 32) * N + n];
+      return round_to<T>(e4m3_to_f32(q) * e8m0_to_f32(sb));
+    }
     case B200MOE_W_FP8_BLOCK_NK:
     case B200MOE_W_FP8_BLOCK_KN: {
       const uint8_t q = (g.fmt == B200MOE_W_FP8_BLOCK_NK)
@@ -136,7 +141,7 @@ gemm_check_kernel(CheckArgs g, bool a_fp8) {
       for (int idx = threadIdx.x; idx < TN * TK; idx += 256) {
         int kk, nn;
         if (g.fmt == B200MOE_W_BF16_KN || g.fmt == B200MOE_W_FP8_TENSOR_KN || g.fmt == B200MOE_W_FP8E5M2_TENSOR_KN ||
-            g.fmt == B200MOE_W_FP8_BLOCK_KN) {
+            g.fmt == B200MOE_W_FP8_BLOCK_KN || g.fmt == B200MOE_W_MXFP8_KN) {
           nn = idx % TN; kk = idx / TN;
         } else {
           kk = idx % TK; nn = idx / TK;

@@ -32,7 +32,10 @@
 // csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:322-360) with the same
 // two-plane activations: the weight tile then is a plain byte tile read as an
 // MN-major operand, its scale factors are 2^0, and the expert's scale
-// multiplies the accumulator in the epilogue.
+// multiplies the accumulator in the epilogue.  MXFP8 weights ([E,K,N] e4m3 with one
+// e8m0 scale per 32 K rows, [E,K/32,N]: the reference's "mxfp8" recipe,
+// vllm_xpu_kernels/moe_utils.py:76-78, 236-403) take the same path with their real
+// scale factors, staged from the transposed scale tensor.
 //
 // Numerics: products of e2m1 and e4m3 codes are exact, scaling by powers of two is
 // exact, accumulation is fp32; the difference from the reference's w4a16 path
@@ -68,11 +71,12 @@ constexpr int kMxWTx = 8192;        // the spreading load reports the packed byt
 constexpr int kMxThreads = 320;
 constexpr int kMxMaxStages = 8;
 constexpr int kMxGroup = 2;         // K blocks per token-scale prefetch group (read two groups ahead)
-constexpr int kMxSfwCap = 24576;    // largest weight-scale piece (128 rows x K/32 bytes) staged in shared memory
+constexpr int kMxSfwCap = 24576 + 16;    // largest weight-scale piece (128 rows x K/32 bytes) staged in shared memory
 
 struct MxParams {
-  const uint8_t* w_scale;   // [E, N, K/32] e8m0 (kW8: unused)
-  const float* w_tensor_scale;  // kW8: [E] fp32, multiplies the result
+  const uint8_t* w_scale;   // [E, N, K/32] e8m0; kW8 with w8_block: [E, K/32, N]; else unused
+  const float* w_tensor_scale;  // kW8 without w8_block: [E] fp32, multiplies the result
+  int w8_block;             // kW8: 1 = MXFP8 weights (scales per 32 K rows), 0 = one scale per expert
   const uint32_t* a_scale;  // [terms][num_kb][M] words of four e8m0 bytes
   const void* bias;
   void* d;
@@ -127,6 +131,29 @@ __device__ __forceinline__ bool stage_w_scales(const MxParams& p, MxCtrl* ctrl, 
   const uint32_t dst = ptx::smem_u32(sfw + b * p.sfw_bytes);
   for (int off = ft * 16; off < len; off += 128 * 16)
     ptx::cp_async_16(dst + off, src + off, (len - off) < 16 ? (len - off) : 16);
+  ptx::cp_async_mbar_arrive(&ctrl->sfw_full[b]);
+  return true;
+}
+
+// The same for MXFP8 weights, whose scales are [E, K/32, N]: for every K group the
+// 128 bytes of the tile's features, stored as [group][128] in the staging buffer.
+// N is a multiple of 16, so a tile's valid bytes per group are whole 16-byte chunks;
+// chunks past N are zero-filled (their rows get 2^0 when the scales are packed).
+__device__ __forceinline__ bool stage_w_scales_kn(const MxParams& p, MxCtrl* ctrl, uint8_t* sfw,
+                                                  const TileInfo& ti, uint32_t seq, int ft, int kgroups,
+                                                  volatile int* abort_flag) {
+  const uint32_t b = seq & 1;
+  if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->sfw_empty[b], ((seq >> 1) & 1) ^ 1, abort_flag)))
+    return false;
+  const int n0 = ti.n_tile * kFeat;
+  const int valid = (p.n - n0) < kFeat ? (p.n - n0) : kFeat;
+  const uint8_t* src = p.w_scale + (int64_t)ti.e * kgroups * p.n + n0;
+  const uint32_t dst = ptx::smem_u32(sfw + b * p.sfw_bytes);
+  for (int c = ft; c < kgroups * 8; c += 128) {
+    const int g = c >> 3, part = c & 7;
+    const int bytes = valid - part * 16 >= 16 ? 16 : 0;
+    ptx::cp_async_16(dst + c * 16, src + (int64_t)g * p.n + (bytes ? part * 16 : 0), bytes);
+  }
   ptx::cp_async_mbar_arrive(&ctrl->sfw_full[b]);
   return true;
 }
@@ -356,21 +383,26 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     uint32_t tile_seq = 0;
     TileInfo ti, ti_next;
-    if (!kW8 && (int)blockIdx.x < total_tiles) {
+    const bool staged = !kW8 || p.w8_block != 0;   // weight scales come through shared memory
+    auto stage = [&](const TileInfo& tn, uint32_t seq) {
+      return kW8 ? stage_w_scales_kn(p, ctrl, sfw, tn, seq, ft, kgroups, abort_flag)
+                 : stage_w_scales(p, ctrl, sfw, tn, seq, ft, kgroups, abort_flag);
+    };
+    if (staged && (int)blockIdx.x < total_tiles) {
       locate_tile<BT>(tile_start, row_start, blockIdx.x, cursor_next, ti_next);
-      if (!stage_w_scales(p, ctrl, sfw, ti_next, 0u, ft, kgroups, abort_flag)) { *abort_flag = 1; ok = false; }
+      if (!stage(ti_next, 0u)) { *abort_flag = 1; ok = false; }
     }
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_seq) {
       locate_tile<BT>(tile_start, row_start, t, cursor, ti);
       const int t_next = t + gridDim.x;
-      if (!kW8 && t_next < total_tiles) {
+      if (staged && t_next < total_tiles) {
         locate_tile<BT>(tile_start, row_start, t_next, cursor_next, ti_next);
-        if (!stage_w_scales(p, ctrl, sfw, ti_next, tile_seq + 1, ft, kgroups, abort_flag)) {
+        if (!stage(ti_next, tile_seq + 1)) {
           *abort_flag = 1; ok = false; break;
         }
       }
       const uint32_t b = tile_seq & 1;
-      if (!kW8 && !__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->sfw_full[b], (tile_seq >> 1) & 1, abort_flag))) {
+      if (staged && !__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->sfw_full[b], (tile_seq >> 1) & 1, abort_flag))) {
         *abort_flag = 1; ok = false; break;
       }
       const uint32_t sfw_s = ptx::smem_u32(sfw + b * p.sfw_bytes);
@@ -394,11 +426,21 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int row = lane + 32 * j;
-              const uint32_t addr = sfw_s + row * kgroups + 4 * kb;
-              const uint32_t lo = ptx::lds32(addr & ~3u), hi = ptx::lds32((addr & ~3u) + 4);
-              const uint32_t v = __funnelshift_r(lo, hi, (addr & 3u) * 8);
-              wa[j] = (n0 + row < p.n) ? ((v & keep) | (0x7f7f7f7fu & ~keep)) : 0x7f7f7f7fu;
-              if (kW8) wa[j] = 0x7f7f7f7fu;   // per-tensor scale: applied in the epilogue
+              if (!kW8) {
+                const uint32_t addr = sfw_s + row * kgroups + 4 * kb;
+                const uint32_t lo = ptx::lds32(addr & ~3u), hi = ptx::lds32((addr & ~3u) + 4);
+                const uint32_t v = __funnelshift_r(lo, hi, (addr & 3u) * 8);
+                wa[j] = (n0 + row < p.n) ? ((v & keep) | (0x7f7f7f7fu & ~keep)) : 0x7f7f7f7fu;
+              } else if (p.w8_block) {
+                // staged as [group][128 features]: one byte per group of this K block
+                uint32_t v = 0;
+#pragma unroll
+                for (int gq = 0; gq < 4; ++gq)
+                  if (gq < left) v |= ptx::lds8(sfw_s + (4 * kb + gq) * 128 + row) << (8 * gq);
+                wa[j] = (n0 + row < p.n) ? (v | (0x7f7f7f7fu & ~keep)) : 0x7f7f7f7fu;
+              } else {
+                wa[j] = 0x7f7f7f7fu;   // per-tensor scale: applied in the epilogue
+              }
             }
             MX_PROF_ADD(fl, l0);
             if (sub == 0) {   // the stage's scale columns and weight buffer are free again
@@ -457,7 +499,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < kW; ++j) { cur_b[u][j] = nxt_b[u][j]; nxt_b[u][j] = nx2_b[u][j]; }
         MX_PROF_ADD(fsw, r0);
       }
-      if (!kW8) {
+      if (staged) {
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&ctrl->sfw_empty[b]);
       }
@@ -483,7 +525,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool feat_ok = feat < p.n;
       float bias_v = 0.f;
       if (p.bias != nullptr && feat_ok) bias_v = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat);
-      const float w_mul = kW8 ? p.w_tensor_scale[ti.e] : 1.0f;
+      const float w_mul = (kW8 && !p.w8_block) ? p.w_tensor_scale[ti.e] : 1.0f;
       const uint32_t a = acc_it & 1;
       // a whole tile's MMAs away: poll from one lane, sleeping in between, so that the
       // wait does not take issue slots from the feeder warp on the same scheduler
@@ -595,10 +637,11 @@ int launch_mx(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& t
 int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
   const bool x2 = a->a_dtype == B200MOE_FP8_E4M3_X2;
   const bool w4 = a->w_format == B200MOE_W_MXFP4_NK;
-  const bool w8 = a->w_format == B200MOE_W_FP8_TENSOR_KN || a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN;
+  const bool w8mx = a->w_format == B200MOE_W_MXFP8_KN;
+  const bool w8 = a->w_format == B200MOE_W_FP8_TENSOR_KN || a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN || w8mx;
   if (!(w4 || w8) || !(a->a_dtype == B200MOE_FP8_E4M3 || x2) || a->a_scale == nullptr)
     return fail(B200MOE_E_UNSUPPORTED,
-                "block-scaled GEMM takes MXFP4 or per-tensor fp8 weights and MXFP8 activations");
+                "block-scaled GEMM takes MXFP4, MXFP8 or per-tensor fp8 weights and MXFP8 activations");
   if (a->epilogue == B200MOE_EPI_SILU_MUL)
     return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM: SiLU epilogue not available");
   if (a->num_experts > kMaxExperts || a->k % 32 != 0 || a->k < 128 || (w4 && a->k % 64 != 0))
@@ -624,6 +667,14 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
   p.terms = x2 ? 2 : 1;
   p.tail = w4 && (a->k % 128) != 0;
   p.sfw_bytes = 0;
+  p.w8_block = w8mx ? 1 : 0;
+  if (w8mx) {
+    // per K group the tile's 128 scale bytes: whole 16-byte chunks from a 16-byte aligned tensor
+    const int piece = 128 * (a->k / 32);
+    if (((uintptr_t)a->w_scale & 15) != 0 || piece > kMxSfwCap)
+      return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM: K at most 6144, scales 16-byte aligned");
+    p.sfw_bytes = piece;
+  }
   if (w4) {
     // The weight scales of a tile (128 rows x K/32 bytes, contiguous in the scale
     // tensor) are staged in shared memory: every tile's piece must start on a

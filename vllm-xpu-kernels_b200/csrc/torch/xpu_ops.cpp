@@ -23,7 +23,10 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   const bool is_weight_fp8 = (B_dtype == at::kFloat8_e4m3fn) || (B_dtype == at::kFloat8_e5m2);
   const bool is_B_mxfp4 = (B_dtype == at::kFloat4_e2m1fn_x2) && ptr_B_scale.has_value();
   const bool is_B_int4 = (B_dtype == at::kChar) && ptr_B_scale.has_value();
-  const bool is_B_fp8_block = is_weight_fp8 && ptr_B_scale.has_value() && ptr_B_scale->dim() == 3;
+  // fp8 weights with one-byte (e8m0) scales: the "mxfp8" recipe of
+  // vllm_xpu_kernels/fused_moe_interface.py:47-61, weights [E,K,N], scales [E,K/32,N]
+  const bool is_B_mxfp8 = is_weight_fp8 && ptr_B_scale.has_value() && ptr_B_scale->element_size() == 1;
+  const bool is_B_fp8_block = is_weight_fp8 && !is_B_mxfp8 && ptr_B_scale.has_value() && ptr_B_scale->dim() == 3;
 
   TORCH_CHECK(N % 8 == 0, "N must be divisible by 8");
   TORCH_CHECK(ptr_A.dim() == 2, "ptr_A must be 2D [Total_M, K]");
@@ -45,6 +48,8 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   } else if (is_B_mxfp4) {
     B_K = ptr_B.size(2) * 2; B_N = ptr_B.size(1);
     fmt = B200MOE_W_MXFP4_NK;
+  } else if (is_B_mxfp8) {
+    fmt = B200MOE_W_MXFP8_KN;
   } else if (is_B_fp8_block) {
     const bool nk = ptr_B.size(1) == N && ptr_B.size(2) == K;
     const bool kn = N != K && ptr_B.size(1) == K && ptr_B.size(2) == N;
@@ -92,6 +97,12 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
     TORCH_CHECK(ptr_B_scale->size(1) == N, "ptr_scales.size(1) of int4 must match N");
     TORCH_CHECK(ptr_B_scale->size(2) * 32 == K, "group_size must be 32, 64, 128 or 256");
     TORCH_CHECK(ptr_B_scale->element_size() == 1, "mxfp4 scales must be e8m0 bytes");
+  } else if (is_B_mxfp8) {
+    TORCH_CHECK(B_dtype == at::kFloat8_e4m3fn, "mxfp8 grouped GEMM only supports float8_e4m3fn weights");
+    TORCH_CHECK(ptr_B_scale->is_contiguous(), "ptr_scales must be contiguous");
+    TORCH_CHECK(K % 32 == 0 && ptr_B_scale->dim() == 3 && ptr_B_scale->size(0) == num_experts &&
+                ptr_B_scale->size(1) == K / 32 && ptr_B_scale->size(2) == N,
+                "mxfp8 scales must have shape [num_experts, K / 32, N]");
   } else if (is_weight_fp8) {
     TORCH_CHECK(ptr_B_scale.has_value(), "w8a16 grouped gemm must have scales");
     TORCH_CHECK(ptr_B_scale->is_contiguous(), "ptr_scales must be contiguous");

@@ -157,7 +157,8 @@ class XpuFusedMoe:
     of the recipe has that epilogue (MXFP4 with SwigluOAI).
 
     ``mxfp4_activations`` (not in the reference; keyword only) chooses what the
-    MXFP4 (and per-tensor fp8) grouped GEMMs multiply the quantised weights with:
+    MXFP4 (and per-tensor fp8, and MXFP8, whose default is one plane as its recipe
+    defines) grouped GEMMs multiply the quantised weights with:
     ``"mxfp8x2"`` (default where the shapes allow it: hidden and intermediate
     sizes multiples of 64) quantises the activations to two MXFP8 planes (e4m3
     codes with one power-of-two scale per 32 values, plus the residual
@@ -194,8 +195,6 @@ class XpuFusedMoe:
 
         (is_fp8, is_int4, is_mxfp4, is_mxfp8,
          is_block_fp8) = _get_weights_dtype(w13, w13_scales)
-        if is_mxfp8:
-            raise NotImplementedError("mxfp8 weights are not built for sm_100a yet")
         if w13.dtype == torch.float8_e5m2 and is_block_fp8:
             raise NotImplementedError("block-scaled float8_e5m2 weights are not built for sm_100a yet")
         if _is_env_enabled(REF_FUSED_MOE_ENV):
@@ -212,7 +211,7 @@ class XpuFusedMoe:
             w2 = (w2 ^ 0x88).view(torch.int8)
         self.w13 = w13
         self.w2 = w2
-        if not (is_fp8 or is_mxfp4 or is_block_fp8 or is_int4):
+        if not (is_fp8 or is_mxfp4 or is_mxfp8 or is_block_fp8 or is_int4):
             self.gemm1_wei_scales = None
             self.gemm2_wei_scales = None
         else:
@@ -242,7 +241,8 @@ class XpuFusedMoe:
             fuse_activation = self.is_mxfp4 and self._act_kind == "swigluoai"
         self.fuse_activation = fuse_activation
         if mxfp4_activations is None:
-            mxfp4_activations = "mxfp8" if self.recipe == "mxfp4_fp8" else "mxfp8x2"
+            # the mxfp8 recipe is defined with MXFP8 activations (reference moe_utils.py:198-200)
+            mxfp4_activations = "mxfp8" if self.recipe in ("mxfp4_fp8", "mxfp8") else "mxfp8x2"
         if mxfp4_activations not in ("mxfp8x2", "mxfp8", "bf16"):
             raise ValueError("mxfp4_activations must be 'mxfp8x2', 'mxfp8' or 'bf16', "
                              f"got {mxfp4_activations!r}")
@@ -252,12 +252,12 @@ class XpuFusedMoe:
         # ([E,N,K/2] resp. [E,K,N] weights; K of both GEMMs a multiple of 64, N of 16)
         if is_mxfp4:
             hidden, gran = w2.shape[-2], 64
-        elif is_fp8:
+        elif is_fp8 or is_mxfp8:
             hidden, gran = w2.shape[-1], 32
         else:
             hidden, gran = 0, 1
         k2 = self.inter_size * self.inter_size_scale
-        self.mx_acts = bool((is_mxfp4 or is_fp8) and mxfp4_activations != "bf16"
+        self.mx_acts = bool((is_mxfp4 or is_fp8 or is_mxfp8) and mxfp4_activations != "bf16"
                             and hidden % gran == 0 and k2 % gran == 0 and hidden >= 128 and k2 >= 128
                             and hidden % 16 == 0 and self.inter_size % 8 == 0)
         if self.mx_acts and self._act_kind == "silu" and fuse_activation:
