@@ -28,7 +28,7 @@ OBJ = HERE / "build"
 INCLUDE = HERE.parent / "include"
 
 CU_SOURCES = ["abi.cu", "routing.cu", "permute.cu", "elementwise.cu", "fused_quant.cu", "gemm.cu",
-              "gemm_check.cu", "gemm_tc.cu", "gemm_tc_dq.cu", "gemm_tc_mx.cu"]
+              "gemm_check.cu", "gemm_tc.cu", "gemm_tc_dq.cu", "gemm_tc_mx.cu", "gemm_tc_fp8t.cu"]
 SHIMS = {"_C": "c_ops.cpp", "_moe_C": "moe_ops.cpp", "_xpu_C": "xpu_ops.cpp"}
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",

@@ -47,6 +47,7 @@
 #endif
 
 namespace b200moe {
+int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st);
 namespace {
 
 constexpr int kWTileBytes = 16384;  // 128 rows x 128 bytes, or the same area K-by-N
@@ -583,6 +584,13 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
     static int force_bt = -1;
     if (force_bt < 0) { const char* e = getenv("B200MOE_BT"); force_bt = e ? atoi(e) : 0; }
     if (force_bt == 16 || force_bt == 64 || force_bt == 128 || (force_bt == 256 && !a_fp8)) bt = force_bt;
+  }
+
+  if (a_fp8 && bt == 128) {
+    // prefill-sized segments: the token-major kernel (one scale register per thread and K block)
+    static int feat_major = -1;
+    if (feat_major < 0) { const char* e = getenv("B200MOE_FP8_FEATURE_MAJOR"); feat_major = e ? atoi(e) : 0; }
+    if (!feat_major) return grouped_gemm_tc_fp8t(a, st);
   }
 
   const uint32_t fmt = a_fp8 ? 0u : (a->a_dtype == B200MOE_BF16 ? 1u : 0u);

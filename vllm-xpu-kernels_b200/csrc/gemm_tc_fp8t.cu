@@ -1,0 +1,342 @@
+// fp8 x block-scaled fp8 grouped GEMM for prefill-sized expert segments, tokens on the
+// 128-row M side of tcgen05.mma and the weight's output features on its N side.
+//
+//   D[r0:r0+rows_e, :] = sum_kb a_scale[row, kb] * w_scale[e, n/128, kb] * (A_kb * W_e,kb^T)
+//
+// The block-scaled recipe (csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:361-383
+// of vllm-xpu-kernels: e4m3 activations with one fp32 scale per 1x128 group, e4m3 weights with
+// one per 128x128 block) needs every 128-wide K block's partial sum multiplied by its own
+// scale before it is added up.  With tokens on the tensor-memory lanes an epilogue thread
+// owns one token row, and the 128 features of the tile share one weight block: the scale of
+// a K block is a single register per thread.  The promotion then is one fused
+// multiply-add per accumulator, and the finished row goes to global memory as
+// consecutive 16-byte stores.  (The feature-major kernel of gemm_tc.cu, which serves the
+// smaller token tiles, has a different scale in every accumulator column and has to stage
+// them through shared memory.)
+//
+// Roles (320 threads, one persistent CTA per SM):
+//   warp 0    : TMA producer, ring of 6 stages of [weights 128x128 B | tokens 128x128 B]
+//   warp 1    : MMA issuer (one lane), kind::f8f6f4, one accumulator stage (128 columns of
+//               tensor memory, four stages) per K block
+//   warps 2-9 : promotion + epilogue; warp w reads lane quarter w & 3, columns
+//               64 * ((w - 2) / 4) .. + 63: 64 accumulators per thread
+// Every mbarrier wait is bounded; on expiry the CTA raises its abort flag, all roles leave
+// their loops, tensor memory is freed and *status is set to 1.
+#include "common.cuh"
+#include "gemm_tc_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kTTok = 128;            // tokens per tile (UMMA M)
+constexpr int kTStages = 6;
+constexpr int kTStageBytes = 32768;   // weights 16 KB, tokens 16 KB
+constexpr int kTAcc = 4;              // accumulator stages
+constexpr int kTThreads = 320;
+constexpr int kTCols = 64;            // accumulator columns per epilogue thread
+constexpr int kTGroup = 4;            // K blocks per scale prefetch group
+
+struct TParams {
+  const float* a_scale;   // [M, K/128]
+  const float* w_scale;   // [E, N/128, K/128]
+  const void* bias;
+  void* d;
+  const int32_t* rows_per_expert;
+  int32_t* status;
+  int64_t m;
+  int n, k, num_experts;
+  int n_tiles, num_kb;
+  uint32_t idesc;
+  int out_f16;
+};
+
+struct TCtrl {
+  uint64_t full[kTStages];
+  uint64_t empty[kTStages];
+  uint64_t acc_full[kTAcc];
+  uint64_t acc_empty[kTAcc];
+  uint32_t tmem_base;
+  int abort_flag;
+  int tile_start[kMaxExperts + 1];
+  int row_start[kMaxExperts + 1];
+};
+
+constexpr size_t kTSmem = 1024 + (size_t)kTStages * kTStageBytes + sizeof(TCtrl);
+
+template <bool kWKn>
+__global__ void __launch_bounds__(kTThreads, 1)
+grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_w, const TParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  TCtrl* ctrl = reinterpret_cast<TCtrl*>(smem + kTStages * kTStageBytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (warp == 0) {
+    build_tile_prefix<kTTok>(p.rows_per_expert, p.num_experts, p.n_tiles, ctrl->row_start, ctrl->tile_start);
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_w);
+    }
+  } else if (warp == 1) {
+    ptx::tmem_alloc(&ctrl->tmem_base, 512);
+    ptx::tmem_relinquish();
+  } else if (warp == 2 && lane == 0) {
+    for (int s = 0; s < kTStages; ++s) {
+      ptx::mbar_init(&ctrl->full[s], 1);
+      ptx::mbar_init(&ctrl->empty[s], 1);
+    }
+    for (int a = 0; a < kTAcc; ++a) {
+      ptx::mbar_init(&ctrl->acc_full[a], 1);
+      ptx::mbar_init(&ctrl->acc_empty[a], 8);
+    }
+    ctrl->abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const int* tile_start = ctrl->tile_start;
+  const int* row_start = ctrl->row_start;
+  const int total_tiles = tile_start[p.num_experts];
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      int cursor = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        TileInfo ti;
+        locate_tile<kTTok>(tile_start, row_start, t, cursor, ti);
+        const int n0 = ti.n_tile * kFeat;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* wdst = smem + s * kTStageBytes;
+          ptx::mbar_expect_tx(&ctrl->full[s], kTStageBytes);
+          if (!kWKn) ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], kb * 128, n0, ti.e);
+          else ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], n0, kb * 128, ti.e);
+          ptx::tma_load_2d(wdst + 16384, &tmap_a, &ctrl->full[s], kb * 128, ti.row0);
+          if (++s == (uint32_t)kTStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0, a = 0, aph = 0;
+      bool ok = true;
+      const uint32_t smem_base = ptx::smem_u32(smem);
+      // weights: K-major rows of 128 bytes, or (kWKn) the [K, N] tile read as an MN-major operand
+      constexpr uint32_t kWLbo = !kWKn ? 16u : 16384u;
+      constexpr uint32_t kWStep = !kWKn ? 32u : 4096u;   // bytes per 32-wide K step
+      int my_tiles = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) ++my_tiles;
+      const int64_t blocks = (int64_t)my_tiles * p.num_kb;   // every tile: same K loop, no tile state needed
+      for (int64_t i = 0; i < blocks && ok; ++i) {
+        if (!ptx::mbar_wait(&ctrl->acc_empty[a], aph ^ 1, abort_flag)) break;
+        if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) break;
+        ptx::tc_fence_after();
+        const uint32_t st_addr = smem_base + s * kTStageBytes;
+        const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
+        const uint64_t adesc0 = ptx::make_smem_desc(st_addr + 16384, 16, 1024);
+        const uint32_t d_tmem = tmem_base + a * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          ptx::umma<true>(d_tmem, adesc0 + (uint64_t)((j * 32) >> 4), wdesc0 + (uint64_t)((j * kWStep) >> 4), p.idesc,
+                          j > 0 ? 1u : 0u);
+        ptx::umma_commit(&ctrl->empty[s]);
+        ptx::umma_commit(&ctrl->acc_full[a]);
+        if (++s == (uint32_t)kTStages) { s = 0; ph ^= 1; }
+        if (++a == (uint32_t)kTAcc) { a = 0; aph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------ promotion and epilogue --------------------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;                       // token row inside the tile
+    const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+    const int col0 = ((warp - 2) >> 2) * kTCols;       // first feature column of this warp
+    const int kbs = p.num_kb;
+    const bool vec4_ok = (kbs % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.a_scale) & 15) == 0);
+    struct ScaleRegs { float a[kTGroup]; float w[kTGroup]; };
+    ScaleRegs cur, pre;
+    bool pre_valid = false;
+    auto fetch_group = [&](const TileInfo& tt, int g, ScaleRegs& sr) {
+      const int kb0 = g * kTGroup;
+      const int64_t wsb = ((int64_t)tt.e * p.n_tiles + tt.n_tile) * kbs + kb0;
+#pragma unroll
+      for (int jb = 0; jb < kTGroup; ++jb) sr.w[jb] = (kb0 + jb < kbs) ? p.w_scale[wsb + jb] : 0.f;
+      const bool live = r < tt.valid;
+      const float* src = p.a_scale + (int64_t)(tt.row0 + r) * kbs + kb0;
+      if (live && vec4_ok) {
+        const float4 q4 = *reinterpret_cast<const float4*>(src);
+        sr.a[0] = q4.x; sr.a[1] = q4.y; sr.a[2] = q4.z; sr.a[3] = q4.w;
+      } else {
+#pragma unroll
+        for (int jb = 0; jb < kTGroup; ++jb) sr.a[jb] = (live && kb0 + jb < kbs) ? src[jb] : 0.f;
+      }
+    };
+    uint32_t a = 0, aph = 0;
+    int cursor = 0;
+    bool ok = true;
+    const int n_groups = (p.num_kb + kTGroup - 1) / kTGroup;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      TileInfo ti;
+      locate_tile<kTTok>(tile_start, row_start, t, cursor, ti);
+      float acc[kTCols];
+#pragma unroll
+      for (int i = 0; i < kTCols; ++i) acc[i] = 0.f;
+      uint32_t va[32], vb[32];
+      // scales are read one group of K blocks ahead of their use (the next tile's first group
+      // during this tile's last)
+      if (!pre_valid) fetch_group(ti, 0, cur);
+      else cur = pre;
+      pre_valid = false;
+      for (int g = 0; g < n_groups && ok; ++g) {
+        if (g + 1 < n_groups) {
+          fetch_group(ti, g + 1, pre);
+        } else if (t + (int)gridDim.x < total_tiles) {
+          int cursor2 = cursor;
+          TileInfo tn;
+          locate_tile<kTTok>(tile_start, row_start, t + gridDim.x, cursor2, tn);
+          fetch_group(tn, 0, pre);
+          pre_valid = true;
+        }
+#pragma unroll
+        for (int jb = 0; jb < kTGroup; ++jb) {
+          if (g * kTGroup + jb >= p.num_kb) break;
+          const float sc = cur.a[jb] * cur.w[jb];
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], aph, abort_flag))) {
+            *abort_flag = 1; ok = false; break;
+          }
+          ptx::tc_fence_after();
+          // both halves in flight together, one wait: tcgen05.wait::ld covers every load before it
+          ptx::tmem_ld_32x32(tmem_base + a * 128 + col0 + lane_sel, va);
+          ptx::tmem_ld_32x32(tmem_base + a * 128 + col0 + 32 + lane_sel, vb);
+          ptx::tmem_wait_ld_tied(va, vb);
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);   // the stage is in registers
+          if (++a == (uint32_t)kTAcc) { a = 0; aph ^= 1; }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            acc[i] = fmaf(__uint_as_float(va[i]), sc, acc[i]);
+            acc[32 + i] = fmaf(__uint_as_float(vb[i]), sc, acc[32 + i]);
+          }
+        }
+        if (g + 1 < n_groups) cur = pre;
+      }
+      if (ok && r < ti.valid) {
+        const int f0 = ti.n_tile * kFeat + col0;
+        uint16_t* drow = reinterpret_cast<uint16_t*>(p.d) + (int64_t)(ti.row0 + r) * p.n + f0;
+#pragma unroll
+        for (int c = 0; c < kTCols; c += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 8; i += 2) {
+            float x0 = acc[c + i], x1 = acc[c + i + 1];
+            if (p.bias != nullptr) {
+              x0 += load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + f0 + c + i);
+              x1 += load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + f0 + c + i + 1);
+            }
+            if (p.out_f16) {
+              const __half2 h = __floats2half2_rn(x0, x1);
+              w[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+              w[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          }
+          *reinterpret_cast<uint4*>(drow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+  }
+
+  // Teardown: everyone meets here, also after an aborted wait.
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    if (*abort_flag != 0) __nanosleep(20000);  // let copies still in flight land
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+template <bool kWKn>
+int launch_fp8t(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& p, int grid, cudaStream_t st) {
+  auto kern = grouped_gemm_fp8t_kernel<kWKn>;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTSmem));
+    configured = true;
+  }
+  kern<<<grid, kTThreads, kTSmem, st>>>(ta, tw, p);
+  B200_LAUNCH_OK("grouped_gemm_fp8t_kernel");
+  return B200MOE_OK;
+}
+
+}  // namespace
+
+// fp8 activations [M,K] (+ fp32 scales [M,K/128]) times block-scaled fp8 weights ([E,N,K] or
+// [E,K,N], scales [E,N/128,K/128]); N and K multiples of 128.  Returns
+// B200MOE_E_UNSUPPORTED (no launch) for anything else.
+int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
+  const bool w8b = a->w_format == B200MOE_W_FP8_BLOCK_NK || a->w_format == B200MOE_W_FP8_BLOCK_KN;
+  if (!w8b || a->a_dtype != B200MOE_FP8_E4M3 || a->a_scale == nullptr || a->w_scale == nullptr ||
+      a->epilogue != B200MOE_EPI_NONE)
+    return fail(B200MOE_E_UNSUPPORTED, "token-major fp8 grouped GEMM takes fp8 x block-scaled fp8, no fused epilogue");
+  if (a->num_experts > kMaxExperts || a->n % 128 != 0 || a->k % 128 != 0)
+    return fail(B200MOE_E_UNSUPPORTED, "token-major fp8 grouped GEMM: N and K must be multiples of 128");
+  if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15) || ((uintptr_t)a->d & 15))
+    return fail(B200MOE_E_BADARG, "grouped GEMM: A, W and D must be 16-byte aligned");
+  if (a->m == 0 || a->n == 0) return B200MOE_OK;
+  const bool kn = a->w_format == B200MOE_W_FP8_BLOCK_KN;
+
+  TParams p;
+  p.a_scale = reinterpret_cast<const float*>(a->a_scale);
+  p.w_scale = reinterpret_cast<const float*>(a->w_scale);
+  p.bias = a->bias; p.d = a->d; p.rows_per_expert = a->rows_per_expert; p.status = a->status;
+  p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
+  p.n_tiles = a->n / kFeat;
+  p.num_kb = a->k / 128;
+  p.out_f16 = a->d_dtype == B200MOE_F16;
+  // A operand = tokens (K-major), B operand = weights (K-major, or MN-major for [E,K,N])
+  p.idesc = ptx::make_idesc(0u, 0u, 0u, kn ? 1u : 0u, kTTok, kFeat);
+
+  CUtensorMap ta, tw;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)a->k, (cuuint64_t)a->m};
+    cuuint64_t strides[1] = {(cuuint64_t)a->k};
+    cuuint32_t box[2] = {128, (cuuint32_t)kTTok};
+    int rc = encode_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->a, dims, strides, box);
+    if (rc) return rc;
+  }
+  if (!kn) {
+    cuuint64_t dims[3] = {(cuuint64_t)a->k, (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
+    cuuint64_t strides[2] = {(cuuint64_t)a->k, (cuuint64_t)a->k * a->n};
+    cuuint32_t box[3] = {128, (cuuint32_t)kFeat, 1};
+    int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box);
+    if (rc) return rc;
+  } else {
+    cuuint64_t dims[3] = {(cuuint64_t)a->n, (cuuint64_t)a->k, (cuuint64_t)a->num_experts};
+    cuuint64_t strides[2] = {(cuuint64_t)a->n, (cuuint64_t)a->k * a->n};
+    cuuint32_t box[3] = {128, 128, 1};
+    int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box);
+    if (rc) return rc;
+  }
+  const int64_t tile_bound = ((a->m + kTTok - 1) / kTTok + a->num_experts) * (int64_t)p.n_tiles;
+  int grid = sm_count();
+  if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
+  if (tile_bound < grid) grid = (int)tile_bound;
+  if (grid < 1) grid = 1;
+  return kn ? launch_fp8t<true>(ta, tw, p, grid, st) : launch_fp8t<false>(ta, tw, p, grid, st);
+}
+
+}  // namespace b200moe

@@ -197,6 +197,15 @@ __device__ __forceinline__ void tmem_wait_ld_tied(uint32_t (&r)[16]) {
                :
                : "memory");
 }
+// The same for two 32-register loads in flight together.  The second statement emits
+// nothing; it only makes every later use of the second array depend on a point after
+// the wait (volatile asm statements keep their order).
+__device__ __forceinline__ void tmem_wait_ld_tied(uint32_t (&r)[32], uint32_t (&q)[32]) {
+#define B200_R8(a, i) "+r"(a[i]), "+r"(a[i + 1]), "+r"(a[i + 2]), "+r"(a[i + 3]), "+r"(a[i + 4]), "+r"(a[i + 5]), "+r"(a[i + 6]), "+r"(a[i + 7])
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : B200_R8(r, 0), B200_R8(r, 8), B200_R8(r, 16), B200_R8(r, 24) : : "memory");
+  asm volatile("" : B200_R8(q, 0), B200_R8(q, 8), B200_R8(q, 16), B200_R8(q, 24) : : "memory");
+#undef B200_R8
+}
 // 32 lanes x N consecutive 32-bit columns written from registers: thread i
 // writes lane (base lane + i).
 __device__ __forceinline__ void tmem_st_32x1(uint32_t taddr, uint32_t r0) {
