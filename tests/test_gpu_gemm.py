@@ -77,6 +77,28 @@ def test_grouped_gemm_fp8_block_w8a8(native, impl, layout, E, M, N, K):
     _close(out, ref, rows, 2e-2)  # same quantised operands on both sides: only fp32 order differs
 
 
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("E,M,N,K", [(3, 700, 640, 1024), (2, 300, 128, 384), (5, 1000, 256, 128), (4, 520, 1152, 640)])
+def test_grouped_gemm_fp8_block_prefill_tiles(native, layout, dtype, E, M, N, K):
+    """Segments of more than 40 rows per expert take the token-major kernels (256-feature tiles
+    from N = 256, else 128): odd and even numbers of 128-feature blocks, bias, both output
+    types, ragged and empty segments."""
+    g = torch.Generator().manual_seed(M + N + K + 1)
+    rows, x, wq, ws = _fp8_case(E, M, N, K, g)
+    x = torch.cat([x, torch.randn(70, K, generator=g).to(torch.bfloat16)])   # rows no segment owns
+    bias = (torch.randn(E, N, generator=g) * 0.1).to(dtype)
+    aq, a_s = to.per_token_group_fp8_quant(x, 128, 1e-10)
+    wdeq = torch.stack([to.dequant_fp8_block_wei(wq[e], ws[e]) for e in range(E)])
+    ref = to.grouped_gemm(to.dequant_fp8_block_act(aq, a_s), wdeq, bias, rows, dtype)
+    wd = wq.to(DEV) if layout == "nk" else wq.transpose(1, 2).contiguous().to(DEV)
+    out = grouped_gemm(aq.to(DEV), a_s.to(DEV), wd, ws.to(DEV), bias.to(DEV), rows.to(DEV), N, K,
+                       layout=1 if layout == "nk" else 2, impl=TC, out_dtype=dtype)
+    _close(out, ref, rows, 2e-2)
+    n = int(rows.sum())
+    assert bool(torch.isnan(out[n:].float()).all())   # rows past the last segment are not written
+
+
 def test_grouped_gemm_fp8_block_w8a16_and_per_tensor(native):
     g = torch.Generator().manual_seed(77)
     rows, x, wq, ws = _fp8_case(4, 50, 256, 256, g)

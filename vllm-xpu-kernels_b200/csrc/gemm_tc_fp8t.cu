@@ -22,9 +22,25 @@
 //               64 * ((w - 2) / 4) .. + 63: 64 accumulators per thread
 // Every mbarrier wait is bounded; on expiry the CTA raises its abort flag, all roles leave
 // their loops, tensor memory is freed and *status is set to 1.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "gemm_tc_common.cuh"
 #include "sm100_ptx.cuh"
+
+// Cycle accounting of CTA 0 (printed at kernel end); compiled in only with -DB200_TC_PROF.
+#ifdef B200_TC_PROF
+#include <stdio.h>
+#define T_PROF_DECL(...) long long __VA_ARGS__
+#define T_PROF_T(var) const long long var = clock64()
+#define T_PROF_ADD(acc, t0) acc += clock64() - (t0)
+#define T_PROF_PRINT(...) if (blockIdx.x == 0) printf(__VA_ARGS__)
+#else
+#define T_PROF_DECL(...)
+#define T_PROF_T(var)
+#define T_PROF_ADD(acc, t0)
+#define T_PROF_PRINT(...)
+#endif
 
 namespace b200moe {
 namespace {
@@ -269,6 +285,281 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
 }
 
+// ---------------------------------------------------------------------------------
+// Wide variant: 128 tokens x 256 features per tile, so that every tcgen05.mma carries
+// twice the work (the issuing thread, not the tensor pipe, bounds the 128-feature tile).
+// A thread then owns 128 accumulators, more than the even register split of 384 threads
+// allows: the warps are laid out in warpgroups and re-balance registers with setmaxnreg
+//   warps 0-3  : producer (warp 0), MMA issuer (warp 1), two idle warps; 40 registers
+//   warps 4-11 : promotion + epilogue, 232 registers; warp w reads lane quarter w & 3 and
+//                the 128 columns of feature block (w - 4) / 4, in two passes of 64
+// Tensor memory holds two accumulator stages of 256 columns.
+constexpr int kT2Threads = 384;
+constexpr int kT2Stages = 4;
+constexpr int kT2StageBytes = 49152;   // weights 2 x 16 KB, tokens 16 KB
+constexpr int kT2Acc = 2;
+
+struct T2Ctrl {
+  uint64_t full[kT2Stages];
+  uint64_t empty[kT2Stages];
+  uint64_t acc_full[kT2Acc];
+  uint64_t acc_empty[kT2Acc];
+  uint32_t tmem_base;
+  int abort_flag;
+  int tile_start[kMaxExperts + 1];
+  int row_start[kMaxExperts + 1];
+};
+constexpr size_t kT2Smem = 1024 + (size_t)kT2Stages * kT2StageBytes + sizeof(T2Ctrl);
+
+template <bool kWKn>
+__global__ void __launch_bounds__(kT2Threads, 1)
+grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                            const __grid_constant__ CUtensorMap tmap_w, const TParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  T2Ctrl* ctrl = reinterpret_cast<T2Ctrl*>(smem + kT2Stages * kT2StageBytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_tiles2 = (p.n_tiles + 1) / 2;   // 256-feature tiles
+
+  if (warp == 0) {
+    build_tile_prefix<kTTok>(p.rows_per_expert, p.num_experts, n_tiles2, ctrl->row_start, ctrl->tile_start);
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_w);
+    }
+  } else if (warp == 1) {
+    ptx::tmem_alloc(&ctrl->tmem_base, 512);
+    ptx::tmem_relinquish();
+  } else if (warp == 2 && lane == 0) {
+    for (int s = 0; s < kT2Stages; ++s) {
+      ptx::mbar_init(&ctrl->full[s], 1);
+      ptx::mbar_init(&ctrl->empty[s], 1);
+    }
+    for (int a = 0; a < kT2Acc; ++a) {
+      ptx::mbar_init(&ctrl->acc_full[a], 1);
+      ptx::mbar_init(&ctrl->acc_empty[a], 8);
+    }
+    ctrl->abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const int* tile_start = ctrl->tile_start;
+  const int* row_start = ctrl->row_start;
+  const int total_tiles = tile_start[p.num_experts];
+
+  if (warp < 4) {
+    ptx::setmaxnreg_dec<40>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      uint32_t s = 0, ph = 0;
+      int cursor = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        TileInfo ti;
+        locate_tile<kTTok>(tile_start, row_start, t, cursor, ti);
+        const int n0 = ti.n_tile * 256;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* wdst = smem + s * kT2StageBytes;
+          ptx::mbar_expect_tx(&ctrl->full[s], kT2StageBytes);
+          // two 128-feature blocks (the second one is zero-filled past N)
+          if (!kWKn) {
+            ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], kb * 128, n0, ti.e);
+            ptx::tma_load_3d(wdst + 16384, &tmap_w, &ctrl->full[s], kb * 128, n0 + 128, ti.e);
+          } else {
+            ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], n0, kb * 128, ti.e);
+            ptx::tma_load_3d(wdst + 16384, &tmap_w, &ctrl->full[s], n0 + 128, kb * 128, ti.e);
+          }
+          ptx::tma_load_2d(wdst + 32768, &tmap_a, &ctrl->full[s], kb * 128, ti.row0);
+          if (++s == (uint32_t)kT2Stages) { s = 0; ph ^= 1; }
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------ MMA issuer --------------------------------
+      uint32_t s = 0, ph = 0, a = 0, aph = 0;
+      const uint32_t smem_base = ptx::smem_u32(smem);
+      constexpr uint32_t kWLbo = !kWKn ? 16u : 16384u;
+      constexpr uint32_t kWStep = !kWKn ? 32u : 4096u;
+      int my_tiles = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) ++my_tiles;
+      const int64_t blocks = (int64_t)my_tiles * p.num_kb;
+      const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((256u >> 3) << 17);
+      T_PROF_DECL(ma = 0, mf = 0, mi = 0, mc = 0, mt0 = clock64());
+      // The barriers of the next block are polled between this block's MMA issues, where
+      // the thread would otherwise only wait for room in the tensor pipe's queue.
+      bool full_ready = false, acc_ready = false;
+      for (int64_t i = 0; i < blocks; ++i) {
+        T_PROF_T(w0);
+        if (!acc_ready && !ptx::mbar_wait(&ctrl->acc_empty[a], aph ^ 1, abort_flag)) break;
+        T_PROF_ADD(ma, w0);
+        T_PROF_T(w1);
+        if (!full_ready && !ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) break;
+        T_PROF_ADD(mf, w1);
+        T_PROF_T(w2);
+        ptx::tc_fence_after();
+        const uint32_t st_addr = smem_base + s * kT2StageBytes;
+        const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
+        const uint64_t adesc0 = ptx::make_smem_desc(st_addr + 32768, 16, 1024);
+        const uint32_t d_tmem = tmem_base + a * 256;
+        const uint32_t s1 = (s + 1 == (uint32_t)kT2Stages) ? 0u : s + 1, ph1 = (s1 == 0u) ? ph ^ 1u : ph;
+        const uint32_t a1 = (a + 1 == (uint32_t)kT2Acc) ? 0u : a + 1, aph1 = (a1 == 0u) ? aph ^ 1u : aph;
+        const bool more = i + 1 < blocks;
+        ptx::umma<true>(d_tmem, adesc0, wdesc0, idesc, 0u);
+        ptx::umma<true>(d_tmem, adesc0 + (uint64_t)(32 >> 4), wdesc0 + (uint64_t)(kWStep >> 4), idesc, 1u);
+        full_ready = more && ptx::mbar_test_wait(&ctrl->full[s1], ph1);
+        ptx::umma<true>(d_tmem, adesc0 + (uint64_t)(64 >> 4), wdesc0 + (uint64_t)((2 * kWStep) >> 4), idesc, 1u);
+        ptx::umma<true>(d_tmem, adesc0 + (uint64_t)(96 >> 4), wdesc0 + (uint64_t)((3 * kWStep) >> 4), idesc, 1u);
+        T_PROF_ADD(mi, w2);
+        T_PROF_T(w3);
+        ptx::umma_commit(&ctrl->empty[s]);
+        ptx::umma_commit(&ctrl->acc_full[a]);
+        T_PROF_ADD(mc, w3);
+        acc_ready = more && ptx::mbar_test_wait(&ctrl->acc_empty[a1], aph1 ^ 1u);
+        s = s1; ph = ph1; a = a1; aph = aph1;
+      }
+      T_PROF_PRINT("mma: blocks %lld total %lld wait_acc %lld wait_full %lld issue %lld commit %lld\n", (long long)blocks,
+                   clock64() - mt0, ma, mf, mi, mc);
+    }
+  } else {
+    // ------------------------ promotion and epilogue --------------------------
+    ptx::setmaxnreg_inc<232>();
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+    const int half = (warp - 4) >> 2;                  // which 128-feature block of the tile
+    const int kbs = p.num_kb;
+    const bool vec4_ok = (kbs % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.a_scale) & 15) == 0);
+    struct ScaleRegs { float a[kTGroup]; float w[kTGroup]; };
+    ScaleRegs cur, pre;
+    bool pre_valid = false;
+    auto fetch_group = [&](const TileInfo& tt, int g, ScaleRegs& sr) {
+      const int kb0 = g * kTGroup;
+      const int nb = tt.n_tile * 2 + half;
+      const int64_t wsb = ((int64_t)tt.e * p.n_tiles + nb) * kbs + kb0;
+#pragma unroll
+      for (int jb = 0; jb < kTGroup; ++jb) sr.w[jb] = (nb < p.n_tiles && kb0 + jb < kbs) ? p.w_scale[wsb + jb] : 0.f;
+      const bool live = r < tt.valid;
+      const float* src = p.a_scale + (int64_t)(tt.row0 + r) * kbs + kb0;
+      if (live && vec4_ok) {
+        const float4 q4 = *reinterpret_cast<const float4*>(src);
+        sr.a[0] = q4.x; sr.a[1] = q4.y; sr.a[2] = q4.z; sr.a[3] = q4.w;
+      } else {
+#pragma unroll
+        for (int jb = 0; jb < kTGroup; ++jb) sr.a[jb] = (live && kb0 + jb < kbs) ? src[jb] : 0.f;
+      }
+    };
+    uint32_t a = 0, aph = 0;
+    int cursor = 0;
+    bool ok = true;
+    const int n_groups = (p.num_kb + kTGroup - 1) / kTGroup;
+    T_PROF_DECL(ew = 0, et0 = clock64());
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      TileInfo ti;
+      locate_tile<kTTok>(tile_start, row_start, t, cursor, ti);
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+      uint32_t va[32], vb[32];
+      if (!pre_valid) fetch_group(ti, 0, cur);
+      else cur = pre;
+      pre_valid = false;
+      for (int g = 0; g < n_groups && ok; ++g) {
+        if (g + 1 < n_groups) {
+          fetch_group(ti, g + 1, pre);
+        } else if (t + (int)gridDim.x < total_tiles) {
+          int cursor2 = cursor;
+          TileInfo tn;
+          locate_tile<kTTok>(tile_start, row_start, t + gridDim.x, cursor2, tn);
+          fetch_group(tn, 0, pre);
+          pre_valid = true;
+        }
+#pragma unroll
+        for (int jb = 0; jb < kTGroup; ++jb) {
+          if (g * kTGroup + jb >= p.num_kb) break;
+          const float sc = cur.a[jb] * cur.w[jb];
+          T_PROF_T(e0);
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], aph, abort_flag))) {
+            *abort_flag = 1; ok = false; break;
+          }
+          T_PROF_ADD(ew, e0);
+          ptx::tc_fence_after();
+          const uint32_t col = tmem_base + a * 256 + half * 128 + lane_sel;
+#pragma unroll
+          for (int pass = 0; pass < 2; ++pass) {
+            ptx::tmem_ld_32x32(col + pass * 64, va);
+            ptx::tmem_ld_32x32(col + pass * 64 + 32, vb);
+            ptx::tmem_wait_ld_tied(va, vb);
+            if (pass == 1) {   // the whole stage is in registers
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
+              if (++a == (uint32_t)kT2Acc) { a = 0; aph ^= 1; }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              acc[pass * 64 + i] = fmaf(__uint_as_float(va[i]), sc, acc[pass * 64 + i]);
+              acc[pass * 64 + 32 + i] = fmaf(__uint_as_float(vb[i]), sc, acc[pass * 64 + 32 + i]);
+            }
+          }
+        }
+        if (g + 1 < n_groups) cur = pre;
+      }
+      const int f0 = ti.n_tile * 256 + half * 128;
+      if (ok && r < ti.valid && f0 < p.n) {
+        uint16_t* drow = reinterpret_cast<uint16_t*>(p.d) + (int64_t)(ti.row0 + r) * p.n + f0;
+#pragma unroll
+        for (int c = 0; c < 128; c += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 8; i += 2) {
+            float x0 = acc[c + i], x1 = acc[c + i + 1];
+            if (p.bias != nullptr) {
+              x0 += load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + f0 + c + i);
+              x1 += load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + f0 + c + i + 1);
+            }
+            if (p.out_f16) {
+              const __half2 h = __floats2half2_rn(x0, x1);
+              w[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+              w[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          }
+          *reinterpret_cast<uint4*>(drow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+    if (warp == 4 && lane == 0) T_PROF_PRINT("epilogue: total %lld wait_acc_full %lld\n", clock64() - et0, ew);
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    if (*abort_flag != 0) __nanosleep(20000);
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+template <bool kWKn>
+int launch_fp8t256(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& p, int grid, cudaStream_t st) {
+  auto kern = grouped_gemm_fp8t256_kernel<kWKn>;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kT2Smem));
+    configured = true;
+  }
+  kern<<<grid, kT2Threads, kT2Smem, st>>>(ta, tw, p);
+  B200_LAUNCH_OK("grouped_gemm_fp8t256_kernel");
+  return B200MOE_OK;
+}
+
 template <bool kWKn>
 int launch_fp8t(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& p, int grid, cudaStream_t st) {
   auto kern = grouped_gemm_fp8t_kernel<kWKn>;
@@ -331,11 +622,15 @@ int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
     int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box);
     if (rc) return rc;
   }
-  const int64_t tile_bound = ((a->m + kTTok - 1) / kTTok + a->num_experts) * (int64_t)p.n_tiles;
   int grid = sm_count();
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
+  static int narrow = -1;
+  if (narrow < 0) { const char* e = getenv("B200MOE_FP8_NARROW"); narrow = e ? atoi(e) : 0; }
+  const bool wide = !narrow && a->n >= 256;
+  const int64_t tile_bound = ((a->m + kTTok - 1) / kTTok + a->num_experts) * (int64_t)(wide ? (p.n_tiles + 1) / 2 : p.n_tiles);
   if (tile_bound < grid) grid = (int)tile_bound;
   if (grid < 1) grid = 1;
+  if (wide) return kn ? launch_fp8t256<true>(ta, tw, p, grid, st) : launch_fp8t256<false>(ta, tw, p, grid, st);
   return kn ? launch_fp8t<true>(ta, tw, p, grid, st) : launch_fp8t<false>(ta, tw, p, grid, st);
 }
 

@@ -206,6 +206,17 @@ __device__ __forceinline__ void tmem_wait_ld_tied(uint32_t (&r)[32], uint32_t (&
   asm volatile("" : B200_R8(q, 0), B200_R8(q, 8), B200_R8(q, 16), B200_R8(q, 24) : : "memory");
 #undef B200_R8
 }
+// Register re-balancing between the warpgroups of a CTA (every warp of a warpgroup
+// executes the same one): dec gives registers back to the CTA's pool, inc waits until
+// the pool holds enough and takes them.
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
 // 32 lanes x N consecutive 32-bit columns written from registers: thread i
 // writes lane (base lane + i).
 __device__ __forceinline__ void tmem_st_32x1(uint32_t taddr, uint32_t r0) {
