@@ -14,13 +14,14 @@
 //   warp 0  : TMA producer  (weights through a 3-D map [E, N, K], activations
 //             through a 2-D map [M, K]; 128-byte swizzle; ring of kStages)
 //   warp 1  : MMA issuer    (one lane), owns the tensor-memory allocation
-//   warps 2-5 (2-9 for the fp8 128-token tile): epilogue (tcgen05.ld ->
-//             registers -> global)
+//   warps 2-5 : epilogue (tcgen05.ld -> registers -> global)
 // 16-bit inputs use kind::f16 with the whole K loop accumulated in tensor
 // memory (two accumulator stages, so the epilogue of one tile overlaps the
 // MMAs of the next).  fp8 inputs use kind::f8f6f4 per 128-wide K block; the
 // epilogue warps promote each block's partial sum into fp32 registers with
 // a_scale[row, kb] * w_scale[e, n/128, kb], as the block-scaled recipe needs.
+// (fp8 segments of more than 40 rows per expert go to the token-major kernels of
+// gemm_tc_fp8t.cu, where that scale is one register per thread.)
 //
 // Every wait on an mbarrier is bounded (see sm100_ptx.cuh): on expiry the CTA
 // raises an abort flag, all roles leave their loops, tensor memory is freed and
@@ -67,7 +68,6 @@ struct TcParams {
   int num_kb;   // K blocks of 128 bytes
   uint32_t idesc;
   int out_f16;  // 1: D and bias are float16, 0: bfloat16
-  int debug;    // experiment switches (B200MOE_DEBUG), 0 in normal use
 };
 
 template <int BT, bool kFp8>
@@ -78,8 +78,8 @@ struct Ctrl {
   uint64_t acc_empty[kMaxAccStages];
   uint32_t tmem_base;
   int abort_flag;
-  alignas(16) float sc[kFp8 ? 8 : 1][2][kFp8 ? (BT >= 128 ? BT / 2 : BT) : 4];  // per epilogue warp, double buffered
-  alignas(16) uint16_t xpose[kFp8 && BT >= 128 ? 8 : 4][32 * 32];  // per epilogue warp: output transpose tile
+  alignas(16) float sc[kFp8 ? 4 : 1][2][kFp8 ? BT : 4];  // per epilogue warp, double buffered
+  alignas(16) uint16_t xpose[4][32 * 32];  // per epilogue warp: output transpose tile
   int tile_start[kMaxExperts + 1];
   int row_start[kMaxExperts + 1];
 };
@@ -107,24 +107,20 @@ __host__ __device__ constexpr uint32_t tmem_cols() {
   const int c = acc_stages<BT, kFp8>() * BT;
   return c <= 32 ? 32u : c <= 64 ? 64u : c <= 128 ? 128u : c <= 256 ? 256u : 512u;
 }
-// Epilogue warps: four cover the 128 TMEM lanes; the fp8 128-token tile uses
-// eight (two per lane quarter, half the columns each) to keep up with the MMAs.
-template <int BT, bool kFp8>
-__host__ __device__ constexpr int epi_warps() { return (kFp8 && BT >= 128) ? 8 : 4; }
-template <int BT, bool kFp8>
-__host__ __device__ constexpr int num_threads() { return 64 + 32 * epi_warps<BT, kFp8>(); }
+// Four epilogue warps cover the 128 TMEM lanes.
+constexpr int kEpiWarps = 4;
+constexpr int kTcThreads = 64 + 32 * kEpiWarps;
 
 template <int BT, bool kFp8, bool kWKn>
-__global__ void __launch_bounds__(num_threads<BT, kFp8>(), 1)
+__global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_w, const TcParams p) {
-  static_assert(!kFp8 || BT <= 128, "fp8 promotion keeps BT accumulators per thread");
+  static_assert(!kFp8 || BT <= 64, "fp8 promotion keeps BT accumulators per thread");
   constexpr int kStages = num_stages<BT>();
   constexpr int kStageBytes = stage_bytes<BT>();
   constexpr int kElemsPerKb = kFp8 ? 128 : 64;  // K elements per 128-byte row
   constexpr int kAccStages = acc_stages<BT, kFp8>();
-  constexpr int kEpiWarps = epi_warps<BT, kFp8>();
-  constexpr int kCols = BT / (kEpiWarps / 4);   // token columns one epilogue warp owns
+  constexpr int kCols = BT;                      // token columns one epilogue warp owns
   constexpr int kChunk = kCols >= 32 ? 32 : 16;  // columns per tcgen05.ld
 
   extern __shared__ uint8_t smem_raw[];
@@ -216,7 +212,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // A partly filled token tile multiplies only its valid columns (UMMA N in steps of 16).
         const uint32_t n_eff = (uint32_t)((ti.valid + 15) & ~15);
         const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((n_eff >> 3) << 17);
-        const bool per_block = kFp8 && !(p.debug & 4);
+        constexpr bool per_block = kFp8;
         if (!per_block) {
           TC_PROF_T(wa0);
           if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) break;
@@ -264,11 +260,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int et = q * 32 + lane;           // feature row inside the tile
     const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
-    const int col0 = ((warp - 2) / 4) * kCols;   // first token column of this warp
+    constexpr int col0 = 0;                 // first token column of this warp
     // fp8 block-scale prefetch state (see the promotion loop below)
-    // (the software-pipelined promotion keeps two chunks of TMEM data in registers: smaller groups)
-    constexpr bool kPipe = kFp8 && BT == 128 && (kCols == 2 * kChunk) && (kChunk == 32);
-    constexpr int kGroup = kPipe ? 2 : 4;
+    constexpr int kGroup = 4;
     constexpr int kPerLane = (kCols + 31) / 32;
     struct ScaleRegs { float a[kPerLane][kGroup]; float w[kGroup]; };
     ScaleRegs cur, pre;
@@ -320,19 +314,17 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < BT; c0 += kChunk) {
-          if (c0 < ti.valid && !(p.debug & 16)) {
+          if (c0 < ti.valid) {
             uint32_t v[kChunk];
             if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
             else ptx::tmem_ld_32x16(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
             ptx::tmem_wait_ld();
-            if (!(p.debug & 8)) {
-              float vals[kChunk];
+            float vals[kChunk];
 #pragma unroll
-              for (int i = 0; i < kChunk; ++i) vals[i] = __uint_as_float(v[i]) + bias_v;
-              store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
-                                                 (int64_t)ti.row0 + c0, ti.valid - c0, p.m, p.n,
-                                                 ti.n_tile * kFeat + q * 32, lane);
-            }
+            for (int i = 0; i < kChunk; ++i) vals[i] = __uint_as_float(v[i]) + bias_v;
+            store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
+                                               (int64_t)ti.row0 + c0, ti.valid - c0, p.m, p.n,
+                                               ti.n_tile * kFeat + q * 32, lane);
           }
         }
         ptx::tc_fence_before();
@@ -343,7 +335,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         float acc[kCols];
 #pragma unroll
         for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
-        uint32_t va[16], vb[16];   // kPipe: TMEM data of the chunk in work / in flight
         // Scales are fetched kGroup K blocks at a time, one group ahead of their
         // use (the first group of the next tile during the last group of this
         // one), so the strided a_scale loads are off the critical path.  Each
@@ -364,91 +355,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             fetch_group(tn, 0, pre);
             pre_valid = true;
           }
-          if (kPipe) {
-            // Four 16-column chunks per K block, two register buffers.  The TMEM load of
-            // the next chunk (or of the next block's first chunk) is in flight while the
-            // current one is promoted: tcgen05.wait::ld waits for every load issued so
-            // far, so each wait sits after the arithmetic that does not need the newest
-            // load.  A buffer is not touched between its load and its wait.
-#pragma unroll
-            for (int jb = 0; jb < kGroup; ++jb) {
-              const int kb = g * kGroup + jb;
-              if (kb >= p.num_kb) break;
-              const uint32_t sc = ptx::smem_u32(ctrl->sc[warp - 2][kb & 1]);
-              uint32_t a = acc_it % kAccStages;
-              if (kb == 0) {   // first block of the tile: nothing was loaded ahead
-#pragma unroll
-                for (int u = 0; u < kPerLane; ++u)
-                  if (lane + 32 * u < kCols) ptx::sts32f(sc + (lane + 32 * u) * 4, cur.a[u][jb] * cur.w[jb]);
-                __syncwarp();
-                TC_PROF_T(e1);
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
-                  *abort_flag = 1; ok = false; break;
-                }
-                TC_PROF_ADD(ew, e1);
-                ptx::tc_fence_after();
-                ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + lane_sel, va);
-                ptx::tmem_wait_ld_tied(va);
-              }
-              const bool more = kb + 1 < p.num_kb;
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                // chunk c of this block sits in (c even ? va : vb); start the load after it
-                if (c < 3) {
-                  if (c & 1) ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + 16 * (c + 1) + lane_sel, va);
-                  else ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + 16 * (c + 1) + lane_sel, vb);
-                } else {
-                  // all of this block is in registers (chunk 3 was waited for): free its stage
-                  ptx::tc_fence_before();
-                  __syncwarp();
-                  if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
-                  ++acc_it;
-                  if (more) {   // next block of the tile: stage its scales, start its chunk 0
-                    const uint32_t scn = ptx::smem_u32(ctrl->sc[warp - 2][(kb + 1) & 1]);
-#pragma unroll
-                    for (int u = 0; u < kPerLane; ++u) {
-                      if (lane + 32 * u < kCols) {
-                        const float sv = (jb + 1 < kGroup) ? cur.a[u][(jb + 1) % kGroup] * cur.w[(jb + 1) % kGroup]
-                                                           : pre.a[u][0] * pre.w[0];
-                        ptx::sts32f(scn + (lane + 32 * u) * 4, sv);
-                      }
-                    }
-                    __syncwarp();
-                    a = acc_it % kAccStages;
-                    TC_PROF_T(e2);
-                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
-                      *abort_flag = 1; ok = false;
-                    }
-                    TC_PROF_ADD(ew, e2);
-                    ptx::tc_fence_after();
-                    if (ok) ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + lane_sel, va);
-                  }
-                }
-                if (col0 + 16 * c < ti.valid) {
-#pragma unroll
-                  for (int i = 0; i < 16; i += 4) {
-                    const float4 s4 = ptx::lds128f(sc + (16 * c + i) * 4);
-                    const uint32_t* v = (c & 1) ? vb : va;
-                    acc[16 * c + i + 0] = fmaf(__uint_as_float(v[i + 0]), s4.x, acc[16 * c + i + 0]);
-                    acc[16 * c + i + 1] = fmaf(__uint_as_float(v[i + 1]), s4.y, acc[16 * c + i + 1]);
-                    acc[16 * c + i + 2] = fmaf(__uint_as_float(v[i + 2]), s4.z, acc[16 * c + i + 2]);
-                    acc[16 * c + i + 3] = fmaf(__uint_as_float(v[i + 3]), s4.w, acc[16 * c + i + 3]);
-                  }
-                }
-                if (c < 3) {
-                  if (c & 1) ptx::tmem_wait_ld_tied(va); else ptx::tmem_wait_ld_tied(vb);
-                } else if (more && ok) {
-                  ptx::tmem_wait_ld_tied(va);
-                }
-              }
-              if (!ok) break;
-            }
-          } else {
 #pragma unroll
           for (int jb = 0; jb < kGroup; ++jb) {
             const int kb = g * kGroup + jb;
             if (kb >= p.num_kb) break;
-            if ((p.debug & 4) && kb + 1 < p.num_kb) continue;
             const uint32_t sc = ptx::smem_u32(ctrl->sc[warp - 2][kb & 1]);
 #pragma unroll
             for (int u = 0; u < kPerLane; ++u)
@@ -465,7 +375,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int c0 = 0; c0 < kCols; c0 += kChunk) {
               const bool last_chunk = (c0 + kChunk >= kCols);
               uint32_t v[kChunk];
-              if (col0 + c0 < ti.valid && !(p.debug & 2)) {
+              if (col0 + c0 < ti.valid) {
                 if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
                 else ptx::tmem_ld_32x16(tmem_base + a * BT + col0 + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
                 ptx::tmem_wait_ld();
@@ -475,7 +385,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
               }
-              if (col0 + c0 < ti.valid && !(p.debug & 3)) {
+              if (col0 + c0 < ti.valid) {
 #pragma unroll
                 for (int i = 0; i < kChunk; i += 4) {
                   const float4 s4 = ptx::lds128f(sc + (c0 + i) * 4);
@@ -487,7 +397,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
             ++acc_it;
-          }
           }
           if (g + 1 < n_groups) cur = pre;
         }
@@ -530,7 +439,7 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, i
                                       (int)smem_bytes<BT, kFp8>()));
     configured = true;
   }
-  kern<<<grid, num_threads<BT, kFp8>(), smem_bytes<BT, kFp8>(), st>>>(ta, tw, p);
+  kern<<<grid, kTcThreads, smem_bytes<BT, kFp8>(), st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_tc_kernel");
   return B200MOE_OK;
 }
@@ -566,11 +475,6 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   p.n_tiles = (a->n + kFeat - 1) / kFeat;
   p.num_kb = (a->k + kpb - 1) / kpb;
   p.out_f16 = a->d_dtype == B200MOE_F16;
-  {
-    static int dbg = -1;
-    if (dbg < 0) { const char* e = getenv("B200MOE_DEBUG"); dbg = e ? atoi(e) : 0; }
-    p.debug = dbg;
-  }
 
   const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
   // Token-tile width from the mean rows per expert (routing is never perfectly
@@ -586,12 +490,8 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
     if (force_bt == 16 || force_bt == 64 || force_bt == 128 || (force_bt == 256 && !a_fp8)) bt = force_bt;
   }
 
-  if (a_fp8 && bt == 128) {
-    // prefill-sized segments: the token-major kernel (one scale register per thread and K block)
-    static int feat_major = -1;
-    if (feat_major < 0) { const char* e = getenv("B200MOE_FP8_FEATURE_MAJOR"); feat_major = e ? atoi(e) : 0; }
-    if (!feat_major) return grouped_gemm_tc_fp8t(a, st);
-  }
+  // prefill-sized fp8 segments: the token-major kernels (one scale register per thread and K block)
+  if (a_fp8 && bt >= 128) return grouped_gemm_tc_fp8t(a, st);
 
   const uint32_t fmt = a_fp8 ? 0u : (a->a_dtype == B200MOE_BF16 ? 1u : 0u);
   p.idesc = ptx::make_idesc(fmt, fmt, kn ? 1u : 0u, 0u, kFeat, (uint32_t)bt);
@@ -630,8 +530,8 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
 #define B200_TC_CASE(BT_)                                                         \
   if (bt == BT_) {                                                                \
     if (a_fp8) {                                                                  \
-      if (kn) return launch_tc<(BT_ > 128 ? 128 : BT_), true, true>(ta, tw, p, grid, st);  \
-      return launch_tc<(BT_ > 128 ? 128 : BT_), true, false>(ta, tw, p, grid, st);         \
+      if (kn) return launch_tc<(BT_ > 64 ? 64 : BT_), true, true>(ta, tw, p, grid, st);  \
+      return launch_tc<(BT_ > 64 ? 64 : BT_), true, false>(ta, tw, p, grid, st);         \
     }                                                                             \
     if (kn) return launch_tc<BT_, false, true>(ta, tw, p, grid, st);              \
     return launch_tc<BT_, false, false>(ta, tw, p, grid, st);                     \

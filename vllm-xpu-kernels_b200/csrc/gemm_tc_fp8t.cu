@@ -14,7 +14,10 @@
 // smaller token tiles, has a different scale in every accumulator column and has to stage
 // them through shared memory.)
 //
-// Roles (320 threads, one persistent CTA per SM):
+// Two kernels: 128 x 128 tiles (below, used when N is a single 128-feature block) and
+// 128 x 256 tiles (further down, the one prefill shapes run).
+//
+// Roles of the 128 x 128 kernel (320 threads, one persistent CTA per SM):
 //   warp 0    : TMA producer, ring of 6 stages of [weights 128x128 B | tokens 128x128 B]
 //   warp 1    : MMA issuer (one lane), kind::f8f6f4, one accumulator stage (128 columns of
 //               tensor memory, four stages) per K block
@@ -22,8 +25,6 @@
 //               64 * ((w - 2) / 4) .. + 63: 64 accumulators per thread
 // Every mbarrier wait is bounded; on expiry the CTA raises its abort flag, all roles leave
 // their loops, tensor memory is freed and *status is set to 1.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "gemm_tc_common.cuh"
 #include "sm100_ptx.cuh"
@@ -624,9 +625,7 @@ int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
   }
   int grid = sm_count();
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
-  static int narrow = -1;
-  if (narrow < 0) { const char* e = getenv("B200MOE_FP8_NARROW"); narrow = e ? atoi(e) : 0; }
-  const bool wide = !narrow && a->n >= 256;
+  const bool wide = a->n >= 256;   // 256-feature tiles; a single 128-feature block takes the narrow kernel
   const int64_t tile_bound = ((a->m + kTTok - 1) / kTTok + a->num_experts) * (int64_t)(wide ? (p.n_tiles + 1) / 2 : p.n_tiles);
   if (tile_bound < grid) grid = (int)tile_bound;
   if (grid < 1) grid = 1;
