@@ -36,7 +36,16 @@ import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the two grouped-GEMM launches of one
 # step, from one ncu capture per workload (see the summaries under profiles/).
-NCU_TRAFFIC_BYTES = {("cfg2_mixtral_bf16", 4096): 3.956e9}
+NCU_TRAFFIC_BYTES = {("cfg2_mixtral_bf16", 4096): 3.956e9,
+                     ("cfg3_qwen3_fp8", 4096): 0.884e9}   # profiles/grouped_gemm_fp8t256_cfg3_T4096.md
+
+
+def _gemm_kernel_name(cfg, T):
+    """The kernel b200moe_grouped_gemm picks for the 16-bit / block-fp8 recipes: fp8 segments of
+    more than 40 rows per expert on average run the token-major kernel."""
+    if cfg.recipe == "fp8block" and (T * cfg.K + cfg.E - 1) // cfg.E > 40:
+        return "grouped_gemm_fp8t256_kernel"
+    return "grouped_gemm_tc_kernel"
 
 METRIC = "fused_moe_layer_tokens_per_s"
 UNIT = "tokens/s"
@@ -414,7 +423,7 @@ def run_ours(args):
         ach = (wbytes + act_bytes) / (ms_pair * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm"], "unit": "GB/s",
                 "frac": round(ach / peaks["hbm"], 4)}
-    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((cfg.name, T)) if ep_world == 1 else None, "kernel": (("grouped_gemm_mx_kernel" if mx else "grouped_gemm_dq_kernel") if cfg.recipe == "mxfp4" else "grouped_gemm_tc_kernel")
+    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((cfg.name, T)) if ep_world == 1 else None, "kernel": (("grouped_gemm_mx_kernel" if mx else "grouped_gemm_dq_kernel") if cfg.recipe == "mxfp4" else _gemm_kernel_name(cfg, T))
                            + " (gemm1 + gemm2 of one step)",
                  "ms_per_launch_pair": round(ms_pair, 4), "peak_source": peaks["source"] + " (sustained)",
                  "experts_active": e_act})
