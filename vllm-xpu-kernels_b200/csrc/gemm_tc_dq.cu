@@ -404,22 +404,24 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ptx::tmem_wait_ld();
           float vals[kChunk];
 #pragma unroll
-          for (int i = 0; i < kChunk; ++i) {
-            float x = __uint_as_float(v[i]) + bias_v;
-            if (p.swiglu) {
+          for (int i = 0; i < kChunk; ++i) vals[i] = __uint_as_float(v[i]) + bias_v;
+          if (p.swiglu) {
+            // One branch around the whole block: the unrolled body stays straight-line code, so
+            // the shuffle / exp / divide chains of the columns overlap.
+            const float c_lim = p.clamp_limit > 0.f ? p.clamp_limit : INFINITY;
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
               // gate sits on even features, up on the next odd one: neighbours in the warp
+              const float x = vals[i];
               const float other = __shfl_xor_sync(0xffffffffu, x, 1);
               float gate = (lane & 1) ? other : x;
               float up = (lane & 1) ? x : other;
-              if (p.clamp_limit > 0.f) {
-                gate = fminf(gate, p.clamp_limit);
-                up = fminf(fmaxf(up, -p.clamp_limit), p.clamp_limit);
-              }
+              gate = fminf(gate, c_lim);
+              up = fminf(fmaxf(up, -c_lim), c_lim);
               gate = fminf(gate, p.limit);
               up = fminf(fmaxf(up, -p.limit), p.limit);
-              x = (up + 1.0f) * gate * (1.0f / (1.0f + __expf(-gate * p.alpha)));
+              vals[i] = (up + 1.0f) * gate * __fdividef(1.0f, 1.0f + __expf(-gate * p.alpha));
             }
-            vals[i] = x;
           }
           if (p.swiglu)
             store_block_transposed<kChunk, 16>(ctrl->xpose[warp - 2 - kDqConvWarps], vals, p.d, p.out_f16,

@@ -171,7 +171,10 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int kNT = kTerms * BT;                  // UMMA N: the planes side by side
   constexpr int kW = kNT >= 32 ? kNT / 32 : 1;       // token-scale columns (words per lane and K block)
   constexpr uint32_t kSfBase = 2 * kNT;
-  constexpr int kSfCols = 8 * kSub;                 // scale columns of one stage (8 per K block)
+  // scale columns per K block: the weight rows' four, then the tokens' kW; the region of a K
+  // block starts on a multiple of 8 columns
+  constexpr int kSfPer = kW <= 4 ? 8 : 16;
+  constexpr int kSfCols = kSfPer * kSub;            // scale columns of one stage
   constexpr int kABytes = kNT * 128;                // activation bytes of one K block (all planes)
   constexpr int kAOff = kSub * kMxWBytes;           // stage: [W blocks][A blocks][raw tail]
   constexpr int kRawOff = kSub * (kMxWBytes + kABytes);
@@ -311,7 +314,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (kb0 + sub < p.num_kb) {
               // The planes' activation tiles are adjacent in the stage: one K-major
               // operand of kNT rows; their results land in adjacent column blocks.
-              const uint32_t sfa = sf0 + 8 * sub;
+              const uint32_t sfa = sf0 + kSfPer * sub;
 #pragma unroll
               for (uint32_t j = 0; j < 4; ++j) {
                 // K-major e2m1 tile: 32 codes further is 32 bytes; MN-major byte tile: 32 K rows
@@ -453,13 +456,16 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             MX_PROF_T(s0);
             if (ok) {
-              const uint32_t col = tmem_base + kSfBase + s * kSfCols + 8 * sub + lane_sel;
+              const uint32_t col = tmem_base + kSfBase + s * kSfCols + kSfPer * sub + lane_sel;
               {
                 // eight columns at once: the weight rows' four, then the tokens' (unused ones 2^0)
                 uint32_t r8[8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { r8[j] = wa[j]; r8[4 + j] = j < kW ? cur_b[u][j < kW ? j : 0] : 0x7f7f7f7fu; }
                 ptx::tmem_st_32x8(col, r8);
+                if (kW > 4)   // token tiles wider than 128 columns: their remaining scale columns
+                  ptx::tmem_st_32x4(col + 8, cur_b[u][4 < kW ? 4 : 0], 5 < kW ? cur_b[u][5 < kW ? 5 : 0] : 0x7f7f7f7fu,
+                                    0x7f7f7f7fu, 0x7f7f7f7fu);
               }
               if (kb == tail_kb) {
                 // Spread the partial block: row ft, 64 packed bytes -> eight 16-byte
@@ -518,6 +524,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_it = 0;
     int cursor = 0;
     bool ok = true;
+    MX_PROF_DECL(ew = 0, el = 0, em = 0, es = 0, et0 = clock64());
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       TileInfo ti;
       locate_tile<BT>(tile_start, row_start, t, cursor, ti);
@@ -529,7 +536,9 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t a = acc_it & 1;
       // a whole tile's MMAs away: poll from one lane, sleeping in between, so that the
       // wait does not take issue slots from the feeder warp on the same scheduler
+      MX_PROF_T(w0);
       if (!ptx::mbar_wait_warp(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag, 128)) { ok = false; break; }
+      MX_PROF_ADD(ew, w0);
       ptx::tc_fence_after();
 #pragma unroll
       for (int c0 = 0; c0 < BT; c0 += kChunk) {
@@ -538,6 +547,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           float acc[kChunk];
 #pragma unroll
           for (int i = 0; i < kChunk; ++i) acc[i] = 0.f;
+          MX_PROF_T(l0);
 #pragma unroll
           for (int term = 0; term < kTerms; ++term) {   // the planes' partial results add up
             const uint32_t col = tmem_base + a * kNT + term * BT + c0 + lane_sel;
@@ -547,25 +557,31 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int i = 0; i < kChunk; ++i) acc[i] += __uint_as_float(v[i]);
           }
+          MX_PROF_ADD(el, l0);
+          MX_PROF_T(m0);
           float vals[kChunk];
 #pragma unroll
-          for (int i = 0; i < kChunk; ++i) {
-            float x = kW8 ? fmaf(acc[i], w_mul, bias_v) : acc[i] + bias_v;
-            if (p.swiglu) {
+          for (int i = 0; i < kChunk; ++i) vals[i] = kW8 ? fmaf(acc[i], w_mul, bias_v) : acc[i] + bias_v;
+          if (p.swiglu) {
+            // One branch around the whole block: the unrolled body stays straight-line code, so
+            // the 32 shuffle / exp / divide chains overlap instead of running one after another.
+            const float c_lim = p.clamp_limit > 0.f ? p.clamp_limit : INFINITY;
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
               // gate sits on even features, up on the next odd one: neighbours in the warp
+              const float x = vals[i];
               const float other = __shfl_xor_sync(0xffffffffu, x, 1);
               float gate = (lane & 1) ? other : x;
               float up = (lane & 1) ? x : other;
-              if (p.clamp_limit > 0.f) {
-                gate = fminf(gate, p.clamp_limit);
-                up = fminf(fmaxf(up, -p.clamp_limit), p.clamp_limit);
-              }
+              gate = fminf(gate, c_lim);
+              up = fminf(fmaxf(up, -c_lim), c_lim);
               gate = fminf(gate, p.limit);
               up = fminf(fmaxf(up, -p.limit), p.limit);
-              x = (up + 1.0f) * gate * (1.0f / (1.0f + __expf(-gate * p.alpha)));
+              vals[i] = (up + 1.0f) * gate * __fdividef(1.0f, 1.0f + __expf(-gate * p.alpha));
             }
-            vals[i] = x;
           }
+          MX_PROF_ADD(em, m0);
+          MX_PROF_T(s0);
           if (p.swiglu)
             store_block_transposed<kChunk, 16>(ctrl->xpose[warp - 6], vals, p.d, p.out_f16,
                                                (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
@@ -574,6 +590,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
             store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 6], vals, p.d, p.out_f16,
                                                (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
                                                ti.n_tile * kFeat + q * 32, lane);
+          MX_PROF_ADD(es, s0);
         }
       }
       ptx::tc_fence_before();
@@ -581,6 +598,8 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
       ++acc_it;
     }
+    if (warp == 6 && lane == 0)
+      MX_PROF_PRINT("epilogue: total %lld wait %lld tmem %lld math %lld store %lld\n", clock64() - et0, ew, el, em, es);
   }
 
   ptx::tc_fence_before();
@@ -597,7 +616,7 @@ template <int BT, int kTerms, int kSub, bool kW8>
 int launch_mx(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& traw, MxParams& p,
               int grid, cudaStream_t st) {
   auto kern = grouped_gemm_mx_kernel<BT, kTerms, kSub, kW8>;
-  const uint32_t need = 2 * kTerms * BT + kMxMaxStages * 8 * kSub;
+  const uint32_t need = 2 * kTerms * BT + kMxMaxStages * (kTerms * BT > 128 ? 16 : 8) * kSub;
   p.tmem_cols = need <= 128 ? 128u : (need <= 256 ? 256u : 512u);
   // The partial K block's packed bytes get one buffer for the whole CTA when a tile
   // has at least as many stages as the pipeline (its next use then comes after
@@ -692,12 +711,15 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
 
   const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
   int bt = avg <= 8 ? 16 : (avg <= 40 ? 64 : 128);
+  // both planes' accumulators share tensor memory: two planes of 96 tokens are one MMA of
+  // N = 192 (enough work per instruction to keep the tensor pipe busy), two stages of them
+  // and the scale columns fill the 512 columns
+  if (x2 && bt > 64) bt = avg > 48 ? 96 : 64;   // measured: 64 rows per expert -22 %, 32 rows +8 %
   {
     static int force = -1;
     if (force < 0) { const char* e = getenv("B200MOE_BT"); force = e ? atoi(e) : 0; }
-    if (force == 16 || force == 64 || force == 128) bt = force;
+    if (force == 16 || force == 64 || (force == 96 && x2) || (force == 128 && !x2)) bt = force;
   }
-  if (x2 && bt > 64) bt = 64;   // both planes' accumulators share tensor memory
   // weights: e2m1 K-major, or e4m3 / e5m2 MN-major; activations e4m3 K-major
   const uint32_t a_fmt = w4 ? 5u : (a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN ? 1u : 0u);
   p.idesc = ptx::make_idesc_mx(a_fmt, 0u, kFeat, (uint32_t)(bt * p.terms)) | (w8 ? (1u << 15) : 0u);
@@ -745,8 +767,10 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
 #define B200_MX_CASES(W8)                                                              \
   if (x2) {                                                                            \
     if (bt == 16) return launch_mx<16, 2, 2, W8>(ta, tw, traw, p, grid, st);           \
+    if (bt == 96) return launch_mx<96, 2, 1, W8>(ta, tw, traw, p, grid, st);           \
     return launch_mx<64, 2, 1, W8>(ta, tw, traw, p, grid, st);                         \
   }                                                                                    \
+  if (bt == 96) bt = 128;                                                              \
   if (bt == 16) return launch_mx<16, 1, 2, W8>(ta, tw, traw, p, grid, st);             \
   if (bt == 64) return launch_mx<64, 1, 2, W8>(ta, tw, traw, p, grid, st);             \
   return launch_mx<128, 1, 1, W8>(ta, tw, traw, p, grid, st);
