@@ -715,10 +715,11 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
   // N = 192 (enough work per instruction to keep the tensor pipe busy), two stages of them
   // and the scale columns fill the 512 columns
   if (x2 && bt > 64) bt = avg > 48 ? 96 : 64;   // measured: 64 rows per expert -22 %, 32 rows +8 %
+  if (!x2 && avg > 128) bt = 192;               // one plane: the same N = 192 instruction
   {
     static int force = -1;
     if (force < 0) { const char* e = getenv("B200MOE_BT"); force = e ? atoi(e) : 0; }
-    if (force == 16 || force == 64 || (force == 96 && x2) || (force == 128 && !x2)) bt = force;
+    if (force == 16 || force == 64 || (force == 96 && x2) || ((force == 128 || force == 192) && !x2)) bt = force;
   }
   // weights: e2m1 K-major, or e4m3 / e5m2 MN-major; activations e4m3 K-major
   const uint32_t a_fmt = w4 ? 5u : (a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN ? 1u : 0u);
@@ -770,7 +771,7 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
     if (bt == 96) return launch_mx<96, 2, 1, W8>(ta, tw, traw, p, grid, st);           \
     return launch_mx<64, 2, 1, W8>(ta, tw, traw, p, grid, st);                         \
   }                                                                                    \
-  if (bt == 96) bt = 128;                                                              \
+  if (bt == 192) return launch_mx<192, 1, 1, W8>(ta, tw, traw, p, grid, st);           \
   if (bt == 16) return launch_mx<16, 1, 2, W8>(ta, tw, traw, p, grid, st);             \
   if (bt == 64) return launch_mx<64, 1, 2, W8>(ta, tw, traw, p, grid, st);             \
   return launch_mx<128, 1, 1, W8>(ta, tw, traw, p, grid, st);
