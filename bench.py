@@ -42,8 +42,8 @@ NCU_TRAFFIC_BYTES = {("cfg2_mixtral_bf16", 4096): 3.956e9,
 
 def _gemm_kernel_name(cfg, T):
     """The kernel b200moe_grouped_gemm picks for the 16-bit / block-fp8 recipes: fp8 segments of
-    more than 40 rows per expert on average run the token-major kernel."""
-    if cfg.recipe == "fp8block" and (T * cfg.K + cfg.E - 1) // cfg.E > 40:
+    12 rows per expert or more on average run the token-major kernel."""
+    if cfg.recipe == "fp8block" and (T * cfg.K + cfg.E - 1) // cfg.E >= 12:
         return "grouped_gemm_fp8t256_kernel"
     return "grouped_gemm_tc_kernel"
 

@@ -81,7 +81,7 @@ def test_grouped_gemm_fp8_block_w8a8(native, impl, layout, E, M, N, K):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("E,M,N,K", [(3, 700, 640, 1024), (2, 300, 128, 384), (5, 1000, 256, 128), (4, 520, 1152, 640)])
 def test_grouped_gemm_fp8_block_prefill_tiles(native, layout, dtype, E, M, N, K):
-    """Segments of more than 40 rows per expert take the token-major kernels (256-feature tiles
+    """Segments of 12 rows per expert or more take the token-major kernels (256-feature tiles
     from N = 256, else 128): odd and even numbers of 128-feature blocks, bias, both output
     types, ragged and empty segments."""
     g = torch.Generator().manual_seed(M + N + K + 1)

@@ -20,7 +20,7 @@
 // MMAs of the next).  fp8 inputs use kind::f8f6f4 per 128-wide K block; the
 // epilogue warps promote each block's partial sum into fp32 registers with
 // a_scale[row, kb] * w_scale[e, n/128, kb], as the block-scaled recipe needs.
-// (fp8 segments of more than 40 rows per expert go to the token-major kernels of
+// (fp8 segments of 12 rows per expert or more go to the token-major kernels of
 // gemm_tc_fp8t.cu, where that scale is one register per thread.)
 //
 // Every wait on an mbarrier is bounded (see sm100_ptx.cuh): on expiry the CTA
@@ -480,9 +480,14 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   // Token-tile width from the mean rows per expert (routing is never perfectly
   // even, so leave headroom before a second token tile re-reads the weights).
   int bt;
-  if (avg <= 8) bt = 16;
+  if (a_fp8) {
+    // fp8 pays a hand-over per 128-wide K block, so wider tiles win earlier (measured on the
+    // DeepSeek and Qwen3 shapes: 8 rows per expert 0.72 / 0.88 / 0.84 of the copy rate at
+    // 16 / 64 / 128 tokens, 32 rows 0.32 / 0.69 / 0.82)
+    bt = avg <= 4 ? 16 : (avg < 12 ? 64 : 128);
+  } else if (avg <= 8) bt = 16;
   else if (avg <= 40) bt = 64;
-  else if (avg <= 96 || a_fp8) bt = 128;   // measured on skewed routing: 128 rows per expert are 13 % faster at 256
+  else if (avg <= 96) bt = 128;   // measured on skewed routing: 128 rows per expert are 13 % faster at 256
   else bt = 256;
   {
     static int force_bt = -1;
