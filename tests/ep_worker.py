@@ -60,6 +60,33 @@ def cpu_worker(rank, world, port, T, result_queue):
         out = to.moe_gather(back, tw, send_pos, x.dtype)
         ref = _oracle_full(cfg, w, x, tw, ids)
         err = float((out.float() - ref.float()).abs().max())
+
+        # the same through the expert-group schedule: rows sorted by (group, destination rank), one
+        # dispatch / combine per group, results collected in send order, one gather at the end
+        from vllm_xpu_kernels.ep_moe import group_bucket_map
+        G = 2
+        bucket = group_bucket_map(cfg.E, world, G, "cpu")
+        assert bucket.tolist() == [(e % E_local) * G // E_local * world + e // E_local for e in range(cfg.E)]
+        g_rows, _, g_counts, g_pos = to.remap_hidden_states(x, None, ids, bucket, G * world)
+        g_eids = torch.empty(M, dtype=torch.int32)
+        g_eids[g_pos.reshape(-1).long()] = (ids.reshape(-1) % E_local).to(torch.int32)
+        by_peer = g_counts.view(G, world).t().contiguous()
+        recv_counts = torch.empty_like(by_peer)
+        dist.all_to_all_single(recv_counts, by_peer)
+        back_all = torch.empty(M, x.shape[1], dtype=x.dtype)
+        start = 0
+        for g in range(G):
+            s_g, r_g = by_peer[:, g].tolist(), recv_counts[:, g].tolist()
+            n = sum(s_g)
+            rr, _, re = a2a.dispatch((g_rows[start:start + n], None, g_eids[start:start + n]), s_g, r_g)
+            assert all(lo + int(e) in range(lo, lo + E_local) and int(e) * G // E_local == g for e in re.tolist())
+            Rg = rr.shape[0]
+            lo_out = to.fused_moe_staged(rr, d13[lo:lo + E_local], None, d2[lo:lo + E_local], None,
+                                         torch.ones(Rg, 1), re.view(Rg, 1), E_local) if Rg else rr
+            back_all[start:start + n] = a2a.combine(lo_out, s_g, r_g)
+            start += n
+        out_g = to.moe_gather(back_all, tw, g_pos, x.dtype)
+        err = max(err, float((out_g.float() - ref.float()).abs().max()))
         result_queue.put((rank, err, s_spl, r_spl))
     finally:
         dist.destroy_process_group()
@@ -95,6 +122,14 @@ def gpu_worker(rank, world, port, T, cfg_name, dims, result_queue):
         layer.apply(out2, x.to(dev), tw.to(dev), ids.to(dev))
         torch.cuda.synchronize()
         err = max(err, float((out2.cpu().float() - ref.float()).abs().max()))
+        # so does the schedule that pipelines the exchange by expert group
+        grouped = EpFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]), cfg.K,
+                             cfg.activation, E_local, expert_groups=3)
+        out3 = torch.empty_like(out)
+        for _ in range(2):
+            grouped.apply(out3, x.to(dev), tw.to(dev), ids.to(dev))
+        torch.cuda.synchronize()
+        err = max(err, float((out3.cpu().float() - ref.float()).abs().max()))
         result_queue.put((rank, err, scale))
     finally:
         dist.destroy_process_group()

@@ -89,9 +89,10 @@ class EpAllToAll:
             out.append(r)
         return out, works
 
-    def combine_async(self, rows, send_splits, recv_splits):
+    def combine_async(self, rows, send_splits, recv_splits, out=None):
         n_send = int(sum(send_splits))
-        back = torch.empty((n_send,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+        back = out if out is not None else torch.empty((n_send,) + tuple(rows.shape[1:]), dtype=rows.dtype,
+                                                       device=rows.device)
         work = dist.all_to_all_single(back, rows, output_split_sizes=send_splits,
                                       input_split_sizes=recv_splits, group=self.group, async_op=True)
         return back, work
@@ -101,6 +102,18 @@ def owner_map(num_experts_total: int, ep_size: int, device) -> torch.Tensor:
     """int32 [E_total]: the rank that owns each expert (contiguous even split)."""
     e_local = num_experts_total // ep_size
     return (torch.arange(num_experts_total, device=device) // e_local).to(torch.int32)
+
+
+def group_bucket_map(num_experts_total: int, ep_size: int, groups: int, device) -> torch.Tensor:
+    """int32 [E_total]: bucket ``g * ep_size + rank`` of each expert, where ``rank`` owns the
+    expert and ``g`` is the group of the expert among its rank's experts (contiguous, as even as
+    possible).  Sorting routed rows by this bucket puts, for every group, the rows of all ranks
+    side by side: one contiguous slice of the send buffer per group, split by rank inside."""
+    e_local = num_experts_total // ep_size
+    e = torch.arange(num_experts_total, device=device)
+    rank = e // e_local
+    g = (e % e_local) * groups // e_local
+    return (g * ep_size + rank).to(torch.int32)
 
 
 class EpFusedMoe:
@@ -115,7 +128,8 @@ class EpFusedMoe:
                  n_experts_per_token, activation, num_local_experts,
                  group: Optional[dist.ProcessGroup] = None,
                  gemm1_clamp_limit: Optional[float] = None,
-                 overlap_chunks: Optional[int] = None, sm_reserve: int = 20):
+                 overlap_chunks: Optional[int] = None, sm_reserve: int = 20,
+                 expert_groups: Optional[int] = None):
         from .fused_moe_interface import XpuFusedMoe
         self.a2a = EpAllToAll(group)
         self.ep_size, self.ep_rank = self.a2a.ep_size, self.a2a.ep_rank
@@ -136,6 +150,15 @@ class EpFusedMoe:
         # 15.2 ms with 4).
         self.overlap_chunks = overlap_chunks
         self.sm_reserve = sm_reserve
+        # Optional: split the local experts into `expert_groups` contiguous groups and run the
+        # exchange group by group, so that the rows of group g+1 arrive and the results of group
+        # g-1 leave while group g's experts compute.  Unlike token chunks this streams every
+        # weight once: a group's GEMMs touch only that group's experts.
+        self.expert_groups = None
+        if expert_groups is not None and expert_groups > 1:
+            self.expert_groups = min(expert_groups, num_local_experts)
+            self.group_bucket = group_bucket_map(self.num_experts_total, self.ep_size, self.expert_groups,
+                                                 w13.device)
         self._sm_count = torch.cuda.get_device_properties(w13.device).multi_processor_count
 
     def _num_chunks(self, T):
@@ -144,6 +167,8 @@ class EpFusedMoe:
         return max(1, min(self.overlap_chunks, T))
 
     def apply(self, output, hidden_states, topk_weights, topk_ids):
+        if self.expert_groups is not None:
+            return self._apply_grouped(output, hidden_states, topk_weights, topk_ids)
         nc = self._num_chunks(hidden_states.shape[0])
         if nc > 1:
             return self._apply_chunked(output, hidden_states, topk_weights, topk_ids, nc)
@@ -262,3 +287,69 @@ class EpFusedMoe:
             finish(*pending)
         finally:
             self.local.gemm_max_ctas = 0
+
+    def _apply_grouped(self, output, hidden_states, topk_weights, topk_ids):
+        T, H = hidden_states.shape
+        K, ep, G, dev = self.topk, self.ep_size, self.expert_groups, hidden_states.device
+        M = T * K
+        ops = torch.ops._moe_C
+        # 1. one stable sort of the routed rows by (group, destination rank)
+        counts = torch.empty((G * ep,), dtype=torch.int32, device=dev)
+        send_pos = torch.empty((T, K), dtype=torch.int32, device=dev)
+        if self.quant:
+            send_rows = torch.empty((M, H), dtype=torch.float8_e4m3fn, device=dev)
+            send_scales = torch.empty((M, H // FP8_BLOCK), dtype=torch.float32, device=dev)
+            ops.b200_remap_quant_fp8(hidden_states, send_rows, send_scales, self.group_bucket, counts,
+                                     send_pos, topk_ids, self.num_experts_total, G * ep)
+        else:
+            send_rows = torch.empty((M, H), dtype=hidden_states.dtype, device=dev)
+            send_scales = None
+            ops.remap_hidden_states(hidden_states, None, send_rows, None, self.group_bucket, counts,
+                                    send_pos, topk_ids, self.num_experts_total, G * ep)
+        send_eids = torch.empty((M,), dtype=torch.int32, device=dev)
+        send_eids[send_pos.reshape(-1).long()] = (topk_ids.reshape(-1) % self.num_local_experts).to(torch.int32)
+
+        # 2. all counts in one exchange, read back once: [ep (peer), G]
+        by_peer = counts.view(G, ep).t().contiguous()
+        recv_counts = torch.empty_like(by_peer)
+        dist.all_to_all_single(recv_counts, by_peer, group=self.a2a.group)
+        both = torch.stack((by_peer, recv_counts)).cpu()
+        send_spl = [both[0][:, g].tolist() for g in range(G)]
+        recv_spl = [both[1][:, g].tolist() for g in range(G)]
+        starts = [0]
+        for g in range(G):
+            starts.append(starts[-1] + int(sum(send_spl[g])))
+
+        def chunk(g):
+            a, b = starts[g], starts[g + 1]
+            return (send_rows[a:b], send_scales[a:b] if send_scales is not None else None, send_eids[a:b])
+
+        # 3. dispatch(g+1) and combine(g-1) run beside the experts of group g
+        back_all = torch.empty((M, H), dtype=output.dtype, device=dev)
+        self.local.gemm_max_ctas = max(1, self._sm_count - self.sm_reserve)
+        try:
+            inflight = [None] * G
+            inflight[0] = self.a2a.dispatch_async(chunk(0), send_spl[0], recv_spl[0])
+            works, keep = [], []
+            for g in range(G):
+                if g + 1 < G:
+                    inflight[g + 1] = self.a2a.dispatch_async(chunk(g + 1), send_spl[g + 1], recv_spl[g + 1])
+                (recv_rows, recv_scales, recv_eids), ws = inflight[g]
+                for w in ws:
+                    w.wait()
+                R = recv_rows.shape[0]
+                local_out = torch.empty((R, H), dtype=output.dtype, device=dev)
+                if R > 0:
+                    ones = torch.ones((R, 1), dtype=torch.float32, device=dev)
+                    self.local.apply(local_out, recv_rows, ones, recv_eids.view(R, 1),
+                                     a1q_scale=recv_scales if self.quant else None)
+                _, work = self.a2a.combine_async(local_out, send_spl[g], recv_spl[g],
+                                                 out=back_all[starts[g]:starts[g + 1]])
+                works.append(work)
+                keep.append((recv_rows, recv_scales, recv_eids, local_out))
+            for w in works:
+                w.wait()
+        finally:
+            self.local.gemm_max_ctas = 0
+        # 4. weighted top-k reduction on the source rank
+        ops.moe_gather(output, back_all, topk_weights, send_pos, self.num_experts_total)
