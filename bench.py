@@ -161,7 +161,8 @@ def launches_per_step(M: int, quant: bool) -> int:
     return 1 + (1 if M <= 2048 else 3) + 1 + 2 + 1 + (1 if quant else 0) + 1
 
 
-def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, ep_chunks=None, ep_sm_reserve=20, ep_groups=None):
+def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, ep_chunks=None, ep_sm_reserve=20, ep_groups=None,
+                       ep_sorted=False):
     """Synthetic weights on the device (this rank's experts only when the experts
     are sharded) and the host-side inputs of one step."""
     import vllm_xpu_kernels.fused_moe_interface as fmi
@@ -197,7 +198,8 @@ def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, ep_chunks=None, ep_sm
     if ep_world > 1:
         from vllm_xpu_kernels.ep_moe import EpFusedMoe
         layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E,
-                           overlap_chunks=ep_chunks, sm_reserve=ep_sm_reserve, expert_groups=ep_groups)
+                           overlap_chunks=ep_chunks, sm_reserve=ep_sm_reserve, expert_groups=ep_groups,
+                           sorted_exchange=ep_sorted)
     else:
         layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
     x_cpu, logits_cpu, bias_cpu = wl.make_inputs(cfg, T, seed=ep_rank)
@@ -306,7 +308,7 @@ def run_ours(args):
     T = args.tokens
     ep_world = world if (args.parallelism == "ep" and world > 1) else 1
     layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev, ep_world, rank if ep_world > 1 else 0,
-                                                            args.ep_chunks, args.ep_sm_reserve, args.ep_groups)
+                                                            args.ep_chunks, args.ep_sm_reserve, args.ep_groups, args.ep_sorted)
     step, (tw, ids) = make_step(cfg, layer, dev, T)
     x, logits = x_cpu.to(dev), logits_cpu.to(dev)
     bias = bias_cpu.to(dev) if bias_cpu is not None else None
@@ -549,6 +551,9 @@ def main():
     ap.add_argument("--ep-groups", type=int, default=None,
                     help="expert parallelism: pipeline the two all-to-alls with the experts by splitting each "
                          "rank's experts into this many groups")
+    ap.add_argument("--ep-sorted", action="store_true",
+                    help="expert parallelism: ship rows sorted by expert so the receiver multiplies them as they "
+                         "arrive (prefill-sized batches)")
     ap.add_argument("--ep-chunks", type=int, default=None,
                     help="ep: token chunks whose exchange overlaps the experts (default: by batch size)")
     ap.add_argument("--ep-sm-reserve", type=int, default=20,

@@ -333,6 +333,13 @@ typedef struct {
                              0 = one per SM                                       */
   int group_size;         /* INT4 weights: K elements per scale (32, 64, 128 or 256);
                              ignored otherwise                                    */
+  int w_experts;          /* 0 or num_experts: one weight set per row segment.  Else
+                             (a divisor of num_experts) rows_per_expert has
+                             num_experts segments and segment s multiplies with weight
+                             set s % w_experts: the rows of an expert-parallel
+                             exchange as they arrive, grouped by source rank and by
+                             local expert inside a source, need no second
+                             permutation.  16-bit and block-scaled fp8 weights.     */
 } b200moe_gemm_args;
 
 int b200moe_grouped_gemm(const b200moe_gemm_args* args, b200moe_stream stream);

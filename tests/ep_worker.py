@@ -130,6 +130,17 @@ def gpu_worker(rank, world, port, T, cfg_name, dims, result_queue):
             grouped.apply(out3, x.to(dev), tw.to(dev), ids.to(dev))
         torch.cuda.synchronize()
         err = max(err, float((out3.cpu().float() - ref.float()).abs().max()))
+        # and the sorted exchange (rows arrive grouped by source and expert, no second permutation),
+        # unpipelined and pipelined by expert group
+        if cfg.recipe in ("bf16", "fp8block"):
+            for groups in (None, 2):
+                direct = EpFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]), cfg.K,
+                                    cfg.activation, E_local, expert_groups=groups, sorted_exchange=True)
+                out4 = torch.full_like(out, float("nan"))
+                for _ in range(2):
+                    direct.apply(out4, x.to(dev), tw.to(dev), ids.to(dev))
+                torch.cuda.synchronize()
+                err = max(err, float((out4.cpu().float() - ref.float()).abs().max()))
         result_queue.put((rank, err, scale))
     finally:
         dist.destroy_process_group()

@@ -54,9 +54,9 @@ def remap(hidden, scales, topk_ids, expert_map, total_experts, local_experts):
 
 
 def grouped_gemm(a, a_scale, w, w_scale, bias, rows, N, K, layout=0, epilogue=0, impl=0,
-                 out_dtype=torch.bfloat16, clamp=0.0, rows_out=None):
+                 out_dtype=torch.bfloat16, clamp=0.0, rows_out=None, weight_sets=None):
     M = a.shape[0] if rows_out is None else rows_out
-    E = rows.numel()
+    E = rows.numel() if weight_sets is None else weight_sets   # fewer weight sets than row segments
     n_out = N // 2 if epilogue else N
     d = torch.full((M, n_out), float("nan"), dtype=out_dtype, device=DEV)
     torch.ops._xpu_C.b200_grouped_gemm(a, a_scale, w, w_scale, bias, d, rows, N, K, E, layout,

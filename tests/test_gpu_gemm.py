@@ -244,3 +244,30 @@ def test_grouped_gemm_int4(native, E, M, N, K, group, dtype, has_bias, impl):
                        N, K, out_dtype=dtype, impl=impl)
     n = int(rows.sum())
     torch.testing.assert_close(out.cpu()[:n].float(), ref[:n].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("impl", [CHECK, TC])
+@pytest.mark.parametrize("recipe", ["bf16", "fp8"])
+@pytest.mark.parametrize("E,src,M,N,K", [(4, 3, 90, 256, 256), (3, 2, 1500, 384, 512), (8, 4, 40, 128, 384)])
+def test_grouped_gemm_row_segments_share_weight_sets(native, impl, recipe, E, src, M, N, K):
+    """rows_per_expert with src * E segments: segment s multiplies with weight set s % E - the rows
+    of an expert-parallel exchange in arrival order (source-major, expert-minor)."""
+    g = torch.Generator().manual_seed(E * M + N)
+    rows = random_rows(E * src, M, g)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    bias = (torch.randn(E, N, generator=g) * 0.1).to(torch.bfloat16)
+    if recipe == "bf16":
+        w = (torch.randn(E, N, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+        ref = to.grouped_gemm(x.float(), w.float().repeat(src, 1, 1), bias.repeat(src, 1), rows, torch.bfloat16)
+        out = grouped_gemm(x.to(DEV), None, w.to(DEV), None, bias.to(DEV), rows.to(DEV), N, K, layout=1, impl=impl,
+                           weight_sets=E)
+    else:
+        wq, ws = zip(*[to.quant_fp8_block_wei(torch.randn(N, K, generator=g) * K ** -0.5) for _ in range(E)])
+        wq, ws = torch.stack(wq), torch.stack(ws)
+        aq, a_s = to.per_token_group_fp8_quant(x, 128, 1e-10)
+        wdeq = torch.stack([to.dequant_fp8_block_wei(wq[e], ws[e]) for e in range(E)])
+        ref = to.grouped_gemm(to.dequant_fp8_block_act(aq, a_s), wdeq.repeat(src, 1, 1), bias.repeat(src, 1), rows,
+                              torch.bfloat16)
+        out = grouped_gemm(aq.to(DEV), a_s.to(DEV), wq.to(DEV), ws.to(DEV), bias.to(DEV), rows.to(DEV), N, K,
+                           layout=1, impl=impl, weight_sets=E)
+    _close(out, ref, rows, 2e-2)

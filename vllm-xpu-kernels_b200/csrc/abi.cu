@@ -32,4 +32,4 @@ extern "C" const char* b200moe_status_string(int status) {
   }
 }
 
-extern "C" int b200moe_abi_version(void) { return 4; }
+extern "C" int b200moe_abi_version(void) { return 5; }

@@ -74,6 +74,12 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
                          a->w_format == B200MOE_W_MXFP8_KN;
   B200_CHECK_ARG(!a_x2 || a->w_format == B200MOE_W_MXFP4_NK || w_tensor8,
                  "grouped_gemm: two-plane fp8 activations need MXFP4, MXFP8 or per-tensor fp8 weights");
+  const bool segmented = a->w_experts > 0 && a->w_experts != a->num_experts;
+  B200_CHECK_ARG(a->w_experts >= 0 && (!segmented || a->num_experts % a->w_experts == 0),
+                 "grouped_gemm: w_experts must divide num_experts");
+  B200_CHECK_ARG(!segmented || a->w_format == B200MOE_W_BF16_KN || a->w_format == B200MOE_W_BF16_NK ||
+                     a->w_format == B200MOE_W_FP8_BLOCK_NK || a->w_format == B200MOE_W_FP8_BLOCK_KN,
+                 "grouped_gemm: row segments that share weight sets need 16-bit or block-scaled fp8 weights");
   B200_CHECK_ARG(a->epilogue == B200MOE_EPI_NONE || a->n % 2 == 0,
                  "grouped_gemm: a gated epilogue needs an even N");
   if (a->m == 0 || a->n == 0) return B200MOE_OK;

@@ -25,6 +25,7 @@ struct CheckArgs {
   const void* bias; void* d; const int32_t* rows_per_expert;
   int64_t m; int n, k, num_experts;
   int fmt, epi; float alpha, limit, clamp_limit;
+  int w_experts;   // >0: segment s uses weight set s % w_experts
   int n_out;  // columns of D
   int group;  // INT4: K elements per scale
 };
@@ -101,7 +102,9 @@ gemm_check_kernel(CheckArgs g, bool a_fp8) {
       tile -= tiles;
       row0 += r;
     }
-    s_expert = found; s_row0 = row0; s_rows = rows < TM ? rows : TM;
+    // from here on the index only selects weights, scales and bias
+    s_expert = (found >= 0 && g.w_experts > 0) ? found % g.w_experts : found;
+    s_row0 = row0; s_rows = rows < TM ? rows : TM;
   }
   __syncthreads();
   const int e = s_expert;
@@ -244,6 +247,7 @@ int grouped_gemm_check(const b200moe_gemm_args* a, cudaStream_t st) {
   g.num_experts = a->num_experts; g.fmt = a->w_format; g.epi = a->epilogue;
   g.alpha = a->act_alpha; g.limit = a->act_limit; g.clamp_limit = a->clamp_limit;
   g.group = a->group_size > 0 ? a->group_size : 32;
+  g.w_experts = (a->w_experts > 0 && a->w_experts != a->num_experts) ? a->w_experts : 0;
   const bool gated = a->epilogue != B200MOE_EPI_NONE;
   g.n_out = gated ? a->n / 2 : a->n;
   const bool a_fp8 = a->a_dtype == B200MOE_FP8_E4M3;

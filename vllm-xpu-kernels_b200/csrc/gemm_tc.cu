@@ -64,6 +64,7 @@ struct TcParams {
   int32_t* status;
   int64_t m;
   int n, k, num_experts;
+  int w_experts;  // >0: segment s uses weight set s % w_experts
   int n_tiles;  // ceil(n / 128)
   int num_kb;   // K blocks of 128 bytes
   uint32_t idesc;
@@ -170,7 +171,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       TC_PROF_DECL(pw = 0, pt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
-        locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+        locate_tile<BT>(tile_start, row_start, t, cursor, ti, p.w_experts);
         const int n0 = ti.n_tile * kFeat;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           TC_PROF_T(w0);
@@ -207,7 +208,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       TC_PROF_DECL(mf = 0, ma = 0, mi = 0, mc = 0, mt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
-        locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+        locate_tile<BT>(tile_start, row_start, t, cursor, ti, p.w_experts);
         uint32_t a = acc_it % kAccStages;
         // A partly filled token tile multiplies only its valid columns (UMMA N in steps of 16).
         const uint32_t n_eff = (uint32_t)((ti.valid + 15) & ~15);
@@ -298,7 +299,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     TC_PROF_DECL(ew = 0, et0 = clock64());
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       TileInfo ti;
-      locate_tile<BT>(tile_start, row_start, t, cursor, ti);
+      locate_tile<BT>(tile_start, row_start, t, cursor, ti, p.w_experts);
       const int feat = ti.n_tile * kFeat + et;
       const bool feat_ok = feat < p.n;
       float bias_v = 0.f;
@@ -351,7 +352,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           } else if (t + (int)gridDim.x < total_tiles) {
             int cursor2 = cursor;
             TileInfo tn;
-            locate_tile<BT>(tile_start, row_start, t + gridDim.x, cursor2, tn);
+            locate_tile<BT>(tile_start, row_start, t + gridDim.x, cursor2, tn, p.w_experts);
             fetch_group(tn, 0, pre);
             pre_valid = true;
           }
@@ -472,6 +473,8 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   p.a_scale = reinterpret_cast<const float*>(a->a_scale); p.w_scale = reinterpret_cast<const float*>(a->w_scale);
   p.bias = a->bias; p.d = a->d; p.rows_per_expert = a->rows_per_expert; p.status = a->status;
   p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
+  const int w_sets = (a->w_experts > 0 && a->w_experts != a->num_experts) ? a->w_experts : a->num_experts;
+  p.w_experts = w_sets != a->num_experts ? w_sets : 0;
   p.n_tiles = (a->n + kFeat - 1) / kFeat;
   p.num_kb = (a->k + kpb - 1) / kpb;
   p.out_f16 = a->d_dtype == B200MOE_F16;
@@ -513,13 +516,13 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
     if (rc) return rc;
   }
   if (!kn) {
-    cuuint64_t dims[3] = {(cuuint64_t)a->k, (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
+    cuuint64_t dims[3] = {(cuuint64_t)a->k, (cuuint64_t)a->n, (cuuint64_t)w_sets};
     cuuint64_t strides[2] = {(cuuint64_t)a->k * es, (cuuint64_t)a->k * a->n * es};
     cuuint32_t box[3] = {(cuuint32_t)kpb, (cuuint32_t)kFeat, 1};
     int rc = encode_map(&tw, dt, 3, a->w, dims, strides, box);
     if (rc) return rc;
   } else {
-    cuuint64_t dims[3] = {(cuuint64_t)a->n, (cuuint64_t)a->k, (cuuint64_t)a->num_experts};
+    cuuint64_t dims[3] = {(cuuint64_t)a->n, (cuuint64_t)a->k, (cuuint64_t)w_sets};
     cuuint64_t strides[2] = {(cuuint64_t)a->n * es, (cuuint64_t)a->k * a->n * es};
     cuuint32_t box[3] = {(cuuint32_t)(a_fp8 ? 128 : 64), (cuuint32_t)kpb, 1};
     int rc = encode_map(&tw, dt, 3, a->w, dims, strides, box);

@@ -12,19 +12,22 @@ constexpr int kFeat = 128;          // features per tile (UMMA M)
 constexpr int kMaxExperts = 1024;
 
 struct TileInfo {
-  int e, n_tile, m_tile, row0, valid;
+  int e, n_tile, m_tile, row0, valid;   // e: index of the weights the tile multiplies with
 };
 
 // Tiles of one expert are numbered feature-tile-major with the token tiles
 // adjacent, so CTAs that run at the same time share a weight tile in L2.
+// With w_experts > 0 the row segments outnumber the weight sets: segment s multiplies with
+// weights s % w_experts (the segments are the (source rank, local expert) pairs of an
+// expert-parallel exchange, source-major).
 template <int BT>
 __device__ __forceinline__ void locate_tile(const int* tile_start, const int* row_start, int t,
-                                            int& cursor, TileInfo& ti) {
+                                            int& cursor, TileInfo& ti, int w_experts = 0) {
   while (t >= tile_start[cursor + 1]) ++cursor;
   const int local = t - tile_start[cursor];
   const int rows = row_start[cursor + 1] - row_start[cursor];
   const int m_tiles = (rows + BT - 1) / BT;
-  ti.e = cursor;
+  ti.e = w_experts > 0 ? cursor % w_experts : cursor;
   ti.n_tile = local / m_tiles;
   ti.m_tile = local - ti.n_tile * m_tiles;
   ti.row0 = row_start[cursor] + ti.m_tile * BT;

@@ -63,6 +63,7 @@ struct TParams {
   int32_t* status;
   int64_t m;
   int n, k, num_experts;
+  int w_experts;          // >0: segment s uses weight set s % w_experts
   int n_tiles, num_kb;
   uint32_t idesc;
   int out_f16;
@@ -129,7 +130,7 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
-        locate_tile<kTTok>(tile_start, row_start, t, cursor, ti);
+        locate_tile<kTTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
         const int n0 = ti.n_tile * kFeat;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
@@ -204,7 +205,7 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int n_groups = (p.num_kb + kTGroup - 1) / kTGroup;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       TileInfo ti;
-      locate_tile<kTTok>(tile_start, row_start, t, cursor, ti);
+      locate_tile<kTTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
       float acc[kTCols];
 #pragma unroll
       for (int i = 0; i < kTCols; ++i) acc[i] = 0.f;
@@ -220,7 +221,7 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
         } else if (t + (int)gridDim.x < total_tiles) {
           int cursor2 = cursor;
           TileInfo tn;
-          locate_tile<kTTok>(tile_start, row_start, t + gridDim.x, cursor2, tn);
+          locate_tile<kTTok>(tile_start, row_start, t + gridDim.x, cursor2, tn, p.w_experts);
           fetch_group(tn, 0, pre);
           pre_valid = true;
         }
@@ -362,7 +363,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
-        locate_tile<kTTok>(tile_start, row_start, t, cursor, ti);
+        locate_tile<kTTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
         const int n0 = ti.n_tile * 256;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
@@ -461,7 +462,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
     T_PROF_DECL(ew = 0, et0 = clock64());
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       TileInfo ti;
-      locate_tile<kTTok>(tile_start, row_start, t, cursor, ti);
+      locate_tile<kTTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
       float acc[128];
 #pragma unroll
       for (int i = 0; i < 128; ++i) acc[i] = 0.f;
@@ -475,7 +476,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
         } else if (t + (int)gridDim.x < total_tiles) {
           int cursor2 = cursor;
           TileInfo tn;
-          locate_tile<kTTok>(tile_start, row_start, t + gridDim.x, cursor2, tn);
+          locate_tile<kTTok>(tile_start, row_start, t + gridDim.x, cursor2, tn, p.w_experts);
           fetch_group(tn, 0, pre);
           pre_valid = true;
         }
@@ -596,6 +597,8 @@ int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
   p.w_scale = reinterpret_cast<const float*>(a->w_scale);
   p.bias = a->bias; p.d = a->d; p.rows_per_expert = a->rows_per_expert; p.status = a->status;
   p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
+  const int w_sets = (a->w_experts > 0 && a->w_experts != a->num_experts) ? a->w_experts : a->num_experts;
+  p.w_experts = w_sets != a->num_experts ? w_sets : 0;
   p.n_tiles = a->n / kFeat;
   p.num_kb = a->k / 128;
   p.out_f16 = a->d_dtype == B200MOE_F16;
@@ -611,13 +614,13 @@ int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
     if (rc) return rc;
   }
   if (!kn) {
-    cuuint64_t dims[3] = {(cuuint64_t)a->k, (cuuint64_t)a->n, (cuuint64_t)a->num_experts};
+    cuuint64_t dims[3] = {(cuuint64_t)a->k, (cuuint64_t)a->n, (cuuint64_t)w_sets};
     cuuint64_t strides[2] = {(cuuint64_t)a->k, (cuuint64_t)a->k * a->n};
     cuuint32_t box[3] = {128, (cuuint32_t)kFeat, 1};
     int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box);
     if (rc) return rc;
   } else {
-    cuuint64_t dims[3] = {(cuuint64_t)a->n, (cuuint64_t)a->k, (cuuint64_t)a->num_experts};
+    cuuint64_t dims[3] = {(cuuint64_t)a->n, (cuuint64_t)a->k, (cuuint64_t)w_sets};
     cuuint64_t strides[2] = {(cuuint64_t)a->n, (cuuint64_t)a->k * a->n};
     cuuint32_t box[3] = {128, 128, 1};
     int rc = encode_map(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box);

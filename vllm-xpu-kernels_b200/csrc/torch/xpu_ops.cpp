@@ -16,7 +16,7 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
                              const std::optional<at::Tensor>& ptr_bias, at::Tensor& ptr_D,
                              at::Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                              int64_t layout, int64_t epilogue, double alpha, double limit,
-                             double clamp_limit, int64_t impl, int64_t max_ctas) {
+                             double clamp_limit, int64_t impl, int64_t max_ctas, bool allow_segments) {
   check_cuda(ptr_A, "ptr_A");
   const auto A_dtype = ptr_A.scalar_type();
   const auto B_dtype = ptr_B.scalar_type();
@@ -68,8 +68,12 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   const int64_t D_total_M = ptr_D.size(0), D_N = ptr_D.size(1);
   const int64_t n_out = epilogue ? N / 2 : N;
   TORCH_CHECK(B_E == num_experts, "ptr_B.size(0) must match num_experts");
+  // Extended op only: rows_per_expert may hold a multiple of num_experts segments; segment s
+  // then multiplies with weight set s % num_experts (b200moe_gemm_args.w_experts).
+  const int64_t segments = rows_per_expert.numel();
   TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
-              rows_per_expert.numel() == num_experts, "rows_per_expert must be int32 [num_experts]");
+              (segments == num_experts || (allow_segments && segments > 0 && segments % num_experts == 0)),
+              "rows_per_expert must be int32 [num_experts]");
   TORCH_CHECK(A_total_M == D_total_M || ((is_B_mxfp4 || (is_weight_fp8 && !is_B_fp8_block)) && A_dtype == at::kFloat8_e4m3fn && A_total_M == 2 * D_total_M),
               "ptr_A.size(0) must match ptr_D.size(0)");
   TORCH_CHECK(A_K == B_K && B_K == K, "ptr_A K dimension must match ptr_B logical K dimension and K");
@@ -159,7 +163,8 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   g.d = ptr_D.data_ptr();
   g.d_dtype = ptr_D.scalar_type() == at::kBFloat16 ? B200MOE_BF16 : B200MOE_F16;
   g.rows_per_expert = rows_per_expert.data_ptr<int32_t>();
-  g.m = D_total_M; g.n = (int)N; g.k = (int)K; g.num_experts = (int)num_experts;
+  g.m = D_total_M; g.n = (int)N; g.k = (int)K; g.num_experts = (int)segments;
+  g.w_experts = segments != num_experts ? (int)num_experts : 0;
   g.epilogue = (b200moe_epilogue)epilogue;
   g.act_alpha = (float)alpha; g.act_limit = (float)limit; g.clamp_limit = (float)clamp_limit;
   g.status = nullptr;
@@ -178,7 +183,7 @@ at::Tensor cutlass_grouped_gemm_interface(at::Tensor ptr_A, const std::optional<
                                           int64_t num_experts) {
   // The reference accepts ptr_A_scale and ignores it for 16-bit activations.
   return grouped_gemm_impl(ptr_A, ptr_A_scale, ptr_B, ptr_B_scale, ptr_bias, ptr_D, rows_per_expert, N,
-                           K, num_experts, 0, 0, 1.702, 7.0, 0.0, 0, 0);
+                           K, num_experts, 0, 0, 1.702, 7.0, 0.0, 0, 0, false);
 }
 
 at::Tensor b200_grouped_gemm(at::Tensor ptr_A, const std::optional<at::Tensor>& ptr_A_scale,
@@ -188,7 +193,7 @@ at::Tensor b200_grouped_gemm(at::Tensor ptr_A, const std::optional<at::Tensor>& 
                              int64_t layout, int64_t epilogue, double alpha, double limit,
                              double clamp_limit, int64_t impl, int64_t max_ctas) {
   return grouped_gemm_impl(ptr_A, ptr_A_scale, ptr_B, ptr_B_scale, ptr_bias, ptr_D, rows_per_expert, N,
-                           K, num_experts, layout, epilogue, alpha, limit, clamp_limit, impl, max_ctas);
+                           K, num_experts, layout, epilogue, alpha, limit, clamp_limit, impl, max_ctas, true);
 }
 
 }  // namespace

@@ -129,7 +129,7 @@ class EpFusedMoe:
                  group: Optional[dist.ProcessGroup] = None,
                  gemm1_clamp_limit: Optional[float] = None,
                  overlap_chunks: Optional[int] = None, sm_reserve: int = 20,
-                 expert_groups: Optional[int] = None):
+                 expert_groups: Optional[int] = None, sorted_exchange: bool = False):
         from .fused_moe_interface import XpuFusedMoe
         self.a2a = EpAllToAll(group)
         self.ep_size, self.ep_rank = self.a2a.ep_size, self.a2a.ep_rank
@@ -154,6 +154,29 @@ class EpFusedMoe:
         # exchange group by group, so that the rows of group g+1 arrive and the results of group
         # g-1 leave while group g's experts compute.  Unlike token chunks this streams every
         # weight once: a group's GEMMs touch only that group's experts.
+        # Optional (`sorted_exchange`): the sender sorts its routed rows by (group, destination
+        # rank, expert) and ships the per-expert counts along, so the rows arrive grouped by source
+        # rank and by expert inside a source.  The grouped GEMMs take those segments as they are
+        # (segment s -> expert s % experts, `XpuFusedMoe.apply_sorted`): the receiver neither permutes
+        # the rows again nor un-permutes the result, and no expert ids travel.  Every source's
+        # segments walk the weights once more, which costs nothing while a segment has enough
+        # rows to be compute-bound: for prefill-sized batches.  Must be set alike on all ranks.
+        self.sorted_exchange = bool(sorted_exchange)
+        if self.sorted_exchange:
+            G = expert_groups if (expert_groups is not None and expert_groups > 1) else 1
+            while num_local_experts % G:
+                G -= 1
+            self.sorted_groups = G
+            eg = num_local_experts // G
+            e = torch.arange(self.num_experts_total, device=w13.device)
+            rank, le = e // num_local_experts, e % num_local_experts
+            # bucket order: group-major, then destination rank, then expert inside the group
+            self.sorted_bucket = ((le // eg) * (self.ep_size * eg) + rank * eg + le % eg).to(torch.int32)
+            sl = lambda t, g: t[g * eg:(g + 1) * eg] if t is not None else None
+            self.group_layers = [XpuFusedMoe(sl(w13, g), sl(w13_scales, g), sl(w13_bias, g), sl(w2, g),
+                                             sl(w2_scales, g), sl(w2_bias, g), 1, activation, eg,
+                                             gemm1_clamp_limit=gemm1_clamp_limit) for g in range(G)]
+            expert_groups = None
         self.expert_groups = None
         if expert_groups is not None and expert_groups > 1:
             self.expert_groups = min(expert_groups, num_local_experts)
@@ -167,6 +190,8 @@ class EpFusedMoe:
         return max(1, min(self.overlap_chunks, T))
 
     def apply(self, output, hidden_states, topk_weights, topk_ids):
+        if self.sorted_exchange:
+            return self._apply_sorted(output, hidden_states, topk_weights, topk_ids)
         if self.expert_groups is not None:
             return self._apply_grouped(output, hidden_states, topk_weights, topk_ids)
         nc = self._num_chunks(hidden_states.shape[0])
@@ -353,3 +378,65 @@ class EpFusedMoe:
             self.local.gemm_max_ctas = 0
         # 4. weighted top-k reduction on the source rank
         ops.moe_gather(output, back_all, topk_weights, send_pos, self.num_experts_total)
+
+    def _apply_sorted(self, output, hidden_states, topk_weights, topk_ids):
+        T, H = hidden_states.shape
+        K, ep, G, dev = self.topk, self.ep_size, self.sorted_groups, hidden_states.device
+        E_t = self.num_experts_total
+        eg = self.num_local_experts // G
+        M = T * K
+        ops = torch.ops._moe_C
+        # 1. one stable sort of the routed rows by (group, destination rank, expert)
+        counts = torch.empty((E_t,), dtype=torch.int32, device=dev)
+        send_pos = torch.empty((T, K), dtype=torch.int32, device=dev)
+        if self.quant:
+            send_rows = torch.empty((M, H), dtype=torch.float8_e4m3fn, device=dev)
+            send_scales = torch.empty((M, H // FP8_BLOCK), dtype=torch.float32, device=dev)
+            ops.b200_remap_quant_fp8(hidden_states, send_rows, send_scales, self.sorted_bucket, counts,
+                                     send_pos, topk_ids, E_t, E_t)
+        else:
+            send_rows = torch.empty((M, H), dtype=hidden_states.dtype, device=dev)
+            send_scales = None
+            ops.remap_hidden_states(hidden_states, None, send_rows, None, self.sorted_bucket, counts,
+                                    send_pos, topk_ids, E_t, E_t)
+        # 2. per-expert counts to their owners: [ep (peer), G, eg]; split sizes read back once
+        by_peer = counts.view(G, ep, eg).permute(1, 0, 2).contiguous()
+        recv_seg = torch.empty_like(by_peer)                       # [ep (source), G, eg]
+        dist.all_to_all_single(recv_seg, by_peer, group=self.a2a.group)
+        both = torch.stack((by_peer.sum(dim=2), recv_seg.sum(dim=2))).cpu()     # [2, ep, G]
+        send_spl = [both[0][:, g].tolist() for g in range(G)]
+        recv_spl = [both[1][:, g].tolist() for g in range(G)]
+        starts = [0]
+        for g in range(G):
+            starts.append(starts[-1] + int(sum(send_spl[g])))
+
+        def chunk(g):
+            a, b = starts[g], starts[g + 1]
+            return (send_rows[a:b], send_scales[a:b] if send_scales is not None else None)
+
+        # 3. dispatch(g+1) and combine(g-1) run beside the experts of group g
+        back_all = torch.empty((M, H), dtype=output.dtype, device=dev)
+        cap = max(1, self._sm_count - self.sm_reserve) if G > 1 else 0
+        inflight = [None] * G
+        inflight[0] = self.a2a.dispatch_async(chunk(0), send_spl[0], recv_spl[0])
+        works, keep = [], []
+        for g in range(G):
+            if g + 1 < G:
+                inflight[g + 1] = self.a2a.dispatch_async(chunk(g + 1), send_spl[g + 1], recv_spl[g + 1])
+            (recv_rows, recv_scales), ws = inflight[g]
+            for w in ws:
+                w.wait()
+            R = recv_rows.shape[0]
+            local_out = torch.empty((R, H), dtype=output.dtype, device=dev)
+            layer = self.group_layers[g]
+            layer.gemm_max_ctas = cap
+            layer.apply_sorted(local_out, recv_rows, recv_seg[:, g, :].reshape(-1),
+                               a1q_scale=recv_scales if self.quant else None)
+            _, work = self.a2a.combine_async(local_out, send_spl[g], recv_spl[g],
+                                             out=back_all[starts[g]:starts[g + 1]])
+            works.append(work)
+            keep.append((recv_rows, recv_scales, local_out))
+        for w in works:
+            w.wait()
+        # 4. weighted top-k reduction on the source rank
+        ops.moe_gather(output, back_all, topk_weights, send_pos, E_t)

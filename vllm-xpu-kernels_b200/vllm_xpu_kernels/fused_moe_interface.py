@@ -339,6 +339,36 @@ class XpuFusedMoe:
                 local_experts_num=self.local_experts_num)
 
         a_scale1 = remapped_scales if quant_acts else None
+        gemm2_output = torch.empty((num_moe_inputs, hidden_size), dtype=output.dtype, device=dev)
+        self._experts(gemm2_output, remapped, a_scale1, rows_per_expert)
+
+        torch.ops._moe_C.moe_gather(output, gemm2_output, topk_weights, row_map, E)
+
+    def apply_sorted(self, output_rows, rows, rows_per_segment, a1q_scale=None):
+        """The experts alone (gemm1 -> activation -> gemm2) on rows that are already grouped:
+        ``rows_per_segment`` (int32, a multiple of ``num_experts`` entries) gives consecutive row
+        segments, segment ``s`` belongs to expert ``s % num_experts``; ``output_rows[i]`` is the
+        result for ``rows[i]``.  No permutation and no top-k reduction happen here: this is what
+        an expert-parallel exchange needs for rows that arrive grouped by source rank and, inside
+        a source, by local expert.  16-bit weights, or block-scaled fp8 weights with fp8 ``rows``
+        and their 1x128 scales in ``a1q_scale``.  (Not in the reference.)"""
+        if self.is_block_fp8:
+            if rows.dtype != torch.float8_e4m3fn or a1q_scale is None:
+                raise ValueError("apply_sorted with block-scaled fp8 weights takes fp8 rows and a1q_scale")
+        elif self.is_fp8 or self.is_mxfp4 or self.is_mxfp8 or self.is_int4:
+            raise NotImplementedError("apply_sorted: 16-bit or block-scaled fp8 weights only")
+        if rows.shape[0] == 0:
+            return
+        self._experts(output_rows, rows, a1q_scale if self.is_block_fp8 else None, rows_per_segment)
+
+    def _experts(self, gemm2_output, remapped, a_scale1, rows_per_expert):
+        """gemm1 (+ activation) and gemm2 on permuted rows; writes gemm2_output [rows, hidden]."""
+        num_moe_inputs, hidden_size = remapped.shape
+        dev = remapped.device
+        E = self.num_experts
+        I = self.inter_size
+        quant_acts = self.is_block_fp8
+        output = gemm2_output
         if self.mx_acts:
             remapped, a_scale1 = self._quant_mx(remapped)
         clamp = float(self.gemm1_clamp_limit) if (self.gemm1_clamp_limit is not None
@@ -377,7 +407,6 @@ class XpuFusedMoe:
                 self.act_func(act_output, gemm1_output)
 
         # ---- gemm2 ----
-        gemm2_output = torch.empty((num_moe_inputs, hidden_size), dtype=output.dtype, device=dev)
         if quant_acts and act_output is None:
             pass   # already quantised together with the activation
         elif quant_acts:
@@ -390,8 +419,6 @@ class XpuFusedMoe:
             act_q, gemm2_act_scale, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_output,
             rows_per_expert, hidden_size, I * self.inter_size_scale, E, 0, _EPI_NONE, 1.702, 7.0, 0.0, 0,
             self.gemm_max_ctas)
-
-        torch.ops._moe_C.moe_gather(output, gemm2_output, topk_weights, row_map, E)
 
 
 def xpu_fused_moe(hidden_states,
