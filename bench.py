@@ -162,7 +162,7 @@ def launches_per_step(M: int, quant: bool) -> int:
 
 
 def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, ep_chunks=None, ep_sm_reserve=20, ep_groups=None,
-                       ep_sorted=False):
+                       ep_sorted=False, ep_per_rank=True):
     """Synthetic weights on the device (this rank's experts only when the experts
     are sharded) and the host-side inputs of one step."""
     import vllm_xpu_kernels.fused_moe_interface as fmi
@@ -199,7 +199,7 @@ def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, ep_chunks=None, ep_sm
         from vllm_xpu_kernels.ep_moe import EpFusedMoe
         layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E,
                            overlap_chunks=ep_chunks, sm_reserve=ep_sm_reserve, expert_groups=ep_groups,
-                           sorted_exchange=ep_sorted)
+                           sorted_exchange=ep_sorted, per_rank_rows=ep_per_rank)
     else:
         layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
     x_cpu, logits_cpu, bias_cpu = wl.make_inputs(cfg, T, seed=ep_rank)
@@ -308,7 +308,9 @@ def run_ours(args):
     T = args.tokens
     ep_world = world if (args.parallelism == "ep" and world > 1) else 1
     layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev, ep_world, rank if ep_world > 1 else 0,
-                                                            args.ep_chunks, args.ep_sm_reserve, args.ep_groups, args.ep_sorted)
+                                                            args.ep_chunks, args.ep_sm_reserve, args.ep_groups, args.ep_sorted,
+                                                            # one row per (token, rank) pays off once the rows, not the launches, cost
+                                                            not args.ep_per_expert_rows and T > 256)
     step, (tw, ids) = make_step(cfg, layer, dev, T)
     x, logits = x_cpu.to(dev), logits_cpu.to(dev)
     bias = bias_cpu.to(dev) if bias_cpu is not None else None
@@ -551,6 +553,8 @@ def main():
     ap.add_argument("--ep-groups", type=int, default=None,
                     help="expert parallelism: pipeline the two all-to-alls with the experts by splitting each "
                          "rank's experts into this many groups")
+    ap.add_argument("--ep-per-expert-rows", action="store_true",
+                    help="expert parallelism: ship one row per (token, expert) instead of one per (token, rank)")
     ap.add_argument("--ep-sorted", action="store_true",
                     help="expert parallelism: ship rows sorted by expert so the receiver multiplies them as they "
                          "arrive (prefill-sized batches)")

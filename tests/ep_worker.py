@@ -87,6 +87,33 @@ def cpu_worker(rank, world, port, T, result_queue):
             start += n
         out_g = to.moe_gather(back_all, tw, g_pos, x.dtype)
         err = max(err, float((out_g.float() - ref.float()).abs().max()))
+
+        # the default schedule: one row per (token, destination rank) with the token's local expert
+        # ids and weights, top-k layer on the owner, one partial sum per (token, rank) back
+        K = ids.shape[1]
+        dest = ids.long() // E_local
+        hit = dest.unsqueeze(1) == torch.arange(world).view(1, world, 1)            # [T, ep, K]
+        rank_ids = torch.where(hit.any(dim=2), torch.arange(world).view(1, world), -1).int()
+        loc_ids = torch.where(hit, (ids.long() % E_local).unsqueeze(1), -1).int()
+        loc_w = torch.where(hit, tw.unsqueeze(1), 0.0).float()
+        p_rows, _, p_counts, p_pos = to.remap_hidden_states(x, None, rank_ids, None, world)
+        Tn = x.shape[0]
+        pos = p_pos.reshape(-1).long()
+        pos = torch.where(pos >= 0, pos, Tn * world)
+        s_ids = torch.empty(Tn * world + 1, K, dtype=torch.int32)
+        s_w = torch.empty(Tn * world + 1, K)
+        s_ids.index_copy_(0, pos, loc_ids.reshape(-1, K))
+        s_w.index_copy_(0, pos, loc_w.reshape(-1, K))
+        ps, pr = a2a.exchange_counts(p_counts)
+        n = sum(ps)
+        assert n <= M and n == int((rank_ids >= 0).sum())
+        r_rows, _, r_ids, r_w = a2a.dispatch((p_rows[:n], None, s_ids[:n], s_w[:n]), ps, pr)
+        part = to.fused_moe_staged(r_rows, d13[lo:lo + E_local], None, d2[lo:lo + E_local], None, r_w, r_ids,
+                                   E_local) if r_rows.shape[0] else r_rows
+        back = a2a.combine(part, ps, pr)
+        out_p = to.moe_gather(back, torch.ones(Tn, world), p_pos, x.dtype)
+        # every partial sum is rounded to 16 bits before the last addition
+        err = max(err, float((out_p.float() - ref.float()).abs().max()))
         result_queue.put((rank, err, s_spl, r_spl))
     finally:
         dist.destroy_process_group()
@@ -116,6 +143,13 @@ def gpu_worker(rank, world, port, T, cfg_name, dims, result_queue):
         ref = _oracle_full(cfg, w, x, tw, ids)
         err = float((out.cpu().float() - ref.float()).abs().max())
         scale = float(ref.float().abs().max())
+        # one row per (token, expert) instead of per (token, rank): the plain schedule
+        plain = EpFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]), cfg.K,
+                           cfg.activation, E_local, per_rank_rows=False)
+        out1 = torch.empty_like(out)
+        plain.apply(out1, x.to(dev), tw.to(dev), ids.to(dev))
+        torch.cuda.synchronize()
+        err = max(err, float((out1.cpu().float() - ref.float()).abs().max()))
         # the chunked, overlapped schedule computes the same rows
         layer.overlap_chunks = 3
         out2 = torch.empty_like(out)

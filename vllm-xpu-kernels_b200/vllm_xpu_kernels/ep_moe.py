@@ -129,7 +129,8 @@ class EpFusedMoe:
                  group: Optional[dist.ProcessGroup] = None,
                  gemm1_clamp_limit: Optional[float] = None,
                  overlap_chunks: Optional[int] = None, sm_reserve: int = 20,
-                 expert_groups: Optional[int] = None, sorted_exchange: bool = False):
+                 expert_groups: Optional[int] = None, sorted_exchange: bool = False,
+                 per_rank_rows: bool = True):
         from .fused_moe_interface import XpuFusedMoe
         self.a2a = EpAllToAll(group)
         self.ep_size, self.ep_rank = self.a2a.ep_size, self.a2a.ep_rank
@@ -141,6 +142,20 @@ class EpFusedMoe:
                                  num_local_experts, gemm1_clamp_limit=gemm1_clamp_limit)
         self.owner = owner_map(self.num_experts_total, self.ep_size, w13.device)
         self.quant = self.local.is_block_fp8
+        # Default schedule (`per_rank_rows`): a token's row travels once to every rank that owns
+        # at least one of its experts, with the token's local expert ids and routing weights; the
+        # owner runs its experts as a top-k layer on the received tokens (slots of other ranks
+        # are id -1 and skipped) and returns one partial sum per (token, rank), which the source
+        # adds up.  Against one row per (token, expert) this divides both exchanges by the mean
+        # number of experts a token has on one rank (DeepSeek-V3 routing: 4 at 2 ranks, 2 at 8).
+        # Each partial sum is rounded to the output type before the final addition, as in the
+        # reference's own scheme (partial outputs all-reduced by the caller).
+        self.per_rank_rows = bool(per_rank_rows) and not sorted_exchange and not (
+            expert_groups is not None and expert_groups > 1) and overlap_chunks is None
+        if self.per_rank_rows:
+            self.local_topk = XpuFusedMoe(w13, w13_scales, w13_bias, w2, w2_scales, w2_bias,
+                                          n_experts_per_token, activation, num_local_experts,
+                                          gemm1_clamp_limit=gemm1_clamp_limit)
         # Optional: cut the batch into `overlap_chunks` token chunks so that the
         # exchange of one chunk runs beside the experts of another (the persistent
         # GEMM kernels then leave `sm_reserve` SMs to the collective's kernels).
@@ -194,6 +209,8 @@ class EpFusedMoe:
             return self._apply_sorted(output, hidden_states, topk_weights, topk_ids)
         if self.expert_groups is not None:
             return self._apply_grouped(output, hidden_states, topk_weights, topk_ids)
+        if self.per_rank_rows and self._num_chunks(hidden_states.shape[0]) == 1:
+            return self._apply_per_rank(output, hidden_states, topk_weights, topk_ids)
         nc = self._num_chunks(hidden_states.shape[0])
         if nc > 1:
             return self._apply_chunked(output, hidden_states, topk_weights, topk_ids, nc)
@@ -440,3 +457,59 @@ class EpFusedMoe:
             w.wait()
         # 4. weighted top-k reduction on the source rank
         ops.moe_gather(output, back_all, topk_weights, send_pos, E_t)
+
+    def _apply_per_rank(self, output, hidden_states, topk_weights, topk_ids):
+        T, H = hidden_states.shape
+        K, ep, dev = self.topk, self.ep_size, hidden_states.device
+        E_l = self.num_local_experts
+        ops = torch.ops._moe_C
+        cap = T * ep                                                   # slots (token, rank)
+
+        # 1. which ranks a token needs, and what each of them has to know about it
+        ids = topk_ids.to(torch.int64)
+        dest = ids // E_l                                              # [T, K]
+        ranks = torch.arange(ep, device=dev)
+        hit = dest.unsqueeze(1) == ranks.view(1, ep, 1)                # [T, ep, K]
+        rank_ids = torch.where(hit.any(dim=2), ranks.view(1, ep), -1).to(torch.int32).contiguous()
+        loc_ids = torch.where(hit, (ids % E_l).unsqueeze(1), -1).to(torch.int32)
+        loc_w = torch.where(hit, topk_weights.unsqueeze(1), 0.0).to(torch.float32)
+
+        # 2. token rows grouped by destination rank (stable), quantised on the way for fp8 experts;
+        #    slots of ranks a token does not need carry id -1 and are dropped
+        send_counts = torch.empty((ep,), dtype=torch.int32, device=dev)
+        send_pos = torch.empty((T, ep), dtype=torch.int32, device=dev)
+        if self.quant:
+            send_rows = torch.empty((cap, H), dtype=torch.float8_e4m3fn, device=dev)
+            send_scales = torch.empty((cap, H // FP8_BLOCK), dtype=torch.float32, device=dev)
+            ops.b200_remap_quant_fp8(hidden_states, send_rows, send_scales, None, send_counts, send_pos,
+                                     rank_ids, ep, ep)
+        else:
+            send_rows = torch.empty((cap, H), dtype=hidden_states.dtype, device=dev)
+            send_scales = None
+            ops.remap_hidden_states(hidden_states, None, send_rows, None, None, send_counts, send_pos,
+                                    rank_ids, ep, ep)
+        pos = send_pos.reshape(-1).long()
+        pos = torch.where(pos >= 0, pos, cap)                          # dropped slots -> spare row
+        send_ids = torch.empty((cap + 1, K), dtype=torch.int32, device=dev)
+        send_w = torch.empty((cap + 1, K), dtype=torch.float32, device=dev)
+        send_ids.index_copy_(0, pos, loc_ids.reshape(cap, K))
+        send_w.index_copy_(0, pos, loc_w.reshape(cap, K))
+
+        # 3. exchange
+        send_splits, recv_splits = self.a2a.exchange_counts(send_counts)
+        n = int(sum(send_splits))
+        recv_rows, recv_scales, recv_ids, recv_w = self.a2a.dispatch(
+            (send_rows[:n], send_scales[:n] if send_scales is not None else None, send_ids[:n], send_w[:n]),
+            send_splits, recv_splits)
+
+        # 4. this rank's experts on the received tokens: top-k layer, foreign slots skipped
+        R = recv_rows.shape[0]
+        local_out = torch.empty((R, H), dtype=output.dtype, device=dev)
+        if R > 0:
+            self.local_topk.apply(local_out, recv_rows, recv_w, recv_ids,
+                                  a1q_scale=recv_scales if self.quant else None)
+
+        # 5. partial sums travel back; the source adds the (at most ep) partial sums of a token
+        back = self.a2a.combine(local_out, send_splits, recv_splits)
+        ones = torch.ones((T, ep), dtype=torch.float32, device=dev)
+        ops.moe_gather(output, back, ones, send_pos, ep)
