@@ -1,7 +1,7 @@
 """Generates the golden vectors in this folder from the reference's own
 pure-torch test references, run on CPU.
 
-Usage:  python tests/golden/make_golden.py [/path/to/vllm-xpu-kernels]
+Usage:  python tests/golden/make_golden.py /path/to/vllm-xpu-kernels
 
 The reference's test helpers import its compiled extensions at module level;
 those imports are satisfied here with empty stand-in modules, which is enough
@@ -137,7 +137,9 @@ def capture_batched_align(align_t, max_tokens, num_experts, block, empty):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/vllm-xpu-kernels")
+    root = sys.argv[1]
     ref = load_reference(root)
     g = torch.Generator().manual_seed(0)
 
