@@ -77,6 +77,40 @@ def test_layer_mxfp8_reference_vectors_and_oracle(native):
             torch.testing.assert_close(o.float(), ref.float(), rtol=2e-2, atol=2e-2 * top)
 
 
+@pytest.mark.parametrize("name,dims", [("cfg2_mixtral_bf16", dict(H=512, I=256, E=4)),
+                                       ("cfg4_deepseek_fp8", dict(H=512, I=256, E=8))])
+@pytest.mark.parametrize("src,rows_per_seg", [(3, 5), (2, 70)])
+def test_layer_apply_sorted_segments(native, name, dims, src, rows_per_seg):
+    """apply_sorted: rows already grouped into src * E segments (source-major, expert-minor, the
+    arrival order of an expert-parallel exchange); every row gets its expert's MLP, no
+    permutation, no reduction.  Against the oracle run as a top-1 layer with unit weights."""
+    cfg = wl.scaled(wl.CONFIGS[name], **dims)
+    E = cfg.E
+    w = wl.make_weights(cfg, seed=3)
+    g = torch.Generator().manual_seed(src * 100 + rows_per_seg)
+    seg = torch.randint(0, 2 * rows_per_seg, (src * E,), generator=g, dtype=torch.int32)
+    seg[1] = 0                                                   # an empty segment
+    M = int(seg.sum())
+    x = (torch.randn(M, cfg.H, generator=g) / 2).to(torch.bfloat16)
+    ids = torch.repeat_interleave(torch.arange(src * E) % E, seg.long()).view(M, 1).int()
+    d13, d2 = wl.dequant_weights(cfg, w)
+    quant = cfg.recipe == "fp8block"
+    ref = to.fused_moe_staged(x, d13, w["w13_bias"], d2, w["w2_bias"], torch.ones(M, 1), ids, E,
+                              activation=cfg.activation, act_quant=quant)
+    w13, s13, w2, s2 = wl.to_op_layout(cfg, w)
+    mv = lambda t: t.to(DEV) if t is not None else None
+    layer = native.XpuFusedMoe(mv(w13), mv(s13), mv(w["w13_bias"]), mv(w2), mv(s2), mv(w["w2_bias"]), 1,
+                               cfg.activation, E)
+    out = torch.full((M, cfg.H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    if quant:
+        q, sc = to.per_token_group_fp8_quant(x, 128, 1e-10)
+        layer.apply_sorted(out, q.to(DEV), seg.to(DEV), a1q_scale=sc.to(DEV))
+    else:
+        layer.apply_sorted(out, x.to(DEV), seg.to(DEV))
+    tol = TOL[cfg.recipe]
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=tol, atol=tol)
+
+
 SMALL = [
     ("cfg1_small_bf16", dict(H=2048, I=1408, E=8), 64),     # the CPU-runnable config at full size
     ("cfg2_mixtral_bf16", dict(H=512, I=1792, E=8), 33),
