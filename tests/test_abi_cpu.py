@@ -83,3 +83,59 @@ def test_no_cpu_kernel_is_registered(native):
     out = torch.empty(2, 4)
     with pytest.raises((NotImplementedError, RuntimeError)):
         torch.ops._C.silu_and_mul(out, torch.randn(2, 8))
+
+
+def _ref_prologue_layout(num_rows, topk, experts, hidden, block_k, elem, scale):
+    """The workspace arithmetic of the reference's own test
+    (tests/fused_moe/test_moe_prologue.py:42-49, 166-212 of vllm-xpu-kernels)."""
+    def tokens_per_block(n, e):
+        for t in (32, 64, 128, 256, 512, 1024):
+            if (n + t - 1) // t * e <= t:
+                return t
+        return 1024
+    n = num_rows * topk
+    blocks = (num_rows + tokens_per_block(num_rows, experts) - 1) // tokens_per_block(num_rows, experts)
+    sizes = [n * 4, n * 4, n * 4, experts * blocks * 4, experts * blocks * 4, experts * num_rows * 4,
+             (experts + 1) * 8, n * 4, n * hidden * elem, (n * hidden // block_k) * scale]
+    off, out = 0, []
+    for sz in sizes:
+        out.append(off)
+        off += (sz + 255) // 256 * 256
+    return out, off
+
+
+@pytest.mark.parametrize("num_rows,topk,experts,hidden,block_k,elem,scale",
+                         [(1, 1, 16, 8192, 1, 2, 0), (16, 2, 16, 8192, 128, 1, 4), (8192, 2, 16, 8192, 32, 1, 1),
+                          (300, 8, 256, 7168, 128, 1, 4), (4, 1, 2, 4096, 16, 1, 1), (100000, 8, 32, 2880, 32, 1, 1)])
+def test_prologue_workspace_layout_matches_the_reference(lib, num_rows, topk, experts, hidden, block_k, elem, scale):
+    """The packed workspace of fused_moe_prologue: same ten offsets and total as the reference's test
+    computes, from the C ABI (a host-only call) and from the C oracle."""
+    from oracle import c_oracle as co
+    want_off, want_total = _ref_prologue_layout(num_rows, topk, experts, hidden, block_k, elem, scale)
+    off = (ctypes.c_size_t * 10)()
+    total = ctypes.c_size_t()
+    rc = lib.b200moe_fused_moe_prologue_layout(ctypes.c_int64(num_rows), topk, experts, ctypes.c_int64(hidden),
+                                                block_k, elem, scale, off, ctypes.byref(total))
+    assert rc == 0 and list(off) == want_off and total.value == want_total
+    layout, ototal = co.prologue_layout(num_rows, topk, experts, hidden, block_k, elem, scale)
+    assert [layout[k] for k in co.PROLOGUE_REGIONS] == want_off and ototal == want_total
+    lib.b200moe_fused_moe_prologue_scratch_bytes.restype = ctypes.c_size_t
+    lib.b200moe_sort_workspace_bytes.restype = ctypes.c_size_t
+    need = lib.b200moe_fused_moe_prologue_scratch_bytes(ctypes.c_int64(num_rows), topk, experts)
+    assert need >= (num_rows * topk + experts) * 4 + lib.b200moe_sort_workspace_bytes(ctypes.c_int64(num_rows * topk), experts)
+
+
+def test_expert_parallel_bucket_maps():
+    """Bucket maps of the expert-parallel schedules: owner (contiguous even split, as
+    csrc/moe/init_expert_map.cpp:45-52 of the reference encodes it) and (group, rank)."""
+    import sys
+    sys.path.insert(0, str(PKG_DIR))
+    from vllm_xpu_kernels.ep_moe import group_bucket_map, owner_map
+    assert owner_map(256, 8, "cpu").tolist() == [e // 32 for e in range(256)]
+    for E_t, ep, G in [(256, 8, 4), (16, 2, 3), (12, 4, 3), (8, 2, 1)]:
+        b = group_bucket_map(E_t, ep, G, "cpu").tolist()
+        E_l = E_t // ep
+        assert b == [(e % E_l) * G // E_l * ep + e // E_l for e in range(E_t)]
+        assert sorted(set(b)) == list(range(G * ep))            # every (group, rank) bucket is used
+        for e in range(E_t):                                     # the rank inside a bucket is the owner
+            assert b[e] % ep == e // E_l
