@@ -37,7 +37,8 @@ import torch  # noqa: E402
 # dram__bytes_read.sum + dram__bytes_write.sum of the two grouped-GEMM launches of one
 # step, from one ncu capture per workload (see the summaries under profiles/).
 NCU_TRAFFIC_BYTES = {("cfg2_mixtral_bf16", 4096): 3.956e9,
-                     ("cfg3_qwen3_fp8", 4096): 0.884e9}   # profiles/grouped_gemm_fp8t256_cfg3_T4096.md
+                     ("cfg3_qwen3_fp8", 4096): 0.884e9,   # profiles/grouped_gemm_fp8t256_cfg3_T4096.md
+                     ("cfg5_gptoss_mxfp4", 2048): 1.883e9}   # profiles/grouped_gemm_mx_mxfp4_cfg5_T2048.md
 
 
 def _gemm_kernel_name(cfg, T):
