@@ -271,3 +271,23 @@ def test_grouped_gemm_row_segments_share_weight_sets(native, impl, recipe, E, sr
         out = grouped_gemm(aq.to(DEV), a_s.to(DEV), wq.to(DEV), ws.to(DEV), bias.to(DEV), rows.to(DEV), N, K,
                            layout=1, impl=impl, weight_sets=E)
     _close(out, ref, rows, 2e-2)
+
+
+def test_fp8_token_major_kernel_against_checking_kernel_at_deepseek_shape(native):
+    """Full-size K and N of the DeepSeek-V3 w13 GEMM (K=7168, N=4096), ragged segments from empty
+    to several tiles: the token-major tensor-core kernel and the plain-CUDA checking kernel see
+    the same fp8 operands and scales, so only the fp32 summation order differs."""
+    E, N, K = 6, 4096, 7168
+    g = torch.Generator(device=DEV).manual_seed(11)
+    rows = torch.tensor([700, 0, 129, 1, 300, 128], dtype=torch.int32)
+    M = int(rows.sum())
+    a = (torch.randn(M, K, generator=g, device=DEV)).to(torch.float8_e4m3fn)
+    a_s = torch.rand(M, K // 128, generator=g, device=DEV) * 0.02 + 0.005
+    w = (torch.randn(E, N, K, generator=g, device=DEV)).to(torch.float8_e4m3fn)
+    w_s = torch.rand(E, N // 128, K // 128, generator=g, device=DEV) * 0.02 + 0.005
+    bias = (torch.randn(E, N, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    tc = grouped_gemm(a, a_s, w, w_s, bias, rows.to(DEV), N, K, layout=1, impl=TC)
+    chk = grouped_gemm(a, a_s, w, w_s, bias, rows.to(DEV), N, K, layout=1, impl=CHECK)
+    top = float(chk.float().abs().max())
+    assert torch.isfinite(tc.float()).all() and top > 0
+    assert float((tc.float() - chk.float()).abs().max()) <= 2 ** -7 * top
