@@ -57,3 +57,11 @@ def test_lora_align_guards_map_dtypes(native):
         torch.ops._moe_C.moe_lora_align_block_size(ids, z, 8, 0, 1, 16, 4, z, z, z, z, z, None)
     with pytest.raises(RuntimeError, match="padded_num_experts must be less than 1024"):
         torch.ops._moe_C.moe_lora_align_block_size(ids, z, 1000, 4, 1, 16, 4, z, z, z, z, z, None)
+
+
+def test_lora_align_only_base_model_tokens(native):
+    """Every token belongs to the base model (-1): lora_ids holds only -1 and no segment is written."""
+    c = make_case(32, 4, 16, 2, 8, base_frac=1.1)
+    assert (c["token_lora_mapping"] == -1).all() and (c["lora_ids"] == -1).all()
+    s, e, p = _both(c)
+    check_properties(c, s, e, p)

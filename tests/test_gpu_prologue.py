@@ -75,3 +75,23 @@ def test_prologue_duplicates_and_errors(native):
         torch.ops._moe_C.fused_moe_prologue(x.to(DEV), None, ids.to(DEV), w.to(DEV), small, 16, 64, 1, 0, 1, 16)
     with pytest.raises(RuntimeError, match="int64"):
         torch.ops._moe_C.fused_moe_prologue(x.to(DEV), None, ids.int().to(DEV), w.to(DEV), small, 16, 64, 1, 0, 1, 16)
+
+
+def test_prologue_empty_and_nothing_local(native):
+    """No rows at all, and rows whose experts all live on another rank: offsets are zero, nothing
+    else is written."""
+    x = torch.zeros(0, 64, dtype=torch.bfloat16)
+    c = dict(hidden_states=x, scales=None, topk=2, num_experts=4, block_k=1,
+             topk_ids=torch.zeros(0, 2, dtype=torch.int64), topk_weights=torch.zeros(0, 2))
+    ws, layout, total = _run_gpu(c, fill=0xEE)
+    r = regions(c, ws, layout)
+    assert r["first"].tolist() == [0] * 5
+    ids = torch.tensor([[0, 1], [2, 3], [1, 0]])
+    x = torch.randn(3, 64).bfloat16()
+    c = dict(hidden_states=x, scales=None, topk=2, num_experts=4, block_k=1, topk_ids=ids,
+             topk_weights=torch.rand(3, 2))
+    ws, layout, total = _run_gpu(c, ep_rank=1, ep_size=2, fill=0xEE)     # rank 1 owns experts 4..7
+    ref = torch.full((total,), 0xEE, dtype=torch.uint8)
+    co.fused_moe_prologue(x, None, ids, c["topk_weights"], ref, 64, 1, 1, 4)
+    assert torch.equal(ws, ref)
+    assert regions(c, ws, layout)["first"].tolist() == [0] * 5
