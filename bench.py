@@ -1,22 +1,24 @@
 #!/usr/bin/env python
-"""Benchmark of the fused-MoE layer (routing + XpuFusedMoe.apply) on B200.
+"""Benchmark of the fused-MoE layer (routing + the layer's apply) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload cfg2_mixtral_bf16] [--tokens T]
+                    [--workload cfg4_deepseek_fp8] [--tokens T] [--sweep]
 
-A step is one pass of the layer over one batch of T synthetic tokens: top-k
-routing followed by the eight stages of ``XpuFusedMoe.apply``.  The default
-workload is the Mixtral-8x7B-shaped bf16 layer at T=4096 tokens per GPU.  With
-N > 1 (launched under torch.distributed.run) every rank runs its own replica on
-its own tokens; no collective is on the data path, so scaling is weak.
+A step is one pass of the layer over one batch of T synthetic tokens per GPU: top-k routing
+followed by the stages of the layer.  The default workload is the DeepSeek-V3-shaped
+block-fp8 layer (H=7168, I=2048, 256 experts, grouped sigmoid top-8) at 8192 tokens per GPU,
+the configuration the 1/2/4/8-GPU metric is quoted on.  With N > 1 (launched under
+torch.distributed.run) the experts are sharded evenly over the ranks and tokens are dispatched
+to their experts' ranks and combined back over NVLink peer memory (``--parallelism ep``, the
+default at N > 1); ``--parallelism replicas`` runs N independent copies instead.
 
-Rank 0 prints one JSON line: whole-job tokens/s with inputs resident in HBM
-(``value``), the same metric through the public API with host buffers and the
-copies inside the timed region (``e2e``), the roofline of the grouped GEMM
-kernel measured live with CUDA events, SM clocks sampled during the timed
-region, and - at N=1 - the CPU oracle timed on a bounded sample of the same
-workload.  ``--impl reference`` times that CPU path alone, with all host
-threads.
+Rank 0 prints one JSON line: whole-job tokens/s with inputs resident in HBM (``value``), the
+same metric through the public API with host buffers and the copies inside the timed region
+(``e2e``), the roofline of the grouped GEMM kernel measured live with CUDA events, per-stage
+times, SM clocks sampled during the timed region, and - at N=1 - the CPU restatement of the
+reference's torch path timed on a bounded sample of the same workload.  ``--impl reference``
+times that CPU path alone, with all host threads.  ``--sweep`` (one GPU) prints one such line
+for every (workload, T) point of the five benchmark layers.
 """
 from __future__ import annotations
 
@@ -34,31 +36,59 @@ sys.path.insert(0, str(ROOT / "vllm-xpu-kernels_b200"))
 
 import torch  # noqa: E402
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the two grouped-GEMM launches of one
-# step, from one ncu capture per workload (see the summaries under profiles/).
-NCU_TRAFFIC_BYTES = {("cfg2_mixtral_bf16", 4096): 3.956e9,
-                     ("cfg3_qwen3_fp8", 4096): 0.884e9,   # profiles/grouped_gemm_fp8t256_cfg3_T4096.md
-                     ("cfg5_gptoss_mxfp4", 2048): 1.883e9}   # profiles/grouped_gemm_mx_mxfp4_cfg5_T2048.md
+import bench_workloads as bw  # noqa: E402
 
-
-def _gemm_kernel_name(cfg, T):
-    """The kernel b200moe_grouped_gemm picks for the 16-bit / block-fp8 recipes: fp8 segments of
-    12 rows per expert or more on average run the token-major kernel."""
-    if cfg.recipe == "fp8block" and (T * cfg.K + cfg.E - 1) // cfg.E >= 12:
-        return "grouped_gemm_fp8t256_kernel"
-    return "grouped_gemm_tc_kernel"
+# dram__bytes_read.sum + dram__bytes_write.sum of the two grouped-GEMM launches of one step, from
+# one ncu capture per workload on a smaller case of the same kernel, scaled by the rows processed.
+# Not measured in the run: the line says "from capture".
+CAPTURED_TRAFFIC_BYTES = {("cfg2_mixtral_bf16", 4096): 3.956e9,
+                          ("cfg3_qwen3_fp8", 4096): 0.884e9,
+                          ("cfg5_gptoss_mxfp4", 2048): 1.883e9}
 
 METRIC = "fused_moe_layer_tokens_per_s"
 UNIT = "tokens/s"
+
+
+def _gemm_kernel_name(cfg, rows_per_expert_avg, mx):
+    if cfg.recipe == "mxfp4":
+        return "grouped_gemm_mx_kernel" if mx else "grouped_gemm_dq_kernel"
+    if cfg.recipe == "fp8block" and rows_per_expert_avg >= 12:
+        return "grouped_gemm_fp8t256_kernel"
+    return "grouped_gemm_tc_kernel"
 
 
 def _peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return dict(hbm=float(d["hbm_gbs"]), tensor=float(d["bf16_tflops_sustained"]),
-                    tensor_burst=float(d["bf16_tflops"]), source="measured")
-    return dict(hbm=6650.0, tensor=1400.0, tensor_burst=1590.0, source="fallback")
+        return dict(hbm=float(d["hbm_gbs"]), tensor=float(d["bf16_tflops"]),
+                    tensor_sustained=float(d["bf16_tflops_sustained"]), source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+def measure_fp8_dense_tflops(dev):
+    """Dense e4m3 x e4m3 GEMM rate of this GPU, as a yardstick for the fp8 kernels: the library
+    GEMM (torch._scaled_mm, 8192^3, unit scales), best of 5 after warm-up.  None if unavailable."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        f = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -121,24 +151,33 @@ def _physical_gpu_index(local_rank: int) -> int:
 
 # ----------------------------------------------------------------------------- CPU arm
 def cpu_layer_tokens_per_s(cfg, seconds_budget: float, steps: int, warmup: int):
-    """Times the oracle's whole-layer restatement on the host cores.  Each step
-    processes a bounded sample of T_s tokens of the workload; returns
-    (tokens/s, T_s, ms per step, cores)."""
+    """Times the restatement of the reference's torch path for the whole layer on the host cores.
+    Each step processes a bounded sample of T_s tokens of the workload; returns
+    (tokens/s, T_s, ms per step, cores, note).  Layers with many large experts draw their
+    experts from at most 8 distinct weight sets so that the fp32 copies fit host memory; the
+    arithmetic per token is unchanged."""
     from oracle import torch_oracle as to
     from oracle import workloads as wl
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    w = wl.make_weights(cfg, seed=0)
+    distinct = cfg.E if cfg.E * bw.weight_bytes_per_expert(cfg) * 4 < 24e9 else 8
+    w = wl.make_weights(cfg, seed=0, num_experts=distinct)
     d13, d2 = wl.dequant_weights(cfg, w)  # fp32 once, outside the timed steps
+    note = ""
+    b13, b2 = w["w13_bias"], w["w2_bias"]
+    if distinct < cfg.E:
+        d13 = wl.ExpertView(cfg.E, 2 * cfg.I, cfg.H, lambda e, d=d13: d[e % distinct])
+        d2 = wl.ExpertView(cfg.E, cfg.H, cfg.I, lambda e, d=d2: d[e % distinct])
+        note = f", the {cfg.E} experts drawn from {distinct} distinct weight sets (host memory)"
 
     def run(T):
         x, logits, bias = wl.make_inputs(cfg, T, seed=0)
         t0 = time.perf_counter()
         tw, ids = wl.route_cpu(cfg, logits, bias)
         if cfg.recipe == "bf16":
-            to.fused_moe_bf16(x, d13, w["w13_bias"], d2, w["w2_bias"], tw, ids, cfg.E)
+            to.fused_moe_bf16(x, d13, b13, d2, b2, tw, ids, cfg.E)
         else:
-            to.fused_moe_staged(x, d13, w["w13_bias"], d2, w["w2_bias"], tw, ids, cfg.E,
+            to.fused_moe_staged(x, d13, b13, d2, b2, tw, ids, cfg.E,
                                 activation=cfg.activation, act_quant=cfg.recipe == "fp8block")
         return time.perf_counter() - t0
 
@@ -151,64 +190,51 @@ def cpu_layer_tokens_per_s(cfg, seconds_budget: float, steps: int, warmup: int):
         run(T_s)
     t = [run(T_s) for _ in range(steps)]
     total = sum(t)
-    return T_s * steps / total, T_s, 1e3 * total / steps, cores
+    return T_s * steps / total, T_s, 1e3 * total / steps, cores, note
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def launches_per_step(M: int, quant: bool) -> int:
-    """Kernels of ours launched by one step: routing 1; permute bookkeeping 1
-    (<= 2048 routed slots) or 3, row copy 1; GEMM 2; activation 1; (fp8: act
-    quant 1); gather 1."""
-    return 1 + (1 if M <= 2048 else 3) + 1 + 2 + 1 + (1 if quant else 0) + 1
+class StageTimer:
+    """CUDA-event marks between the stages of a layer call (the per-stage timing of the
+    reference's harness, benchmark/src/fused_moe_interface_.py:12-40 of vllm-xpu-kernels)."""
+
+    def __init__(self):
+        self.marks = []
+
+    def mark(self, name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.marks.append((name, ev))
+
+    def durations_ms(self):
+        out = {}
+        for (_, e0), (name, e1) in zip(self.marks[:-1], self.marks[1:]):
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        return out
 
 
-def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, ep_chunks=None, ep_sm_reserve=20, ep_groups=None,
-                       ep_sorted=False, ep_per_rank=True):
-    """Synthetic weights on the device (this rank's experts only when the experts
-    are sharded) and the host-side inputs of one step."""
+def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, transport="peer"):
+    """Synthetic weights on the device (this rank's experts only when the experts are sharded)
+    and the host-side inputs of one step."""
     import vllm_xpu_kernels.fused_moe_interface as fmi
-    from oracle import workloads as wl
     assert fmi.FUSEDMOE_AVAILABLE, fmi.FUSEDMOE_UNAVAILABLE_REASON
-    g = torch.Generator(device=dev).manual_seed(1234 + ep_rank)
-    E, H, I = cfg.E // ep_world, cfg.H, cfg.I
-    if cfg.recipe == "bf16":
-        # op layout [E,K,N], drawn on the device expert by expert
-        w13 = torch.empty(E, H, 2 * I, dtype=torch.bfloat16, device=dev)
-        w2 = torch.empty(E, I, H, dtype=torch.bfloat16, device=dev)
-        for e in range(E):
-            w13[e] = (torch.randn(H, 2 * I, generator=g, device=dev) * H ** -0.5).to(torch.bfloat16)
-            w2[e] = (torch.randn(I, H, generator=g, device=dev) * I ** -0.5).to(torch.bfloat16)
-        s13 = s2 = b13 = b2 = None
-    elif cfg.recipe == "fp8block":
-        from oracle import torch_oracle as to
-        w13 = torch.empty(E, 2 * I, H, dtype=torch.float8_e4m3fn, device=dev)
-        w2 = torch.empty(E, H, I, dtype=torch.float8_e4m3fn, device=dev)
-        s13 = torch.empty(E, 2 * I // 128, H // 128, dtype=torch.float32, device=dev)
-        s2 = torch.empty(E, H // 128, I // 128, dtype=torch.float32, device=dev)
-        for e in range(E):  # quantised from N(0, 1/fan_in), amax/448 per 128x128 block
-            w13[e], s13[e] = to.quant_fp8_block_wei(torch.randn(2 * I, H, generator=g, device=dev) * H ** -0.5)
-            w2[e], s2[e] = to.quant_fp8_block_wei(torch.randn(H, I, generator=g, device=dev) * I ** -0.5)
-        b13 = b2 = None
-    else:  # mxfp4: uniform e2m1 codes, e8m0 exponents in [-10, -4], bf16 biases N(0, 0.02)
-        w13 = torch.randint(0, 256, (E, 2 * I, H // 2), generator=g, device=dev, dtype=torch.int32).to(torch.uint8).view(torch.float4_e2m1fn_x2)
-        w2 = torch.randint(0, 256, (E, H, I // 2), generator=g, device=dev, dtype=torch.int32).to(torch.uint8).view(torch.float4_e2m1fn_x2)
-        s13 = torch.randint(117, 124, (E, 2 * I, H // 32), generator=g, device=dev, dtype=torch.int32).to(torch.uint8)
-        s2 = torch.randint(117, 124, (E, H, I // 32), generator=g, device=dev, dtype=torch.int32).to(torch.uint8)
-        b13 = (torch.randn(E, 2 * I, generator=g, device=dev) * 0.02).to(torch.bfloat16)
-        b2 = (torch.randn(E, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
-    if ep_world > 1:
+    E = cfg.E // ep_world
+    w13, s13, b13, w2, s2, b2 = bw.make_device_weights(cfg, E, dev, seed=1234 + ep_rank)
+    if ep_world > 1 and transport == "peer":
+        from vllm_xpu_kernels.ep_moe import EpPeerFusedMoe, SymmetricPeerGroup
+        layer = EpPeerFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E,
+                               SymmetricPeerGroup(dev), T, cfg.H)
+    elif ep_world > 1:
         from vllm_xpu_kernels.ep_moe import EpFusedMoe
-        layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E,
-                           overlap_chunks=ep_chunks, sm_reserve=ep_sm_reserve, expert_groups=ep_groups,
-                           sorted_exchange=ep_sorted, per_rank_rows=ep_per_rank)
+        layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E, per_rank_rows=T > 256)
     else:
         layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
-    x_cpu, logits_cpu, bias_cpu = wl.make_inputs(cfg, T, seed=ep_rank)
+    x_cpu, logits_cpu, bias_cpu = bw.make_inputs(cfg, T, seed=ep_rank)
     return layer, x_cpu, logits_cpu, bias_cpu
 
 
 def make_step(cfg, layer, dev, T):
-    K, E = cfg.K, cfg.E
+    K = cfg.K
     tw = torch.empty(T, K, dtype=torch.float32, device=dev)
     ids = torch.empty(T, K, dtype=torch.int32, device=dev)
     src = torch.empty(T, K, dtype=torch.int32, device=dev)
@@ -230,10 +256,10 @@ def make_step(cfg, layer, dev, T):
 
 
 def time_gemms(cfg, layer, ids, T, dev, iters, ep_world=1, ep_rank=0):
-    """Average duration of the two grouped-GEMM launches of a step, CUDA events
-    on the launching stream, on this step's real row distribution (with sharded
-    experts: the rows all ranks route to this rank's experts)."""
-    H, I, K = cfg.H, cfg.I, cfg.K
+    """Average duration of the two grouped-GEMM launches of a step, CUDA events on the launching
+    stream, on this step's real row distribution (with sharded experts: the rows all ranks route
+    to this rank's experts)."""
+    H, I = cfg.H, cfg.I
     E = cfg.E // ep_world
     if ep_world > 1:
         import torch.distributed as dist
@@ -257,8 +283,10 @@ def time_gemms(cfg, layer, ids, T, dev, iters, ep_world=1, ep_rank=0):
     f = torch.ops._xpu_C.cutlass_grouped_gemm_interface
     if getattr(layer, "mx_acts", False):
         # block-scaled MXFP4 path: MXFP8 activations, SwigluOAI inside gemm1's epilogue
+        layer.persistent_workspace = False
         a1, s1 = layer._quant_mx(a1)
         a2, s2 = layer._quant_mx(a2)
+        layer.persistent_workspace = True
         d1 = torch.empty(M, I, dtype=torch.bfloat16, device=dev)
         g = torch.ops._xpu_C.b200_grouped_gemm
 
@@ -286,32 +314,44 @@ def time_gemms(cfg, layer, ids, T, dev, iters, ep_world=1, ep_rank=0):
     return ms_pair, e_act, M
 
 
-def weight_bytes_per_expert(cfg):
-    n = 3 * cfg.H * cfg.I
-    if cfg.recipe == "bf16":
-        return 2 * n
-    if cfg.recipe == "fp8block":
-        return n + 4 * (3 * cfg.H * cfg.I // (128 * 128))
-    return n // 2 + n // 32 + (2 * (2 * cfg.I + cfg.H) if cfg.has_bias else 0)
+def launches_per_step(cfg, T, layer, ep_world, transport) -> int:
+    """Kernels of this repository launched by one step, counted from the code path taken:
+    routing 1; sort 1 (<= 2048 slots) or 3; row copy (+quant) 1; gemm1 1; activation (+quant) 1
+    unless fused into gemm1; MX activation quantisers 2; gemm2 1; gather 1.  Expert parallelism
+    over peer memory: routing 1, dispatch sort 1|3 + dispatch 1, mask 1, the local layer without
+    its gather, combine 1, final gather 1."""
+    local = layer.local if ep_world > 1 else layer
+    act = 0 if local.fuse_activation else 1
+    mx = 2 if getattr(local, "mx_acts", False) else 0
+    sort = lambda slots: 1 if slots <= 2048 else 3
+    if ep_world == 1:
+        return 1 + sort(T * cfg.K) + 1 + 1 + act + mx + 1 + 1
+    if transport == "peer":
+        return 1 + sort(T * ep_world) + 1 + 1 + sort(ep_world * T * cfg.K) + 1 + 1 + act + mx + 1 + 1 + 1
+    return 1 + sort(T * ep_world) + 1 + sort(T * ep_world * cfg.K) + 1 + 1 + act + mx + 1 + 1 + 1
 
 
-def run_ours(args):
-    import torch.distributed as dist
-    from oracle import workloads as wl
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    cfg = wl.CONFIGS[args.workload]
-    T = args.tokens
+def stage_times(cfg, layer, step, x, logits, bias, reps=5):
+    """Per-stage device time of a step (single GPU): the layer is given a hook that records a
+    CUDA event after every stage; averaged over `reps` steps outside the timed region."""
+    acc = {}
+    for _ in range(reps):
+        timer = StageTimer()
+        layer.stage_hook = timer.mark
+        timer.mark("start")
+        step(x, logits, bias)
+        layer.stage_hook = None
+        torch.cuda.synchronize()
+        for k, v in timer.durations_ms().items():
+            acc[k] = acc.get(k, 0.0) + v / reps
+    return {k: round(v, 4) for k, v in acc.items()}
+
+
+def run_point(args, cfg, T, world, rank, local_rank, dev, dist):
+    """One (workload, T) measurement -> the JSON line as a dict."""
     ep_world = world if (args.parallelism == "ep" and world > 1) else 1
     layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev, ep_world, rank if ep_world > 1 else 0,
-                                                            args.ep_chunks, args.ep_sm_reserve, args.ep_groups, args.ep_sorted,
-                                                            # one row per (token, rank) pays off once the rows, not the launches, cost
-                                                            not args.ep_per_expert_rows and T > 256)
+                                                            args.ep_transport)
     step, (tw, ids) = make_step(cfg, layer, dev, T)
     x, logits = x_cpu.to(dev), logits_cpu.to(dev)
     bias = bias_cpu.to(dev) if bias_cpu is not None else None
@@ -322,7 +362,8 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident throughput ------------------------------------------------
-    for _ in range(max(3, args.warmup)):
+    warm = max(3, args.warmup)
+    for _ in range(warm):
         step(x, logits, bias)
     barrier()
     run_step = lambda: step(x, logits, bias)
@@ -410,56 +451,122 @@ def run_ours(args):
 
     # ---- roofline of the grouped GEMM kernel ---------------------------------------------
     peaks = _peaks()
+    local = layer.local if ep_world > 1 else layer
     ms_pair, e_act, m_rows = time_gemms(cfg, layer, ids, T, dev, max(3, min(20, args.steps)), ep_world, rank)
     flops = 6.0 * m_rows * cfg.H * cfg.I
-    wbytes = e_act * weight_bytes_per_expert(cfg)
+    wbytes = e_act * bw.weight_bytes_per_expert(cfg)
     act_bytes = m_rows * (cfg.H + 2 * cfg.I + cfg.I + cfg.H) * 2  # A and D of both launches
-    mx = getattr(layer.local if ep_world > 1 else layer, "mx_acts", False)
+    if cfg.recipe == "fp8block":  # e4m3 rows + fp32 scale per 128 in, 16-bit out
+        act_bytes = m_rows * ((cfg.H + cfg.I) * (1 + 4 / 128) + (2 * cfg.I + cfg.H) * 2)
+    mx = getattr(local, "mx_acts", False)
     if mx:  # per plane 1-byte codes + 1/32 scale byte in, 16-bit out; gemm1 writes the activated [M, I]
-        planes = (layer.local if ep_world > 1 else layer).mx_planes
-        act_bytes = m_rows * (planes * (cfg.H + cfg.I) * 33 // 32 + (cfg.I + cfg.H) * 2)
-    t_tensor = flops / (peaks["tensor"] * 1e12)
+        act_bytes = m_rows * (local.mx_planes * (cfg.H + cfg.I) * 33 // 32 + (cfg.I + cfg.H) * 2)
+    # tensor peak of the instruction kind the kernel issues: kind::f16 -> the measured bf16 GEMM
+    # (burst: the pair is timed alone); kind::f8f6f4 / mxf8f6f4 -> a dense fp8 GEMM measured here
+    fp8_kind = cfg.recipe != "bf16"
+    tensor_peak, tensor_src = peaks["tensor"], peaks["source"] + " bf16 GEMM (burst)"
+    if fp8_kind:
+        fp8_peak = measure_fp8_dense_tflops(dev)
+        if fp8_peak is not None:
+            tensor_peak, tensor_src = fp8_peak, "measured in this run: torch._scaled_mm e4m3 8192^3 (burst)"
+        else:
+            tensor_peak, tensor_src = 2.0 * peaks["tensor"], "2 x " + tensor_src + ": no fp8 GEMM available"
+    t_tensor = flops / (tensor_peak * 1e12)
     t_hbm = (wbytes + act_bytes) / (peaks["hbm"] * 1e9)
+    tf = flops / (ms_pair * 1e-3) / 1e12
+    gbs = (wbytes + act_bytes) / (ms_pair * 1e-3) / 1e9
     if t_tensor >= t_hbm:
-        ach = flops / (ms_pair * 1e-3) / 1e12
-        roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": peaks["tensor"], "unit": "TFLOP/s",
-                "frac": round(ach / peaks["tensor"], 4)}
+        roof = {"bound": "tensor", "achieved": round(tf, 2), "peak": round(tensor_peak, 1), "unit": "TFLOP/s",
+                "frac": round(tf / tensor_peak, 4), "peak_source": tensor_src}
     else:
-        ach = (wbytes + act_bytes) / (ms_pair * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm"], "unit": "GB/s",
-                "frac": round(ach / peaks["hbm"], 4)}
-    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((cfg.name, T)) if ep_world == 1 else None, "kernel": (("grouped_gemm_mx_kernel" if mx else "grouped_gemm_dq_kernel") if cfg.recipe == "mxfp4" else _gemm_kernel_name(cfg, T))
-                           + " (gemm1 + gemm2 of one step)",
-                 "ms_per_launch_pair": round(ms_pair, 4), "peak_source": peaks["source"] + " (sustained)",
-                 "experts_active": e_act})
+        roof = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm"], "unit": "GB/s",
+                "frac": round(gbs / peaks["hbm"], 4), "peak_source": peaks["source"] + " copy bandwidth"}
+    # both limits, whichever binds: the time the launch pair would take at each peak over its time
+    roof.update({"tflops": round(tf, 2), "tensor_frac": round(tf / tensor_peak, 4), "tensor_peak": round(tensor_peak, 1),
+                 "tensor_peak_source": tensor_src, "frac_of_bf16_peak": round(tf / peaks["tensor"], 4),
+                 "gbs": round(gbs, 1), "hbm_frac": round(gbs / peaks["hbm"], 4)})
+    traffic = CAPTURED_TRAFFIC_BYTES.get((cfg.name, T)) if ep_world == 1 else None
+    roof.update({"traffic": traffic, "traffic_source": "from capture" if traffic else None,
+                 "kernel": _gemm_kernel_name(cfg, m_rows / max(1, cfg.E // ep_world), mx) + " (gemm1 + gemm2 of one step)",
+                 "ms_per_launch_pair": round(ms_pair, 4), "experts_active": e_act, "rows": m_rows})
+    # the whole layer against its algorithmic bytes / flops (intermediates not counted)
+    e_act_layer = e_act
+    layer_t_hbm = bw.layer_bytes(cfg, T, e_act_layer) / (peaks["hbm"] * 1e9)
+    layer_t_tensor = bw.layer_flops(cfg, T) / (tensor_peak * 1e12)
+    layer_roof = {"hbm_frac": round(layer_t_hbm / (ms_per_step * 1e-3), 4),
+                  "tensor_frac": round(layer_t_tensor / (ms_per_step * 1e-3), 4)} if ep_world == 1 else None
 
+    par = (f"ep{world}: {cfg.E // world} experts per GPU, dispatch/combine "
+           + ("by peer stores over NVLink (symmetric memory), two barriers per step"
+              if args.ep_transport == "peer" else "by NCCL all-to-all")) if ep_world > 1 else (
+        f"replicas x{world}" if world > 1 else "single GPU")
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "warmup": warm, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": {"bf16": "bf16", "fp8block": "fp8_e4m3",
                                                           "mxfp4": "mxfp4"}[cfg.recipe],
         "data": "synthetic",
         "config": {"workload": f"{cfg.name} T={T} per GPU", "H": cfg.H, "I": cfg.I, "E": cfg.E, "top_k": cfg.K,
-                   "tokens_per_gpu": T, "routing": cfg.routing, "parallelism": (f"ep{world}: {cfg.E // world} experts per GPU, NCCL all-to-all dispatch/combine"
-                                   if ep_world > 1 else f"replicas x{world}"),
+                   "tokens_per_gpu": T, "routing": cfg.routing, "parallelism": par,
                    "l2": "inputs exceed L2: the weights streamed per step are larger than the 126 MB L2"
-                         if e_act * weight_bytes_per_expert(cfg) > 126e6 else "inputs smaller than L2",
+                         if e_act * bw.weight_bytes_per_expert(cfg) > 126e6 else "inputs smaller than L2",
                    "launch": "cuda graph replay" if (args.cuda_graph and ep_world == 1) else "eager torch ops",
                    "seed": 0},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches_per_step(T * cfg.K, cfg.recipe == "fp8block") * args.steps,
+        "gpu_launches": launches_per_step(cfg, T, layer, ep_world, args.ep_transport) * args.steps,
         "clocks": clocks.summary(),
         "roofline": roof,
+        "layer_roofline": layer_roof,
     }
+    if ep_world == 1 and world == 1:
+        line["stages_ms"] = stage_times(cfg, layer, step, x, logits, bias)
+    if ep_world > 1 and args.ep_transport == "peer":
+        # bytes one rank stores into its peers per step (rows + scales + ids + weights out, partial
+        # sums back), from the counts of the last step
+        sent = int(layer.send_counts.sum())
+        remote = sent - int(layer.send_counts[rank])
+        row = cfg.H + (cfg.H // 128) * 4 if layer.quant else 2 * cfg.H
+        recvd = int(layer.recv_counts.sum()) - int(layer.recv_counts[rank])
+        line["ep"] = {"rows_sent": sent, "rows_sent_remote": remote,
+                      "dispatch_bytes_remote": remote * (row + cfg.K * 8),
+                      "combine_bytes_remote": recvd * cfg.H * 2}
+    return line
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        dist.init_process_group("nccl", device_id=dev)
+    if args.parallelism == "auto":
+        args.parallelism = "ep" if world > 1 else "replicas"
+    if args.sweep:
+        assert world == 1, "--sweep runs on one GPU"
+        for name, cfg in bw.CONFIGS.items():
+            for T in cfg.tokens:
+                line = run_point(args, cfg, T, 1, 0, local_rank, dev, dist)
+                print(json.dumps(line), flush=True)
+                from vllm_xpu_kernels.fused_moe_interface import _WORKSPACE
+                _WORKSPACE.clear()
+                torch.cuda.empty_cache()
+        return
+    cfg = bw.CONFIGS[args.workload]
+    line = run_point(args, cfg, args.tokens, world, rank, local_rank, dev, dist)
     if world == 1 and not args.no_cpu_baseline:
-        v, T_s, ms_cpu, cores = cpu_layer_tokens_per_s(cfg, 20.0, 2, 1)
+        v, T_s, ms_cpu, cores, note = cpu_layer_tokens_per_s(cfg, 20.0, 2, 1)
         line["cpu_baseline"] = {"value": round(v, 2), "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": f"{T_s} tokens of the same layer per step, 2 timed steps, "
-                                          f"weights pre-converted to fp32, {ms_cpu:.0f} ms per step"}
+                                          f"weights pre-converted to fp32{note}, {ms_cpu:.0f} ms per step"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -520,13 +627,12 @@ def run_ops(args):
 def run_reference(args):
     """The reference's own CPU path for this layer (its pure-torch test
     reference, restated in oracle/), timed on the host cores of this box."""
-    from oracle import workloads as wl
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    cfg = wl.CONFIGS[args.workload]
-    v, T_s, ms_cpu, cores = cpu_layer_tokens_per_s(cfg, 120.0, args.steps, args.warmup)
+    cfg = bw.CONFIGS[args.workload]
+    v, T_s, ms_cpu, cores, note = cpu_layer_tokens_per_s(cfg, 90.0, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": round(v, 2), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_cpu, 2), "higher_is_better": True,
@@ -534,7 +640,7 @@ def run_reference(args):
         "config": {"workload": f"{cfg.name} T={args.tokens} per GPU", "H": cfg.H, "I": cfg.I, "E": cfg.E,
                    "top_k": cfg.K, "tokens_per_gpu": args.tokens, "routing": cfg.routing, "seed": 0},
         "cpu_baseline": {"value": round(v, 2), "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{T_s} tokens of the same layer per step"},
+                         "sample": f"{T_s} tokens of the same layer per step{note}"},
         "e2e": {"value": round(v, 2), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -546,25 +652,18 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2_mixtral_bf16")
-    ap.add_argument("--tokens", type=int, default=4096)
-    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
-                    help="N > 1: independent replicas (default) or experts sharded over the ranks "
-                         "with all-to-all token dispatch / combine")
-    ap.add_argument("--ep-groups", type=int, default=None,
-                    help="expert parallelism: pipeline the two all-to-alls with the experts by splitting each "
-                         "rank's experts into this many groups")
-    ap.add_argument("--ep-per-expert-rows", action="store_true",
-                    help="expert parallelism: ship one row per (token, expert) instead of one per (token, rank)")
-    ap.add_argument("--ep-sorted", action="store_true",
-                    help="expert parallelism: ship rows sorted by expert so the receiver multiplies them as they "
-                         "arrive (prefill-sized batches)")
-    ap.add_argument("--ep-chunks", type=int, default=None,
-                    help="ep: token chunks whose exchange overlaps the experts (default: by batch size)")
-    ap.add_argument("--ep-sm-reserve", type=int, default=20,
-                    help="ep: SMs the GEMM kernels leave to the collective while chunks overlap")
+    ap.add_argument("--workload", default="cfg4_deepseek_fp8")
+    ap.add_argument("--tokens", type=int, default=8192, help="tokens per GPU and step")
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "replicas", "ep"],
+                    help="N > 1: experts sharded over the ranks with token dispatch / combine (ep, the "
+                         "default) or independent replicas")
+    ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
+                    help="ep: dispatch / combine by this repository's kernels storing into peer memory over "
+                         "NVLink (default) or by NCCL all-to-all (the comparison point)")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="device-resident loop replays the step from a CUDA graph instead of eager ops")
+    ap.add_argument("--sweep", action="store_true",
+                    help="one GPU: one JSON line for every (workload, T) point of the benchmark table")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.workload == "ops":

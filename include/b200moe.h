@@ -56,6 +56,23 @@ const char* b200moe_last_error(void);
 /* ABI version: bumped when a signature changes. */
 int b200moe_abi_version(void);
 
+/* Status words.  The tensor-core kernels bound every wait on an mbarrier; a CTA
+ * whose wait runs out raises a flag, all its warps leave, tensor memory is
+ * freed and the caller's status word (b200moe_gemm_args.status) is set to 1 with
+ * a plain store - the word may live in device memory or in mapped (pinned) host
+ * memory, which a host can poll without synchronising.
+ * b200moe_status_to_code turns the value read from such a word into B200MOE_OK or
+ * B200MOE_E_DEVICE_TIMEOUT (with a message for b200moe_last_error).
+ * b200moe_selftest_bounded_wait launches one small CTA that waits, with the
+ * same wait routine and teardown as the GEMM kernels but a budget of
+ * `budget_cycles` SM clock cycles (at most 2e8, about 0.1 s), on an mbarrier
+ * nobody arrives at; it gives up, returns and sets *status = 1.  Hosts use it
+ * to check that the failure path reaches them.  Neither function has a
+ * counterpart in the reference (its kernels have no bounded waits). */
+int b200moe_status_to_code(int32_t status_word);
+int b200moe_selftest_bounded_wait(int32_t* status, int64_t budget_cycles,
+                                  b200moe_stream stream);
+
 /* ------------------------------------------------------------------------- */
 /* Routing                                                                    */
 /* ------------------------------------------------------------------------- */
@@ -154,6 +171,11 @@ int b200moe_moe_align_block_size(const void* topk_ids, b200moe_dtype ids_dtype,
  * streams, no ordering between them) race on it - serialise them.  The array
  * keeps whatever the previous call left; the kernels rewrite every cell they
  * read, so nothing needs clearing.
+ * The device that is current at the call must be the one that owns `stream`
+ * and the buffers (the array that is used is the current device's).  The
+ * looked-up address is remembered per device ordinal for the life of the
+ * process: after cudaDeviceReset on that device it is stale and the entry
+ * point must not be used again in that process.
  * This entry point has no counterpart in the reference. */
 int b200moe_moe_align_block_size_noalloc(const void* topk_ids,
                                          b200moe_dtype ids_dtype,
@@ -324,8 +346,9 @@ typedef struct {
   float act_alpha, act_limit; /* SwigluOAI parameters                             */
   float clamp_limit;      /* >0: gate=min(gate,L), up=clamp(up,-L,L) before the
                              gated epilogue (only with a gated epilogue)          */
-  int32_t* status;        /* device int, written non-zero if a bounded wait gave
-                             up; may be NULL                                      */
+  int32_t* status;        /* int the device can write (device memory or mapped host
+                             memory): set to 1 if a bounded wait gave up; may be
+                             NULL                                                 */
   int impl;               /* 0 = auto, 1 = tensor-core kernel, 2 = plain-CUDA
                              checking kernel                                      */
   int max_ctas;           /* >0: the persistent tensor-core kernel uses at most this
@@ -340,6 +363,10 @@ typedef struct {
                              exchange as they arrive, grouped by source rank and by
                              local expert inside a source, need no second
                              permutation.  16-bit and block-scaled fp8 weights.     */
+  int64_t rows_hint;      /* 0, or the number of rows expected to be in use when `m`
+                             is only a loose upper bound (buffers sized for the worst
+                             case): tile sizes are picked for rows_hint / num_experts
+                             rows per expert.  Never changes the result.            */
 } b200moe_gemm_args;
 
 int b200moe_grouped_gemm(const b200moe_gemm_args* args, b200moe_stream stream);
@@ -469,6 +496,90 @@ int b200moe_moe_sum(void* out, const void* in, b200moe_dtype dtype,
                     int64_t num_tokens, int topk, int hidden,
                     const void* topk_ids, b200moe_dtype ids_dtype,
                     const int32_t* expert_map, b200moe_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Expert parallelism over peer memory                                        */
+/* ------------------------------------------------------------------------- */
+
+/* The reference has no communication layer: its expert parallelism is the
+ * per-rank mask of `init_expert_map` (csrc/moe/init_expert_map.cpp:33-53,
+ * vllm_xpu_kernels/fused_moe_interface.py:256-271), which leaves every rank with
+ * all tokens.  These three entry points add token dispatch and combine for one
+ * process per GPU: every rank keeps receive buffers that its peers can address
+ * (symmetric memory or IPC mappings; over NVLink), and the kernels below store
+ * straight into them with ordinary global stores - no staging copy, no host
+ * read of any count.  Experts are split contiguously and evenly: expert g lives
+ * on rank g / num_local_experts.
+ *
+ * Buffers of rank d, each in `ep_size` regions of `capacity` rows, region s
+ * written by source rank s (capacity >= the tokens any rank dispatches per call):
+ *   recv_rows    [ep][capacity][row_bytes]   the token's row: e4m3 (hidden bytes,
+ *                                            with recv_scales) or 16-bit
+ *   recv_scales  [ep][capacity][hidden/128]  fp32, only with quantised rows
+ *   recv_ids     [ep][capacity][topk] i32    the token's expert ids local to rank d
+ *                                            (-1 for experts of other ranks)
+ *   recv_weights [ep][capacity][topk] f32    routing weights (0 for those slots)
+ *   recv_counts  [ep] i32                    rows received from each source
+ *   comb_rows    [ep][capacity][hidden]      16-bit partial sums coming back:
+ *                                            region d holds what rank d computed
+ * The tables below hold, for every rank, the address of that rank's buffer as
+ * this process sees it.
+ *
+ * One layer call is: b200moe_ep_dispatch on every rank; a barrier between the
+ * ranks (any mechanism that orders the peers' kernels, e.g. a small NCCL
+ * all-reduce on the same stream); b200moe_ep_mask_unused, the local experts on
+ * the [ep*capacity] received rows as a top-k layer, b200moe_ep_combine; a second
+ * barrier; b200moe_moe_gather over comb_rows with send_pos as the row map and
+ * unit weights.  No kernel here waits for another rank: ordering comes from the
+ * barriers between the launches. */
+#define B200MOE_MAX_EP 16
+typedef struct {
+  int ep_size, ep_rank;
+  int num_local_experts;
+  int topk;
+  int hidden;
+  int quantized;          /* 1: rows travel as e4m3 + 1x128 fp32 scales, 0: 16-bit */
+  int64_t capacity;
+  void* recv_rows[B200MOE_MAX_EP];
+  float* recv_scales[B200MOE_MAX_EP];
+  int32_t* recv_ids[B200MOE_MAX_EP];
+  float* recv_weights[B200MOE_MAX_EP];
+  int32_t* recv_counts[B200MOE_MAX_EP];
+  void* comb_rows[B200MOE_MAX_EP];
+} b200moe_ep_peers;
+
+/* Scratch of b200moe_ep_dispatch for `num_tokens` tokens. */
+size_t b200moe_ep_dispatch_workspace_bytes(int64_t num_tokens, int ep_size);
+
+/* Sends every token once to every rank that owns at least one of its experts.
+ * hidden [T,H] bf16/f16 (quantised on the way to e4m3 with dynamic 1x128 scales
+ * when peers->quantized, the math of b200moe_per_token_group_fp8_quant), topk_ids
+ * [T,K] global expert ids, topk_weights [T,K].  Outputs on this rank:
+ * send_counts [ep] (rows sent to each rank) and send_pos [T,ep] = d * capacity +
+ * the row's index among this rank's rows for rank d (ascending token order), -1
+ * where the token does not go to d.  The same index addresses the row in region
+ * `ep_rank` of rank d's receive buffers and, later, the partial sum in region d
+ * of this rank's comb_rows. */
+int b200moe_ep_dispatch(const b200moe_ep_peers* peers, const void* hidden,
+                        b200moe_dtype dtype, const void* topk_ids,
+                        b200moe_dtype ids_dtype, const float* topk_weights,
+                        int64_t num_tokens, int32_t* send_counts,
+                        int32_t* send_pos, void* workspace,
+                        size_t workspace_bytes, b200moe_stream stream);
+
+/* After the barrier: marks the rows of this rank's recv_ids that no source
+ * filled in this call (index >= recv_counts[s] in region s) with -1, so the local
+ * top-k layer skips them. */
+int b200moe_ep_mask_unused(const b200moe_ep_peers* peers, b200moe_stream stream);
+
+/* The weighted top-k reduction of the local experts' output, stored straight
+ * into the source ranks' comb_rows: for received row i of region s
+ *   comb_rows[s][ep_rank][i][:] = sum_k recv_weights[s][i][k] * moe_out[row_map[s*capacity+i][k]][:]
+ * (fp32, k ascending, row_map -1 skipped; the math of b200moe_moe_gather).
+ * moe_out [M,H] and the result are `dtype` (bf16/f16); row_map [ep*capacity, topk]. */
+int b200moe_ep_combine(const b200moe_ep_peers* peers, const void* moe_out,
+                       const int32_t* row_map, b200moe_dtype dtype,
+                       b200moe_stream stream);
 
 #ifdef __cplusplus
 }

@@ -134,6 +134,28 @@ def remap_hidden_states(hidden, scales, topk_ids, expert_map, local_experts):
     return remapped, rs, rows, row_map.view(T, K)
 
 
+def ep_dispatch_plan(topk_ids, ep_size, num_local_experts, capacity):
+    """The bookkeeping of the expert-parallel dispatch, sequentially: a token goes once to every
+    rank that owns one of its experts (expert g on rank g // num_local_experts, the split of
+    csrc/moe/init_expert_map.cpp:45-52); its row index at rank d is the number of earlier tokens
+    of this source that also go to d.  -> send_counts [ep] i32, send_pos [T, ep] i32
+    (d * capacity + index, or -1), loc_ids [T, ep, K] i32 (expert id local to rank d, -1 for
+    experts of other ranks)."""
+    T, K = topk_ids.shape
+    ids = topk_ids.long()
+    counts = torch.zeros(ep_size, dtype=torch.int32)
+    pos = torch.full((T, ep_size), -1, dtype=torch.int32)
+    loc = torch.full((T, ep_size, K), -1, dtype=torch.int32)
+    for t in range(T):
+        for d in range(ep_size):
+            mine = (ids[t] >= 0) & (ids[t] // num_local_experts == d)
+            if bool(mine.any()):
+                pos[t, d] = d * capacity + int(counts[d])
+                counts[d] += 1
+                loc[t, d] = torch.where(mine, ids[t] - d * num_local_experts, -1).to(torch.int32)
+    return counts, pos, loc
+
+
 def init_expert_map(n_local, ep_rank, ep_size):
     """tests/fused_moe/test_remap_hidden_states.py:333-345."""
     m = torch.full((n_local * ep_size,), -1, dtype=torch.int32)

@@ -10,50 +10,13 @@ in the logical ``[E, N, K]`` layout; ``to_op_layout`` converts them to what
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-
 import torch
 
 from . import torch_oracle as to
 
 
-@dataclass
-class MoeConfig:
-    name: str
-    H: int
-    I: int
-    E: int
-    K: int
-    recipe: str            # "bf16" | "fp8block" | "mxfp4"
-    routing: str           # "softmax" | "grouped_sigmoid"
-    activation: str = "silu"
-    renormalize: bool = True
-    n_group: int = 1
-    topk_group: int = 1
-    routed_scaling_factor: float = 1.0
-    logit_offset_std: float = 0.0
-    has_bias: bool = False
-    tokens: tuple = field(default_factory=tuple)
-
-
-CONFIGS = {
-    "cfg1_small_bf16": MoeConfig("cfg1_small_bf16", 2048, 1408, 8, 2, "bf16", "softmax", tokens=(64,)),
-    "cfg2_mixtral_bf16": MoeConfig("cfg2_mixtral_bf16", 4096, 14336, 8, 2, "bf16", "softmax",
-                                   logit_offset_std=0.5, tokens=(1, 32, 512, 4096)),
-    "cfg3_qwen3_fp8": MoeConfig("cfg3_qwen3_fp8", 2048, 768, 128, 8, "fp8block", "softmax",
-                                tokens=(16, 256, 4096, 16384)),
-    "cfg4_deepseek_fp8": MoeConfig("cfg4_deepseek_fp8", 7168, 2048, 256, 8, "fp8block",
-                                   "grouped_sigmoid", n_group=8, topk_group=4,
-                                   routed_scaling_factor=2.5, tokens=(64, 1024, 8192)),
-    "cfg5_gptoss_mxfp4": MoeConfig("cfg5_gptoss_mxfp4", 2880, 2880, 128, 4, "mxfp4", "softmax",
-                                   activation="swigluoai", has_bias=True, tokens=(1, 128, 2048)),
-}
-
-
-def scaled(cfg: MoeConfig, H=None, I=None, E=None) -> MoeConfig:
-    """A smaller layer of the same kind, for tests the CPU oracle can finish."""
-    import dataclasses
-    return dataclasses.replace(cfg, H=H or cfg.H, I=I or cfg.I, E=E or cfg.E)
+# One table of shapes for the bench and the tests: it lives beside the bench.
+from bench_workloads import CONFIGS, MoeConfig, make_inputs, scaled  # noqa: E402,F401
 
 
 def _randn(gen, shape, std=1.0, chunk_rows=None):
@@ -104,19 +67,6 @@ def make_weights(cfg: MoeConfig, seed: int = 0, num_experts=None, device="cpu"):
     return out
 
 
-def make_inputs(cfg: MoeConfig, T: int, seed: int = 0):
-    """-> x bf16 [T,H], router logits fp32 [T,E], routing bias fp32 [E] or None."""
-    gen = torch.Generator().manual_seed(seed * 1000 + 2)
-    x = _randn(gen, (T, cfg.H)).to(torch.bfloat16)
-    logits = _randn(gen, (T, cfg.E))
-    if cfg.logit_offset_std > 0:
-        logits = logits + _randn(gen, (cfg.E,), cfg.logit_offset_std).unsqueeze(0)
-    bias = None
-    if cfg.routing == "grouped_sigmoid":
-        bias = _randn(gen, (cfg.E,), 0.1)
-    return x, logits, bias
-
-
 def route_cpu(cfg: MoeConfig, logits, bias):
     """Routing with the torch restatements -> (weights f32 [T,K], ids i32 [T,K])."""
     if cfg.routing == "softmax":
@@ -140,6 +90,35 @@ def dequant_weights(cfg: MoeConfig, w):
     d13 = to.dequant_mxfp4(w["w13"].cpu(), w["w13_scale"].cpu()).to(torch.bfloat16).float()
     d2 = to.dequant_mxfp4(w["w2"].cpu(), w["w2_scale"].cpu()).to(torch.bfloat16).float()
     return d13, d2
+
+
+class ExpertView:
+    """[E, N, K] fp32 weights for the layer restatements (they index ``w[e]`` and read
+    ``w.shape``) without holding E dequantised experts: expert e is produced on access by
+    `fetch(e)`.  Bounds host memory when a layer has hundreds of large experts."""
+
+    def __init__(self, num_experts, n, k, fetch):
+        self.shape = (num_experts, n, k)
+        self._fetch = fetch
+
+    def __getitem__(self, e):
+        return self._fetch(int(e))
+
+
+def expert_views(cfg: MoeConfig, w13, s13, w2, s2):
+    """Lazy fp32 views of op-layout weights that may live on a GPU (``to_op_layout`` /
+    ``bench_workloads.make_device_weights`` layouts): -> (w13 [E,2I,H], w2 [E,H,I])."""
+    E = w13.shape[0]
+    if cfg.recipe == "bf16":      # op layout [E,K,N]
+        f13 = lambda e: w13[e].cpu().float().T
+        f2 = lambda e: w2[e].cpu().float().T
+    elif cfg.recipe == "fp8block":
+        f13 = lambda e: to.dequant_fp8_block_wei(w13[e].cpu(), s13[e].cpu())
+        f2 = lambda e: to.dequant_fp8_block_wei(w2[e].cpu(), s2[e].cpu())
+    else:
+        f13 = lambda e: to.dequant_mxfp4(w13[e:e + 1].cpu().view(torch.uint8), s13[e:e + 1].cpu())[0].to(torch.bfloat16).float()
+        f2 = lambda e: to.dequant_mxfp4(w2[e:e + 1].cpu().view(torch.uint8), s2[e:e + 1].cpu())[0].to(torch.bfloat16).float()
+    return (ExpertView(E, 2 * cfg.I, cfg.H, f13), ExpertView(E, cfg.H, cfg.I, f2))
 
 
 def to_op_layout(cfg: MoeConfig, w):

@@ -46,7 +46,7 @@ def cpu_worker(rank, world, port, T, result_queue):
         M = ids.numel()
         send_eids = torch.empty(M, dtype=torch.int32)
         send_eids[send_pos.reshape(-1).long()] = (ids.reshape(-1) % E_local).to(torch.int32)
-        s_spl, r_spl = a2a.exchange_counts(send_counts)
+        s_spl, r_spl = a2a.exchange_counts(send_counts, verify=True)
         assert sum(s_spl) == M
         recv_rows, none, recv_eids = a2a.dispatch((send_rows, None, send_eids), s_spl, r_spl)
         assert none is None and recv_rows.shape[0] == sum(r_spl) == recv_eids.numel()
@@ -60,33 +60,6 @@ def cpu_worker(rank, world, port, T, result_queue):
         out = to.moe_gather(back, tw, send_pos, x.dtype)
         ref = _oracle_full(cfg, w, x, tw, ids)
         err = float((out.float() - ref.float()).abs().max())
-
-        # the same through the expert-group schedule: rows sorted by (group, destination rank), one
-        # dispatch / combine per group, results collected in send order, one gather at the end
-        from vllm_xpu_kernels.ep_moe import group_bucket_map
-        G = 2
-        bucket = group_bucket_map(cfg.E, world, G, "cpu")
-        assert bucket.tolist() == [(e % E_local) * G // E_local * world + e // E_local for e in range(cfg.E)]
-        g_rows, _, g_counts, g_pos = to.remap_hidden_states(x, None, ids, bucket, G * world)
-        g_eids = torch.empty(M, dtype=torch.int32)
-        g_eids[g_pos.reshape(-1).long()] = (ids.reshape(-1) % E_local).to(torch.int32)
-        by_peer = g_counts.view(G, world).t().contiguous()
-        recv_counts = torch.empty_like(by_peer)
-        dist.all_to_all_single(recv_counts, by_peer)
-        back_all = torch.empty(M, x.shape[1], dtype=x.dtype)
-        start = 0
-        for g in range(G):
-            s_g, r_g = by_peer[:, g].tolist(), recv_counts[:, g].tolist()
-            n = sum(s_g)
-            rr, _, re = a2a.dispatch((g_rows[start:start + n], None, g_eids[start:start + n]), s_g, r_g)
-            assert all(lo + int(e) in range(lo, lo + E_local) and int(e) * G // E_local == g for e in re.tolist())
-            Rg = rr.shape[0]
-            lo_out = to.fused_moe_staged(rr, d13[lo:lo + E_local], None, d2[lo:lo + E_local], None,
-                                         torch.ones(Rg, 1), re.view(Rg, 1), E_local) if Rg else rr
-            back_all[start:start + n] = a2a.combine(lo_out, s_g, r_g)
-            start += n
-        out_g = to.moe_gather(back_all, tw, g_pos, x.dtype)
-        err = max(err, float((out_g.float() - ref.float()).abs().max()))
 
         # the default schedule: one row per (token, destination rank) with the token's local expert
         # ids and weights, top-k layer on the owner, one partial sum per (token, rank) back
@@ -119,6 +92,54 @@ def cpu_worker(rank, world, port, T, result_queue):
         dist.destroy_process_group()
 
 
+def cpu_failure_worker(rank, world, port, result_queue):
+    """Gloo ranks on CPU, failures made on the host: (1) a count message that arrives short is
+    caught by the consistency check before any row moves; (2) a rank that leaves between two
+    steps ends the next exchange of the others with an error inside the group's timeout."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from vllm_xpu_kernels.ep_moe import EpAllToAll, check_count_matrix
+    outcome = {}
+    try:
+        a2a = EpAllToAll()
+        # step 1: a healthy exchange
+        send_counts = torch.tensor([3 + rank, 5 - rank], dtype=torch.int32)
+        s_spl, r_spl = a2a.exchange_counts(send_counts, verify=True)
+        outcome["healthy"] = (s_spl, r_spl)
+        # step 2: rank 1's count message is tampered with on its way (one row short)
+        recv = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv, send_counts)
+        sent = [torch.empty_like(send_counts) for _ in range(world)]
+        dist.all_gather(sent, send_counts)
+        if rank == 0:
+            recv[1] -= 1   # the dropped row
+        try:
+            check_count_matrix(torch.stack(sent), recv, rank, capacity=16)
+            outcome["short_count_caught"] = rank != 0
+        except RuntimeError as e:
+            outcome["short_count_caught"] = rank == 0 and "rank 1 sent" in str(e)
+        dist.barrier()
+        # step 3: rank 1 leaves between steps; rank 0's next exchange must fail, not hang
+        if rank == 1:
+            outcome["left"] = True
+        else:
+            import time
+            time.sleep(1.0)   # the peer is gone by now
+            t0 = time.time()
+            try:
+                a2a.exchange_counts(send_counts)
+                outcome["peer_loss_raised"] = False
+            except Exception as e:  # the backend's error type is not part of the contract
+                outcome["peer_loss_raised"] = True
+                outcome["peer_loss_seconds"] = time.time() - t0
+        result_queue.put((rank, outcome))
+    finally:
+        if rank == 1:
+            dist.destroy_process_group()
+        # rank 0's group is broken after the failed exchange: nothing left to tear down cleanly
+
+
 def gpu_worker(rank, world, port, T, cfg_name, dims, result_queue):
     """NCCL ranks, one GPU each: EpFusedMoe against the single-process oracle."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -143,38 +164,25 @@ def gpu_worker(rank, world, port, T, cfg_name, dims, result_queue):
         ref = _oracle_full(cfg, w, x, tw, ids)
         err = float((out.cpu().float() - ref.float()).abs().max())
         scale = float(ref.float().abs().max())
-        # one row per (token, expert) instead of per (token, rank): the plain schedule
+        # one row per (token, expert) instead of per (token, rank)
         plain = EpFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]), cfg.K,
                            cfg.activation, E_local, per_rank_rows=False)
         out1 = torch.empty_like(out)
         plain.apply(out1, x.to(dev), tw.to(dev), ids.to(dev))
         torch.cuda.synchronize()
         err = max(err, float((out1.cpu().float() - ref.float()).abs().max()))
-        # the chunked, overlapped schedule computes the same rows
-        layer.overlap_chunks = 3
-        out2 = torch.empty_like(out)
-        layer.apply(out2, x.to(dev), tw.to(dev), ids.to(dev))
+        # the peer-memory transport: symmetric buffers, stores over NVLink, two barriers per call
+        from vllm_xpu_kernels.ep_moe import EpPeerFusedMoe, SymmetricPeerGroup
+        peers = SymmetricPeerGroup(dev)
+        cap = T + 5 * (world - 1)
+        peer_layer = EpPeerFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]), cfg.K,
+                                    cfg.activation, E_local, peers, cap, cfg.H)
+        out2 = torch.full_like(out, float("nan"))
+        for _ in range(3):
+            peer_layer.apply(out2, x.to(dev), tw.to(dev), ids.to(dev).to(torch.int32))
+        peer_layer.check_counts()
         torch.cuda.synchronize()
         err = max(err, float((out2.cpu().float() - ref.float()).abs().max()))
-        # so does the schedule that pipelines the exchange by expert group
-        grouped = EpFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]), cfg.K,
-                             cfg.activation, E_local, expert_groups=3)
-        out3 = torch.empty_like(out)
-        for _ in range(2):
-            grouped.apply(out3, x.to(dev), tw.to(dev), ids.to(dev))
-        torch.cuda.synchronize()
-        err = max(err, float((out3.cpu().float() - ref.float()).abs().max()))
-        # and the sorted exchange (rows arrive grouped by source and expert, no second permutation),
-        # unpipelined and pipelined by expert group
-        if cfg.recipe in ("bf16", "fp8block"):
-            for groups in (None, 2):
-                direct = EpFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]), cfg.K,
-                                    cfg.activation, E_local, expert_groups=groups, sorted_exchange=True)
-                out4 = torch.full_like(out, float("nan"))
-                for _ in range(2):
-                    direct.apply(out4, x.to(dev), tw.to(dev), ids.to(dev))
-                torch.cuda.synchronize()
-                err = max(err, float((out4.cpu().float() - ref.float()).abs().max()))
         result_queue.put((rank, err, scale))
     finally:
         dist.destroy_process_group()

@@ -32,7 +32,7 @@ def test_every_declared_symbol_is_exported(lib):
 def test_status_strings_and_version(lib):
     lib.b200moe_status_string.restype = ctypes.c_char_p
     lib.b200moe_last_error.restype = ctypes.c_char_p
-    assert lib.b200moe_abi_version() == 5
+    assert lib.b200moe_abi_version() == 6
     assert lib.b200moe_status_string(0) == b"ok"
     assert b"bad argument" in lib.b200moe_status_string(-1)
 
@@ -125,17 +125,20 @@ def test_prologue_workspace_layout_matches_the_reference(lib, num_rows, topk, ex
     assert need >= (num_rows * topk + experts) * 4 + lib.b200moe_sort_workspace_bytes(ctypes.c_int64(num_rows * topk), experts)
 
 
-def test_expert_parallel_bucket_maps():
-    """Bucket maps of the expert-parallel schedules: owner (contiguous even split, as
-    csrc/moe/init_expert_map.cpp:45-52 of the reference encodes it) and (group, rank)."""
+def test_expert_parallel_owner_map_and_workspace_size(lib):
+    """The owner of an expert (contiguous even split, as csrc/moe/init_expert_map.cpp:45-52 of the
+    reference encodes it), the argument checks of the peer-memory dispatch, and the scratch size
+    the Python layer computes for it."""
     import sys
     sys.path.insert(0, str(PKG_DIR))
-    from vllm_xpu_kernels.ep_moe import group_bucket_map, owner_map
+    from vllm_xpu_kernels.ep_moe import owner_map
     assert owner_map(256, 8, "cpu").tolist() == [e // 32 for e in range(256)]
-    for E_t, ep, G in [(256, 8, 4), (16, 2, 3), (12, 4, 3), (8, 2, 1)]:
-        b = group_bucket_map(E_t, ep, G, "cpu").tolist()
-        E_l = E_t // ep
-        assert b == [(e % E_l) * G // E_l * ep + e // E_l for e in range(E_t)]
-        assert sorted(set(b)) == list(range(G * ep))            # every (group, rank) bucket is used
-        for e in range(E_t):                                     # the rank inside a bucket is the owner
-            assert b[e] % ep == e // E_l
+    lib.b200moe_ep_dispatch_workspace_bytes.restype = ctypes.c_size_t
+    lib.b200moe_last_error.restype = ctypes.c_char_p
+    for cap, ep in [(8192, 8), (64, 2), (300, 16), (1, 1)]:
+        need = lib.b200moe_ep_dispatch_workspace_bytes(ctypes.c_int64(cap), ep)
+        chunks = (cap * ep + 255) // 256
+        assert need <= (ep * chunks + ep + 1) * 4 + 256       # what EpPeerFusedMoe allocates
+    assert lib.b200moe_ep_dispatch(None, None, 2, None, 5, None, ctypes.c_int64(0), None, None, None,
+                                   ctypes.c_size_t(0), None) == -1
+    assert b"null peer table" in lib.b200moe_last_error()

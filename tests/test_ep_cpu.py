@@ -4,7 +4,7 @@ import socket
 import torch
 import torch.multiprocessing as mp
 
-from ep_worker import cpu_worker
+from ep_worker import cpu_failure_worker, cpu_worker
 
 
 def _free_port():
@@ -29,6 +29,34 @@ def test_ep_all_to_all_two_gloo_ranks_match_the_oracle():
         assert err <= 2e-2, f"rank {rank}: max abs err {err}"
     # what rank 0 sends to rank 1 is what rank 1 receives from rank 0, and vice versa
     assert results[0][2][1] == results[1][3][0] and results[1][2][0] == results[0][3][1]
+
+
+def test_ep_host_side_failures_are_detected_not_hung():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=cpu_failure_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert results[0]["healthy"][0][1] == results[1]["healthy"][1][0]     # what 0 sent to 1 arrived at 1
+    assert results[0]["short_count_caught"] and results[1]["short_count_caught"]
+    assert results[1]["left"]
+    assert results[0]["peer_loss_raised"], "the exchange after a peer left must raise"
+    assert results[0]["peer_loss_seconds"] < 30
+
+
+def test_check_count_matrix_names_the_offending_rank():
+    import pytest
+    from vllm_xpu_kernels.ep_moe import check_count_matrix
+    sent = torch.tensor([[1, 2], [3, 4]], dtype=torch.int32)
+    check_count_matrix(sent, torch.tensor([2, 4]), rank=1, capacity=4)
+    with pytest.raises(RuntimeError, match="rank 0 sent 2 rows to rank 1"):
+        check_count_matrix(sent, torch.tensor([1, 4]), rank=1)
+    with pytest.raises(RuntimeError, match="exceed the capacity"):
+        check_count_matrix(sent, torch.tensor([2, 4]), rank=1, capacity=3)
 
 
 def test_owner_map_is_the_contiguous_even_split():

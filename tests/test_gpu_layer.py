@@ -290,3 +290,117 @@ def test_full_size_mixtral_properties(native):
     torch.ops._xpu_C.b200_grouped_gemm(a, None, w13, None, None, d1, rows, 2 * I, H, E, 2, 0, 1.702, 7.0, 0.0, 1, 0)
     torch.ops._xpu_C.b200_grouped_gemm(a, None, w13, None, None, d2, rows, 2 * I, H, E, 2, 0, 1.702, 7.0, 0.0, 2, 0)
     torch.testing.assert_close(d1.float(), d2.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_functional_entry_point_matches_the_oracle(native):
+    """`xpu_fused_moe` (vllm_xpu_kernels/fused_moe_interface.py:421-619 of the reference): one call,
+    recipe read off the weights, output allocated when not given."""
+    for name, dims, T in (("cfg1_small_bf16", dict(H=512, I=256, E=8), 37),
+                          ("cfg3_qwen3_fp8", dict(H=512, I=256, E=32), 29)):
+        cfg = wl.scaled(wl.CONFIGS[name], **dims)
+        w = wl.make_weights(cfg, seed=4)
+        x, logits, bias = wl.make_inputs(cfg, T, seed=4)
+        tw, ids = wl.route_cpu(cfg, logits, bias)
+        d13, d2 = wl.dequant_weights(cfg, w)
+        ref = to.fused_moe_staged(x, d13, None, d2, None, tw, ids, cfg.E, activation=cfg.activation,
+                                  act_quant=cfg.recipe == "fp8block")
+        w13, s13, w2, s2 = wl.to_op_layout(cfg, w)
+        mv = lambda t: t.to(DEV) if t is not None else None
+        out = native.xpu_fused_moe(x.to(DEV), mv(w13), mv(s13), None, mv(w2), mv(s2), None, tw.to(DEV), ids.to(DEV),
+                                   cfg.K, cfg.activation, cfg.E, is_block_fp8=cfg.recipe == "fp8block")
+        assert out.shape == x.shape and out.dtype == x.dtype
+        tol = TOL[cfg.recipe]
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=tol, atol=tol)
+        given = torch.empty_like(x, device=DEV)
+        back = native.xpu_fused_moe(x.to(DEV), mv(w13), mv(s13), None, mv(w2), mv(s2), None, tw.to(DEV),
+                                    ids.to(DEV), cfg.K, cfg.activation, cfg.E, output=given)
+        assert back is given and torch.equal(given, out)
+
+
+def test_functional_entry_point_int4_converts_the_weights_once(native):
+    T, H, I, E, K, group = 24, 256, 128, 4, 2, 128
+    g = torch.Generator().manual_seed(9)
+    a = (torch.randn(T, H, generator=g) / 16).to(torch.bfloat16)
+    w13 = torch.randint(0, 255, (E, 2 * I, H // 2), generator=g, dtype=torch.int32).to(torch.uint8)
+    w2 = torch.randint(0, 255, (E, H, I // 2), generator=g, dtype=torch.int32).to(torch.uint8)
+    s13 = torch.exp2(torch.randint(-5, -4, (E, 2 * I, H // group), generator=g).float()).to(torch.bfloat16)
+    s2 = torch.exp2(torch.randint(-5, -4, (E, H, I // group), generator=g).float()).to(torch.bfloat16)
+    tw, ids = torch.topk(torch.randn(T, E, generator=g), k=K, dim=-1, sorted=False)
+    ref = to.fused_moe_bf16(a, to.dequant_int4(w13, s13, group), None, to.dequant_int4(w2, s2, group), None, tw,
+                            ids.int(), E)
+    w13d, w2d = w13.to(DEV), w2.to(DEV)
+    args = (a.to(DEV), w13d, s13.to(DEV), None, w2d, s2.to(DEV), None, tw.to(DEV), ids.int().to(DEV), K, "silu", E)
+    out1 = native.xpu_fused_moe(*args, is_int4=True)
+    conv = w13d._b200_signed_nibbles[1]
+    out2 = native.xpu_fused_moe(*args, is_int4=True)
+    assert w13d._b200_signed_nibbles[1] is conv, "the second call must reuse the converted weights"
+    assert torch.equal(w13d.cpu(), w13), "the caller's weights stay as they were"
+    torch.testing.assert_close(out1.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(out1, out2)
+
+
+def test_layer_takes_prequantised_fp8_hidden_states(native):
+    """`apply(..., a1q_scale=...)` with e4m3 hidden_states and their 1x128 scales
+    (vllm_xpu_kernels/fused_moe_interface.py:273-281, 356-366 of the reference): the rows and
+    scales are permuted as they are, so the result equals the layer quantising the 16-bit input
+    itself, bit for bit."""
+    cfg = wl.scaled(wl.CONFIGS["cfg3_qwen3_fp8"], H=512, I=256, E=32)
+    w = wl.make_weights(cfg, seed=6)
+    x, logits, bias = wl.make_inputs(cfg, 45, seed=6)
+    tw, ids = wl.route_cpu(cfg, logits, bias)
+    w13, s13, w2, s2 = wl.to_op_layout(cfg, w)
+    mv = lambda t: t.to(DEV) if t is not None else None
+    layer = native.XpuFusedMoe(mv(w13), mv(s13), None, mv(w2), mv(s2), None, cfg.K, cfg.activation, cfg.E)
+    out16 = torch.empty(x.shape, dtype=torch.bfloat16, device=DEV)
+    layer.apply(out16, x.to(DEV), tw.to(DEV), ids.to(DEV))
+    q, sc = to.per_token_group_fp8_quant(x, 128, 1e-10)
+    outq = torch.full_like(out16, float("nan"))
+    layer.apply(outq, q.to(DEV), tw.to(DEV), ids.to(DEV), a1q_scale=sc.to(DEV))
+    assert torch.equal(outq, out16)
+    d13, d2 = wl.dequant_weights(cfg, w)
+    ref = to.fused_moe_staged(x, d13, None, d2, None, tw, ids, cfg.E, activation=cfg.activation, act_quant=True)
+    torch.testing.assert_close(outq.cpu().float(), ref.float(), rtol=5e-2, atol=5e-2)
+
+
+def test_prequantised_hidden_states_are_refused_for_other_recipes(native):
+    cfg = wl.scaled(wl.CONFIGS["cfg5_gptoss_mxfp4"], H=576, I=576, E=8)
+    w = wl.make_weights(cfg, seed=1)
+    w13, s13, w2, s2 = wl.to_op_layout(cfg, w)
+    mv = lambda t: t.to(DEV) if t is not None else None
+    layer = native.XpuFusedMoe(mv(w13), mv(s13), mv(w["w13_bias"]), mv(w2), mv(s2), mv(w["w2_bias"]), cfg.K,
+                               cfg.activation, cfg.E)
+    q = torch.zeros(4, cfg.H, dtype=torch.float8_e4m3fn, device=DEV)
+    sc = torch.zeros(4, cfg.H // 32, dtype=torch.uint8, device=DEV)
+    out = torch.empty(4, cfg.H, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(NotImplementedError, match="block-scaled fp8 weights only"):
+        layer.apply(out, q, torch.zeros(4, cfg.K, device=DEV), torch.zeros(4, cfg.K, dtype=torch.int32, device=DEV),
+                    a1q_scale=sc)
+
+
+def test_a_bounded_wait_that_runs_out_reaches_the_caller(native):
+    """The failure path of the tensor-core kernels, made on purpose without faulting anything: a
+    small kernel waits with the kernels' own bounded wait, and a budget of about a millisecond,
+    on an mbarrier that nobody arrives at; it gives up, returns and sets the device's status
+    word.  The next status check - and the next grouped-GEMM call - raise, and clear it."""
+    anchor = torch.zeros(1, device=DEV)
+    X = torch.ops._xpu_C
+    assert X.b200_check_status(anchor, True) == 0
+    X.b200_selftest_bounded_wait(anchor, 2_000_000)
+    with pytest.raises(RuntimeError, match="gave up a bounded wait"):
+        X.b200_check_status(anchor, True)
+    assert X.b200_check_status(anchor, True) == 0          # cleared by the raise
+    # the same through the op a layer calls
+    X.b200_selftest_bounded_wait(anchor, 2_000_000)
+    torch.cuda.synchronize()
+    E, M, N, K = 2, 32, 128, 128
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    wt = torch.randn(E, K, N, device=DEV).to(torch.bfloat16)
+    d = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    rows = torch.tensor([20, 12], dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError, match="device-side wait timed out"):
+        X.cutlass_grouped_gemm_interface(a, None, wt, None, None, d, rows, N, K, E)
+    X.cutlass_grouped_gemm_interface(a, None, wt, None, None, d, rows, N, K, E)   # the context is intact
+    torch.cuda.synchronize()
+    ref = torch.cat([a[:20].float() @ wt[0].float(), a[20:].float() @ wt[1].float()])
+    torch.testing.assert_close(d.float(), ref, rtol=2e-2, atol=2e-2)
+    assert X.b200_check_status(anchor, True) == 0

@@ -31,7 +31,7 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-def _align(lib, ids, E, bs, noalloc):
+def _align(lib, ids, E, bs, noalloc, expert_map=None):
     dev = ids.device
     numel = ids.numel()
     n = numel + E * (bs - 1)
@@ -40,17 +40,18 @@ def _align(lib, ids, E, bs, noalloc):
     e = torch.full((nb,), -7, dtype=torch.int32, device=dev)
     p = torch.full((1,), -7, dtype=torch.int32, device=dev)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    I32 = 5
+    I32 = {torch.int32: 5, torch.int64: 6}[ids.dtype]
+    emap = _ptr(expert_map) if expert_map is not None else None
     if noalloc:
         rc = lib.b200moe_moe_align_block_size_noalloc(
             _ptr(ids), I32, ctypes.c_int64(numel), E, bs, _ptr(s), ctypes.c_int64(n), _ptr(e),
-            ctypes.c_int64(nb), _ptr(p), None, stream)
+            ctypes.c_int64(nb), _ptr(p), emap, stream)
     else:
         need = lib.b200moe_sort_workspace_bytes(ctypes.c_int64(numel), E)
         ws = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
         rc = lib.b200moe_moe_align_block_size(
             _ptr(ids), I32, ctypes.c_int64(numel), E, bs, _ptr(s), ctypes.c_int64(n), _ptr(e),
-            ctypes.c_int64(nb), _ptr(p), None, _ptr(ws), ctypes.c_size_t(need), stream)
+            ctypes.c_int64(nb), _ptr(p), emap, _ptr(ws), ctypes.c_size_t(need), stream)
     assert rc == 0, lib.b200moe_last_error()
     torch.cuda.synchronize()
     return s, e, p
@@ -75,6 +76,23 @@ def test_noalloc_align_matches_workspace_align_twice_in_a_row():
     ids = torch.randint(0, 8, (16, 2), generator=g, dtype=torch.int32).to(dev)
     for a, b in zip(_align(lib, ids, 8, 4, False), _align(lib, ids, 8, 4, True)):
         assert torch.equal(a, b)
+
+
+def test_noalloc_align_with_int64_ids_and_an_expert_map():
+    # the same entry point with the other id width and with the id -> local expert map of an
+    # expert-parallel rank (-1 = not on this rank: those slots are dropped)
+    lib = _lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(1)
+    m, topk, E, bs = 2500, 4, 64, 32
+    ids = torch.randint(0, E, (m, topk), generator=g, dtype=torch.int64).to(dev)
+    emap = torch.full((E,), -1, dtype=torch.int32)
+    emap[16:32] = torch.arange(16, dtype=torch.int32)
+    emap = emap.to(dev)
+    for _ in range(2):
+        for a, b in zip(_align(lib, ids, E, bs, False, emap), _align(lib, ids, E, bs, True, emap)):
+            assert torch.equal(a, b)
 
 
 def test_noalloc_align_refuses_requests_beyond_its_scratch():

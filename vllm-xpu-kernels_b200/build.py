@@ -27,14 +27,12 @@ PKG = HERE / "vllm_xpu_kernels"
 OBJ = HERE / "build"
 INCLUDE = HERE.parent / "include"
 
-CU_SOURCES = ["abi.cu", "routing.cu", "permute.cu", "elementwise.cu", "fused_quant.cu", "gemm.cu",
+CU_SOURCES = ["abi.cu", "routing.cu", "permute.cu", "ep.cu", "elementwise.cu", "fused_quant.cu", "gemm.cu",
               "gemm_check.cu", "gemm_tc.cu", "gemm_tc_dq.cu", "gemm_tc_mx.cu", "gemm_tc_fp8t.cu"]
 SHIMS = {"_C": "c_ops.cpp", "_moe_C": "moe_ops.cpp", "_xpu_C": "xpu_ops.cpp"}
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
               "-std=c++17", "-Xcompiler", "-fPIC", "--threads", "2"]
-# extra nvcc flags for experiments (e.g. -DB200_MX_PROF); a change needs a clean rebuild
-NVCC_FLAGS += os.environ.get("B200MOE_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

@@ -26,26 +26,10 @@
 // Every wait on an mbarrier is bounded (see sm100_ptx.cuh): on expiry the CTA
 // raises an abort flag, all roles leave their loops, tensor memory is freed and
 // *status is set to 1.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "gemm_tc_common.cuh"
 
-// Cycle accounting of the roles of CTA 0 (printed at kernel end); compiled in
-// only with -DB200_TC_PROF, for experiments.
-#ifdef B200_TC_PROF
-#include <stdio.h>
-#define TC_PROF_DECL(...) long long __VA_ARGS__
-#define TC_PROF_T(var) const long long var = clock64()
-#define TC_PROF_ADD(acc, t0) acc += clock64() - (t0)
-#define TC_PROF_PRINT(...) if (blockIdx.x == 0) printf(__VA_ARGS__)
-#else
-#define TC_PROF_DECL(...)
-#define TC_PROF_T(var)
-#define TC_PROF_ADD(acc, t0)
-#define TC_PROF_PRINT(...)
-#endif
 
 namespace b200moe {
 int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st);
@@ -168,15 +152,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t it = 0, s = 0, ph = 0;
       int cursor = 0;
       bool ok = true;
-      TC_PROF_DECL(pw = 0, pt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti, p.w_experts);
         const int n0 = ti.n_tile * kFeat;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-          TC_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-          TC_PROF_ADD(pw, w0);
           uint8_t* wdst = smem + s * kStageBytes;
           uint8_t* adst = wdst + kWTileBytes;
           ptx::mbar_expect_tx(&ctrl->full[s], kStageBytes);
@@ -193,7 +174,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1; }
         }
       }
-      TC_PROF_PRINT("producer: total %lld wait_empty %lld blocks %u\n", clock64() - pt0, pw, it);
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
@@ -205,7 +185,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // leading-dimension byte offset of the weight operand: K-major 16, MN-major 8192 (16-bit) / 16384 (fp8)
       constexpr uint32_t kWLbo = !kWKn ? 16u : (kFp8 ? 16384u : 8192u);
       constexpr uint32_t kWStep = !kWKn ? 32u : (kFp8 ? 4096u : 2048u);   // bytes per 32-byte K step
-      TC_PROF_DECL(mf = 0, ma = 0, mi = 0, mc = 0, mt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti, p.w_experts);
@@ -215,22 +194,15 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((n_eff >> 3) << 17);
         constexpr bool per_block = kFp8;
         if (!per_block) {
-          TC_PROF_T(wa0);
           if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) break;
-          TC_PROF_ADD(ma, wa0);
           ptx::tc_fence_after();
         }
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (per_block) {
             a = acc_it % kAccStages;
-            TC_PROF_T(wa1);
             if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-            TC_PROF_ADD(ma, wa1);
           }
-          TC_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
-          TC_PROF_ADD(mf, w0);
-          TC_PROF_T(w2);
           ptx::tc_fence_after();
           // every operand descriptor of the stage = one base descriptor + a compile-time
           // offset (the address field counts 16-byte units), so the issue loop is adds only
@@ -244,17 +216,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::umma<kFp8>(d_tmem, wdesc0 + (uint64_t)((j * kWStep) >> 4), adesc0 + (uint64_t)((j * 32) >> 4), idesc,
                             accumulate);
           }
-          TC_PROF_ADD(mi, w2);
-          TC_PROF_T(w3);
           ptx::umma_commit(&ctrl->empty[s]);
           if (per_block) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
-          TC_PROF_ADD(mc, w3);
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1; }
         }
         if (!per_block && ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
       }
-      TC_PROF_PRINT("mma: total %lld wait_full %lld wait_acc %lld issue %lld commit %lld\n", clock64() - mt0, mf, ma,
-                    mi, mc);
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
@@ -296,7 +263,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_it = 0;
     int cursor = 0;
     bool ok = true;
-    TC_PROF_DECL(ew = 0, et0 = clock64());
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       TileInfo ti;
       locate_tile<BT>(tile_start, row_start, t, cursor, ti, p.w_experts);
@@ -307,11 +273,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       if (!kFp8) {
         const uint32_t a = acc_it % kAccStages;
-        TC_PROF_T(e0);
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
           *abort_flag = 1; ok = false; break;
         }
-        TC_PROF_ADD(ew, e0);
         ptx::tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < BT; c0 += kChunk) {
@@ -366,11 +330,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               if (lane + 32 * u < kCols) ptx::sts32f(sc + (lane + 32 * u) * 4, cur.a[u][jb] * cur.w[jb]);
             __syncwarp();
             const uint32_t a = acc_it % kAccStages;
-            TC_PROF_T(e1);
             if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it / kAccStages) & 1, abort_flag))) {
               *abort_flag = 1; ok = false; break;
             }
-            TC_PROF_ADD(ew, e1);
             ptx::tc_fence_after();
 #pragma unroll
             for (int c0 = 0; c0 < kCols; c0 += kChunk) {
@@ -416,7 +378,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-    if (warp == 2 && lane == 0) TC_PROF_PRINT("epilogue: total %lld wait_acc_full %lld\n", clock64() - et0, ew);
   }
 
   // Teardown: everyone meets here, also after an aborted wait.
@@ -427,19 +388,15 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (*abort_flag != 0) __nanosleep(20000);  // let copies still in flight land
     ptx::tmem_dealloc(tmem_base, tmem_cols<BT, kFp8>());
   }
-  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+  if (tid == 0 && *abort_flag != 0) report_timeout(p.status);
 }
 
 template <int BT, bool kFp8, bool kWKn>
 int launch_tc(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, int grid,
               cudaStream_t st) {
   auto kern = grouped_gemm_tc_kernel<BT, kFp8, kWKn>;
-  static bool configured = false;
-  if (!configured) {
-    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem_bytes<BT, kFp8>()));
-    configured = true;
-  }
+  static SmemConfig configured;
+  if (int rc = configured.ensure(kern, smem_bytes<BT, kFp8>())) return rc;
   kern<<<grid, kTcThreads, smem_bytes<BT, kFp8>(), st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_tc_kernel");
   return B200MOE_OK;
@@ -479,7 +436,8 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   p.num_kb = (a->k + kpb - 1) / kpb;
   p.out_f16 = a->d_dtype == B200MOE_F16;
 
-  const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
+  const int64_t rows_in_use = (a->rows_hint > 0 && a->rows_hint < a->m) ? a->rows_hint : a->m;
+  const int64_t avg = (rows_in_use + a->num_experts - 1) / a->num_experts;
   // Token-tile width from the mean rows per expert (routing is never perfectly
   // even, so leave headroom before a second token tile re-reads the weights).
   int bt;
@@ -492,11 +450,6 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   else if (avg <= 40) bt = 64;
   else if (avg <= 96) bt = 128;   // measured on skewed routing: 128 rows per expert are 13 % faster at 256
   else bt = 256;
-  {
-    static int force_bt = -1;
-    if (force_bt < 0) { const char* e = getenv("B200MOE_BT"); force_bt = e ? atoi(e) : 0; }
-    if (force_bt == 16 || force_bt == 64 || force_bt == 128 || (force_bt == 256 && !a_fp8)) bt = force_bt;
-  }
 
   // prefill-sized fp8 segments: the token-major kernels (one scale register per thread and K block)
   if (a_fp8 && bt >= 128) return grouped_gemm_tc_fp8t(a, st);

@@ -2,6 +2,8 @@
 // ragged expert segments, output conversion, and host-side tensor-map encoding.
 #pragma once
 
+#include <atomic>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -38,6 +40,15 @@ __device__ __forceinline__ void locate_tile(const int* tile_start, const int* ro
 __device__ __forceinline__ void store_out(void* d, int out_f16, int64_t idx, float v) {
   if (out_f16) reinterpret_cast<__half*>(d)[idx] = __float2half_rn(v);
   else reinterpret_cast<__nv_bfloat16*>(d)[idx] = __float2bfloat16_rn(v);
+}
+// A bounded wait gave up: tell the caller through its status word.  A plain store, so the
+// word may live in device memory or in mapped host memory that the host polls without a
+// synchronisation.
+__device__ __forceinline__ void report_timeout(int32_t* status) {
+  if (status != nullptr) {
+    *reinterpret_cast<volatile int32_t*>(status) = 1;
+    __threadfence_system();
+  }
 }
 __device__ __forceinline__ float load_bias(const void* b, int out_f16, int64_t idx) {
   if (out_f16) return __half2float(reinterpret_cast<const __half*>(b)[idx]);
@@ -145,16 +156,42 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* b
   return B200MOE_OK;
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
+constexpr int kMaxDevices = 64;
+
+inline int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
 }
+
+// SM count of the current device (cached per device: a process may drive several).
+int sm_count() {
+  static std::atomic<int> n[kMaxDevices];
+  const int dev = current_device();
+  int v = n[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    if (v <= 0) v = 148;
+    n[dev].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (kernel, device) pair: the
+// largest size set so far is remembered per device, so a process that drives several GPUs
+// configures the kernel on each of them.  One static instance per kernel instantiation.
+struct SmemConfig {
+  std::atomic<size_t> bytes[kMaxDevices];
+  template <typename Kern>
+  int ensure(Kern kern, size_t need) {
+    const int dev = current_device();
+    if (bytes[dev].load(std::memory_order_acquire) < need) {
+      B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
+      bytes[dev].store(need, std::memory_order_release);
+    }
+    return B200MOE_OK;
+  }
+};
 
 
 }  // namespace

@@ -23,8 +23,6 @@
 // vllm-xpu-kernels: LUT[code] * 2^(byte-127) (INT4: nibble * scale) rounded to
 // the activation type before the multiply, fp32 accumulation, bias added in fp32.
 #include <cuda_fp4.h>
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "gemm_tc_common.cuh"
 #include "sm100_ptx.cuh"
@@ -447,7 +445,7 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (*abort_flag != 0) __nanosleep(20000);
     ptx::tmem_dealloc(tmem_base, dq_tmem_cols<BT>());
   }
-  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+  if (tid == 0 && *abort_flag != 0) report_timeout(p.status);
 }
 
 template <int BT, bool kInt4, bool kF16, int kSub>
@@ -459,11 +457,8 @@ int launch_dq(const CUtensorMap& ta, const CUtensorMap& tw, DqParams& p, int gri
   if (p.stages > kDqMaxStages) p.stages = kDqMaxStages;
   if (p.stages < 2) return fail(B200MOE_E_UNSUPPORTED, "dequantising tensor-core GEMM: tile does not fit shared memory");
   const size_t smem = (size_t)fixed + (size_t)p.stages * p.stage_bytes;
-  static size_t configured = 0;
-  if (configured < smem) {
-    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
-  }
+  static SmemConfig configured;
+  if (int rc = configured.ensure(kern, smem)) return rc;
   kern<<<grid, kDqThreads, smem, st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_dq_kernel");
   return B200MOE_OK;
@@ -506,13 +501,9 @@ int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st) {
   p.swiglu = a->epilogue == B200MOE_EPI_SWIGLUOAI;
   p.alpha = a->act_alpha; p.limit = a->act_limit; p.clamp_limit = a->clamp_limit;
 
-  const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
+  const int64_t rows_in_use = (a->rows_hint > 0 && a->rows_hint < a->m) ? a->rows_hint : a->m;
+  const int64_t avg = (rows_in_use + a->num_experts - 1) / a->num_experts;
   int bt = avg <= 8 ? 16 : (avg <= 40 ? 64 : 128);
-  {
-    static int force = -1;
-    if (force < 0) { const char* e = getenv("B200MOE_BT"); force = e ? atoi(e) : 0; }
-    if (force == 16 || force == 64 || force == 128) bt = force;
-  }
   const bool f16 = a->a_dtype == B200MOE_F16;
   const uint32_t fmt = f16 ? 0u : 1u;
   p.idesc = ptx::make_idesc(fmt, fmt, 0u, 0u, kFeat, (uint32_t)bt);

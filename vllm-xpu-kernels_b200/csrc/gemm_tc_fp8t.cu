@@ -29,19 +29,6 @@
 #include "gemm_tc_common.cuh"
 #include "sm100_ptx.cuh"
 
-// Cycle accounting of CTA 0 (printed at kernel end); compiled in only with -DB200_TC_PROF.
-#ifdef B200_TC_PROF
-#include <stdio.h>
-#define T_PROF_DECL(...) long long __VA_ARGS__
-#define T_PROF_T(var) const long long var = clock64()
-#define T_PROF_ADD(acc, t0) acc += clock64() - (t0)
-#define T_PROF_PRINT(...) if (blockIdx.x == 0) printf(__VA_ARGS__)
-#else
-#define T_PROF_DECL(...)
-#define T_PROF_T(var)
-#define T_PROF_ADD(acc, t0)
-#define T_PROF_PRINT(...)
-#endif
 
 namespace b200moe {
 namespace {
@@ -284,7 +271,7 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (*abort_flag != 0) __nanosleep(20000);  // let copies still in flight land
     ptx::tmem_dealloc(tmem_base, 512);
   }
-  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+  if (tid == 0 && *abort_flag != 0) report_timeout(p.status);
 }
 
 // ---------------------------------------------------------------------------------
@@ -391,18 +378,12 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) ++my_tiles;
       const int64_t blocks = (int64_t)my_tiles * p.num_kb;
       const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((256u >> 3) << 17);
-      T_PROF_DECL(ma = 0, mf = 0, mi = 0, mc = 0, mt0 = clock64());
       // The barriers of the next block are polled between this block's MMA issues, where
       // the thread would otherwise only wait for room in the tensor pipe's queue.
       bool full_ready = false, acc_ready = false;
       for (int64_t i = 0; i < blocks; ++i) {
-        T_PROF_T(w0);
         if (!acc_ready && !ptx::mbar_wait(&ctrl->acc_empty[a], aph ^ 1, abort_flag)) break;
-        T_PROF_ADD(ma, w0);
-        T_PROF_T(w1);
         if (!full_ready && !ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) break;
-        T_PROF_ADD(mf, w1);
-        T_PROF_T(w2);
         ptx::tc_fence_after();
         const uint32_t st_addr = smem_base + s * kT2StageBytes;
         const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
@@ -416,16 +397,11 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
         full_ready = more && ptx::mbar_test_wait(&ctrl->full[s1], ph1);
         ptx::umma<true>(d_tmem, adesc0 + (uint64_t)(64 >> 4), wdesc0 + (uint64_t)((2 * kWStep) >> 4), idesc, 1u);
         ptx::umma<true>(d_tmem, adesc0 + (uint64_t)(96 >> 4), wdesc0 + (uint64_t)((3 * kWStep) >> 4), idesc, 1u);
-        T_PROF_ADD(mi, w2);
-        T_PROF_T(w3);
         ptx::umma_commit(&ctrl->empty[s]);
         ptx::umma_commit(&ctrl->acc_full[a]);
-        T_PROF_ADD(mc, w3);
         acc_ready = more && ptx::mbar_test_wait(&ctrl->acc_empty[a1], aph1 ^ 1u);
         s = s1; ph = ph1; a = a1; aph = aph1;
       }
-      T_PROF_PRINT("mma: blocks %lld total %lld wait_acc %lld wait_full %lld issue %lld commit %lld\n", (long long)blocks,
-                   clock64() - mt0, ma, mf, mi, mc);
     }
   } else {
     // ------------------------ promotion and epilogue --------------------------
@@ -459,7 +435,6 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int cursor = 0;
     bool ok = true;
     const int n_groups = (p.num_kb + kTGroup - 1) / kTGroup;
-    T_PROF_DECL(ew = 0, et0 = clock64());
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       TileInfo ti;
       locate_tile<kTTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
@@ -484,11 +459,9 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int jb = 0; jb < kTGroup; ++jb) {
           if (g * kTGroup + jb >= p.num_kb) break;
           const float sc = cur.a[jb] * cur.w[jb];
-          T_PROF_T(e0);
           if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], aph, abort_flag))) {
             *abort_flag = 1; ok = false; break;
           }
-          T_PROF_ADD(ew, e0);
           ptx::tc_fence_after();
           const uint32_t col = tmem_base + a * 256 + half * 128 + lane_sel;
 #pragma unroll
@@ -536,7 +509,6 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-    if (warp == 4 && lane == 0) T_PROF_PRINT("epilogue: total %lld wait_acc_full %lld\n", clock64() - et0, ew);
   }
 
   ptx::tc_fence_before();
@@ -546,17 +518,14 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (*abort_flag != 0) __nanosleep(20000);
     ptx::tmem_dealloc(tmem_base, 512);
   }
-  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+  if (tid == 0 && *abort_flag != 0) report_timeout(p.status);
 }
 
 template <bool kWKn>
 int launch_fp8t256(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& p, int grid, cudaStream_t st) {
   auto kern = grouped_gemm_fp8t256_kernel<kWKn>;
-  static bool configured = false;
-  if (!configured) {
-    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kT2Smem));
-    configured = true;
-  }
+  static SmemConfig configured;
+  if (int rc = configured.ensure(kern, kT2Smem)) return rc;
   kern<<<grid, kT2Threads, kT2Smem, st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_fp8t256_kernel");
   return B200MOE_OK;
@@ -565,11 +534,8 @@ int launch_fp8t256(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& 
 template <bool kWKn>
 int launch_fp8t(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& p, int grid, cudaStream_t st) {
   auto kern = grouped_gemm_fp8t_kernel<kWKn>;
-  static bool configured = false;
-  if (!configured) {
-    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTSmem));
-    configured = true;
-  }
+  static SmemConfig configured;
+  if (int rc = configured.ensure(kern, kTSmem)) return rc;
   kern<<<grid, kTThreads, kTSmem, st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_fp8t_kernel");
   return B200MOE_OK;

@@ -41,26 +41,10 @@
 // exact, accumulation is fp32; the difference from the reference's w4a16 path
 // (csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:411-471 of vllm-xpu-kernels) is the
 // rounding of the activations to MXFP8 only.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "gemm_tc_common.cuh"
 #include "sm100_ptx.cuh"
 
-// Cycle accounting of the roles of CTA 0 (printed at kernel end); compiled in
-// only with -DB200_MX_PROF, for experiments.
-#ifdef B200_MX_PROF
-#include <stdio.h>
-#define MX_PROF_DECL(...) long long __VA_ARGS__
-#define MX_PROF_T(var) const long long var = clock64()
-#define MX_PROF_ADD(acc, t0) acc += clock64() - (t0)
-#define MX_PROF_PRINT(...) if (blockIdx.x == 0) printf(__VA_ARGS__)
-#else
-#define MX_PROF_DECL(...)
-#define MX_PROF_T(var)
-#define MX_PROF_ADD(acc, t0)
-#define MX_PROF_PRINT(...)
-#endif
 
 namespace b200moe {
 namespace {
@@ -236,15 +220,12 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t s = 0, ph = 0;
       int cursor = 0;
       bool ok = true;
-      MX_PROF_DECL(pw = 0, pt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         const int n0 = ti.n_tile * kFeat;
         for (int si = 0; si < num_st; ++si) {
-          MX_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-          MX_PROF_ADD(pw, w0);
           uint8_t* st = smem + s * stage_bytes;
           const int kb0 = si * kSub;
           const int nsub = (p.num_kb - kb0) < kSub ? (p.num_kb - kb0) : kSub;
@@ -268,7 +249,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (++s == (uint32_t)stages) { s = 0; ph ^= 1; }
         }
       }
-      MX_PROF_PRINT("producer: total %lld wait_empty %lld\n", clock64() - pt0, pw);
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
@@ -280,14 +260,11 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t idesc_j[4];
 #pragma unroll
       for (uint32_t j = 0; j < 4; ++j) idesc_j[j] = (p.idesc & ~(0x3fu << 17)) | (j << 29) | (j << 4);
-      MX_PROF_DECL(mf = 0, ms = 0, ma = 0, mi = 0, mc = 0, mt0 = clock64());
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         const uint32_t a = acc_it & 1;
-        MX_PROF_T(wa0);
         if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) break;
-        MX_PROF_ADD(ma, wa0);
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * kNT;
         // A partly filled token tile multiplies only up to its last valid column (UMMA N in
@@ -295,13 +272,8 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t n_eff = (uint32_t)((kTerms - 1) * BT + ((ti.valid + 15) & ~15));
         const uint32_t n_bits = (n_eff >> 3) << 17;
         for (int si = 0; si < num_st; ++si) {
-          MX_PROF_T(w0);
           if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
-          MX_PROF_ADD(mf, w0);
-          MX_PROF_T(w1);
           if (!ptx::mbar_wait(&ctrl->sf_full[s], ph, abort_flag)) { ok = false; break; }
-          MX_PROF_ADD(ms, w1);
-          MX_PROF_T(w2);
           ptx::tc_fence_after();
           // Every operand descriptor of the stage is the first weight block's plus a
           // compile-time offset (the address field counts 16-byte units).
@@ -324,16 +296,11 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           }
-          MX_PROF_ADD(mi, w2);
-          MX_PROF_T(w3);
           ptx::umma_commit(&ctrl->empty[s]);
-          MX_PROF_ADD(mc, w3);
           if (++s == (uint32_t)stages) { s = 0; ph ^= 1; }
         }
         if (ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
       }
-      MX_PROF_PRINT("mma: total %lld wait_full %lld wait_sf %lld wait_acc %lld issue %lld commit %lld\n",
-                    clock64() - mt0, mf, ms, ma, mi, mc);
     }
   } else if (warp < 6) {
     // ------------------------------ scale feeders ------------------------------
@@ -347,7 +314,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t s = 0, ph = 0;
     int cursor = 0, cursor_next = 0, cursor_la = 0;
     bool ok = true;
-    MX_PROF_DECL(fw = 0, fl = 0, fs = 0, ff = 0, fsw = 0, fq = 0, ft0 = clock64());
 
     // Token scales of kMxGroup K blocks: word [plane][kb][row], coalesced over the
     // lanes.  They are read two groups ahead of their use (cur <- nxt <- nx2), by a
@@ -411,9 +377,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t sfw_s = ptx::smem_u32(sfw + b * p.sfw_bytes);
       const int n0 = ti.n_tile * kFeat;
       for (int g = 0; g < n_groups && ok; ++g) {
-        MX_PROF_T(q0);
         if (la_valid) { fetch_b(la_ti, la_g, nx2_b); B200_MX_LA_ADVANCE(); }
-        MX_PROF_ADD(fq, q0);
 #pragma unroll
         for (int u = 0; u < kMxGroup; ++u) {
           const int kb = g * kMxGroup + u;
@@ -422,7 +386,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // Four scale bytes per row from the staged piece: two aligned words and a
             // funnel shift (rows are K/32 bytes apart, any alignment); bytes of groups
             // past the row end become 0x7f.
-            MX_PROF_T(l0);
             uint32_t wa[4];
             const int left = kgroups - 4 * kb;
             const uint32_t keep = left >= 4 ? 0xffffffffu : ((1u << (8 * left)) - 1u);
@@ -445,16 +408,12 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 wa[j] = 0x7f7f7f7fu;   // per-tensor scale: applied in the epilogue
               }
             }
-            MX_PROF_ADD(fl, l0);
             if (sub == 0) {   // the stage's scale columns and weight buffer are free again
-              MX_PROF_T(w0);
               if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag))) {
                 *abort_flag = 1; ok = false;
               }
               ptx::tc_fence_after();
-              MX_PROF_ADD(fw, w0);
             }
-            MX_PROF_T(s0);
             if (ok) {
               const uint32_t col = tmem_base + kSfBase + s * kSfCols + kSfPer * sub + lane_sel;
               {
@@ -485,8 +444,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   ptx::fence_proxy_async();
                 }
               }
-              MX_PROF_ADD(fs, s0);
-              MX_PROF_T(f0);
               if (sub == kSub - 1 || kb == p.num_kb - 1) {   // last K block of the stage
                 ptx::tmem_wait_st();
                 ptx::tc_fence_before();
@@ -494,16 +451,13 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (lane == 0) ptx::mbar_arrive(&ctrl->sf_full[s]);
                 if (++s == (uint32_t)stages) { s = 0; ph ^= 1; }
               }
-              MX_PROF_ADD(ff, f0);
             }
           }
         }
-        MX_PROF_T(r0);
 #pragma unroll
         for (int u = 0; u < kMxGroup; ++u)
 #pragma unroll
           for (int j = 0; j < kW; ++j) { cur_b[u][j] = nxt_b[u][j]; nxt_b[u][j] = nx2_b[u][j]; }
-        MX_PROF_ADD(fsw, r0);
       }
       if (staged) {
         __syncwarp();
@@ -512,8 +466,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 #undef B200_MX_LA_ADVANCE
     if (warp == 2 && lane == 0)
-      MX_PROF_PRINT("feeder: total %lld wait_empty %lld lds %lld st %lld finish %lld rotate %lld fetch %lld\n",
-                    clock64() - ft0, fw, fl, fs, ff, fsw, fq);
     ptx::cp_async_wait_all();
   } else {
     // ------------------------------ epilogue ----------------------------------
@@ -524,7 +476,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_it = 0;
     int cursor = 0;
     bool ok = true;
-    MX_PROF_DECL(ew = 0, el = 0, em = 0, es = 0, et0 = clock64());
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       TileInfo ti;
       locate_tile<BT>(tile_start, row_start, t, cursor, ti);
@@ -536,9 +487,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t a = acc_it & 1;
       // a whole tile's MMAs away: poll from one lane, sleeping in between, so that the
       // wait does not take issue slots from the feeder warp on the same scheduler
-      MX_PROF_T(w0);
       if (!ptx::mbar_wait_warp(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag, 128)) { ok = false; break; }
-      MX_PROF_ADD(ew, w0);
       ptx::tc_fence_after();
 #pragma unroll
       for (int c0 = 0; c0 < BT; c0 += kChunk) {
@@ -547,7 +496,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
           float acc[kChunk];
 #pragma unroll
           for (int i = 0; i < kChunk; ++i) acc[i] = 0.f;
-          MX_PROF_T(l0);
 #pragma unroll
           for (int term = 0; term < kTerms; ++term) {   // the planes' partial results add up
             const uint32_t col = tmem_base + a * kNT + term * BT + c0 + lane_sel;
@@ -557,8 +505,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int i = 0; i < kChunk; ++i) acc[i] += __uint_as_float(v[i]);
           }
-          MX_PROF_ADD(el, l0);
-          MX_PROF_T(m0);
           float vals[kChunk];
 #pragma unroll
           for (int i = 0; i < kChunk; ++i) vals[i] = kW8 ? fmaf(acc[i], w_mul, bias_v) : acc[i] + bias_v;
@@ -580,8 +526,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
               vals[i] = (up + 1.0f) * gate * __fdividef(1.0f, 1.0f + __expf(-gate * p.alpha));
             }
           }
-          MX_PROF_ADD(em, m0);
-          MX_PROF_T(s0);
           if (p.swiglu)
             store_block_transposed<kChunk, 16>(ctrl->xpose[warp - 6], vals, p.d, p.out_f16,
                                                (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
@@ -590,7 +534,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
             store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 6], vals, p.d, p.out_f16,
                                                (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
                                                ti.n_tile * kFeat + q * 32, lane);
-          MX_PROF_ADD(es, s0);
         }
       }
       ptx::tc_fence_before();
@@ -598,8 +541,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (lane == 0) ptx::mbar_arrive(&ctrl->acc_empty[a]);
       ++acc_it;
     }
-    if (warp == 6 && lane == 0)
-      MX_PROF_PRINT("epilogue: total %lld wait %lld tmem %lld math %lld store %lld\n", clock64() - et0, ew, el, em, es);
   }
 
   ptx::tc_fence_before();
@@ -609,7 +550,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (*abort_flag != 0) __nanosleep(20000);
     ptx::tmem_dealloc(tmem_base, p.tmem_cols);
   }
-  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 1);
+  if (tid == 0 && *abort_flag != 0) report_timeout(p.status);
 }
 
 template <int BT, int kTerms, int kSub, bool kW8>
@@ -637,11 +578,8 @@ int launch_mx(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& t
   if (p.stages > kMxMaxStages) p.stages = kMxMaxStages;
   if (p.stages < 2) return fail(B200MOE_E_UNSUPPORTED, "block-scaled GEMM: tile does not fit shared memory");
   const size_t smem = (size_t)fixed + (size_t)p.stages * p.stage_bytes + (p.raw_shared ? kMxRawBytes : 0);
-  static size_t configured = 0;
-  if (configured < smem) {
-    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
-  }
+  static SmemConfig configured;
+  if (int rc = configured.ensure(kern, smem)) return rc;
   kern<<<grid, kMxThreads, smem, st>>>(ta, tw, traw, p);
   B200_LAUNCH_OK("grouped_gemm_mx_kernel");
   return B200MOE_OK;
@@ -709,18 +647,14 @@ int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st) {
   p.swiglu = a->epilogue == B200MOE_EPI_SWIGLUOAI;
   p.alpha = a->act_alpha; p.limit = a->act_limit; p.clamp_limit = a->clamp_limit;
 
-  const int64_t avg = (a->m + a->num_experts - 1) / a->num_experts;
+  const int64_t rows_in_use = (a->rows_hint > 0 && a->rows_hint < a->m) ? a->rows_hint : a->m;
+  const int64_t avg = (rows_in_use + a->num_experts - 1) / a->num_experts;
   int bt = avg <= 8 ? 16 : (avg <= 40 ? 64 : 128);
   // both planes' accumulators share tensor memory: two planes of 96 tokens are one MMA of
   // N = 192 (enough work per instruction to keep the tensor pipe busy), two stages of them
   // and the scale columns fill the 512 columns
   if (x2 && bt > 64) bt = avg > 48 ? 96 : 64;   // measured: 64 rows per expert -22 %, 32 rows +8 %
   if (!x2 && avg > 128) bt = 192;               // one plane: the same N = 192 instruction
-  {
-    static int force = -1;
-    if (force < 0) { const char* e = getenv("B200MOE_BT"); force = e ? atoi(e) : 0; }
-    if (force == 16 || force == 64 || (force == 96 && x2) || ((force == 128 || force == 192) && !x2)) bt = force;
-  }
   // weights: e2m1 K-major, or e4m3 / e5m2 MN-major; activations e4m3 K-major
   const uint32_t a_fmt = w4 ? 5u : (a->w_format == B200MOE_W_FP8E5M2_TENSOR_KN ? 1u : 0u);
   p.idesc = ptx::make_idesc_mx(a_fmt, 0u, kFeat, (uint32_t)(bt * p.terms)) | (w8 ? (1u << 15) : 0u);

@@ -60,7 +60,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag, bool spin = false) {
+                                          volatile int* abort_flag, bool spin = false,
+                                          long long budget_cycles = kWaitBudgetCycles) {
   if (spin) {
     if (mbar_test_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -68,7 +69,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     while (!mbar_test_wait(bar, parity)) {
       if ((++spins & 0xfff) == 0) {
         if (*abort_flag != 0) return false;
-        if (clock64() - t0 > kWaitBudgetCycles) {
+        if (clock64() - t0 > budget_cycles) {
           *abort_flag = 1;
           return false;
         }
@@ -82,7 +83,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xff) == 0) {
       if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget_cycles) {
         *abort_flag = 1;
         return false;
       }

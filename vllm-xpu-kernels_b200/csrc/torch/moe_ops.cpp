@@ -429,6 +429,78 @@ void b200_remap_quant_fp8(at::Tensor& hidden_states, at::Tensor& remapped_q, at:
       (int)local_experts_num, ws.numel() ? ws.data_ptr() : nullptr, (size_t)ws.numel(), current_stream()));
 }
 
+
+// ---- expert parallelism over peer memory (no counterpart in the reference) ----------
+// `tables` is an int64 CPU tensor [6, ep]: for every rank the addresses, as this process
+// sees them, of recv_rows, recv_scales, recv_ids, recv_weights, recv_counts, comb_rows.
+b200moe_ep_peers make_peers(const at::Tensor& tables, int64_t ep_rank, int64_t num_local_experts,
+                            int64_t topk, int64_t hidden, int64_t capacity, bool quantized) {
+  TORCH_CHECK(tables.device().is_cpu() && tables.scalar_type() == at::kLong && tables.dim() == 2 &&
+              tables.size(0) == 6 && tables.is_contiguous(), "tables must be an int64 CPU tensor [6, ep]");
+  const int64_t ep = tables.size(1);
+  TORCH_CHECK(ep >= 1 && ep <= B200MOE_MAX_EP, "at most ", B200MOE_MAX_EP, " expert-parallel ranks");
+  b200moe_ep_peers pe = {};
+  pe.ep_size = (int)ep; pe.ep_rank = (int)ep_rank; pe.num_local_experts = (int)num_local_experts;
+  pe.topk = (int)topk; pe.hidden = (int)hidden; pe.quantized = quantized ? 1 : 0; pe.capacity = capacity;
+  const int64_t* t = tables.data_ptr<int64_t>();
+  for (int64_t d = 0; d < ep; ++d) {
+    pe.recv_rows[d] = reinterpret_cast<void*>(t[0 * ep + d]);
+    pe.recv_scales[d] = reinterpret_cast<float*>(t[1 * ep + d]);
+    pe.recv_ids[d] = reinterpret_cast<int32_t*>(t[2 * ep + d]);
+    pe.recv_weights[d] = reinterpret_cast<float*>(t[3 * ep + d]);
+    pe.recv_counts[d] = reinterpret_cast<int32_t*>(t[4 * ep + d]);
+    pe.comb_rows[d] = reinterpret_cast<void*>(t[5 * ep + d]);
+  }
+  return pe;
+}
+
+void b200_ep_dispatch(const at::Tensor& hidden_states, const at::Tensor& topk_ids, const at::Tensor& topk_weights,
+                      at::Tensor& send_counts, at::Tensor& send_pos, at::Tensor& workspace,
+                      const at::Tensor& tables, int64_t ep_rank, int64_t num_local_experts, int64_t capacity,
+                      bool quantized) {
+  check_cuda(hidden_states, "hidden_states");
+  TORCH_CHECK(hidden_states.dim() == 2 && hidden_states.is_contiguous(), "hidden_states must be contiguous [T, H]");
+  const int64_t T = hidden_states.size(0), H = hidden_states.size(1);
+  TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.size(0) == T && topk_ids.is_contiguous(), "topk_ids must be [T, K]");
+  const int64_t K = topk_ids.size(1), ep = tables.size(1);
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat && topk_weights.is_contiguous() &&
+              topk_weights.numel() == T * K, "topk_weights must be float32 [T, K]");
+  TORCH_CHECK(send_counts.scalar_type() == at::kInt && send_counts.numel() == ep && send_counts.is_contiguous(),
+              "send_counts must be int32 [ep]");
+  TORCH_CHECK(send_pos.scalar_type() == at::kInt && send_pos.numel() == T * ep && send_pos.is_contiguous(),
+              "send_pos must be int32 [T, ep]");
+  const b200moe_ep_peers pe = make_peers(tables, ep_rank, num_local_experts, K, H, capacity, quantized);
+  const size_t need = b200moe_ep_dispatch_workspace_bytes(T, (int)ep);
+  TORCH_CHECK((size_t)workspace.numel() * workspace.element_size() >= need, "workspace of ", need, " bytes needed");
+  const c10::cuda::CUDAGuard guard(hidden_states.device());
+  check_status(b200moe_ep_dispatch(&pe, hidden_states.data_ptr(), float_dtype(hidden_states, "b200_ep_dispatch"),
+                                   topk_ids.data_ptr(), index_dtype(topk_ids), topk_weights.data_ptr<float>(), T,
+                                   send_counts.data_ptr<int32_t>(), send_pos.data_ptr<int32_t>(),
+                                   need ? workspace.data_ptr() : nullptr, need, current_stream()));
+}
+
+void b200_ep_mask_unused(const at::Tensor& anchor, const at::Tensor& tables, int64_t ep_rank,
+                         int64_t num_local_experts, int64_t topk, int64_t hidden, int64_t capacity, bool quantized) {
+  check_cuda(anchor, "anchor");
+  const b200moe_ep_peers pe = make_peers(tables, ep_rank, num_local_experts, topk, hidden, capacity, quantized);
+  const c10::cuda::CUDAGuard guard(anchor.device());
+  check_status(b200moe_ep_mask_unused(&pe, current_stream()));
+}
+
+void b200_ep_combine(const at::Tensor& moe_output, const at::Tensor& row_map, const at::Tensor& tables,
+                     int64_t ep_rank, int64_t num_local_experts, int64_t capacity, bool quantized) {
+  check_cuda(moe_output, "moe_output");
+  TORCH_CHECK(moe_output.dim() == 2 && moe_output.is_contiguous(), "moe_output must be contiguous [M, H]");
+  const int64_t ep = tables.size(1);
+  TORCH_CHECK(row_map.scalar_type() == at::kInt && row_map.is_contiguous() && row_map.dim() == 2 &&
+              row_map.size(0) == ep * capacity, "row_map must be int32 [ep * capacity, K]");
+  const b200moe_ep_peers pe = make_peers(tables, ep_rank, num_local_experts, row_map.size(1), moe_output.size(1),
+                                         capacity, quantized);
+  const c10::cuda::CUDAGuard guard(moe_output.device());
+  check_status(b200moe_ep_combine(&pe, moe_output.data_ptr(), row_map.data_ptr<int32_t>(),
+                                  float_dtype(moe_output, "b200_ep_combine"), current_stream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(_moe_C, m) {
@@ -489,6 +561,16 @@ TORCH_LIBRARY_FRAGMENT(_moe_C, m) {
       "()");
   m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
   m.def(
+      "b200_ep_dispatch(Tensor hidden_states, Tensor topk_ids, Tensor topk_weights, Tensor(a!) send_counts, "
+      "Tensor(b!) send_pos, Tensor(c!) workspace, Tensor tables, int ep_rank, int num_local_experts, "
+      "int capacity, bool quantized) -> ()");
+  m.def(
+      "b200_ep_mask_unused(Tensor anchor, Tensor tables, int ep_rank, int num_local_experts, int topk, "
+      "int hidden, int capacity, bool quantized) -> ()");
+  m.def(
+      "b200_ep_combine(Tensor moe_output, Tensor row_map, Tensor tables, int ep_rank, int num_local_experts, "
+      "int capacity, bool quantized) -> ()");
+  m.def(
       "remap_hidden_states(Tensor hidden_states, Tensor? hidden_states_scales, "
       "Tensor remapped_hidden_states,"
       "Tensor? remapped_hidden_states_scales,"
@@ -515,6 +597,9 @@ TORCH_LIBRARY_IMPL(_moe_C, CUDA, m) {
   m.impl("topk_sigmoid", &topk_sigmoid);
   m.impl("moe_gather", &moe_gather);
   m.impl("init_expert_map", &init_expert_map);
+  m.impl("b200_ep_dispatch", &b200_ep_dispatch);
+  m.impl("b200_ep_mask_unused", &b200_ep_mask_unused);
+  m.impl("b200_ep_combine", &b200_ep_combine);
   m.impl("remap_hidden_states", &remap_hidden_states);
   m.impl("b200_remap_quant_fp8", &b200_remap_quant_fp8);
 }

@@ -6,9 +6,36 @@
 // 322-383, 397-398.
 #include "shim.h"
 
+#include <mutex>
+
 using namespace b200shim;
 
 namespace {
+
+// One status word per device, in pinned host memory that the device can write and the host
+// can read without a synchronisation.  A grouped GEMM whose bounded wait ran out sets it to 1
+// (b200moe_gemm_args.status); the next grouped-GEMM call on that device, or an explicit
+// b200_check_status, raises and clears it.  Allocated on first use, kept for the process.
+constexpr int kMaxStatusDevices = 64;
+std::mutex g_status_mutex;
+at::Tensor g_status[kMaxStatusDevices];
+
+int32_t* device_status_word(int device) {
+  TORCH_CHECK(device >= 0 && device < kMaxStatusDevices, "device index out of range");
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (!g_status[device].defined()) {
+    g_status[device] = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCPU).pinned_memory(true));
+  }
+  return g_status[device].data_ptr<int32_t>();
+}
+
+void raise_if_timed_out(int32_t* word) {
+  volatile int32_t* w = word;
+  if (*w != 0) {
+    *w = 0;
+    check_status(b200moe_status_to_code(1));
+  }
+}
 
 // layout: 0 = as the reference infers it from shapes, 1 = [E,N,K], 2 = [E,K,N]
 at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>& ptr_A_scale,
@@ -16,7 +43,8 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
                              const std::optional<at::Tensor>& ptr_bias, at::Tensor& ptr_D,
                              at::Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                              int64_t layout, int64_t epilogue, double alpha, double limit,
-                             double clamp_limit, int64_t impl, int64_t max_ctas, bool allow_segments) {
+                             double clamp_limit, int64_t impl, int64_t max_ctas, bool allow_segments,
+                             int64_t rows_hint = 0) {
   check_cuda(ptr_A, "ptr_A");
   const auto A_dtype = ptr_A.scalar_type();
   const auto B_dtype = ptr_B.scalar_type();
@@ -167,10 +195,13 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   g.w_experts = segments != num_experts ? (int)num_experts : 0;
   g.epilogue = (b200moe_epilogue)epilogue;
   g.act_alpha = (float)alpha; g.act_limit = (float)limit; g.clamp_limit = (float)clamp_limit;
-  g.status = nullptr;
+  int32_t* status_word = device_status_word(ptr_A.get_device());
+  raise_if_timed_out(status_word);   // an earlier call on this device gave up a wait
+  g.status = status_word;
   g.impl = (int)impl;
   g.max_ctas = (int)max_ctas;
   g.group_size = (int)group_size;
+  g.rows_hint = rows_hint;
   const c10::cuda::CUDAGuard guard(ptr_A.device());
   check_status(b200moe_grouped_gemm(&g, current_stream()));
   return ptr_D;
@@ -191,9 +222,30 @@ at::Tensor b200_grouped_gemm(at::Tensor ptr_A, const std::optional<at::Tensor>& 
                              const std::optional<at::Tensor>& ptr_bias, at::Tensor ptr_D,
                              at::Tensor rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                              int64_t layout, int64_t epilogue, double alpha, double limit,
-                             double clamp_limit, int64_t impl, int64_t max_ctas) {
+                             double clamp_limit, int64_t impl, int64_t max_ctas, int64_t rows_hint) {
   return grouped_gemm_impl(ptr_A, ptr_A_scale, ptr_B, ptr_B_scale, ptr_bias, ptr_D, rows_per_expert, N,
-                           K, num_experts, layout, epilogue, alpha, limit, clamp_limit, impl, max_ctas, true);
+                           K, num_experts, layout, epilogue, alpha, limit, clamp_limit, impl, max_ctas, true,
+                           rows_hint);
+}
+
+// Raises if a grouped GEMM on `like`'s device has given up a bounded wait since the last
+// check; with `synchronize` the device is synchronised first, so every call made so far is
+// covered.  Returns 0 otherwise.
+int64_t b200_check_status(const at::Tensor& like, bool synchronize) {
+  check_cuda(like, "like");
+  const c10::cuda::CUDAGuard guard(like.device());
+  if (synchronize) C10_CUDA_CHECK(cudaDeviceSynchronize());
+  raise_if_timed_out(device_status_word(like.get_device()));
+  return 0;
+}
+
+// Launches the bounded-wait self test (b200moe_selftest_bounded_wait) against this device's
+// status word: after it has run, b200_check_status raises exactly as it would after a
+// grouped GEMM that gave up.
+void b200_selftest_bounded_wait(const at::Tensor& like, int64_t budget_cycles) {
+  check_cuda(like, "like");
+  const c10::cuda::CUDAGuard guard(like.device());
+  check_status(b200moe_selftest_bounded_wait(device_status_word(like.get_device()), budget_cycles, current_stream()));
 }
 
 }  // namespace
@@ -207,12 +259,16 @@ TORCH_LIBRARY_FRAGMENT(_xpu_C, m) {
       "b200_grouped_gemm(Tensor ptr_A, Tensor? ptr_A_scale, Tensor ptr_B, Tensor? ptr_B_scale, "
       "Tensor? ptr_bias, Tensor(a!) ptr_D, Tensor rows_per_expert, int N, int K, int num_experts, "
       "int layout=0, int epilogue=0, float alpha=1.702, float limit=7.0, float clamp_limit=0.0, "
-      "int impl=0, int max_ctas=0) -> Tensor(a!)");
+      "int impl=0, int max_ctas=0, int rows_hint=0) -> Tensor(a!)");
+  m.def("b200_check_status(Tensor like, bool synchronize=True) -> int");
+  m.def("b200_selftest_bounded_wait(Tensor like, int budget_cycles) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(_xpu_C, CUDA, m) {
   m.impl("cutlass_grouped_gemm_interface", &cutlass_grouped_gemm_interface);
   m.impl("b200_grouped_gemm", &b200_grouped_gemm);
+  m.impl("b200_check_status", &b200_check_status);
+  m.impl("b200_selftest_bounded_wait", &b200_selftest_bounded_wait);
 }
 
 B200_REGISTER_EXTENSION(_xpu_C)

@@ -122,6 +122,37 @@ def compute_num_tokens_per_block(num_tokens, num_experts_per_node):
     return 1024
 
 
+# Intermediates of a layer call (permuted rows, the two GEMM outputs, scales, index maps) live
+# in one grow-only pool per device, shared by all layer objects: layers of a model run one after
+# the other on a stream, so the next call may overwrite what the previous one left.  A caller
+# that runs layer calls concurrently on several streams of one device must pass
+# ``persistent_workspace=False`` (fresh torch allocations per call, as the reference does).
+_WORKSPACE = {}
+
+
+def _pooled(name, shape, dtype, device):
+    n = 1
+    for d in shape:
+        n *= int(d)
+    key = (device, name, dtype)
+    buf = _WORKSPACE.get(key)
+    if buf is None or buf.numel() < n:
+        buf = torch.empty(max(n, 1), dtype=dtype, device=device)
+        _WORKSPACE[key] = buf
+    return buf[:n].view(shape)
+
+
+def _signed_nibbles(w):
+    """uint8 pairs of uint4 (zero point 8) -> int8 pairs of two's-complement int4, cached on
+    the source tensor while its contents are unchanged."""
+    cached = getattr(w, "_b200_signed_nibbles", None)
+    if cached is not None and cached[0] == w._version:
+        return cached[1]
+    conv = (w ^ 0x88).view(torch.int8)
+    w._b200_signed_nibbles = (w._version, conv)
+    return conv
+
+
 def _activation_kind(activation):
     """Maps the reference's activation names (:119-133, :239-254) to an op."""
     if activation in ("silu", "gelu", "gelu_tanh", "relu2_no_mul", "swiglustep"):
@@ -189,6 +220,7 @@ class XpuFusedMoe:
         *,
         fuse_activation: Optional[bool] = None,
         mxfp4_activations: Optional[str] = None,
+        persistent_workspace: bool = True,
     ):
         assert w13.is_contiguous() and w2.is_contiguous()
         _require_native()
@@ -205,10 +237,11 @@ class XpuFusedMoe:
         self.inter_size = _get_inter_size(w13, w13_scales, is_int4, is_mxfp4, is_block_fp8)
         if is_int4 and not getattr(w13, "xpu_fused_moe", False):
             # uint4 with the default zero point 8 -> two's-complement int4 (reference
-            # implement_zp, :135-162: u4 - 8 re-encoded per nibble, i.e. bit 3 flipped);
-            # the caller's tensors are left as they are
-            w13 = (w13 ^ 0x88).view(torch.int8)
-            w2 = (w2 ^ 0x88).view(torch.int8)
+            # implement_zp, :135-162: u4 - 8 re-encoded per nibble, i.e. bit 3 flipped).
+            # The caller's tensors are left as they are; the converted copy rides on them,
+            # so the functional form (a new layer object per call) converts once, as the
+            # reference does by marking its in-place conversion with `xpu_fused_moe`.
+            w13, w2 = _signed_nibbles(w13), _signed_nibbles(w2)
         self.w13 = w13
         self.w2 = w2
         if not (is_fp8 or is_mxfp4 or is_mxfp8 or is_block_fp8 or is_int4):
@@ -280,6 +313,23 @@ class XpuFusedMoe:
         # >0: cap on the CTAs of the persistent GEMM kernels (set by callers that
         # overlap a collective with this layer and need free SMs for it)
         self.gemm_max_ctas = 0
+        # >0: rows expected in use when the row buffers are sized for a worst case (set by the
+        # expert-parallel layer, whose receive regions are mostly empty): tile sizes only
+        self.rows_hint = 0
+        self.persistent_workspace = persistent_workspace
+        # optional callable(name), called after every stage of a call (routing is what precedes the
+        # first mark): lets a harness put CUDA events between the stages, as the reference's
+        # benchmark does (benchmark/src/fused_moe_interface_.py:12-40)
+        self.stage_hook = None
+
+    def _mark(self, name):
+        if self.stage_hook is not None:
+            self.stage_hook(name)
+
+    def _buf(self, name, shape, dtype, device):
+        if self.persistent_workspace:
+            return _pooled(name, shape, dtype, device)
+        return torch.empty(shape, dtype=dtype, device=device)
 
     def apply(self, output, hidden_states, topk_weights, topk_ids,
               expert_map=None, a1q_scale=None):
@@ -291,8 +341,8 @@ class XpuFusedMoe:
         [planes, ceil(cols / 128), rows]); planes = 2 adds the residual plane."""
         rows, cols = x.shape
         planes = self.mx_planes
-        q = torch.empty((planes * rows, cols), dtype=torch.float8_e4m3fn, device=x.device)
-        s = torch.empty((planes, (cols + 127) // 128, rows), dtype=torch.int32, device=x.device)
+        q = self._buf(f"mxq{cols}", (planes * rows, cols), torch.float8_e4m3fn, x.device)
+        s = self._buf(f"mxs{cols}", (planes, (cols + 127) // 128, rows), torch.int32, x.device)
         torch.ops._C.b200_quant_mxfp8(x, q, s)
         return q, s
 
@@ -300,7 +350,11 @@ class XpuFusedMoe:
     # is inside the ops and, for block fp8, that activations really are
     # quantised to e4m3 per 1x128 group and multiplied on the fp8 tensor cores.
     def _apply_kernel(self, output, hidden_states, topk_weights, topk_ids,
-                      expert_map=None, a1q_scale=None):
+                      expert_map=None, a1q_scale=None, gather=True, out_dtype=None):
+        """With ``gather=False`` the last stage is left to the caller: returns the expert-major
+        rows ``[T*K, hidden]`` after gemm2 and the row map ``[T, K]`` (valid until the next
+        layer call on this device)."""
+        self._mark("routing")
         num_rows, hidden_size = hidden_states.shape
         K = self.n_experts_per_token
         num_moe_inputs = K * num_rows
@@ -309,26 +363,34 @@ class XpuFusedMoe:
         I = self.inter_size
         if expert_map is None and self.ep_size > 1:
             expert_map = self.expert_map
+        if out_dtype is None:
+            out_dtype = output.dtype if output is not None else hidden_states.dtype
+        if (a1q_scale is not None and hidden_states.dtype != out_dtype and not self.is_block_fp8):
+            # The reference forwards caller-quantised activations and their scales to gemm1 for
+            # every recipe; here only the block-scaled fp8 kernels take them (1x128 fp32 scales).
+            raise NotImplementedError(
+                f"a1q_scale with pre-quantised hidden_states is built for block-scaled fp8 weights only "
+                f"(recipe of this layer: {self.recipe}); pass 16-bit hidden_states instead")
 
-        rows_per_expert = torch.empty((E,), dtype=torch.int32, device=dev)
-        row_map = torch.empty((num_rows, K), dtype=torch.int32, device=dev)
+        rows_per_expert = self._buf("rows_per_expert", (E,), torch.int32, dev)
+        row_map = self._buf("row_map", (num_rows, K), torch.int32, dev)
 
         quant_acts = self.is_block_fp8
         if quant_acts and a1q_scale is None:
             # permute + dynamic 1x128 e4m3 quantisation in one pass
-            remapped = torch.empty((num_moe_inputs, hidden_size), dtype=torch.float8_e4m3fn, device=dev)
-            remapped_scales = torch.empty((num_moe_inputs, hidden_size // FP8_BLOCK_SIZE),
-                                          dtype=torch.float32, device=dev)
+            remapped = self._buf("remapped", (num_moe_inputs, hidden_size), torch.float8_e4m3fn, dev)
+            remapped_scales = self._buf("remapped_scales", (num_moe_inputs, hidden_size // FP8_BLOCK_SIZE),
+                                        torch.float32, dev)
             torch.ops._moe_C.b200_remap_quant_fp8(
                 hidden_states, remapped, remapped_scales, expert_map, rows_per_expert,
                 row_map, topk_ids, self.total_experts_num, self.local_experts_num)
         else:
             if a1q_scale is not None:
-                remapped_scales = torch.empty((num_moe_inputs, a1q_scale.shape[1]),
-                                              dtype=a1q_scale.dtype, device=dev)
+                remapped_scales = self._buf("remapped_scales", (num_moe_inputs, a1q_scale.shape[1]),
+                                            a1q_scale.dtype, dev)
             else:
                 remapped_scales = None
-            remapped = torch.empty((num_moe_inputs, hidden_size), dtype=hidden_states.dtype, device=dev)
+            remapped = self._buf("remapped", (num_moe_inputs, hidden_size), hidden_states.dtype, dev)
             torch.ops._moe_C.remap_hidden_states(
                 hidden_states=hidden_states, hidden_states_scales=a1q_scale,
                 remapped_hidden_states=remapped,
@@ -338,11 +400,14 @@ class XpuFusedMoe:
                 total_experts_num=self.total_experts_num,
                 local_experts_num=self.local_experts_num)
 
+        self._mark("permute")
         a_scale1 = remapped_scales if quant_acts else None
-        gemm2_output = torch.empty((num_moe_inputs, hidden_size), dtype=output.dtype, device=dev)
+        gemm2_output = self._buf("gemm2_output", (num_moe_inputs, hidden_size), out_dtype, dev)
         self._experts(gemm2_output, remapped, a_scale1, rows_per_expert)
-
+        if not gather:
+            return gemm2_output, row_map
         torch.ops._moe_C.moe_gather(output, gemm2_output, topk_weights, row_map, E)
+        self._mark("gather")
 
     def apply_sorted(self, output_rows, rows, rows_per_segment, a1q_scale=None):
         """The experts alone (gemm1 -> activation -> gemm2) on rows that are already grouped:
@@ -376,18 +441,20 @@ class XpuFusedMoe:
 
         # ---- gemm1 (+ activation) ----
         if self.fuse_activation:
-            act_output = torch.empty((num_moe_inputs, I), dtype=output.dtype, device=dev)
+            act_output = self._buf("act_output", (num_moe_inputs, I), output.dtype, dev)
             torch.ops._xpu_C.b200_grouped_gemm(
                 remapped, a_scale1, self.w13, self.gemm1_wei_scales, self.w13_bias, act_output,
                 rows_per_expert, 2 * I, hidden_size, E, 0,
                 _EPI_SILU if self._act_kind == "silu" else _EPI_SWIGLUOAI, 1.702, 7.0, clamp, 0,
-                self.gemm_max_ctas)
+                self.gemm_max_ctas, self.rows_hint)
+            self._mark("gemm1")
         else:
-            gemm1_output = torch.empty((num_moe_inputs, 2 * I), dtype=output.dtype, device=dev)
+            gemm1_output = self._buf("gemm1_output", (num_moe_inputs, 2 * I), output.dtype, dev)
             torch.ops._xpu_C.b200_grouped_gemm(
                 remapped, a_scale1, self.w13, self.gemm1_wei_scales, self.w13_bias, gemm1_output,
                 rows_per_expert, 2 * I, hidden_size, E, 0, _EPI_NONE, 1.702, 7.0, 0.0, 0,
-                self.gemm_max_ctas)
+                self.gemm_max_ctas, self.rows_hint)
+            self._mark("gemm1")
             if clamp > 0:
                 gate = gemm1_output[:, :I]
                 up = gemm1_output[:, I:]
@@ -396,16 +463,15 @@ class XpuFusedMoe:
             if quant_acts and self._act_kind == "silu" and I % FP8_BLOCK_SIZE == 0:
                 # SiLU, multiply and the 1x128 e4m3 quantisation of gemm2's input in one pass
                 act_output = None
-                act_q = torch.empty((num_moe_inputs, I), dtype=torch.float8_e4m3fn, device=dev)
-                gemm2_act_scale = torch.empty((num_moe_inputs, I // FP8_BLOCK_SIZE), dtype=torch.float32,
-                                              device=dev)
+                act_q = self._buf("act_q", (num_moe_inputs, I), torch.float8_e4m3fn, dev)
+                gemm2_act_scale = self._buf("act_q_scale", (num_moe_inputs, I // FP8_BLOCK_SIZE), torch.float32, dev)
                 torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_output, gemm2_act_scale,
                                                           FP8_BLOCK_SIZE, None, False, False)
             else:
-                act_output = torch.empty((num_moe_inputs, I * self.inter_size_scale), dtype=output.dtype,
-                                         device=dev)
+                act_output = self._buf("act_output", (num_moe_inputs, I * self.inter_size_scale), output.dtype, dev)
                 self.act_func(act_output, gemm1_output)
 
+        self._mark("activation")
         # ---- gemm2 ----
         if quant_acts and act_output is None:
             pass   # already quantised together with the activation
@@ -418,7 +484,8 @@ class XpuFusedMoe:
         torch.ops._xpu_C.b200_grouped_gemm(
             act_q, gemm2_act_scale, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_output,
             rows_per_expert, hidden_size, I * self.inter_size_scale, E, 0, _EPI_NONE, 1.702, 7.0, 0.0, 0,
-            self.gemm_max_ctas)
+            self.gemm_max_ctas, self.rows_hint)
+        self._mark("gemm2")
 
 
 def xpu_fused_moe(hidden_states,
