@@ -519,7 +519,8 @@ def run_point(args, cfg, T, world, rank, local_rank, dev, dist):
         "roofline": roof,
         "layer_roofline": layer_roof,
     }
-    if ep_world == 1 and world == 1:
+    if (ep_world == 1 and world == 1) or (ep_world > 1 and args.ep_transport == "peer"):
+        # (with sharded experts: rank 0's view; a barrier's time includes waiting for the slowest rank)
         line["stages_ms"] = stage_times(cfg, layer, step, x, logits, bias)
     if ep_world > 1 and args.ep_transport == "peer":
         # bytes one rank stores into its peers per step (rows + scales + ids + weights out, partial

@@ -433,6 +433,18 @@ int b200moe_silu_and_mul_per_block_quant(void* out, b200moe_dtype out_dtype,
                                          int64_t s_stride_group,
                                          int scale_ue8m0, b200moe_stream stream);
 
+/* The same with e4m3 output, group 128 and dense scales [rows, hidden/128], for row buffers
+ * that are sized for a worst case: only the first sum(rows_per_segment[0..num_segments))
+ * rows are in use (the expert-major rows of a grouped GEMM and its device-side row counts)
+ * and only those are read and written.  No counterpart op in the reference, whose layer
+ * sizes its buffers exactly (vllm_xpu_kernels/fused_moe_interface.py:336-396). */
+int b200moe_silu_and_mul_per_block_quant_ragged(void* out, float* scales, const void* in,
+                                                b200moe_dtype dtype, int64_t rows,
+                                                int hidden,
+                                                const int32_t* rows_per_segment,
+                                                int num_segments,
+                                                b200moe_stream stream);
+
 /* Replaces `silu_and_mul_mxfp4_quant`
  * (csrc/quantization/fused_kernels/fused_silu_mul_mxfp4_quant.cpp:134-210, kernel
  * :19-131; schema csrc/torch_bindings.cpp:103-107).  in [rows, 2*hidden] ->

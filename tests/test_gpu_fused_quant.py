@@ -140,3 +140,23 @@ def test_silu_and_mul_quant(native, T, d, dtype):
         o = torch.empty_like(c["q"], device=DEV)
         torch.ops._C.silu_and_mul_quant(o, c["x"].to(DEV), c["scale"].to(DEV))
         torch.testing.assert_close(o.cpu().float(), c["q"].float(), rtol=0.13, atol=2e-3)
+
+
+def test_block_quant_over_the_rows_in_use_only():
+    """b200_silu_and_mul_block_quant_rows: the layer's form of silu_and_mul_per_block_quant for row
+    buffers sized for a worst case - the rows the segments use get exactly the full op's result,
+    the rows past them are neither read nor written."""
+    rows, hidden = 300, 512
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(rows, 2 * hidden, generator=g).to(torch.bfloat16).to(DEV)
+    seg = torch.tensor([40, 0, 91, 7], dtype=torch.int32, device=DEV)       # 138 rows in use
+    used = int(seg.sum())
+    ref_q = torch.empty(rows, hidden, dtype=torch.float8_e4m3fn, device=DEV)
+    ref_s = torch.empty(rows, hidden // 128, dtype=torch.float32, device=DEV)
+    torch.ops._C.silu_and_mul_per_block_quant(ref_q, x, ref_s, 128, None, False, False)
+    q = torch.full((rows, hidden), 0x55, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    s = torch.full((rows, hidden // 128), -3.0, dtype=torch.float32, device=DEV)
+    torch.ops._C.b200_silu_and_mul_block_quant_rows(q, x, s, seg)
+    assert torch.equal(q.view(torch.uint8)[:used], ref_q.view(torch.uint8)[:used])
+    assert torch.equal(s[:used], ref_s[:used])
+    assert bool((q.view(torch.uint8)[used:] == 0x55).all()) and bool((s[used:] == -3.0).all())

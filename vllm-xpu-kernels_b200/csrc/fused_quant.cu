@@ -55,6 +55,10 @@ struct GroupQuantArgs {
   int64_t s_stride_row, s_stride_group;
   float eps;
   int ue8m0;
+  // optional: only the first sum(rows_per_segment[0..num_segments)) rows are in use (row
+  // buffers sized for a worst case); blocks past them return at once
+  const int32_t* rows_per_segment = nullptr;
+  int num_segments = 0;
 };
 
 // kGated: input rows are [gate(hidden) | up(hidden)] and the quantised value is
@@ -68,6 +72,19 @@ __global__ void __launch_bounds__(1024)
 group_quant_kernel(const GroupQuantArgs a, int64_t rows) {
   constexpr int N = Vec16<T>::N;
   const int64_t r0 = (int64_t)blockIdx.x * kRows;
+  if (a.rows_per_segment != nullptr) {
+    __shared__ int64_t in_use;
+    if (threadIdx.x < 32) {
+      int64_t sum = 0;
+      for (int e = threadIdx.x; e < a.num_segments; e += 32) sum += max(a.rows_per_segment[e], 0);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      if (threadIdx.x == 0) in_use = sum;
+    }
+    __syncthreads();
+    if (in_use < rows) rows = in_use;
+    if (r0 >= rows) return;
+  }
   const int lanes_per_group = a.group / N;
   const int nvec = a.hidden / N;
   const int64_t in_pitch = (int64_t)a.hidden * (kGated ? 2 : 1);
@@ -231,6 +248,20 @@ extern "C" int b200moe_silu_and_mul_per_block_quant(void* out, b200moe_dtype out
   GroupQuantArgs a = {in, out, scales, scale_ub, hidden, group_size, s_stride_row, s_stride_group, 0.f, scale_ue8m0};
   if (out_dtype == B200MOE_I8)
     return launch_group_quant<true, kOutI8>(dtype, a, rows, as_stream(stream), "silu_and_mul_per_block_quant");
+  return launch_group_quant<true, kOutE4m3>(dtype, a, rows, as_stream(stream), "silu_and_mul_per_block_quant");
+}
+
+extern "C" int b200moe_silu_and_mul_per_block_quant_ragged(void* out, float* scales, const void* in,
+                                                           b200moe_dtype dtype, int64_t rows, int hidden,
+                                                           const int32_t* rows_per_segment, int num_segments,
+                                                           b200moe_stream stream) {
+  B200_CHECK_ARG(dtype == B200MOE_BF16 || dtype == B200MOE_F16, "input must be float16 or bfloat16");
+  B200_CHECK_ARG(rows >= 0 && hidden >= 0 && hidden % 128 == 0, "hidden_size must be divisible by group_size");
+  B200_CHECK_ARG(rows_per_segment != nullptr && num_segments >= 1, "silu_and_mul_per_block_quant_ragged: no row counts");
+  if (rows == 0 || hidden == 0) return B200MOE_OK;
+  B200_CHECK_ARG(out && scales && in, "silu_and_mul_per_block_quant: null pointer");
+  B200_CHECK_ARG(aligned16(in) && (((uintptr_t)out & 7) == 0), "silu_and_mul_per_block_quant: misaligned buffer");
+  GroupQuantArgs a = {in, out, scales, nullptr, hidden, 128, hidden / 128, 1, 0.f, 0, rows_per_segment, num_segments};
   return launch_group_quant<true, kOutE4m3>(dtype, a, rows, as_stream(stream), "silu_and_mul_per_block_quant");
 }
 

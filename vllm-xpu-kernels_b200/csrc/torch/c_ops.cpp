@@ -152,6 +152,25 @@ void silu_and_mul_per_block_quant(at::Tensor& out, const at::Tensor& input, at::
       is_scale_transposed ? 1 : num_groups, is_scale_transposed ? num_tokens : 1, scale_ue8m0, current_stream()));
 }
 
+// The layer's form: e4m3, group 128, and only the rows the grouped GEMM's segments use.
+void b200_silu_and_mul_block_quant_rows(at::Tensor& out, const at::Tensor& input, at::Tensor& scales,
+                                        const at::Tensor& rows_per_segment) {
+  check_cuda(input, "input");
+  TORCH_CHECK(out.scalar_type() == at::kFloat8_e4m3fn && scales.scalar_type() == at::kFloat, "out must be float8_e4m3fn, scales float32");
+  TORCH_CHECK(input.scalar_type() == at::kHalf || input.scalar_type() == at::kBFloat16, "input must be float16 or bfloat16");
+  TORCH_CHECK(out.is_contiguous() && input.is_contiguous() && scales.is_contiguous() && input.dim() == 2 && out.dim() == 2,
+              "out, input and scales must be contiguous 2-D tensors");
+  const int64_t rows = input.size(0), hidden = out.size(1);
+  TORCH_CHECK(input.size(1) == 2 * hidden && out.size(0) == rows && hidden % 128 == 0 && scales.numel() == rows * (hidden / 128),
+              "shapes: input [rows, 2 * hidden], out [rows, hidden], scales [rows, hidden / 128]");
+  TORCH_CHECK(rows_per_segment.scalar_type() == at::kInt && rows_per_segment.is_contiguous(), "rows_per_segment must be int32");
+  if (rows == 0) return;
+  const c10::cuda::CUDAGuard guard(input.device());
+  check_status(b200moe_silu_and_mul_per_block_quant_ragged(
+      out.data_ptr(), scales.data_ptr<float>(), input.data_ptr(), float_dtype(input, "silu_and_mul_per_block_quant"), rows,
+      (int)hidden, rows_per_segment.data_ptr<int32_t>(), (int)rows_per_segment.numel(), current_stream()));
+}
+
 // csrc/quantization/fused_kernels/fused_silu_mul_mxfp4_quant.cpp:134-185 of the reference.
 void silu_and_mul_mxfp4_quant(at::Tensor& out, const at::Tensor& input, at::Tensor& scales, int64_t group_size,
                               double eps) {
@@ -238,6 +257,7 @@ TORCH_LIBRARY_FRAGMENT(_C, m) {
       "Tensor? scale_ub=None, "
       "bool is_scale_transposed=False, "
       "bool scale_ue8m0=False) -> ()");
+  m.def("b200_silu_and_mul_block_quant_rows(Tensor! out, Tensor input, Tensor! scales, Tensor rows_per_segment) -> ()");
   m.def(
       "silu_and_mul_mxfp4_quant("
       "Tensor! out, Tensor input, Tensor! scales, "
@@ -267,6 +287,7 @@ TORCH_LIBRARY_IMPL(_C, CUDA, m) {
   m.impl("swiglustep_and_mul", &swiglustep_and_mul);
   m.impl("silu_and_mul_quant", &silu_and_mul_quant);
   m.impl("silu_and_mul_per_block_quant", &silu_and_mul_per_block_quant);
+  m.impl("b200_silu_and_mul_block_quant_rows", &b200_silu_and_mul_block_quant_rows);
   m.impl("silu_and_mul_mxfp4_quant", &silu_and_mul_mxfp4_quant);
   m.impl("per_token_group_quant_mxfp4", &per_token_group_quant_mxfp4);
 }

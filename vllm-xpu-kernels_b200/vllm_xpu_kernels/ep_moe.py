@@ -200,6 +200,12 @@ class EpPeerFusedMoe:
         chunks = (cap * ep + 255) // 256
         self._workspace = torch.empty((ep * chunks + ep + 1) * 4 + 256, dtype=torch.uint8, device=dev)
         self._tokens = 0
+        # optional callable(name) called after every stage (see XpuFusedMoe.stage_hook)
+        self.stage_hook = None
+
+    def _mark(self, name):
+        if self.stage_hook is not None:
+            self.stage_hook(name)
 
     # ---- plumbing ------------------------------------------------------------------------
     def _peer_tables(self):
@@ -218,29 +224,38 @@ class EpPeerFusedMoe:
         if T > self.capacity:
             raise ValueError(f"{T} tokens exceed max_tokens={self.capacity} this layer was built for")
         self._tokens = T
+        self._mark("routing")
         torch.ops._moe_C.b200_ep_dispatch(hidden_states, topk_ids, topk_weights, self.send_counts,
                                           self.send_pos[:T], self._workspace, self._peer_tables(), *self._common())
+        self._mark("dispatch")
 
     def experts_and_combine(self):
         ep, cap, K, H = self.ep_size, self.capacity, self.topk, self.hidden
         rank, E_l, _, quant = self._common()
         torch.ops._moe_C.b200_ep_mask_unused(self.recv_ids, self._peer_tables(), rank, E_l, K, H, cap, quant)
+        self._mark("mask")
+        self.local.stage_hook = (lambda name: self._mark("local_" + name) if name != "routing" else None) \
+            if self.stage_hook is not None else None
         # on average a rank receives as many routed slots as it sends
         self.local.rows_hint = max(1, self._tokens * K)
         moe_out, row_map = self.local._apply_kernel(None, self.recv_rows, self.recv_weights, self.recv_ids,
                                                     a1q_scale=self.recv_scales, gather=False,
                                                     out_dtype=self.out_dtype)
         torch.ops._moe_C.b200_ep_combine(moe_out, row_map, self._peer_tables(), rank, E_l, cap, quant)
+        self._mark("combine")
 
     def finish(self, output):
         T = self._tokens
         torch.ops._moe_C.moe_gather(output, self.comb_rows, self._ones[:T], self.send_pos[:T], self.ep_size)
+        self._mark("finish")
 
     def apply(self, output, hidden_states, topk_weights, topk_ids):
         self.dispatch(hidden_states, topk_weights, topk_ids)
         self.peers.barrier()      # every rank's rows have arrived
+        self._mark("barrier1")
         self.experts_and_combine()
         self.peers.barrier()      # every rank's partial sums have arrived
+        self._mark("barrier2")
         self.finish(output)
 
     def check_counts(self):

@@ -465,8 +465,9 @@ class XpuFusedMoe:
                 act_output = None
                 act_q = self._buf("act_q", (num_moe_inputs, I), torch.float8_e4m3fn, dev)
                 gemm2_act_scale = self._buf("act_q_scale", (num_moe_inputs, I // FP8_BLOCK_SIZE), torch.float32, dev)
-                torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_output, gemm2_act_scale,
-                                                          FP8_BLOCK_SIZE, None, False, False)
+                # (only the rows the experts' segments use: the buffers may be sized for a worst case)
+                torch.ops._C.b200_silu_and_mul_block_quant_rows(act_q, gemm1_output, gemm2_act_scale,
+                                                                rows_per_expert)
             else:
                 act_output = self._buf("act_output", (num_moe_inputs, I * self.inter_size_scale), output.dtype, dev)
                 self.act_func(act_output, gemm1_output)
