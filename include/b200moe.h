@@ -338,7 +338,11 @@ typedef struct {
   const void* w_scale;    /* per w_format, else NULL                              */
   const void* bias;       /* [E,N] in d_dtype, or NULL                            */
   void* d;                /* [M,N] (or [M,N/2] with a gated epilogue) d_dtype     */
-  b200moe_dtype d_dtype;  /* BF16 or F16                                          */
+  b200moe_dtype d_dtype;  /* BF16 or F16; FP8_E4M3 with EPI_SILU_MUL on fp8 x
+                             block-scaled fp8: the activated values leave the
+                             kernel quantised per token and 128 features, as
+                             b200moe_silu_and_mul_per_block_quant would quantise
+                             the unfused output (same values)                     */
   const int32_t* rows_per_expert; /* [E] device                                   */
   int64_t m;              /* rows of A and D (upper bound of the rows in use)     */
   int n, k, num_experts;
@@ -363,6 +367,11 @@ typedef struct {
                              exchange as they arrive, grouped by source rank and by
                              local expert inside a source, need no second
                              permutation.  16-bit and block-scaled fp8 weights.     */
+  void* d_scale;          /* FP8_E4M3 output: fp32 scales [M, N/256]; else NULL     */
+  b200moe_dtype mid_dtype;/* FP8_E4M3 output: BF16 or F16, the type the
+                             pre-activation values (and the bias) have: they are
+                             rounded to it before the activation, as the unfused
+                             GEMM's output would be                                */
   int64_t rows_hint;      /* 0, or the number of rows expected to be in use when `m`
                              is only a loose upper bound (buffers sized for the worst
                              case): tile sizes are picked for rows_hint / num_experts

@@ -291,3 +291,39 @@ def test_fp8_token_major_kernel_against_checking_kernel_at_deepseek_shape(native
     top = float(chk.float().abs().max())
     assert torch.isfinite(tc.float()).all() and top > 0
     assert float((tc.float() - chk.float()).abs().max()) <= 2 ** -7 * top
+
+
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+@pytest.mark.parametrize("dtype,has_bias,clamp", [(torch.bfloat16, False, 0.0), (torch.float16, True, 0.0),
+                                                 (torch.bfloat16, True, 0.4)])
+@pytest.mark.parametrize("E,M,N,K", [(3, 700, 512, 1024), (5, 1000, 256, 128), (4, 130, 1280, 384), (8, 40, 768, 256)])
+def test_fp8_gemm_with_silu_and_quantisation_in_the_epilogue(native, layout, dtype, has_bias, clamp, E, M, N, K):
+    """gemm1 of a block-scaled fp8 layer with SiLU-and-mul and the 1x128 e4m3 quantisation of
+    gemm2's input inside the tensor-core epilogue: codes and scales must equal, value for
+    value, what the unfused GEMM followed by silu_and_mul_per_block_quant
+    (csrc/quantization/fused_kernels/fused_silu_mul_block_quant.cpp:14-128 of the reference)
+    produces - the epilogue rounds gate and up to the 16-bit type first, as the unfused output
+    is.  Ragged and empty segments, rows no segment owns, both weight layouts."""
+    g = torch.Generator().manual_seed(M + N + K + 3)
+    rows, x, wq, ws = _fp8_case(E, M, N, K, g)
+    x = torch.cat([x, torch.randn(33, K, generator=g).to(torch.bfloat16)])
+    bias = (torch.randn(E, N, generator=g) * 0.1).to(dtype).to(DEV) if has_bias else None
+    aq, a_s = to.per_token_group_fp8_quant(x, 128, 1e-10)
+    wd = wq.to(DEV) if layout == "nk" else wq.transpose(1, 2).contiguous().to(DEV)
+    lay = 1 if layout == "nk" else 2
+    Mt, n = x.shape[0], int(rows.sum())
+    full = grouped_gemm(aq.to(DEV), a_s.to(DEV), wd, ws.to(DEV), bias, rows.to(DEV), N, K, layout=lay, impl=TC,
+                        out_dtype=dtype)
+    if clamp > 0:
+        full[:, :N // 2].clamp_(max=clamp)
+        full[:, N // 2:].clamp_(min=-clamp, max=clamp)
+    ref_q = torch.empty(Mt, N // 2, dtype=torch.float8_e4m3fn, device=DEV)
+    ref_s = torch.empty(Mt, N // 256, dtype=torch.float32, device=DEV)
+    torch.ops._C.silu_and_mul_per_block_quant(ref_q, full, ref_s, 128, None, False, False)
+    q = torch.full((Mt, N // 2), 0x7f, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+    s = torch.full((Mt, N // 256), -1.0, dtype=torch.float32, device=DEV)
+    torch.ops._xpu_C.b200_grouped_gemm(aq.to(DEV), a_s.to(DEV), wd, ws.to(DEV), bias, q, rows.to(DEV), N, K, E, lay, 1,
+                                       1.702, 7.0, clamp, 0, 0, 0, s, dtype == torch.float16)
+    assert torch.equal(q.view(torch.uint8)[:n], ref_q.view(torch.uint8)[:n])
+    assert torch.equal(s[:n], ref_s[:n])
+    assert bool((q.view(torch.uint8)[n:] == 0x7f).all()) and bool((s[n:] == -1.0).all())   # rows past the segments

@@ -404,3 +404,31 @@ def test_a_bounded_wait_that_runs_out_reaches_the_caller(native):
     ref = torch.cat([a[:20].float() @ wt[0].float(), a[20:].float() @ wt[1].float()])
     torch.testing.assert_close(d.float(), ref, rtol=2e-2, atol=2e-2)
     assert X.b200_check_status(anchor, True) == 0
+
+
+@pytest.mark.parametrize("T", [40, 700])
+def test_fp8_layer_fused_and_unfused_activation_agree_bit_for_bit(native, T):
+    """Block-scaled fp8 layer: gemm1's epilogue can apply SiLU and the 1x128 quantisation (one kernel
+    less, no [T*K, 2I] round trip; the default for many rows per expert, forced here) or the
+    two-kernel form runs (fuse_activation=False, and below 12 rows per expert).  Same values either way."""
+    cfg = wl.scaled(wl.CONFIGS["cfg3_qwen3_fp8"], H=512, I=384, E=16)
+    w = wl.make_weights(cfg, seed=8)
+    x, logits, bias = wl.make_inputs(cfg, T, seed=8)
+    tw, ids = wl.route_cpu(cfg, logits, bias)
+    w13, s13, w2, s2 = wl.to_op_layout(cfg, w)
+    mv = lambda t: t.to(DEV) if t is not None else None
+    outs = []
+    for fuse in (True, False):
+        layer = native.XpuFusedMoe(mv(w13), mv(s13), None, mv(w2), mv(s2), None, cfg.K, cfg.activation, cfg.E,
+                                   fuse_activation=fuse, gemm1_clamp_limit=0.8)
+        marks = []
+        layer.stage_hook = marks.append
+        out = torch.empty(x.shape, dtype=torch.bfloat16, device=DEV)
+        layer.apply(out, x.to(DEV), tw.to(DEV), ids.to(DEV))
+        outs.append(out)
+        assert "gemm1" in marks
+    assert torch.equal(outs[0], outs[1])
+    d13, d2 = wl.dequant_weights(cfg, w)
+    ref = to.fused_moe_staged(x, d13, None, d2, None, tw, ids, cfg.E, activation=cfg.activation, act_quant=True,
+                              gemm1_clamp_limit=0.8)
+    torch.testing.assert_close(outs[0].cpu().float(), ref.float(), rtol=5e-2, atol=5e-2)

@@ -6,6 +6,7 @@
 
 namespace b200moe {
 int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st);
+int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st);
 int grouped_gemm_tc_dq(const b200moe_gemm_args* a, cudaStream_t st);
 int grouped_gemm_tc_mx(const b200moe_gemm_args* a, cudaStream_t st);
 int grouped_gemm_check(const b200moe_gemm_args* a, cudaStream_t st);
@@ -19,8 +20,15 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
   B200_CHECK_ARG(a->m >= 0 && a->n >= 0 && a->k > 0 && a->num_experts >= 1,
                  "grouped_gemm: bad sizes (m=%lld n=%d k=%d experts=%d)", (long long)a->m, a->n,
                  a->k, a->num_experts);
-  B200_CHECK_ARG(a->d_dtype == B200MOE_BF16 || a->d_dtype == B200MOE_F16,
+  const bool d_quant = a->d_dtype == B200MOE_FP8_E4M3;
+  B200_CHECK_ARG(a->d_dtype == B200MOE_BF16 || a->d_dtype == B200MOE_F16 || d_quant,
                  "grouped_gemm: ptr_D must be bfloat16 or float16");
+  B200_CHECK_ARG(!d_quant || (a->epilogue == B200MOE_EPI_SILU_MUL && a->d_scale != nullptr &&
+                              a->a_dtype == B200MOE_FP8_E4M3 &&
+                              (a->w_format == B200MOE_W_FP8_BLOCK_NK || a->w_format == B200MOE_W_FP8_BLOCK_KN) &&
+                              (a->mid_dtype == B200MOE_BF16 || a->mid_dtype == B200MOE_F16)),
+                 "grouped_gemm: e4m3 output needs the SiLU epilogue, d_scale, a 16-bit mid_dtype, fp8 "
+                 "activations and block-scaled fp8 weights");
   const bool a_x2 = a->a_dtype == B200MOE_FP8_E4M3_X2;
   const bool a_fp8 = a->a_dtype == B200MOE_FP8_E4M3 || a_x2;
   B200_CHECK_ARG(a_fp8 || a->a_dtype == a->d_dtype,
@@ -87,6 +95,10 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
   cudaStream_t st = as_stream(stream);
   // MXFP8 activations exist on the block-scaled tensor-core path only.
   if ((a->w_format == B200MOE_W_MXFP4_NK || w_tensor8) && a_fp8) return grouped_gemm_tc_mx(a, st);
+  if (d_quant) {
+    B200_CHECK_ARG(a->impl != 2, "grouped_gemm: the checking kernel has no quantised output");
+    return grouped_gemm_tc_fp8t(a, st);
+  }
   if (a->impl == 2 || a->w_format == B200MOE_W_MXFP8_KN) return grouped_gemm_check(a, st);   // 16-bit activations
   int rc = (a->w_format == B200MOE_W_MXFP4_NK || a->w_format == B200MOE_W_INT4_NK) ? grouped_gemm_tc_dq(a, st)
                                                                                     : grouped_gemm_tc(a, st);

@@ -54,6 +54,10 @@ struct TParams {
   int n_tiles, num_kb;
   uint32_t idesc;
   int out_f16;
+  // gated epilogue of the 128 x 256 kernel (kGated): D is [M, n/2] e4m3 with one fp32 scale per
+  // token and 128 features in d_scale [M, n/256]
+  float* d_scale;
+  float clamp;            // >0: gate = min(gate, clamp), up = clamp(up, -clamp, clamp)
 };
 
 struct TCtrl {
@@ -295,12 +299,24 @@ struct T2Ctrl {
   uint64_t acc_empty[kT2Acc];
   uint32_t tmem_base;
   int abort_flag;
+  float xchg[2][2][128];   // gated epilogue: group maxima exchanged between the two warps of a token row
+  uint64_t xbar[4];        // ... and the barrier of each such pair of warps (one per lane quarter)
   int tile_start[kMaxExperts + 1];
   int row_start[kMaxExperts + 1];
 };
 constexpr size_t kT2Smem = 1024 + (size_t)kT2Stages * kT2StageBytes + sizeof(T2Ctrl);
 
-template <bool kWKn>
+//
+// kGated (the first grouped GEMM of a SiLU layer with block-scaled fp8 experts): a tile pairs the
+// 128 gate features j0.. with the 128 up features n/2 + j0.. of the same tokens; warp w reads
+// lane quarter w & 3 and, of both blocks, the 64 columns of half (w - 4) / 4, so a thread holds
+// gate and up of the same 64 features of its token.  The epilogue rounds both to the 16-bit
+// type an unfused GEMM would have stored, applies silu(gate) * up, finds the maximum of the
+// token's 128-feature group together with the partner warp (shared memory, a named barrier of
+// the two warps) and stores e4m3 codes and the group's fp32 scale: the arithmetic of
+// silu_and_mul_per_block_quant on the unfused output, value for value, without the [M, n]
+// round trip through HBM.
+template <bool kWKn, bool kGated>
 __global__ void __launch_bounds__(kT2Threads, 1)
 grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_w, const TParams p) {
@@ -309,7 +325,9 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
   T2Ctrl* ctrl = reinterpret_cast<T2Ctrl*>(smem + kT2Stages * kT2StageBytes);
   volatile int* abort_flag = &ctrl->abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_tiles2 = (p.n_tiles + 1) / 2;   // 256-feature tiles
+  // 256-feature tiles; gated: one tile per 128 gate features (p.n_tiles counts 128-feature blocks of n)
+  const int n_tiles2 = kGated ? p.n_tiles / 2 : (p.n_tiles + 1) / 2;
+  const int up_block0 = p.n_tiles / 2;        // gated: first 128-feature block of the up half
 
   if (warp == 0) {
     build_tile_prefix<kTTok>(p.rows_per_expert, p.num_experts, n_tiles2, ctrl->row_start, ctrl->tile_start);
@@ -329,6 +347,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::mbar_init(&ctrl->acc_full[a], 1);
       ptx::mbar_init(&ctrl->acc_empty[a], 8);
     }
+    for (int x = 0; x < 4; ++x) ptx::mbar_init(&ctrl->xbar[x], 2);
     ctrl->abort_flag = 0;
     ptx::fence_barrier_init();
   }
@@ -351,7 +370,8 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         TileInfo ti;
         locate_tile<kTTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
-        const int n0 = ti.n_tile * 256;
+        const int n0 = kGated ? ti.n_tile * 128 : ti.n_tile * 256;
+        const int n1 = kGated ? (up_block0 + ti.n_tile) * 128 : n0 + 128;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* wdst = smem + s * kT2StageBytes;
@@ -359,10 +379,10 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // two 128-feature blocks (the second one is zero-filled past N)
           if (!kWKn) {
             ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], kb * 128, n0, ti.e);
-            ptx::tma_load_3d(wdst + 16384, &tmap_w, &ctrl->full[s], kb * 128, n0 + 128, ti.e);
+            ptx::tma_load_3d(wdst + 16384, &tmap_w, &ctrl->full[s], kb * 128, n1, ti.e);
           } else {
             ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], n0, kb * 128, ti.e);
-            ptx::tma_load_3d(wdst + 16384, &tmap_w, &ctrl->full[s], n0 + 128, kb * 128, ti.e);
+            ptx::tma_load_3d(wdst + 16384, &tmap_w, &ctrl->full[s], n1, kb * 128, ti.e);
           }
           ptx::tma_load_2d(wdst + 32768, &tmap_a, &ctrl->full[s], kb * 128, ti.row0);
           if (++s == (uint32_t)kT2Stages) { s = 0; ph ^= 1; }
@@ -409,29 +429,39 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
-    const int half = (warp - 4) >> 2;                  // which 128-feature block of the tile
+    const int half = (warp - 4) >> 2;                  // which 128-feature block of the tile (gated: which 64 features of both)
     const int kbs = p.num_kb;
     const bool vec4_ok = (kbs % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.a_scale) & 15) == 0);
-    struct ScaleRegs { float a[kTGroup]; float w[kTGroup]; };
+    // combined scales a_scale[row, kb] * w_scale[block, kb] of a group of K blocks: s0 for this warp's
+    // (first) feature block, s1 (gated) for the up block
+    struct ScaleRegs { float s0[kTGroup]; float s1[kGated ? kTGroup : 1]; };
     ScaleRegs cur, pre;
     bool pre_valid = false;
     auto fetch_group = [&](const TileInfo& tt, int g, ScaleRegs& sr) {
       const int kb0 = g * kTGroup;
-      const int nb = tt.n_tile * 2 + half;
+      const int nb = kGated ? tt.n_tile : tt.n_tile * 2 + half;
       const int64_t wsb = ((int64_t)tt.e * p.n_tiles + nb) * kbs + kb0;
-#pragma unroll
-      for (int jb = 0; jb < kTGroup; ++jb) sr.w[jb] = (nb < p.n_tiles && kb0 + jb < kbs) ? p.w_scale[wsb + jb] : 0.f;
+      float av[kTGroup];
       const bool live = r < tt.valid;
       const float* src = p.a_scale + (int64_t)(tt.row0 + r) * kbs + kb0;
       if (live && vec4_ok) {
         const float4 q4 = *reinterpret_cast<const float4*>(src);
-        sr.a[0] = q4.x; sr.a[1] = q4.y; sr.a[2] = q4.z; sr.a[3] = q4.w;
+        av[0] = q4.x; av[1] = q4.y; av[2] = q4.z; av[3] = q4.w;
       } else {
 #pragma unroll
-        for (int jb = 0; jb < kTGroup; ++jb) sr.a[jb] = (live && kb0 + jb < kbs) ? src[jb] : 0.f;
+        for (int jb = 0; jb < kTGroup; ++jb) av[jb] = (live && kb0 + jb < kbs) ? src[jb] : 0.f;
+      }
+#pragma unroll
+      for (int jb = 0; jb < kTGroup; ++jb)
+        sr.s0[jb] = av[jb] * ((nb < p.n_tiles && kb0 + jb < kbs) ? p.w_scale[wsb + jb] : 0.f);
+      if (kGated) {
+        const int64_t wsb2 = ((int64_t)tt.e * p.n_tiles + up_block0 + tt.n_tile) * kbs + kb0;
+#pragma unroll
+        for (int jb = 0; jb < kTGroup; ++jb)
+          sr.s1[kGated ? jb : 0] = av[jb] * ((kb0 + jb < kbs) ? p.w_scale[wsb2 + jb] : 0.f);
       }
     };
-    uint32_t a = 0, aph = 0;
+    uint32_t a = 0, aph = 0, xpar = 0;
     int cursor = 0;
     bool ok = true;
     const int n_groups = (p.num_kb + kTGroup - 1) / kTGroup;
@@ -458,16 +488,20 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int jb = 0; jb < kTGroup; ++jb) {
           if (g * kTGroup + jb >= p.num_kb) break;
-          const float sc = cur.a[jb] * cur.w[jb];
+          const float sc0 = cur.s0[jb];
+          const float sc1 = kGated ? cur.s1[kGated ? jb : 0] : sc0;
           if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], aph, abort_flag))) {
             *abort_flag = 1; ok = false; break;
           }
           ptx::tc_fence_after();
-          const uint32_t col = tmem_base + a * 256 + half * 128 + lane_sel;
+          // plain: the 128 columns of this warp's block in two passes; gated: 64 gate columns, then
+          // the 64 up columns of the same features
+          const uint32_t col = tmem_base + a * 256 + (kGated ? half * 64 : half * 128) + lane_sel;
 #pragma unroll
           for (int pass = 0; pass < 2; ++pass) {
-            ptx::tmem_ld_32x32(col + pass * 64, va);
-            ptx::tmem_ld_32x32(col + pass * 64 + 32, vb);
+            const float sc = pass == 0 ? sc0 : sc1;
+            ptx::tmem_ld_32x32(col + pass * (kGated ? 128 : 64), va);
+            ptx::tmem_ld_32x32(col + pass * (kGated ? 128 : 64) + 32, vb);
             ptx::tmem_wait_ld_tied(va, vb);
             if (pass == 1) {   // the whole stage is in registers
               ptx::tc_fence_before();
@@ -483,6 +517,62 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         if (g + 1 < n_groups) cur = pre;
+      }
+      if (kGated) {
+        // acc[0..64) = gate, acc[64..128) = up of features j0 + half * 64 ..
+        const int half_n = p.n >> 1;
+        const int j0 = ti.n_tile * 128 + half * 64;
+        float amax = 0.f;
+        // acc[i] becomes the activated value of feature j0 + i (the up half is consumed)
+        auto activate = [&](auto round16) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            float g = acc[i], u = acc[64 + i];
+            if (p.bias != nullptr) {
+              g += load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + j0 + i);
+              u += load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + half_n + j0 + i);
+            }
+            // what the unfused GEMM would have stored, then (optionally) the clamp on those values
+            g = round16(g);
+            u = round16(u);
+            if (p.clamp > 0.f) {
+              g = round16(fminf(g, p.clamp));
+              u = round16(fminf(fmaxf(u, -p.clamp), p.clamp));
+            }
+            acc[i] = __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), u);
+            amax = fmaxf(amax, fabsf(acc[i]));
+          }
+        };
+        if (p.out_f16) activate([](float x) { return __half2float(__float2half_rn(x)); });
+        else activate([](float x) { return __bfloat162float(__float2bfloat16_rn(x)); });
+        // the other 64 features of the token's 128-feature group are with the partner warp
+        // (two buffers by tile parity: the partner has read the previous value of a buffer before
+        // it arrived at the barrier of the tile in between)
+        ctrl->xchg[xpar][half][r] = amax;
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctrl->xbar[q]);
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->xbar[q], xpar, abort_flag))) { *abort_flag = 1; ok = false; }
+        amax = fmaxf(amax, ctrl->xchg[xpar][half ^ 1][r]);
+        xpar ^= 1u;
+        if (ok && r < ti.valid) {
+          const float scale = fmaxf(__fdiv_rn(amax, 448.0f), 1.0f / (448.0f * 512.0f));
+          uint8_t* drow = reinterpret_cast<uint8_t*>(p.d) + (int64_t)(ti.row0 + r) * half_n + j0;
+#pragma unroll
+          for (int c = 0; c < 64; c += 16) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              uint32_t x = 0;
+#pragma unroll
+              for (int b = 0; b < 4; ++b)
+                x |= (uint32_t)f32_to_e4m3(fmaxf(-448.0f, fminf(__fdividef(acc[c + i + b], scale), 448.0f))) << (8 * b);
+              w[i >> 2] = x;
+            }
+            *reinterpret_cast<uint4*>(drow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          if (half == 0) p.d_scale[(int64_t)(ti.row0 + r) * (half_n >> 7) + ti.n_tile] = scale;
+        }
+        continue;
       }
       const int f0 = ti.n_tile * 256 + half * 128;
       if (ok && r < ti.valid && f0 < p.n) {
@@ -521,9 +611,9 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (tid == 0 && *abort_flag != 0) report_timeout(p.status);
 }
 
-template <bool kWKn>
+template <bool kWKn, bool kGated>
 int launch_fp8t256(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& p, int grid, cudaStream_t st) {
-  auto kern = grouped_gemm_fp8t256_kernel<kWKn>;
+  auto kern = grouped_gemm_fp8t256_kernel<kWKn, kGated>;
   static SmemConfig configured;
   if (int rc = configured.ensure(kern, kT2Smem)) return rc;
   kern<<<grid, kT2Threads, kT2Smem, st>>>(ta, tw, p);
@@ -548,9 +638,15 @@ int launch_fp8t(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& p, 
 // B200MOE_E_UNSUPPORTED (no launch) for anything else.
 int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
   const bool w8b = a->w_format == B200MOE_W_FP8_BLOCK_NK || a->w_format == B200MOE_W_FP8_BLOCK_KN;
+  const bool gated = a->epilogue == B200MOE_EPI_SILU_MUL;
   if (!w8b || a->a_dtype != B200MOE_FP8_E4M3 || a->a_scale == nullptr || a->w_scale == nullptr ||
-      a->epilogue != B200MOE_EPI_NONE)
-    return fail(B200MOE_E_UNSUPPORTED, "token-major fp8 grouped GEMM takes fp8 x block-scaled fp8, no fused epilogue");
+      (a->epilogue != B200MOE_EPI_NONE && !gated))
+    return fail(B200MOE_E_UNSUPPORTED, "token-major fp8 grouped GEMM takes fp8 x block-scaled fp8; fused epilogue: SiLU-and-mul");
+  if (gated && (a->d_dtype != B200MOE_FP8_E4M3 || a->d_scale == nullptr || a->n % 256 != 0))
+    return fail(B200MOE_E_UNSUPPORTED, "token-major fp8 grouped GEMM: the fused SiLU epilogue writes e4m3 + 1x128 scales "
+                                       "(d_dtype FP8_E4M3, d_scale) and needs N / 2 divisible by 128");
+  if (!gated && a->d_dtype == B200MOE_FP8_E4M3)
+    return fail(B200MOE_E_UNSUPPORTED, "token-major fp8 grouped GEMM: e4m3 output only with the fused SiLU epilogue");
   if (a->num_experts > kMaxExperts || a->n % 128 != 0 || a->k % 128 != 0)
     return fail(B200MOE_E_UNSUPPORTED, "token-major fp8 grouped GEMM: N and K must be multiples of 128");
   if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15) || ((uintptr_t)a->d & 15))
@@ -567,7 +663,9 @@ int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
   p.w_experts = w_sets != a->num_experts ? w_sets : 0;
   p.n_tiles = a->n / kFeat;
   p.num_kb = a->k / 128;
-  p.out_f16 = a->d_dtype == B200MOE_F16;
+  p.out_f16 = gated ? (a->mid_dtype == B200MOE_F16) : (a->d_dtype == B200MOE_F16);
+  p.d_scale = reinterpret_cast<float*>(a->d_scale);
+  p.clamp = a->clamp_limit;
   // A operand = tokens (K-major), B operand = weights (K-major, or MN-major for [E,K,N])
   p.idesc = ptx::make_idesc(0u, 0u, 0u, kn ? 1u : 0u, kTTok, kFeat);
 
@@ -598,7 +696,8 @@ int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
   const int64_t tile_bound = ((a->m + kTTok - 1) / kTTok + a->num_experts) * (int64_t)(wide ? (p.n_tiles + 1) / 2 : p.n_tiles);
   if (tile_bound < grid) grid = (int)tile_bound;
   if (grid < 1) grid = 1;
-  if (wide) return kn ? launch_fp8t256<true>(ta, tw, p, grid, st) : launch_fp8t256<false>(ta, tw, p, grid, st);
+  if (gated) return kn ? launch_fp8t256<true, true>(ta, tw, p, grid, st) : launch_fp8t256<false, true>(ta, tw, p, grid, st);
+  if (wide) return kn ? launch_fp8t256<true, false>(ta, tw, p, grid, st) : launch_fp8t256<false, false>(ta, tw, p, grid, st);
   return kn ? launch_fp8t<true>(ta, tw, p, grid, st) : launch_fp8t<false>(ta, tw, p, grid, st);
 }
 

@@ -44,7 +44,8 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
                              at::Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                              int64_t layout, int64_t epilogue, double alpha, double limit,
                              double clamp_limit, int64_t impl, int64_t max_ctas, bool allow_segments,
-                             int64_t rows_hint = 0) {
+                             int64_t rows_hint = 0, const std::optional<at::Tensor>& ptr_D_scale = std::nullopt,
+                             bool mid_f16 = false) {
   check_cuda(ptr_A, "ptr_A");
   const auto A_dtype = ptr_A.scalar_type();
   const auto B_dtype = ptr_B.scalar_type();
@@ -109,7 +110,10 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
   if (ptr_bias.has_value()) {
     TORCH_CHECK(ptr_bias->size(0) == num_experts, "ptr_bias.size(0) must match num_experts");
     TORCH_CHECK(ptr_bias->size(1) == N, "ptr_bias.size(1) must match N");
-    TORCH_CHECK(ptr_bias->scalar_type() == ptr_D.scalar_type(), "ptr_bias must have ptr_D's dtype");
+    TORCH_CHECK(ptr_bias->scalar_type() == ptr_D.scalar_type() ||
+                    (ptr_D.scalar_type() == at::kFloat8_e4m3fn &&
+                     ptr_bias->scalar_type() == (mid_f16 ? at::kHalf : at::kBFloat16)),
+                "ptr_bias must have ptr_D's dtype");
   }
   int64_t group_size = 0;
   if (is_B_int4) {
@@ -182,14 +186,25 @@ at::Tensor grouped_gemm_impl(at::Tensor& ptr_A, const std::optional<at::Tensor>&
     TORCH_CHECK(A_dtype == ptr_D.scalar_type(), "ptr_A and ptr_D must have the same dtype");
     g.a_dtype = A_dtype == at::kBFloat16 ? B200MOE_BF16 : B200MOE_F16;
   }
-  TORCH_CHECK(ptr_D.scalar_type() == at::kBFloat16 || ptr_D.scalar_type() == at::kHalf,
+  const bool d_quant = ptr_D.scalar_type() == at::kFloat8_e4m3fn;
+  TORCH_CHECK(ptr_D.scalar_type() == at::kBFloat16 || ptr_D.scalar_type() == at::kHalf || d_quant,
               "ptr_D must be bfloat16 or float16");
+  if (d_quant) {
+    // extended op only: quantised output of the fused SiLU epilogue, scales [Total_M, N / 256]
+    TORCH_CHECK(allow_segments && epilogue == 1 && ptr_D_scale.has_value() && is_B_fp8_block &&
+                A_dtype == at::kFloat8_e4m3fn, "float8_e4m3fn ptr_D needs the SiLU epilogue, ptr_D_scale, fp8 "
+                "activations and block-scaled fp8 weights");
+    TORCH_CHECK(N % 256 == 0 && ptr_D_scale->scalar_type() == at::kFloat && ptr_D_scale->is_contiguous() &&
+                ptr_D_scale->numel() == D_total_M * (N / 256), "ptr_D_scale must be float32 [Total_M, N / 256]");
+  }
   g.w = ptr_B.data_ptr();
   g.w_format = fmt;
   g.w_scale = ptr_B_scale.has_value() ? ptr_B_scale->data_ptr() : nullptr;
   g.bias = ptr_bias.has_value() ? ptr_bias->data_ptr() : nullptr;
   g.d = ptr_D.data_ptr();
-  g.d_dtype = ptr_D.scalar_type() == at::kBFloat16 ? B200MOE_BF16 : B200MOE_F16;
+  g.d_dtype = d_quant ? B200MOE_FP8_E4M3 : (ptr_D.scalar_type() == at::kBFloat16 ? B200MOE_BF16 : B200MOE_F16);
+  g.d_scale = d_quant ? ptr_D_scale->data_ptr() : nullptr;
+  g.mid_dtype = mid_f16 ? B200MOE_F16 : B200MOE_BF16;
   g.rows_per_expert = rows_per_expert.data_ptr<int32_t>();
   g.m = D_total_M; g.n = (int)N; g.k = (int)K; g.num_experts = (int)segments;
   g.w_experts = segments != num_experts ? (int)num_experts : 0;
@@ -222,10 +237,11 @@ at::Tensor b200_grouped_gemm(at::Tensor ptr_A, const std::optional<at::Tensor>& 
                              const std::optional<at::Tensor>& ptr_bias, at::Tensor ptr_D,
                              at::Tensor rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                              int64_t layout, int64_t epilogue, double alpha, double limit,
-                             double clamp_limit, int64_t impl, int64_t max_ctas, int64_t rows_hint) {
+                             double clamp_limit, int64_t impl, int64_t max_ctas, int64_t rows_hint,
+                             const std::optional<at::Tensor>& ptr_D_scale, bool mid_f16) {
   return grouped_gemm_impl(ptr_A, ptr_A_scale, ptr_B, ptr_B_scale, ptr_bias, ptr_D, rows_per_expert, N,
                            K, num_experts, layout, epilogue, alpha, limit, clamp_limit, impl, max_ctas, true,
-                           rows_hint);
+                           rows_hint, ptr_D_scale, mid_f16);
 }
 
 // Raises if a grouped GEMM on `like`'s device has given up a bounded wait since the last
@@ -259,7 +275,7 @@ TORCH_LIBRARY_FRAGMENT(_xpu_C, m) {
       "b200_grouped_gemm(Tensor ptr_A, Tensor? ptr_A_scale, Tensor ptr_B, Tensor? ptr_B_scale, "
       "Tensor? ptr_bias, Tensor(a!) ptr_D, Tensor rows_per_expert, int N, int K, int num_experts, "
       "int layout=0, int epilogue=0, float alpha=1.702, float limit=7.0, float clamp_limit=0.0, "
-      "int impl=0, int max_ctas=0, int rows_hint=0) -> Tensor(a!)");
+      "int impl=0, int max_ctas=0, int rows_hint=0, Tensor(b!)? ptr_D_scale=None, bool mid_f16=False) -> Tensor(a!)");
   m.def("b200_check_status(Tensor like, bool synchronize=True) -> int");
   m.def("b200_selftest_bounded_wait(Tensor like, int budget_cycles) -> ()");
 }
