@@ -2,6 +2,8 @@
 // csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:184-243, 267-287,
 // 322-383 of vllm-xpu-kernels) and the choice between the tensor-core kernel
 // and the plain-CUDA checking kernel.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -102,6 +104,16 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
   if (a->impl == 2 || a->w_format == B200MOE_W_MXFP8_KN) return grouped_gemm_check(a, st);   // 16-bit activations
   int rc = (a->w_format == B200MOE_W_MXFP4_NK || a->w_format == B200MOE_W_INT4_NK) ? grouped_gemm_tc_dq(a, st)
                                                                                     : grouped_gemm_tc(a, st);
-  if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) return grouped_gemm_check(a, st);
+  if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) {
+    // A request no tensor-core kernel covers (16-bit activations against fp8 weights, a gated
+    // epilogue on 16-bit weights, a row pitch that is not a multiple of 16 bytes) still gets its
+    // result from the plain-CUDA checking kernel, which is correct and one to two orders of
+    // magnitude slower: say so once per process instead of degrading silently.
+    static std::atomic<bool> warned{false};
+    if (!warned.exchange(true))
+      fprintf(stderr, "b200moe: grouped GEMM request outside the tensor-core kernels (%s); running the slow "
+                      "checking kernel for it (reported once)\n", b200moe_last_error());
+    return grouped_gemm_check(a, st);
+  }
   return rc;
 }
