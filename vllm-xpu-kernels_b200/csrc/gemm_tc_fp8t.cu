@@ -58,6 +58,12 @@ struct TParams {
   // token and 128 features in d_scale [M, n/256]
   float* d_scale;
   float clamp;            // >0: gate = min(gate, clamp), up = clamp(up, -clamp, clamp)
+  // 128 x 256 kernel: 4 stages and rows stored straight from the registers (few rows per expert:
+  // HBM-bound, bytes in flight matter, few rows to store), or 3 stages and the rows transposed
+  // through shared memory into whole 256-byte segments (many rows per expert: the store of a
+  // tile, which the promotion warps cannot overlap with anything, is 4 us as scattered 16-byte
+  // pieces and under 1 us as rows)
+  int stages;
 };
 
 struct TCtrl {
@@ -288,7 +294,9 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
 //                the 128 columns of feature block (w - 4) / 4, in two passes of 64
 // Tensor memory holds two accumulator stages of 256 columns.
 constexpr int kT2Threads = 384;
-constexpr int kT2Stages = 4;
+constexpr int kT2Stages = 4;          // ring of up to 4 stages (192 KB in flight per SM) ...
+constexpr int kT2StagesStaged = 3;    // ... or 3 with the fourth stage's room given to the store tiles
+constexpr int kT2RowPitch = 272;      // bytes per staged output row: 128 16-bit values + 16 (conflict-free 16-byte accesses)
 constexpr int kT2StageBytes = 49152;   // weights 2 x 16 KB, tokens 16 KB
 constexpr int kT2Acc = 2;
 
@@ -304,7 +312,13 @@ struct T2Ctrl {
   int tile_start[kMaxExperts + 1];
   int row_start[kMaxExperts + 1];
 };
-constexpr size_t kT2Smem = 1024 + (size_t)kT2Stages * kT2StageBytes + sizeof(T2Ctrl);
+// store tiles (3-stage form): per epilogue warp its 32 token rows x 128 features in 16 bits
+constexpr size_t kT2XposeBytes = 8 * 32 * kT2RowPitch;
+constexpr size_t kT2Ring = (size_t)kT2Stages * kT2StageBytes;      // the ring's room either way
+constexpr size_t kT2Smem = 1024 + kT2Ring + ((sizeof(T2Ctrl) + 15) & ~(size_t)15);
+static_assert(kT2XposeBytes <= kT2StageBytes + 24 * 1024, "store tiles must fit the fourth stage's room");
+constexpr size_t kT2SmemStaged = 1024 + (size_t)kT2StagesStaged * kT2StageBytes + kT2XposeBytes +
+                                 ((sizeof(T2Ctrl) + 15) & ~(size_t)15);
 
 //
 // kGated (the first grouped GEMM of a SiLU layer with block-scaled fp8 experts): a tile pairs the
@@ -322,7 +336,9 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_w, const TParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  T2Ctrl* ctrl = reinterpret_cast<T2Ctrl*>(smem + kT2Stages * kT2StageBytes);
+  const uint32_t stages = (uint32_t)p.stages;
+  uint8_t* xpose_base = smem + stages * kT2StageBytes;     // used by the 3-stage form only
+  T2Ctrl* ctrl = reinterpret_cast<T2Ctrl*>(xpose_base + (stages == (uint32_t)kT2Stages ? 0 : kT2XposeBytes));
   volatile int* abort_flag = &ctrl->abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // 256-feature tiles; gated: one tile per 128 gate features (p.n_tiles counts 128-feature blocks of n)
@@ -385,7 +401,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tma_load_3d(wdst + 16384, &tmap_w, &ctrl->full[s], n1, kb * 128, ti.e);
           }
           ptx::tma_load_2d(wdst + 32768, &tmap_a, &ctrl->full[s], kb * 128, ti.row0);
-          if (++s == (uint32_t)kT2Stages) { s = 0; ph ^= 1; }
+          if (++s == stages) { s = 0; ph ^= 1; }
         }
       }
     } else if (warp == 1 && lane == 0) {
@@ -409,7 +425,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
         const uint64_t adesc0 = ptx::make_smem_desc(st_addr + 32768, 16, 1024);
         const uint32_t d_tmem = tmem_base + a * 256;
-        const uint32_t s1 = (s + 1 == (uint32_t)kT2Stages) ? 0u : s + 1, ph1 = (s1 == 0u) ? ph ^ 1u : ph;
+        const uint32_t s1 = (s + 1 == stages) ? 0u : s + 1, ph1 = (s1 == 0u) ? ph ^ 1u : ph;
         const uint32_t a1 = (a + 1 == (uint32_t)kT2Acc) ? 0u : a + 1, aph1 = (a1 == 0u) ? aph ^ 1u : aph;
         const bool more = i + 1 < blocks;
         ptx::umma<true>(d_tmem, adesc0, wdesc0, idesc, 0u);
@@ -556,7 +572,8 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
         xpar ^= 1u;
         if (ok && r < ti.valid) {
           const float scale = fmaxf(__fdiv_rn(amax, 448.0f), 1.0f / (448.0f * 512.0f));
-          uint8_t* drow = reinterpret_cast<uint8_t*>(p.d) + (int64_t)(ti.row0 + r) * half_n + j0;
+          // 64 codes of this thread's row into the warp's staging tile (rows of 64 + 16 bytes)
+          const uint32_t my_row = ptx::smem_u32(xpose_base + (warp - 4) * 32 * kT2RowPitch) + lane * 80;
 #pragma unroll
           for (int c = 0; c < 64; c += 16) {
             uint32_t w[4];
@@ -568,18 +585,30 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 x |= (uint32_t)f32_to_e4m3(fmaxf(-448.0f, fminf(__fdividef(acc[c + i + b], scale), 448.0f))) << (8 * b);
               w[i >> 2] = x;
             }
-            *reinterpret_cast<uint4*>(drow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+            ptx::sts128(my_row + c, make_uint4(w[0], w[1], w[2], w[3]));
           }
           if (half == 0) p.d_scale[(int64_t)(ti.row0 + r) * (half_n >> 7) + ti.n_tile] = scale;
         }
+        __syncwarp();
+        if (ok) {
+          // eight rows per store: four lanes cover the 64 bytes of a row
+          const uint32_t xp = ptx::smem_u32(xpose_base + (warp - 4) * 32 * kT2RowPitch);
+          const int piece = lane & 3;
+          uint8_t* dbase = reinterpret_cast<uint8_t*>(p.d) + (int64_t)(ti.row0 + q * 32) * half_n + j0 + piece * 16;
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 8 + (lane >> 2);
+            if (q * 32 + rr < ti.valid)
+              *reinterpret_cast<uint4*>(dbase + (int64_t)rr * half_n) = ptx::lds128(xp + rr * 80 + piece * 16);
+          }
+        }
+        __syncwarp();
         continue;
       }
       const int f0 = ti.n_tile * 256 + half * 128;
-      if (ok && r < ti.valid && f0 < p.n) {
-        uint16_t* drow = reinterpret_cast<uint16_t*>(p.d) + (int64_t)(ti.row0 + r) * p.n + f0;
-#pragma unroll
-        for (int c = 0; c < 128; c += 8) {
-          uint32_t w[4];
+      if (ok && f0 < p.n) {
+        // the 128 finished values of this thread's row, bias added and rounded, as 16 x 16 bytes
+        auto packed = [&](int c, uint32_t (&w)[4]) {
 #pragma unroll
           for (int i = 0; i < 8; i += 2) {
             float x0 = acc[c + i], x1 = acc[c + i + 1];
@@ -595,7 +624,38 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
               w[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
             }
           }
-          *reinterpret_cast<uint4*>(drow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+        };
+        if (stages == (uint32_t)kT2Stages) {
+          if (r < ti.valid) {
+            uint16_t* drow = reinterpret_cast<uint16_t*>(p.d) + (int64_t)(ti.row0 + r) * p.n + f0;
+#pragma unroll
+            for (int c = 0; c < 128; c += 8) {
+              uint32_t w[4];
+              packed(c, w);
+              *reinterpret_cast<uint4*>(drow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        } else {
+          // into the warp's staging tile ...
+          const uint32_t xp = ptx::smem_u32(xpose_base + (warp - 4) * 32 * kT2RowPitch);
+          const uint32_t my_row = xp + lane * kT2RowPitch;
+#pragma unroll
+          for (int c = 0; c < 128; c += 8) {
+            uint32_t w[4];
+            packed(c, w);
+            ptx::sts128(my_row + c * 2, make_uint4(w[0], w[1], w[2], w[3]));
+          }
+          __syncwarp();
+          // ... and out again two whole rows per store: 16 lanes cover the 256 bytes of a row
+          const int piece = lane & 15;
+          uint16_t* dbase = reinterpret_cast<uint16_t*>(p.d) + (int64_t)(ti.row0 + q * 32) * p.n + f0 + piece * 8;
+#pragma unroll
+          for (int it = 0; it < 16; ++it) {
+            const int rr = it * 2 + (lane >> 4);
+            if (q * 32 + rr < ti.valid)
+              *reinterpret_cast<uint4*>(dbase + (int64_t)rr * p.n) = ptx::lds128(xp + rr * kT2RowPitch + piece * 16);
+          }
+          __syncwarp();
         }
       }
     }
@@ -615,8 +675,9 @@ template <bool kWKn, bool kGated>
 int launch_fp8t256(const CUtensorMap& ta, const CUtensorMap& tw, const TParams& p, int grid, cudaStream_t st) {
   auto kern = grouped_gemm_fp8t256_kernel<kWKn, kGated>;
   static SmemConfig configured;
-  if (int rc = configured.ensure(kern, kT2Smem)) return rc;
-  kern<<<grid, kT2Threads, kT2Smem, st>>>(ta, tw, p);
+  const size_t smem = p.stages == kT2Stages ? kT2Smem : kT2SmemStaged;
+  if (int rc = configured.ensure(kern, kT2SmemStaged > kT2Smem ? kT2SmemStaged : kT2Smem)) return rc;
+  kern<<<grid, kT2Threads, smem, st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_fp8t256_kernel");
   return B200MOE_OK;
 }
@@ -666,6 +727,10 @@ int grouped_gemm_tc_fp8t(const b200moe_gemm_args* a, cudaStream_t st) {
   p.out_f16 = gated ? (a->mid_dtype == B200MOE_F16) : (a->d_dtype == B200MOE_F16);
   p.d_scale = reinterpret_cast<float*>(a->d_scale);
   p.clamp = a->clamp_limit;
+  {
+    const int64_t in_use = (a->rows_hint > 0 && a->rows_hint < a->m) ? a->rows_hint : a->m;
+    p.stages = (gated || in_use / a->num_experts >= 128) ? kT2StagesStaged : kT2Stages;
+  }
   // A operand = tokens (K-major), B operand = weights (K-major, or MN-major for [E,K,N])
   p.idesc = ptx::make_idesc(0u, 0u, 0u, kn ? 1u : 0u, kTTok, kFeat);
 
