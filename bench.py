@@ -229,7 +229,11 @@ def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, transport="peer"):
         layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E, per_rank_rows=T > 256)
     else:
         layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
+    # every rank draws its own tokens and router logits; the routing bias belongs to the layer and is
+    # the same on all ranks (the one the single-GPU run uses)
     x_cpu, logits_cpu, bias_cpu = bw.make_inputs(cfg, T, seed=ep_rank)
+    if ep_rank != 0 and bias_cpu is not None:
+        bias_cpu = bw.make_inputs(cfg, T, seed=0)[2]
     return layer, x_cpu, logits_cpu, bias_cpu
 
 
@@ -529,9 +533,17 @@ def run_point(args, cfg, T, world, rank, local_rank, dev, dist):
         remote = sent - int(layer.send_counts[rank])
         row = cfg.H + (cfg.H // 128) * 4 if layer.quant else 2 * cfg.H
         recvd = int(layer.recv_counts.sum()) - int(layer.recv_counts[rank])
+        # routed (token, expert) slots every rank's experts received: the synthetic routing bias makes
+        # experts unequally popular, and a step lasts as long as its busiest rank
+        mine = torch.tensor([float((layer.recv_ids >= 0).sum())], device=dev)
+        loads = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(loads, mine)
+        loads = [float(v) for v in loads]
         line["ep"] = {"rows_sent": sent, "rows_sent_remote": remote,
                       "dispatch_bytes_remote": remote * (row + cfg.K * 8),
-                      "combine_bytes_remote": recvd * cfg.H * 2}
+                      "combine_bytes_remote": recvd * cfg.H * 2,
+                      "expert_slots_per_rank": [int(v) for v in loads],
+                      "load_max_over_mean": round(max(loads) * world / max(1.0, sum(loads)), 3)}
     return line
 
 

@@ -432,3 +432,43 @@ def test_fp8_layer_fused_and_unfused_activation_agree_bit_for_bit(native, T):
     ref = to.fused_moe_staged(x, d13, None, d2, None, tw, ids, cfg.E, activation=cfg.activation, act_quant=True,
                               gemm1_clamp_limit=0.8)
     torch.testing.assert_close(outs[0].cpu().float(), ref.float(), rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("name,dims,T", [("cfg3_qwen3_fp8", dict(H=512, I=256, E=32), 24),
+                                         ("cfg5_gptoss_mxfp4", dict(H=576, I=576, E=16), 9)])
+def test_layer_call_replays_from_a_cuda_graph(native, name, dims, T):
+    """After one warm-up call the layer allocates nothing, reads nothing back and picks no
+    launch parameter from device data, so a call can be captured in a CUDA graph (how serving
+    engines run decode steps) and replayed on new inputs."""
+    cfg = wl.scaled(wl.CONFIGS[name], **dims)
+    w = wl.make_weights(cfg, seed=2)
+    w13, s13, w2, s2 = wl.to_op_layout(cfg, w)
+    mv = lambda t: t.to(DEV) if t is not None else None
+    layer = native.XpuFusedMoe(mv(w13), mv(s13), mv(w["w13_bias"]), mv(w2), mv(s2), mv(w["w2_bias"]), cfg.K,
+                               cfg.activation, cfg.E)
+    ins = []
+    for seed in (1, 2):
+        x, logits, bias = wl.make_inputs(cfg, T, seed=seed)
+        tw, ids = wl.route_cpu(cfg, logits, bias)
+        ins.append((x.to(DEV), tw.to(DEV), ids.to(DEV)))
+    eager = []
+    for x, tw, ids in ins:
+        out = torch.empty(T, cfg.H, dtype=torch.bfloat16, device=DEV)
+        layer.apply(out, x, tw, ids)
+        eager.append(out.clone())
+    sx, stw, sids = (t.clone() for t in ins[0])
+    sout = torch.empty(T, cfg.H, dtype=torch.bfloat16, device=DEV)
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer.apply(sout, sx, stw, sids)
+        with torch.cuda.graph(g, stream=side):
+            layer.apply(sout, sx, stw, sids)
+    torch.cuda.current_stream().wait_stream(side)
+    for (x, tw, ids), ref in zip(ins, eager):
+        sx.copy_(x); stw.copy_(tw); sids.copy_(ids)
+        sout.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(sout, ref)
