@@ -220,10 +220,24 @@ def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, transport="peer"):
     assert fmi.FUSEDMOE_AVAILABLE, fmi.FUSEDMOE_UNAVAILABLE_REASON
     E = cfg.E // ep_world
     w13, s13, b13, w2, s2, b2 = bw.make_device_weights(cfg, E, dev, seed=1234 + ep_rank)
+    layer = None
     if ep_world > 1 and transport == "peer":
+        # symmetric memory is a property of the box (driver, IPC permissions): if any rank cannot
+        # set it up, all ranks fall back to the collective-library transport and the line says so
+        import torch.distributed as dist
         from vllm_xpu_kernels.ep_moe import EpPeerFusedMoe, SymmetricPeerGroup
-        layer = EpPeerFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E,
-                               SymmetricPeerGroup(dev), T, cfg.H)
+        ok = torch.ones(1, device=dev)
+        try:
+            layer = EpPeerFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E,
+                                   SymmetricPeerGroup(dev), T, cfg.H)
+        except Exception as e:  # noqa: BLE001
+            print(f"rank {ep_rank}: peer-memory transport unavailable ({e!r})", file=sys.stderr, flush=True)
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok) == 0.0:
+            layer = None
+    if layer is not None:
+        pass
     elif ep_world > 1:
         from vllm_xpu_kernels.ep_moe import EpFusedMoe
         layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E, per_rank_rows=T > 256)
@@ -235,6 +249,10 @@ def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, transport="peer"):
     if ep_rank != 0 and bias_cpu is not None:
         bias_cpu = bw.make_inputs(cfg, T, seed=0)[2]
     return layer, x_cpu, logits_cpu, bias_cpu
+
+
+def _transport_of(layer):
+    return "peer" if type(layer).__name__ == "EpPeerFusedMoe" else "nccl"
 
 
 def make_step(cfg, layer, dev, T):
@@ -325,7 +343,7 @@ def launches_per_step(cfg, T, layer, ep_world, transport) -> int:
     over peer memory: routing 1, dispatch sort 1|3 + dispatch 1, mask 1, the local layer without
     its gather, combine 1, final gather 1."""
     local = layer.local if ep_world > 1 else layer
-    act = 0 if local.fuse_activation else 1
+    act = 0 if local.fuses_activation(T * cfg.K) else 1
     mx = 2 if getattr(local, "mx_acts", False) else 0
     sort = lambda slots: 1 if slots <= 2048 else 3
     if ep_world == 1:
@@ -356,6 +374,8 @@ def run_point(args, cfg, T, world, rank, local_rank, dev, dist):
     ep_world = world if (args.parallelism == "ep" and world > 1) else 1
     layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev, ep_world, rank if ep_world > 1 else 0,
                                                             args.ep_transport)
+    if ep_world > 1:
+        args.ep_transport = _transport_of(layer)     # what actually runs
     step, (tw, ids) = make_step(cfg, layer, dev, T)
     x, logits = x_cpu.to(dev), logits_cpu.to(dev)
     bias = bias_cpu.to(dev) if bias_cpu is not None else None

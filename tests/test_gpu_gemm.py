@@ -327,3 +327,31 @@ def test_fp8_gemm_with_silu_and_quantisation_in_the_epilogue(native, layout, dty
     assert torch.equal(q.view(torch.uint8)[:n], ref_q.view(torch.uint8)[:n])
     assert torch.equal(s[:n], ref_s[:n])
     assert bool((q.view(torch.uint8)[n:] == 0x7f).all()) and bool((s[n:] == -1.0).all())   # rows past the segments
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("E,M,N,K,clamp,dtype", [(4, 20, 512, 256, 0.0, torch.bfloat16),      # 16-token tiles
+                                                 (8, 300, 2816, 512, 0.0, torch.bfloat16),    # 64-token tiles, cfg1's N
+                                                 (3, 330, 416, 192, 0.5, torch.bfloat16),     # 128-token tiles, I = 208
+                                                 (2, 900, 768, 320, 0.0, torch.float16)])     # beyond 96 rows per expert
+def test_16bit_gemm_with_silu_in_the_tensor_core_epilogue(native, layout, E, M, N, K, clamp, dtype):
+    """gemm1 with SiLU-and-mul fused on 16-bit weights: gate tile j and up tile I/128 + j of the same
+    tokens go into two accumulators and the epilogue writes silu(gate) * up as [M, N/2].  Against
+    the checking kernel's fused form (fp32 throughout) and against the unfused GEMM followed by
+    the torch statement of silu_and_mul."""
+    g = torch.Generator().manual_seed(E + M + N)
+    rows, a, w, bias = _bf16_case(E, M, N, K, g, True)
+    a, w, bias = a.to(dtype), w.to(dtype), bias.to(dtype)
+    wd = (w.transpose(1, 2).contiguous() if layout == "kn" else w).to(DEV)
+    lay = 2 if layout == "kn" else 1
+    args = (a.to(DEV), None, wd, None, bias.to(DEV), rows.to(DEV), N, K)
+    fused = grouped_gemm(*args, layout=lay, epilogue=1, impl=TC, out_dtype=dtype, clamp=clamp)
+    check = grouped_gemm(*args, layout=lay, epilogue=1, impl=CHECK, out_dtype=dtype, clamp=clamp)
+    n = int(rows.sum())
+    torch.testing.assert_close(fused[:n].float(), check[:n].float(), rtol=1e-2, atol=1e-2)
+    assert bool(torch.isnan(fused[n:].float()).all())            # rows past the segments are not written
+    full = grouped_gemm(*args, layout=lay, impl=TC, out_dtype=dtype).cpu().float()
+    if clamp > 0:
+        full[:, :N // 2].clamp_(max=clamp)
+        full[:, N // 2:].clamp_(min=-clamp, max=clamp)
+    torch.testing.assert_close(fused.cpu()[:n].float(), to.silu_and_mul(full)[:n].float(), rtol=2e-2, atol=2e-2)

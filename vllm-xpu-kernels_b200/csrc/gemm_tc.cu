@@ -53,6 +53,7 @@ struct TcParams {
   int num_kb;   // K blocks of 128 bytes
   uint32_t idesc;
   int out_f16;  // 1: D and bias are float16, 0: bfloat16
+  float clamp;  // gated epilogue: >0 clamps gate from above and up to +-clamp first
 };
 
 template <int BT, bool kFp8>
@@ -69,16 +70,20 @@ struct Ctrl {
   int row_start[kMaxExperts + 1];
 };
 
-template <int BT>
-__host__ __device__ constexpr int stage_bytes() { return kWTileBytes + BT * 128; }
-template <int BT>
+// kGated (16-bit inputs, token tiles up to 128): a tile pairs the 128 gate features j0.. with the
+// 128 up features n/2 + j0.. (the SiLU-and-mul layout, csrc/activation.cpp:131-133 of the
+// reference); a stage carries both weight tiles, the MMAs fill two accumulators and the epilogue
+// writes silu(gate) * up as [M, n/2].
+template <int BT, bool kGated = false>
+__host__ __device__ constexpr int stage_bytes() { return (kGated ? 2 : 1) * kWTileBytes + BT * 128; }
+template <int BT, bool kGated = false>
 __host__ __device__ constexpr int num_stages() {
-  return (200 * 1024) / stage_bytes<BT>() > kMaxStages ? kMaxStages
-                                                        : (200 * 1024) / stage_bytes<BT>();
+  return (200 * 1024) / stage_bytes<BT, kGated>() > kMaxStages ? kMaxStages
+                                                                : (200 * 1024) / stage_bytes<BT, kGated>();
 }
-template <int BT, bool kFp8>
+template <int BT, bool kFp8, bool kGated = false>
 __host__ __device__ constexpr size_t smem_bytes() {
-  return 1024 + (size_t)num_stages<BT>() * stage_bytes<BT>() + sizeof(Ctrl<BT, kFp8>);
+  return 1024 + (size_t)num_stages<BT, kGated>() * stage_bytes<BT, kGated>() + sizeof(Ctrl<BT, kFp8>);
 }
 // Accumulator stages in tensor memory.  16-bit inputs hand over one whole tile
 // per stage (two are enough); fp8 hands over every 128-wide K block, so more
@@ -87,22 +92,25 @@ template <int BT, bool kFp8>
 __host__ __device__ constexpr int acc_stages() {
   return !kFp8 ? 2 : (512 / BT > kMaxAccStages ? kMaxAccStages : 512 / BT);
 }
-template <int BT, bool kFp8>
+template <int BT, bool kFp8, bool kGated = false>
 __host__ __device__ constexpr uint32_t tmem_cols() {
-  const int c = acc_stages<BT, kFp8>() * BT;
+  const int c = acc_stages<BT, kFp8>() * BT * (kGated ? 2 : 1);
   return c <= 32 ? 32u : c <= 64 ? 64u : c <= 128 ? 128u : c <= 256 ? 256u : 512u;
 }
 // Four epilogue warps cover the 128 TMEM lanes.
 constexpr int kEpiWarps = 4;
 constexpr int kTcThreads = 64 + 32 * kEpiWarps;
 
-template <int BT, bool kFp8, bool kWKn>
+template <int BT, bool kFp8, bool kWKn, bool kGated = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_w, const TcParams p) {
   static_assert(!kFp8 || BT <= 64, "fp8 promotion keeps BT accumulators per thread");
-  constexpr int kStages = num_stages<BT>();
-  constexpr int kStageBytes = stage_bytes<BT>();
+  static_assert(!kGated || (!kFp8 && BT <= 128), "gated epilogue: 16-bit inputs, two accumulators of BT columns per stage");
+  constexpr int kStages = num_stages<BT, kGated>();
+  constexpr int kStageBytes = stage_bytes<BT, kGated>();
+  constexpr int kAOff = (kGated ? 2 : 1) * kWTileBytes;   // activations follow the weight tile(s) in a stage
+  constexpr int kAccCols = BT * (kGated ? 2 : 1);         // tensor-memory columns of one accumulator stage
   constexpr int kElemsPerKb = kFp8 ? 128 : 64;  // K elements per 128-byte row
   constexpr int kAccStages = acc_stages<BT, kFp8>();
   constexpr int kCols = BT;                      // token columns one epilogue warp owns
@@ -123,7 +131,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::prefetch_tensormap(&tmap_w);
     }
   } else if (warp == 1) {
-    ptx::tmem_alloc(&ctrl->tmem_base, tmem_cols<BT, kFp8>());
+    ptx::tmem_alloc(&ctrl->tmem_base, tmem_cols<BT, kFp8, kGated>());
     ptx::tmem_relinquish();
   } else if (warp == 2 && lane == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -159,16 +167,21 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* wdst = smem + s * kStageBytes;
-          uint8_t* adst = wdst + kWTileBytes;
+          uint8_t* adst = wdst + kAOff;
           ptx::mbar_expect_tx(&ctrl->full[s], kStageBytes);
           const int k0 = kb * kElemsPerKb;
-          if (!kWKn) {
-            ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], k0, n0, ti.e);
-          } else if (kFp8) {
-            ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], n0, k0, ti.e);
-          } else {
-            ptx::tma_load_3d(wdst, &tmap_w, &ctrl->full[s], n0, k0, ti.e);
-            ptx::tma_load_3d(wdst + kWTileBytes / 2, &tmap_w, &ctrl->full[s], n0 + 64, k0, ti.e);
+#pragma unroll
+          for (int half = 0; half < (kGated ? 2 : 1); ++half) {   // gate tile, then (gated) the up tile
+            uint8_t* wd = wdst + half * kWTileBytes;
+            const int nn = n0 + half * (p.n >> 1);
+            if (!kWKn) {
+              ptx::tma_load_3d(wd, &tmap_w, &ctrl->full[s], k0, nn, ti.e);
+            } else if (kFp8) {
+              ptx::tma_load_3d(wd, &tmap_w, &ctrl->full[s], nn, k0, ti.e);
+            } else {
+              ptx::tma_load_3d(wd, &tmap_w, &ctrl->full[s], nn, k0, ti.e);
+              ptx::tma_load_3d(wd + kWTileBytes / 2, &tmap_w, &ctrl->full[s], nn + 64, k0, ti.e);
+            }
           }
           ptx::tma_load_2d(adst, &tmap_a, &ctrl->full[s], k0, ti.row0);
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1; }
@@ -208,13 +221,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // offset (the address field counts 16-byte units), so the issue loop is adds only
           const uint32_t st_addr = smem_base + s * kStageBytes;
           const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
-          const uint64_t adesc0 = ptx::make_smem_desc(st_addr + kWTileBytes, 16, 1024);
-          const uint32_t d_tmem = tmem_base + a * BT;
+          const uint64_t adesc0 = ptx::make_smem_desc(st_addr + kAOff, 16, 1024);
+          const uint32_t d_tmem = tmem_base + a * kAccCols;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t accumulate = per_block ? (j > 0) : (kb > 0 || j > 0);
-            ptx::umma<kFp8>(d_tmem, wdesc0 + (uint64_t)((j * kWStep) >> 4), adesc0 + (uint64_t)((j * 32) >> 4), idesc,
-                            accumulate);
+          for (int half = 0; half < (kGated ? 2 : 1); ++half) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t accumulate = per_block ? (j > 0) : (kb > 0 || j > 0);
+              ptx::umma<kFp8>(d_tmem + half * BT, wdesc0 + (uint64_t)((half * kWTileBytes + j * kWStep) >> 4),
+                              adesc0 + (uint64_t)((j * 32) >> 4), idesc, accumulate);
+            }
           }
           ptx::umma_commit(&ctrl->empty[s]);
           if (per_block) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
@@ -267,9 +283,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       TileInfo ti;
       locate_tile<BT>(tile_start, row_start, t, cursor, ti, p.w_experts);
       const int feat = ti.n_tile * kFeat + et;
-      const bool feat_ok = feat < p.n;
-      float bias_v = 0.f;
-      if (p.bias != nullptr && feat_ok) bias_v = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat);
+      const int n_out = kGated ? (p.n >> 1) : p.n;
+      const bool feat_ok = feat < n_out;
+      float bias_v = 0.f, bias_up = 0.f;
+      if (p.bias != nullptr && feat_ok) {
+        bias_v = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat);
+        if (kGated) bias_up = load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + (p.n >> 1) + feat);
+      }
 
       if (!kFp8) {
         const uint32_t a = acc_it % kAccStages;
@@ -280,15 +300,27 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int c0 = 0; c0 < BT; c0 += kChunk) {
           if (c0 < ti.valid) {
-            uint32_t v[kChunk];
-            if (kChunk == 32) ptx::tmem_ld_32x32(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(v));
-            else ptx::tmem_ld_32x16(tmem_base + a * BT + c0 + lane_sel, reinterpret_cast<uint32_t(&)[16]>(v));
+            uint32_t v[kChunk], vu[kGated ? kChunk : 1];
+            const uint32_t col = tmem_base + a * kAccCols + c0 + lane_sel;
+            if (kChunk == 32) ptx::tmem_ld_32x32(col, reinterpret_cast<uint32_t(&)[32]>(v));
+            else ptx::tmem_ld_32x16(col, reinterpret_cast<uint32_t(&)[16]>(v));
+            if (kGated) {
+              if (kChunk == 32) ptx::tmem_ld_32x32(col + BT, reinterpret_cast<uint32_t(&)[32]>(vu));
+              else ptx::tmem_ld_32x16(col + BT, reinterpret_cast<uint32_t(&)[16]>(vu));
+            }
             ptx::tmem_wait_ld();
             float vals[kChunk];
 #pragma unroll
-            for (int i = 0; i < kChunk; ++i) vals[i] = __uint_as_float(v[i]) + bias_v;
+            for (int i = 0; i < kChunk; ++i) {
+              vals[i] = __uint_as_float(v[i]) + bias_v;
+              if (kGated) {
+                float g = vals[i], u = __uint_as_float(vu[kGated ? i : 0]) + bias_up;
+                if (p.clamp > 0.f) { g = fminf(g, p.clamp); u = fminf(fmaxf(u, -p.clamp), p.clamp); }
+                vals[i] = g * __fdividef(1.0f, 1.0f + __expf(-g)) * u;
+              }
+            }
             store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
-                                               (int64_t)ti.row0 + c0, ti.valid - c0, p.m, p.n,
+                                               (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
                                                ti.n_tile * kFeat + q * 32, lane);
           }
         }
@@ -386,18 +418,18 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 1) {
     ptx::tc_fence_after();
     if (*abort_flag != 0) __nanosleep(20000);  // let copies still in flight land
-    ptx::tmem_dealloc(tmem_base, tmem_cols<BT, kFp8>());
+    ptx::tmem_dealloc(tmem_base, tmem_cols<BT, kFp8, kGated>());
   }
   if (tid == 0 && *abort_flag != 0) report_timeout(p.status);
 }
 
-template <int BT, bool kFp8, bool kWKn>
+template <int BT, bool kFp8, bool kWKn, bool kGated = false>
 int launch_tc(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, int grid,
               cudaStream_t st) {
-  auto kern = grouped_gemm_tc_kernel<BT, kFp8, kWKn>;
+  auto kern = grouped_gemm_tc_kernel<BT, kFp8, kWKn, kGated>;
   static SmemConfig configured;
-  if (int rc = configured.ensure(kern, smem_bytes<BT, kFp8>())) return rc;
-  kern<<<grid, kTcThreads, smem_bytes<BT, kFp8>(), st>>>(ta, tw, p);
+  if (int rc = configured.ensure(kern, smem_bytes<BT, kFp8, kGated>())) return rc;
+  kern<<<grid, kTcThreads, smem_bytes<BT, kFp8, kGated>(), st>>>(ta, tw, p);
   B200_LAUNCH_OK("grouped_gemm_tc_kernel");
   return B200MOE_OK;
 }
@@ -410,8 +442,9 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   const bool a_fp8 = a->a_dtype == B200MOE_FP8_E4M3;
   const bool w16 = a->w_format == B200MOE_W_BF16_KN || a->w_format == B200MOE_W_BF16_NK;
   const bool w8b = a->w_format == B200MOE_W_FP8_BLOCK_NK || a->w_format == B200MOE_W_FP8_BLOCK_KN;
-  if (a->epilogue != B200MOE_EPI_NONE)
-    return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: gated epilogues not available");
+  const bool gated = a->epilogue == B200MOE_EPI_SILU_MUL;
+  if (a->epilogue != B200MOE_EPI_NONE && !(gated && w16 && !a_fp8 && (a->n / 2) % 16 == 0))
+    return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: fused epilogue only as SiLU-and-mul on 16-bit weights");
   if (!((w16 && !a_fp8) || (w8b && a_fp8)))
     return fail(B200MOE_E_UNSUPPORTED,
                 "tensor-core grouped GEMM takes 16-bit x 16-bit or fp8 x block-scaled fp8");
@@ -432,7 +465,8 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   p.m = a->m; p.n = a->n; p.k = a->k; p.num_experts = a->num_experts;
   const int w_sets = (a->w_experts > 0 && a->w_experts != a->num_experts) ? a->w_experts : a->num_experts;
   p.w_experts = w_sets != a->num_experts ? w_sets : 0;
-  p.n_tiles = (a->n + kFeat - 1) / kFeat;
+  p.n_tiles = ((gated ? a->n / 2 : a->n) + kFeat - 1) / kFeat;
+  p.clamp = a->clamp_limit;
   p.num_kb = (a->k + kpb - 1) / kpb;
   p.out_f16 = a->d_dtype == B200MOE_F16;
 
@@ -450,6 +484,8 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   else if (avg <= 40) bt = 64;
   else if (avg <= 96) bt = 128;   // measured on skewed routing: 128 rows per expert are 13 % faster at 256
   else bt = 256;
+  // two accumulators per stage: tensor memory holds the gated form up to 128-token tiles
+  if (gated && bt > 128) bt = 128;
 
   // prefill-sized fp8 segments: the token-major kernels (one scale register per thread and K block)
   if (a_fp8 && bt >= 128) return grouped_gemm_tc_fp8t(a, st);
@@ -496,6 +532,17 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
     }                                                                             \
     if (kn) return launch_tc<BT_, false, true>(ta, tw, p, grid, st);              \
     return launch_tc<BT_, false, false>(ta, tw, p, grid, st);                     \
+  }
+  if (gated) {
+#define B200_TC_GATED(BT_)                                                          \
+    if (bt == BT_) {                                                                \
+      if (kn) return launch_tc<BT_, false, true, true>(ta, tw, p, grid, st);        \
+      return launch_tc<BT_, false, false, true>(ta, tw, p, grid, st);               \
+    }
+    B200_TC_GATED(16)
+    B200_TC_GATED(64)
+    B200_TC_GATED(128)
+#undef B200_TC_GATED
   }
   B200_TC_CASE(16)
   B200_TC_CASE(64)

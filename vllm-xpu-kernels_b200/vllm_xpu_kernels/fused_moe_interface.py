@@ -185,8 +185,18 @@ class XpuFusedMoe:
 
     ``fuse_activation`` (not in the reference; keyword only) applies the gated
     activation inside the first grouped GEMM's epilogue instead of a separate
-    pass over ``[T*K, 2I]``; the default picks it where the tensor-core kernel
-    of the recipe has that epilogue (MXFP4 with SwigluOAI).
+    pass over ``[T*K, 2I]``.  ``None`` (default) picks it where the tensor-core
+    kernel of the recipe has that epilogue and it pays: MXFP4 with SwigluOAI
+    always; block-scaled fp8 with SiLU (where the epilogue also quantises
+    gemm2's input to e4m3 per 1x128 group, with the same values as the
+    two-kernel form) from ``FP8_FUSED_MIN_ROWS`` routed rows per expert on.
+    ``True`` forces it wherever a kernel has it (on 16-bit weights only the
+    slow checking kernel does), ``False`` never fuses.
+
+    ``persistent_workspace`` (not in the reference; keyword only, default
+    True): intermediates come from one grow-only pool per device shared by all
+    layer objects instead of fresh allocations per call; a layer object (and
+    the pool) must then be used from one stream at a time.
 
     ``mxfp4_activations`` (not in the reference; keyword only) chooses what the
     MXFP4 (and per-tensor fp8, and MXFP8, whose default is one plane as its recipe
@@ -280,6 +290,15 @@ class XpuFusedMoe:
         self._fp8_fused_ok = (is_block_fp8 and self._act_kind == "silu" and self.inter_size % FP8_BLOCK_SIZE == 0
                               and fuse_activation is not False)
         self._fp8_fused_min_rows = 12 if fuse_activation else FP8_FUSED_MIN_ROWS
+        # 16-bit weights with SiLU: the tensor-core kernel pairs gate and up tiles in two
+        # accumulators, which tensor memory holds for token tiles up to 128 - the sizes it picks up
+        # to 96 routed rows per expert.  Beyond that the 256-token tile plus a separate
+        # silu_and_mul is faster, so the fused form is taken per call below that size
+        # (fuse_activation=True forces it at every size).
+        is_16bit = not (is_fp8 or is_mxfp4 or is_mxfp8 or is_block_fp8 or is_int4)
+        self._w16_fused_ok = (is_16bit and self._act_kind == "silu" and self.inter_size % 16 == 0
+                              and fuse_activation is not False)
+        self._w16_fused_max_rows = None if fuse_activation else 96
         if fuse_activation is None:
             # fused where the tensor-core kernel of this recipe has the epilogue
             fuse_activation = self.is_mxfp4 and self._act_kind == "swigluoai"
@@ -439,6 +458,19 @@ class XpuFusedMoe:
             return
         self._experts(output_rows, rows, a1q_scale if self.is_block_fp8 else None, rows_per_segment)
 
+    def fuses_activation(self, num_moe_inputs):
+        """Which form gemm1 takes for a call with `num_moe_inputs` routed rows: "fp8" (SiLU and the
+        1x128 quantisation in the epilogue), "epilogue" (the gated activation in the epilogue), or
+        None (a separate activation kernel)."""
+        rows_expected = self.rows_hint if self.rows_hint > 0 else num_moe_inputs
+        E = self.num_experts
+        if self._fp8_fused_ok and rows_expected >= self._fp8_fused_min_rows * E:
+            return "fp8"
+        if self.fuse_activation or (self._w16_fused_ok and (
+                self._w16_fused_max_rows is None or rows_expected <= self._w16_fused_max_rows * E)):
+            return "epilogue"
+        return None
+
     def _experts(self, gemm2_output, remapped, a_scale1, rows_per_expert):
         """gemm1 (+ activation) and gemm2 on permuted rows; writes gemm2_output [rows, hidden]."""
         num_moe_inputs, hidden_size = remapped.shape
@@ -453,8 +485,8 @@ class XpuFusedMoe:
                                                    and self.gemm1_clamp_limit > 0) else 0.0
 
         # ---- gemm1 (+ activation) ----
-        rows_expected = self.rows_hint if self.rows_hint > 0 else num_moe_inputs
-        if self._fp8_fused_ok and rows_expected >= self._fp8_fused_min_rows * E:
+        fused = self.fuses_activation(num_moe_inputs)
+        if fused == "fp8":
             act_output = None
             act_q = self._buf("act_q", (num_moe_inputs, I), torch.float8_e4m3fn, dev)
             gemm2_act_scale = self._buf("act_q_scale", (num_moe_inputs, I // FP8_BLOCK_SIZE), torch.float32, dev)
@@ -463,7 +495,7 @@ class XpuFusedMoe:
                 rows_per_expert, 2 * I, hidden_size, E, 0, _EPI_SILU, 1.702, 7.0, clamp, 0,
                 self.gemm_max_ctas, self.rows_hint, gemm2_act_scale, output.dtype == torch.float16)
             self._mark("gemm1")
-        elif self.fuse_activation:
+        elif fused == "epilogue":
             act_output = self._buf("act_output", (num_moe_inputs, I), output.dtype, dev)
             torch.ops._xpu_C.b200_grouped_gemm(
                 remapped, a_scale1, self.w13, self.gemm1_wei_scales, self.w13_bias, act_output,
