@@ -294,6 +294,10 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
 //                the 128 columns of feature block (w - 4) / 4, in two passes of 64
 // Tensor memory holds two accumulator stages of 256 columns.
 constexpr int kT2Threads = 384;
+// setmaxnreg.inc waits - without any limit - until the CTA's register pool holds what it asks
+// for, so the re-balanced total must fit what the CTA got at launch (threads x launch registers)
+constexpr int kT2LaunchRegs = 168, kT2LowRegs = 40, kT2HighRegs = 232;
+static_assert(128 * kT2LowRegs + 256 * kT2HighRegs <= kT2Threads * kT2LaunchRegs, "setmaxnreg budget");
 constexpr int kT2Stages = 4;          // ring of up to 4 stages (192 KB in flight per SM) ...
 constexpr int kT2StagesStaged = 3;    // ... or 3 with the fourth stage's room given to the store tiles
 constexpr int kT2RowPitch = 272;      // bytes per staged output row: 128 16-bit values + 16 (conflict-free 16-byte accesses)
@@ -377,7 +381,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int total_tiles = tile_start[p.num_experts];
 
   if (warp < 4) {
-    ptx::setmaxnreg_dec<40>();
+    ptx::setmaxnreg_dec<kT2LowRegs>();
     if (warp == 0 && lane == 0) {
       // ------------------------------ TMA producer ------------------------------
       uint32_t s = 0, ph = 0;
@@ -441,7 +445,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------ promotion and epilogue --------------------------
-    ptx::setmaxnreg_inc<232>();
+    ptx::setmaxnreg_inc<kT2HighRegs>();
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
