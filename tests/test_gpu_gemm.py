@@ -355,3 +355,30 @@ def test_16bit_gemm_with_silu_in_the_tensor_core_epilogue(native, layout, E, M, 
         full[:, :N // 2].clamp_(max=clamp)
         full[:, N // 2:].clamp_(min=-clamp, max=clamp)
     torch.testing.assert_close(fused.cpu()[:n].float(), to.silu_and_mul(full)[:n].float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("E,M,N,K,clamp,dtype", [(4, 20, 512, 256, 0.0, torch.bfloat16),      # 16-token tiles
+                                                 (8, 300, 2816, 512, 0.0, torch.bfloat16),    # 64-token tiles
+                                                 (3, 330, 416, 192, 0.5, torch.bfloat16),     # 128-token tiles, I = 208
+                                                 (2, 900, 768, 320, 0.0, torch.float16)])     # 256-token tiles
+def test_16bit_gemm_with_swigluoai_in_the_tensor_core_epilogue(native, layout, E, M, N, K, clamp, dtype):
+    """gemm1 with SwigluOAI fused on 16-bit weights: gate (even feature) and up (odd feature) of an
+    output sit on neighbouring accumulator lanes, the epilogue writes [M, N/2].  Against the checking
+    kernel's fused form and against the unfused GEMM followed by the torch statement of the op."""
+    g = torch.Generator().manual_seed(E + M + N + 1)
+    rows, a, w, bias = _bf16_case(E, M, N, K, g, True)
+    a, w, bias = a.to(dtype), w.to(dtype), bias.to(dtype)
+    wd = (w.transpose(1, 2).contiguous() if layout == "kn" else w).to(DEV)
+    lay = 2 if layout == "kn" else 1
+    args = (a.to(DEV), None, wd, None, bias.to(DEV), rows.to(DEV), N, K)
+    fused = grouped_gemm(*args, layout=lay, epilogue=2, impl=TC, out_dtype=dtype, clamp=clamp)
+    check = grouped_gemm(*args, layout=lay, epilogue=2, impl=CHECK, out_dtype=dtype, clamp=clamp)
+    n = int(rows.sum())
+    torch.testing.assert_close(fused[:n].float(), check[:n].float(), rtol=1e-2, atol=1e-2)
+    assert bool(torch.isnan(fused[n:].float()).all())            # rows past the segments are not written
+    full = grouped_gemm(*args, layout=lay, impl=TC, out_dtype=dtype).cpu().float()
+    if clamp > 0:
+        full[:, 0::2].clamp_(max=clamp)
+        full[:, 1::2].clamp_(min=-clamp, max=clamp)
+    torch.testing.assert_close(fused.cpu()[:n].float(), to.swigluoai_and_mul(full)[:n].float(), rtol=2e-2, atol=2e-2)

@@ -106,7 +106,8 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* a, b200moe_stream s
                                                                                     : grouped_gemm_tc(a, st);
   if (rc == B200MOE_E_UNSUPPORTED && a->impl == 0) {
     // A request no tensor-core kernel covers (16-bit activations against fp8 weights, a gated
-    // epilogue on 16-bit weights, a row pitch that is not a multiple of 16 bytes) still gets its
+    // epilogue whose output width is not a multiple of 16, a row pitch that is not a multiple of
+    // 16 bytes) still gets its
     // result from the plain-CUDA checking kernel, which is correct and one to two orders of
     // magnitude slower: say so once per process instead of degrading silently.
     static std::atomic<bool> warned{false};

@@ -54,6 +54,8 @@ struct TcParams {
   uint32_t idesc;
   int out_f16;  // 1: D and bias are float16, 0: bfloat16
   float clamp;  // gated epilogue: >0 clamps gate from above and up to +-clamp first
+  int swiglu;   // 1: gate on even, up on odd features; D = (up + 1) * gate * sigmoid(alpha * gate), n / 2 wide
+  float alpha, limit;
 };
 
 template <int BT, bool kFp8>
@@ -319,9 +321,28 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 vals[i] = g * __fdividef(1.0f, 1.0f + __expf(-g)) * u;
               }
             }
-            store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
-                                               (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
-                                               ti.n_tile * kFeat + q * 32, lane);
+            if (!kGated && p.swiglu) {
+              // gate and up of one output feature sit on neighbouring lanes
+              const float c_lim = p.clamp > 0.f ? p.clamp : INFINITY;
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i) {
+                const float x = vals[i];
+                const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+                float gate = (lane & 1) ? other : x;
+                float up = (lane & 1) ? x : other;
+                gate = fminf(fminf(gate, c_lim), p.limit);
+                up = fminf(fmaxf(up, -c_lim), c_lim);
+                up = fminf(fmaxf(up, -p.limit), p.limit);
+                vals[i] = (up + 1.0f) * gate * __fdividef(1.0f, 1.0f + __expf(-gate * p.alpha));
+              }
+              store_block_transposed<kChunk, 16>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
+                                                 (int64_t)ti.row0 + c0, ti.valid - c0, p.m, p.n >> 1,
+                                                 (ti.n_tile * kFeat + q * 32) >> 1, lane);
+            } else {
+              store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
+                                                 (int64_t)ti.row0 + c0, ti.valid - c0, p.m, n_out,
+                                                 ti.n_tile * kFeat + q * 32, lane);
+            }
           }
         }
         ptx::tc_fence_before();
@@ -443,8 +464,9 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   const bool w16 = a->w_format == B200MOE_W_BF16_KN || a->w_format == B200MOE_W_BF16_NK;
   const bool w8b = a->w_format == B200MOE_W_FP8_BLOCK_NK || a->w_format == B200MOE_W_FP8_BLOCK_KN;
   const bool gated = a->epilogue == B200MOE_EPI_SILU_MUL;
-  if (a->epilogue != B200MOE_EPI_NONE && !(gated && w16 && !a_fp8 && (a->n / 2) % 16 == 0))
-    return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: fused epilogue only as SiLU-and-mul on 16-bit weights");
+  const bool swiglu = a->epilogue == B200MOE_EPI_SWIGLUOAI;
+  if (a->epilogue != B200MOE_EPI_NONE && !((gated || swiglu) && w16 && !a_fp8 && (a->n / 2) % 16 == 0))
+    return fail(B200MOE_E_UNSUPPORTED, "tensor-core grouped GEMM: fused gated activations only on 16-bit weights");
   if (!((w16 && !a_fp8) || (w8b && a_fp8)))
     return fail(B200MOE_E_UNSUPPORTED,
                 "tensor-core grouped GEMM takes 16-bit x 16-bit or fp8 x block-scaled fp8");
@@ -467,6 +489,7 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   p.w_experts = w_sets != a->num_experts ? w_sets : 0;
   p.n_tiles = ((gated ? a->n / 2 : a->n) + kFeat - 1) / kFeat;
   p.clamp = a->clamp_limit;
+  p.swiglu = swiglu ? 1 : 0; p.alpha = a->act_alpha; p.limit = a->act_limit;
   p.num_kb = (a->k + kpb - 1) / kpb;
   p.out_f16 = a->d_dtype == B200MOE_F16;
 

@@ -393,7 +393,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int n0 = kGated ? ti.n_tile * 128 : ti.n_tile * 256;
         const int n1 = kGated ? (up_block0 + ti.n_tile) * 128 : n0 + 128;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag, true)) { ok = false; break; }
           uint8_t* wdst = smem + s * kT2StageBytes;
           ptx::mbar_expect_tx(&ctrl->full[s], kT2StageBytes);
           // two 128-feature blocks (the second one is zero-filled past N)
@@ -408,8 +408,9 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (++s == stages) { s = 0; ph ^= 1; }
         }
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
       // ------------------------------ MMA issuer --------------------------------
+      // (the whole warp runs the loop with the same values; one elected lane issues)
       uint32_t s = 0, ph = 0, a = 0, aph = 0;
       const uint32_t smem_base = ptx::smem_u32(smem);
       constexpr uint32_t kWLbo = !kWKn ? 16u : 16384u;
@@ -418,12 +419,19 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) ++my_tiles;
       const int64_t blocks = (int64_t)my_tiles * p.num_kb;
       const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((256u >> 3) << 17);
+      auto mma = [&](uint32_t d, uint64_t ad, uint64_t wd, uint32_t accumulate) {
+        ptx::umma_fp8_elect(d, ad, wd, idesc, accumulate);
+      };
       // The barriers of the next block are polled between this block's MMA issues, where
       // the thread would otherwise only wait for room in the tensor pipe's queue.
       bool full_ready = false, acc_ready = false;
       for (int64_t i = 0; i < blocks; ++i) {
-        if (!acc_ready && !ptx::mbar_wait(&ctrl->acc_empty[a], aph ^ 1, abort_flag)) break;
-        if (!full_ready && !ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) break;
+        // (spinning waits here and in the promotion warps: the hand-over of an accumulator stage
+        // is the kernel's critical loop, and a suspended try_wait wakes up late)
+        bool go = true;
+        if (!acc_ready) go = ptx::mbar_wait(&ctrl->acc_empty[a], aph ^ 1, abort_flag, true);
+        if (go && !full_ready) go = ptx::mbar_wait(&ctrl->full[s], ph, abort_flag, true);
+        if (!__all_sync(0xffffffffu, go)) break;
         ptx::tc_fence_after();
         const uint32_t st_addr = smem_base + s * kT2StageBytes;
         const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
@@ -432,14 +440,14 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t s1 = (s + 1 == stages) ? 0u : s + 1, ph1 = (s1 == 0u) ? ph ^ 1u : ph;
         const uint32_t a1 = (a + 1 == (uint32_t)kT2Acc) ? 0u : a + 1, aph1 = (a1 == 0u) ? aph ^ 1u : aph;
         const bool more = i + 1 < blocks;
-        ptx::umma<true>(d_tmem, adesc0, wdesc0, idesc, 0u);
-        ptx::umma<true>(d_tmem, adesc0 + (uint64_t)(32 >> 4), wdesc0 + (uint64_t)(kWStep >> 4), idesc, 1u);
-        full_ready = more && ptx::mbar_test_wait(&ctrl->full[s1], ph1);
-        ptx::umma<true>(d_tmem, adesc0 + (uint64_t)(64 >> 4), wdesc0 + (uint64_t)((2 * kWStep) >> 4), idesc, 1u);
-        ptx::umma<true>(d_tmem, adesc0 + (uint64_t)(96 >> 4), wdesc0 + (uint64_t)((3 * kWStep) >> 4), idesc, 1u);
-        ptx::umma_commit(&ctrl->empty[s]);
-        ptx::umma_commit(&ctrl->acc_full[a]);
-        acc_ready = more && ptx::mbar_test_wait(&ctrl->acc_empty[a1], aph1 ^ 1u);
+        mma(d_tmem, adesc0, wdesc0, 0u);
+        mma(d_tmem, adesc0 + (uint64_t)(32 >> 4), wdesc0 + (uint64_t)(kWStep >> 4), 1u);
+        full_ready = __all_sync(0xffffffffu, more && ptx::mbar_test_wait(&ctrl->full[s1], ph1));
+        mma(d_tmem, adesc0 + (uint64_t)(64 >> 4), wdesc0 + (uint64_t)((2 * kWStep) >> 4), 1u);
+        mma(d_tmem, adesc0 + (uint64_t)(96 >> 4), wdesc0 + (uint64_t)((3 * kWStep) >> 4), 1u);
+        ptx::umma_commit_elect(&ctrl->empty[s]);
+        ptx::umma_commit_elect(&ctrl->acc_full[a]);
+        acc_ready = __all_sync(0xffffffffu, more && ptx::mbar_test_wait(&ctrl->acc_empty[a1], aph1 ^ 1u));
         s = s1; ph = ph1; a = a1; aph = aph1;
       }
     }
@@ -510,7 +518,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (g * kTGroup + jb >= p.num_kb) break;
           const float sc0 = cur.s0[jb];
           const float sc1 = kGated ? cur.s1[kGated ? jb : 0] : sc0;
-          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], aph, abort_flag))) {
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], aph, abort_flag, true))) {
             *abort_flag = 1; ok = false; break;
           }
           ptx::tc_fence_after();

@@ -310,6 +310,26 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// The same two instructions for a warp that runs the issue loop convergently (all lanes hold
+// the same operands): one elected lane issues.  A warp-uniform loop lets the compiler keep
+// descriptors and barrier addresses in uniform registers (measured on the fp8 kernel: 4 MMAs
+// and 2 commits issue in 370 instead of 640 cycles).
+__device__ __forceinline__ void umma_fp8_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred pe, pa;\n\telect.sync _|pe, 0xffffffff;\n\tsetp.ne.b32 pa, %4, 0;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, pa;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar))
+      : "memory");
+}
+
 // Explicit shared-space accesses (32-bit shared addresses): pointers derived
 // from the re-aligned dynamic shared memory base are otherwise treated as
 // generic and take the slower generic load/store path.

@@ -186,12 +186,12 @@ class XpuFusedMoe:
     ``fuse_activation`` (not in the reference; keyword only) applies the gated
     activation inside the first grouped GEMM's epilogue instead of a separate
     pass over ``[T*K, 2I]``.  ``None`` (default) picks it where the tensor-core
-    kernel of the recipe has that epilogue and it pays: MXFP4 with SwigluOAI
-    always; block-scaled fp8 with SiLU (where the epilogue also quantises
-    gemm2's input to e4m3 per 1x128 group, with the same values as the
-    two-kernel form) from ``FP8_FUSED_MIN_ROWS`` routed rows per expert on.
-    ``True`` forces it wherever a kernel has it (on 16-bit weights only the
-    slow checking kernel does), ``False`` never fuses.
+    kernel of the recipe has that epilogue and it pays: MXFP4 and 16-bit
+    weights with SwigluOAI always; 16-bit weights with SiLU up to 96 routed
+    rows per expert; block-scaled fp8 with SiLU (where the epilogue also
+    quantises gemm2's input to e4m3 per 1x128 group, with the same values as
+    the two-kernel form) from ``FP8_FUSED_MIN_ROWS`` routed rows per expert on.
+    ``True`` forces it wherever a kernel has it, ``False`` never fuses.
 
     ``persistent_workspace`` (not in the reference; keyword only, default
     True): intermediates come from one grow-only pool per device shared by all
@@ -296,9 +296,11 @@ class XpuFusedMoe:
         # silu_and_mul is faster, so the fused form is taken per call below that size
         # (fuse_activation=True forces it at every size).
         is_16bit = not (is_fp8 or is_mxfp4 or is_mxfp8 or is_block_fp8 or is_int4)
-        self._w16_fused_ok = (is_16bit and self._act_kind == "silu" and self.inter_size % 16 == 0
+        # SwigluOAI keeps gate and up of a feature on neighbouring accumulator lanes: one accumulator,
+        # every tile size, so it is fused at every size.
+        self._w16_fused_ok = (is_16bit and self._act_kind in ("silu", "swigluoai") and self.inter_size % 16 == 0
                               and fuse_activation is not False)
-        self._w16_fused_max_rows = None if fuse_activation else 96
+        self._w16_fused_max_rows = None if (fuse_activation or self._act_kind == "swigluoai") else 96
         if fuse_activation is None:
             # fused where the tensor-core kernel of this recipe has the epilogue
             fuse_activation = self.is_mxfp4 and self._act_kind == "swigluoai"
