@@ -215,13 +215,45 @@ class StageTimer:
         return out
 
 
-def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, transport="peer"):
+def route_on_device(cfg, logits, bias):
+    """Top-k routing of the workload: (weights [T, K] f32, ids [T, K])."""
+    T = logits.shape[0]
+    if cfg.routing == "softmax":
+        tw = torch.empty(T, cfg.K, dtype=torch.float32, device=logits.device)
+        ids = torch.empty(T, cfg.K, dtype=torch.int32, device=logits.device)
+        torch.ops._moe_C.topk_softmax(tw, ids, torch.empty_like(ids), logits, cfg.renormalize, None)
+        return tw, ids
+    scores = torch.sigmoid(logits)
+    return torch.ops._moe_C.grouped_topk(scores, scores + bias, cfg.n_group, cfg.topk_group, cfg.K,
+                                         cfg.renormalize, cfg.routed_scaling_factor)
+
+
+CALIBRATION_SEED, CALIBRATION_TOKENS = 777_001, 8192
+
+
+def balanced_placement(cfg, dev, ep_world, bias):
+    """expert -> slot for the sharded experts, from the expert histogram of a calibration batch:
+    tokens of the workload's distribution (a seed no timed batch uses) routed with the layer's
+    own routing bias.  Deterministic, so every rank computes the same table."""
+    from vllm_xpu_kernels.ep_moe import balanced_expert_slots
+    _, logits, _ = bw.make_inputs(cfg, CALIBRATION_TOKENS, seed=CALIBRATION_SEED)
+    _, ids = route_on_device(cfg, logits.to(dev), bias.to(dev) if bias is not None else None)
+    load = torch.bincount(ids.reshape(-1).long().cpu(), minlength=cfg.E)
+    return balanced_expert_slots(load, ep_world)
+
+
+def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, transport="peer", placement="balanced"):
     """Synthetic weights on the device (this rank's experts only when the experts are sharded)
     and the host-side inputs of one step."""
     import vllm_xpu_kernels.fused_moe_interface as fmi
     assert fmi.FUSEDMOE_AVAILABLE, fmi.FUSEDMOE_UNAVAILABLE_REASON
     E = cfg.E // ep_world
     w13, s13, b13, w2, s2, b2 = bw.make_device_weights(cfg, E, dev, seed=1234 + ep_rank)
+    # every rank draws its own tokens and router logits; the routing bias belongs to the layer and is
+    # the same on all ranks (the one the single-GPU run uses)
+    x_cpu, logits_cpu, bias_cpu = bw.make_inputs(cfg, T, seed=ep_rank)
+    if ep_rank != 0 and bias_cpu is not None:
+        bias_cpu = bw.make_inputs(cfg, T, seed=0)[2]
     layer = None
     if ep_world > 1 and transport == "peer":
         # symmetric memory is a property of the box (driver, IPC permissions): if any rank cannot
@@ -230,8 +262,9 @@ def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, transport="peer"):
         from vllm_xpu_kernels.ep_moe import EpPeerFusedMoe, SymmetricPeerGroup
         ok = torch.ones(1, device=dev)
         try:
+            slot = balanced_placement(cfg, dev, ep_world, bias_cpu) if placement == "balanced" else None
             layer = EpPeerFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E,
-                                   SymmetricPeerGroup(dev), T, cfg.H)
+                                   SymmetricPeerGroup(dev), T, cfg.H, expert_slot=slot)
         except Exception as e:  # noqa: BLE001
             print(f"rank {ep_rank}: peer-memory transport unavailable ({e!r})", file=sys.stderr, flush=True)
             ok.zero_()
@@ -245,11 +278,6 @@ def build_gpu_workload(cfg, T, dev, ep_world=1, ep_rank=0, transport="peer"):
         layer = EpFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E, per_rank_rows=T > 256)
     else:
         layer = fmi.XpuFusedMoe(w13, s13, b13, w2, s2, b2, cfg.K, cfg.activation, E)
-    # every rank draws its own tokens and router logits; the routing bias belongs to the layer and is
-    # the same on all ranks (the one the single-GPU run uses)
-    x_cpu, logits_cpu, bias_cpu = bw.make_inputs(cfg, T, seed=ep_rank)
-    if ep_rank != 0 and bias_cpu is not None:
-        bias_cpu = bw.make_inputs(cfg, T, seed=0)[2]
     return layer, x_cpu, logits_cpu, bias_cpu
 
 
@@ -290,6 +318,8 @@ def time_gemms(cfg, layer, ids, T, dev, iters, ep_world=1, ep_rank=0):
         gathered = [torch.empty_like(ids) for _ in range(ep_world)]
         dist.all_gather(gathered, ids)
         flat = torch.cat([g.reshape(-1) for g in gathered]).long()
+        if getattr(layer, "expert_slot", None) is not None:
+            flat = layer.expert_slot.long()[flat]
         flat = flat[(flat >= ep_rank * E) & (flat < (ep_rank + 1) * E)] - ep_rank * E
         layer = layer.local
     else:
@@ -375,7 +405,7 @@ def run_point(args, cfg, T, world, rank, local_rank, dev, dist):
     """One (workload, T) measurement -> the JSON line as a dict."""
     ep_world = world if (args.parallelism == "ep" and world > 1) else 1
     layer, x_cpu, logits_cpu, bias_cpu = build_gpu_workload(cfg, T, dev, ep_world, rank if ep_world > 1 else 0,
-                                                            args.ep_transport)
+                                                            args.ep_transport, args.ep_placement)
     if ep_world > 1:
         args.ep_transport = _transport_of(layer)     # what actually runs
     step, (tw, ids) = make_step(cfg, layer, dev, T)
@@ -528,7 +558,9 @@ def run_point(args, cfg, T, world, rank, local_rank, dev, dist):
     layer_roof = {"hbm_frac": round(layer_t_hbm / (ms_per_step * 1e-3), 4),
                   "tensor_frac": round(layer_t_tensor / (ms_per_step * 1e-3), 4)} if ep_world == 1 else None
 
-    par = (f"ep{world}: {cfg.E // world} experts per GPU, dispatch/combine "
+    par = (f"ep{world}: {cfg.E // world} experts per GPU"
+           + (" placed by load" if getattr(layer, "expert_slot", None) is not None else "")
+           + ", dispatch/combine "
            + ("by peer stores over NVLink (symmetric memory), two barriers per step"
               if args.ep_transport == "peer" else "by NCCL all-to-all")) if ep_world > 1 else (
         f"replicas x{world}" if world > 1 else "single GPU")
@@ -570,6 +602,9 @@ def run_point(args, cfg, T, world, rank, local_rank, dev, dist):
         line["ep"] = {"rows_sent": sent, "rows_sent_remote": remote,
                       "dispatch_bytes_remote": remote * (row + cfg.K * 8),
                       "combine_bytes_remote": recvd * cfg.H * 2,
+                      "placement": ("experts placed by the load of a calibration batch (%d tokens, seed %d)"
+                                    % (CALIBRATION_TOKENS, CALIBRATION_SEED)
+                                    if layer.expert_slot is not None else "contiguous"),
                       "expert_slots_per_rank": [int(v) for v in loads],
                       "load_max_over_mean": round(max(loads) * world / max(1.0, sum(loads)), 3)}
     return line
@@ -701,6 +736,10 @@ def main():
     ap.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                     help="ep: dispatch / combine by this repository's kernels storing into peer memory over "
                          "NVLink (default) or by NCCL all-to-all (the comparison point)")
+    ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "contiguous"],
+                    help="ep over peer memory: which rank holds which experts - placed so that the ranks' "
+                         "loads even out, from the expert histogram of a calibration batch (default), or "
+                         "expert g on rank g // (E / N)")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="device-resident loop replays the step from a CUDA graph instead of eager ops")
     ap.add_argument("--sweep", action="store_true",

@@ -529,8 +529,10 @@ int b200moe_moe_sum(void* out, const void* in, b200moe_dtype dtype,
  * process per GPU: every rank keeps receive buffers that its peers can address
  * (symmetric memory or IPC mappings; over NVLink), and the kernels below store
  * straight into them with ordinary global stores - no staging copy, no host
- * read of any count.  Experts are split contiguously and evenly: expert g lives
- * on rank g / num_local_experts.
+ * read of any count.  Every rank holds num_local_experts experts: expert g sits in
+ * slot expert_slot[g] (slot g without a table), on rank slot / num_local_experts as
+ * its local expert slot % num_local_experts.  The table lets a deployment place
+ * experts by load instead of contiguously.
  *
  * Buffers of rank d, each in `ep_size` regions of `capacity` rows, region s
  * written by source rank s (capacity >= the tokens any rank dispatches per call):
@@ -567,6 +569,8 @@ typedef struct {
   float* recv_weights[B200MOE_MAX_EP];
   int32_t* recv_counts[B200MOE_MAX_EP];
   void* comb_rows[B200MOE_MAX_EP];
+  const int32_t* expert_slot; /* device, [ep_size * num_local_experts]: a permutation
+                                 of the slots, the same on every rank; NULL = identity */
 } b200moe_ep_peers;
 
 /* Scratch of b200moe_ep_dispatch for `num_tokens` tokens. */

@@ -134,15 +134,18 @@ def remap_hidden_states(hidden, scales, topk_ids, expert_map, local_experts):
     return remapped, rs, rows, row_map.view(T, K)
 
 
-def ep_dispatch_plan(topk_ids, ep_size, num_local_experts, capacity):
+def ep_dispatch_plan(topk_ids, ep_size, num_local_experts, capacity, expert_slot=None):
     """The bookkeeping of the expert-parallel dispatch, sequentially: a token goes once to every
     rank that owns one of its experts (expert g on rank g // num_local_experts, the split of
-    csrc/moe/init_expert_map.cpp:45-52); its row index at rank d is the number of earlier tokens
+    csrc/moe/init_expert_map.cpp:45-52; with `expert_slot` [E], a permutation expert -> slot,
+    the slot takes the place of g); its row index at rank d is the number of earlier tokens
     of this source that also go to d.  -> send_counts [ep] i32, send_pos [T, ep] i32
     (d * capacity + index, or -1), loc_ids [T, ep, K] i32 (expert id local to rank d, -1 for
     experts of other ranks)."""
     T, K = topk_ids.shape
     ids = topk_ids.long()
+    if expert_slot is not None:
+        ids = torch.where(ids >= 0, expert_slot.long()[ids.clamp(min=0)], ids)
     counts = torch.zeros(ep_size, dtype=torch.int32)
     pos = torch.full((T, ep_size), -1, dtype=torch.int32)
     loc = torch.full((T, ep_size, K), -1, dtype=torch.int32)

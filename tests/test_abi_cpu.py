@@ -32,7 +32,7 @@ def test_every_declared_symbol_is_exported(lib):
 def test_status_strings_and_version(lib):
     lib.b200moe_status_string.restype = ctypes.c_char_p
     lib.b200moe_last_error.restype = ctypes.c_char_p
-    assert lib.b200moe_abi_version() == 6
+    assert lib.b200moe_abi_version() == 7
     assert lib.b200moe_status_string(0) == b"ok"
     assert b"bad argument" in lib.b200moe_status_string(-1)
 

@@ -1,6 +1,8 @@
 """CPU, world_size 2 over Gloo: the expert-parallel dispatch / combine plumbing."""
 import socket
 
+import pytest
+
 import torch
 import torch.multiprocessing as mp
 
@@ -67,3 +69,26 @@ def test_owner_map_is_the_contiguous_even_split():
     for r in range(8):  # consistent with init_expert_map: rank r maps exactly its own experts
         local = co.init_expert_map(32, r, 8)
         assert torch.equal(local >= 0, m == r)
+
+
+def test_balanced_expert_slots_even_out_the_ranks():
+    from vllm_xpu_kernels.ep_moe import balanced_expert_slots, experts_in_slots
+    from oracle import torch_oracle as to
+    g = torch.Generator().manual_seed(0)
+    load = torch.rand(64, generator=g) ** 3 * 1000          # a few hot experts
+    slot = balanced_expert_slots(load, 8)
+    assert slot.dtype == torch.int32 and sorted(slot.tolist()) == list(range(64))
+    per_rank = torch.zeros(8, dtype=torch.float64).index_add_(0, (slot // 8).long(), load.double())
+    contiguous = load.double().view(8, 8).sum(1)
+    assert float(per_rank.max() / per_rank.mean()) < 1.05 < float(contiguous.max() / contiguous.mean())
+    # the experts a rank stacks, slot by slot, and the table agree
+    for r in range(8):
+        held = experts_in_slots(slot, r, 8)
+        assert slot[held].tolist() == list(range(r * 8, (r + 1) * 8))
+    with pytest.raises(ValueError):
+        balanced_expert_slots(torch.ones(10), 4)
+    # the dispatch bookkeeping with a placement = the contiguous bookkeeping on relabelled ids
+    ids = torch.randint(0, 64, (20, 4), generator=g).to(torch.int32)
+    a = to.ep_dispatch_plan(ids, 8, 8, 32, slot)
+    b = to.ep_dispatch_plan(slot[ids.long()], 8, 8, 32)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))

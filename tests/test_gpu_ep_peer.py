@@ -16,19 +16,21 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _build(native, cfg, ep, cap, seed):
-    from vllm_xpu_kernels.ep_moe import EpPeerFusedMoe, LocalPeerWorld
+def _build(native, cfg, ep, cap, seed, slot=None):
+    from vllm_xpu_kernels.ep_moe import EpPeerFusedMoe, LocalPeerWorld, experts_in_slots
     w = wl.make_weights(cfg, seed=seed)
     E_local = cfg.E // ep
     world = LocalPeerWorld(ep, DEV)
     layers = []
     for r in range(ep):
-        sl = slice(r * E_local, (r + 1) * E_local)
+        # the experts this rank holds, in the order of its local slots
+        sl = slice(r * E_local, (r + 1) * E_local) if slot is None else experts_in_slots(slot, r, E_local)
         wr = {k: (v[sl] if v is not None else None) for k, v in w.items()}
         w13, s13, w2, s2 = wl.to_op_layout(cfg, wr)
         mv = lambda t: t.to(DEV) if t is not None else None
         layers.append(EpPeerFusedMoe(mv(w13), mv(s13), mv(wr["w13_bias"]), mv(w2), mv(s2), mv(wr["w2_bias"]),
-                                     cfg.K, cfg.activation, E_local, world.member(r), cap, cfg.H))
+                                     cfg.K, cfg.activation, E_local, world.member(r), cap, cfg.H,
+                                     expert_slot=slot))
     return w, layers
 
 
@@ -38,16 +40,23 @@ def _oracle_full(cfg, w, x, tw, ids):
                                activation=cfg.activation, act_quant=cfg.recipe == "fp8block")
 
 
-@pytest.mark.parametrize("cfg_name,dims,ep,tokens,tol", [
-    ("cfg1_small_bf16", dict(H=256, I=128, E=8), 2, (40, 45), 2e-2),
-    ("cfg1_small_bf16", dict(H=256, I=128, E=8), 4, (33, 0, 64, 7), 2e-2),       # an idle rank, a full one
-    ("cfg4_deepseek_fp8", dict(H=512, I=256, E=64), 4, (50, 64, 1, 23), 5e-2),
-    ("cfg4_deepseek_fp8", dict(H=512, I=256, E=64), 8, (300, 290, 310, 5, 300, 0, 299, 320), 5e-2),  # multi-block sort
+@pytest.mark.parametrize("cfg_name,dims,ep,tokens,tol,placed", [
+    ("cfg1_small_bf16", dict(H=256, I=128, E=8), 2, (40, 45), 2e-2, False),
+    ("cfg1_small_bf16", dict(H=256, I=128, E=8), 4, (33, 0, 64, 7), 2e-2, False),       # an idle rank, a full one
+    ("cfg1_small_bf16", dict(H=256, I=128, E=8), 4, (33, 0, 64, 7), 2e-2, True),        # experts placed by load
+    ("cfg4_deepseek_fp8", dict(H=512, I=256, E=64), 4, (50, 64, 1, 23), 5e-2, False),
+    ("cfg4_deepseek_fp8", dict(H=512, I=256, E=64), 4, (50, 64, 1, 23), 5e-2, True),
+    ("cfg4_deepseek_fp8", dict(H=512, I=256, E=64), 8, (300, 290, 310, 5, 300, 0, 299, 320), 5e-2, False),  # multi-block sort
 ])
-def test_peer_ep_layer_matches_the_single_process_oracle(native, cfg_name, dims, ep, tokens, tol):
+def test_peer_ep_layer_matches_the_single_process_oracle(native, cfg_name, dims, ep, tokens, tol, placed):
+    from vllm_xpu_kernels.ep_moe import balanced_expert_slots
     cfg = wl.scaled(wl.CONFIGS[cfg_name], **dims)
     cap = max(tokens)
-    w, layers = _build(native, cfg, ep, cap, seed=3)
+    slot = None
+    if placed:   # a placement from a made-up load estimate: any permutation must give the same layer
+        slot = balanced_expert_slots(torch.rand(cfg.E, generator=torch.Generator().manual_seed(5)), ep)
+        assert sorted(slot.tolist()) == list(range(cfg.E))
+    w, layers = _build(native, cfg, ep, cap, seed=3, slot=slot)
     E_local = cfg.E // ep
     for call in range(2):  # the second call runs over the first one's leftovers in every buffer
         inputs = []
@@ -65,7 +74,7 @@ def test_peer_ep_layer_matches_the_single_process_oracle(native, cfg_name, dims,
             layers[r].dispatch(*dev_in[r])
         torch.cuda.synchronize()
         # bookkeeping: exact against the sequential restatement
-        plans = [to.ep_dispatch_plan(inputs[r][2], ep, E_local, cap) for r in range(ep)]
+        plans = [to.ep_dispatch_plan(inputs[r][2], ep, E_local, cap, slot) for r in range(ep)]
         for r in range(ep):
             counts, pos, loc = plans[r]
             T = tokens[r]

@@ -33,7 +33,7 @@ extern "C" const char* b200moe_status_string(int status) {
   }
 }
 
-extern "C" int b200moe_abi_version(void) { return 6; }
+extern "C" int b200moe_abi_version(void) { return 7; }
 
 // ---- the failure path of the bounded waits, on its own -------------------------
 namespace b200moe {

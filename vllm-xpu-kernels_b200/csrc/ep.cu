@@ -25,6 +25,7 @@ struct EpDispatchParams {
   const float* weights;       // [T, K]
   const int32_t* send_counts; // [ep]
   const int32_t* send_pos;    // [T, ep]
+  const int32_t* slot;        // [ep * e_local] expert -> slot, or null (identity)
   int64_t num_tokens, capacity;
   int ep, rank, e_local, H, K;
 };
@@ -109,7 +110,9 @@ ep_dispatch_kernel(const T* __restrict__ src, const __grid_constant__ EpDispatch
     const int d = u / p.K, k = u - d * p.K;
     const int r = dest[d];
     if (r < 0) continue;
-    const int64_t g = ep_raw_id(p.ids, p.ids_dtype, tok * p.K + k);
+    int64_t g = ep_raw_id(p.ids, p.ids_dtype, tok * p.K + k);
+    if (g >= (int64_t)p.ep * p.e_local) g = -1;
+    if (g >= 0 && p.slot != nullptr) g = p.slot[g];
     const bool mine = g >= 0 && g / p.e_local == d;
     const int64_t cell = (region + r) * p.K + k;
     p.peer.ids[d][cell] = mine ? (int32_t)(g - (int64_t)d * p.e_local) : -1;
@@ -228,6 +231,7 @@ extern "C" int b200moe_ep_dispatch(const b200moe_ep_peers* pe, const void* hidde
   sp.numel = num_tokens * ep;
   sp.id_limit = ep; sp.n_buckets = ep; sp.block_size = 1;
   sp.topk = pe->topk; sp.ep_size = ep; sp.ep_local_experts = pe->num_local_experts;
+  sp.ep_slot = pe->expert_slot;
   sp.bucket_stride = pe->capacity;
   AlignOut ao = {};
   RemapOut ro = {send_counts, send_pos};
@@ -243,7 +247,7 @@ extern "C" int b200moe_ep_dispatch(const b200moe_ep_peers* pe, const void* hidde
     p.peer.counts[d] = pe->recv_counts[d];
   }
   p.ids = topk_ids; p.ids_dtype = ids_dtype; p.weights = topk_weights;
-  p.send_counts = send_counts; p.send_pos = send_pos;
+  p.send_counts = send_counts; p.send_pos = send_pos; p.slot = pe->expert_slot;
   p.num_tokens = num_tokens; p.capacity = pe->capacity;
   p.ep = ep; p.rank = pe->ep_rank; p.e_local = pe->num_local_experts; p.H = pe->hidden; p.K = pe->topk;
   const unsigned grid = (unsigned)(num_tokens > 0 ? num_tokens : 1);

@@ -192,7 +192,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    // (the whole warp runs the loop with the same values; one elected lane issues)
+    {
       uint32_t s = 0, ph = 0, acc_it = 0;
       int cursor = 0;
       bool ok = true;
@@ -209,15 +210,17 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((n_eff >> 3) << 17);
         constexpr bool per_block = kFp8;
         if (!per_block) {
-          if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) break;
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag))) break;
           ptx::tc_fence_after();
         }
         for (int kb = 0; kb < p.num_kb; ++kb) {
+          bool go = true;
           if (per_block) {
             a = acc_it % kAccStages;
-            if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            go = ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it / kAccStages) & 1) ^ 1, abort_flag);
           }
-          if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
+          if (go) go = ptx::mbar_wait(&ctrl->full[s], ph, abort_flag);
+          if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
           ptx::tc_fence_after();
           // every operand descriptor of the stage = one base descriptor + a compile-time
           // offset (the address field counts 16-byte units), so the issue loop is adds only
@@ -230,15 +233,15 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const uint32_t accumulate = per_block ? (j > 0) : (kb > 0 || j > 0);
-              ptx::umma<kFp8>(d_tmem + half * BT, wdesc0 + (uint64_t)((half * kWTileBytes + j * kWStep) >> 4),
-                              adesc0 + (uint64_t)((j * 32) >> 4), idesc, accumulate);
+              ptx::umma_elect<kFp8>(d_tmem + half * BT, wdesc0 + (uint64_t)((half * kWTileBytes + j * kWStep) >> 4),
+                                    adesc0 + (uint64_t)((j * 32) >> 4), idesc, accumulate);
             }
           }
-          ptx::umma_commit(&ctrl->empty[s]);
-          if (per_block) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+          ptx::umma_commit_elect(&ctrl->empty[s]);
+          if (per_block) { ptx::umma_commit_elect(&ctrl->acc_full[a]); ++acc_it; }
           if (++s == (uint32_t)kStages) { s = 0; ph ^= 1; }
         }
-        if (!per_block && ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+        if (!per_block && ok) { ptx::umma_commit_elect(&ctrl->acc_full[a]); ++acc_it; }
       }
     }
   } else {

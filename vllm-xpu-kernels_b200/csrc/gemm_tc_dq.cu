@@ -255,7 +255,8 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    // (the whole warp runs the loop with the same values; one elected lane issues)
+    {
       uint32_t s = 0, ph = 0, acc_it = 0;
       int cursor = 0;
       bool ok = true;
@@ -264,12 +265,12 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         const uint32_t a = acc_it & 1;
-        if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) break;
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag))) break;
         ptx::tc_fence_after();
         // a partly filled token tile multiplies only its valid columns (UMMA N in steps of 16)
         const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((uint32_t)(((ti.valid + 15) & ~15) >> 3) << 17);
         for (int si = 0; si < num_st; ++si) {
-          if (!ptx::mbar_wait(&ctrl->full_op[s], ph, abort_flag)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->full_op[s], ph, abort_flag))) { ok = false; break; }
           ptx::tc_fence_after();
           // every operand descriptor of the stage = the first one + a compile-time offset
           const uint64_t desc0 = ptx::make_smem_desc(smem_base + s * stage_bytes, 16, 1024);
@@ -281,14 +282,14 @@ grouped_gemm_dq_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (int j = 0; j < 4; ++j) {
                 const uint64_t wdesc = desc0 + (uint64_t)((sub * kOpBytes + j * 32) >> 4);
                 const uint64_t adesc = desc0 + (uint64_t)((kAOff + sub * kABytes + j * 32) >> 4);
-                ptx::umma<false>(tmem_base + a * BT, wdesc, adesc, idesc, (kb0 + sub > 0 || j > 0) ? 1u : 0u);
+                ptx::umma_elect<false>(tmem_base + a * BT, wdesc, adesc, idesc, (kb0 + sub > 0 || j > 0) ? 1u : 0u);
               }
             }
           }
-          ptx::umma_commit(&ctrl->empty[s]);
+          ptx::umma_commit_elect(&ctrl->empty[s]);
           if (++s == (uint32_t)stages) { s = 0; ph ^= 1; }
         }
-        if (ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+        if (ok) { ptx::umma_commit_elect(&ctrl->acc_full[a]); ++acc_it; }
       }
     }
   } else if (warp < 2 + kDqConvWarps) {

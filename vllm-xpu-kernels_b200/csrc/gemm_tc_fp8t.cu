@@ -142,7 +142,8 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    // (the whole warp runs the loop with the same values; one elected lane issues)
+    {
       uint32_t s = 0, ph = 0, a = 0, aph = 0;
       bool ok = true;
       const uint32_t smem_base = ptx::smem_u32(smem);
@@ -153,8 +154,9 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) ++my_tiles;
       const int64_t blocks = (int64_t)my_tiles * p.num_kb;   // every tile: same K loop, no tile state needed
       for (int64_t i = 0; i < blocks && ok; ++i) {
-        if (!ptx::mbar_wait(&ctrl->acc_empty[a], aph ^ 1, abort_flag)) break;
-        if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) break;
+        bool go = ptx::mbar_wait(&ctrl->acc_empty[a], aph ^ 1, abort_flag);
+        if (go) go = ptx::mbar_wait(&ctrl->full[s], ph, abort_flag);
+        if (!__all_sync(0xffffffffu, go)) break;
         ptx::tc_fence_after();
         const uint32_t st_addr = smem_base + s * kTStageBytes;
         const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
@@ -162,10 +164,10 @@ grouped_gemm_fp8t_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t d_tmem = tmem_base + a * 128;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          ptx::umma<true>(d_tmem, adesc0 + (uint64_t)((j * 32) >> 4), wdesc0 + (uint64_t)((j * kWStep) >> 4), p.idesc,
-                          j > 0 ? 1u : 0u);
-        ptx::umma_commit(&ctrl->empty[s]);
-        ptx::umma_commit(&ctrl->acc_full[a]);
+          ptx::umma_elect<true>(d_tmem, adesc0 + (uint64_t)((j * 32) >> 4), wdesc0 + (uint64_t)((j * kWStep) >> 4),
+                                p.idesc, j > 0 ? 1u : 0u);
+        ptx::umma_commit_elect(&ctrl->empty[s]);
+        ptx::umma_commit_elect(&ctrl->acc_full[a]);
         if (++s == (uint32_t)kTStages) { s = 0; ph ^= 1; }
         if (++a == (uint32_t)kTAcc) { a = 0; aph ^= 1; }
       }
@@ -420,7 +422,7 @@ grouped_gemm_fp8t256_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int64_t blocks = (int64_t)my_tiles * p.num_kb;
       const uint32_t idesc = (p.idesc & ~(0x3fu << 17)) | ((256u >> 3) << 17);
       auto mma = [&](uint32_t d, uint64_t ad, uint64_t wd, uint32_t accumulate) {
-        ptx::umma_fp8_elect(d, ad, wd, idesc, accumulate);
+        ptx::umma_elect<true>(d, ad, wd, idesc, accumulate);
       };
       // The barriers of the next block are polled between this block's MMA issues, where
       // the thread would otherwise only wait for room in the tensor pipe's queue.

@@ -252,7 +252,8 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    // (the whole warp runs the loop with the same values; one elected lane issues)
+    {
       uint32_t s = 0, ph = 0, acc_it = 0;
       int cursor = 0;
       bool ok = true;
@@ -264,7 +265,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
         TileInfo ti;
         locate_tile<BT>(tile_start, row_start, t, cursor, ti);
         const uint32_t a = acc_it & 1;
-        if (!ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag)) break;
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag))) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * kNT;
         // A partly filled token tile multiplies only up to its last valid column (UMMA N in
@@ -272,8 +273,9 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t n_eff = (uint32_t)((kTerms - 1) * BT + ((ti.valid + 15) & ~15));
         const uint32_t n_bits = (n_eff >> 3) << 17;
         for (int si = 0; si < num_st; ++si) {
-          if (!ptx::mbar_wait(&ctrl->full[s], ph, abort_flag)) { ok = false; break; }
-          if (!ptx::mbar_wait(&ctrl->sf_full[s], ph, abort_flag)) { ok = false; break; }
+          bool go = ptx::mbar_wait(&ctrl->full[s], ph, abort_flag);
+          if (go) go = ptx::mbar_wait(&ctrl->sf_full[s], ph, abort_flag);
+          if (!__all_sync(0xffffffffu, go)) { ok = false; break; }
           ptx::tc_fence_after();
           // Every operand descriptor of the stage is the first weight block's plus a
           // compile-time offset (the address field counts 16-byte units).
@@ -292,14 +294,14 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 // K-major e2m1 tile: 32 codes further is 32 bytes; MN-major byte tile: 32 K rows
                 const uint64_t wdesc = desc0w + (uint64_t)((sub * kMxWBytes + j * (kW8 ? 4096 : 32)) >> 4);
                 const uint64_t adesc = desc0 + (uint64_t)((kAOff + sub * kABytes + j * 32) >> 4);
-                ptx::umma_mx(d_tmem, wdesc, adesc, idesc_j[j] | n_bits, (kb0 + sub > 0 || j > 0) ? 1u : 0u, sfa, sfa + 4);
+                ptx::umma_mx_elect(d_tmem, wdesc, adesc, idesc_j[j] | n_bits, (kb0 + sub > 0 || j > 0) ? 1u : 0u, sfa, sfa + 4);
               }
             }
           }
-          ptx::umma_commit(&ctrl->empty[s]);
+          ptx::umma_commit_elect(&ctrl->empty[s]);
           if (++s == (uint32_t)stages) { s = 0; ph ^= 1; }
         }
-        if (ok) { ptx::umma_commit(&ctrl->acc_full[a]); ++acc_it; }
+        if (ok) { ptx::umma_commit_elect(&ctrl->acc_full[a]); ++acc_it; }
       }
     }
   } else if (warp < 6) {

@@ -314,13 +314,31 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 // the same operands): one elected lane issues.  A warp-uniform loop lets the compiler keep
 // descriptors and barrier addresses in uniform registers (measured on the fp8 kernel: 4 MMAs
 // and 2 commits issue in 370 instead of 640 cycles).
-__device__ __forceinline__ void umma_fp8_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                               uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_mx_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                              uint32_t idesc, uint32_t accumulate, uint32_t sfa,
+                                              uint32_t sfb) {
   asm volatile(
       "{\n\t.reg .pred pe, pa;\n\telect.sync _|pe, 0xffffffff;\n\tsetp.ne.b32 pa, %4, 0;\n\t"
-      "@pe tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, pa;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "@pe tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], pa;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
       : "memory");
+}
+template <bool kFp8>
+__device__ __forceinline__ void umma_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                           uint32_t idesc, uint32_t accumulate) {
+  if (kFp8) {
+    asm volatile(
+        "{\n\t.reg .pred pe, pa;\n\telect.sync _|pe, 0xffffffff;\n\tsetp.ne.b32 pa, %4, 0;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, pa;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred pe, pa;\n\telect.sync _|pe, 0xffffffff;\n\tsetp.ne.b32 pa, %4, 0;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pa;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
 }
 __device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
   asm volatile(

@@ -44,9 +44,10 @@ struct SortParams {
   bool first_match_only = false;
   // expert-parallel dispatch: `ids` is [numel / ep_size, topk] global expert ids and slot
   // i = (token, rank d) belongs to bucket d when one of the token's experts lives on rank d
-  // (expert g on rank g / ep_local_experts), else to none
+  // (expert g on rank slot(g) / ep_local_experts, slot(g) = ep_slot[g] or g), else to none
   int ep_size = 0;
   int ep_local_experts = 0;
+  const int32_t* ep_slot = nullptr;
   // > 0: bucket b's rows are numbered from b * bucket_stride (fixed-capacity regions)
   // instead of from the end of bucket b - 1
   int64_t bucket_stride = 0;
@@ -65,8 +66,10 @@ __device__ __forceinline__ int bucket_of(const SortParams& p, int64_t i) {
     const int64_t tok = i / p.ep_size;
     const int d = (int)(i - tok * p.ep_size);
     for (int k = 0; k < p.topk; ++k) {
-      const int64_t g = raw_id(p, tok * p.topk + k);
-      if (g >= 0 && g / p.ep_local_experts == d) return d;
+      int64_t g = raw_id(p, tok * p.topk + k);
+      if (g < 0 || g >= (int64_t)p.ep_size * p.ep_local_experts) continue;
+      if (p.ep_slot != nullptr) g = p.ep_slot[g];
+      if (g / p.ep_local_experts == d) return d;
     }
     return -1;
   }

@@ -457,7 +457,7 @@ b200moe_ep_peers make_peers(const at::Tensor& tables, int64_t ep_rank, int64_t n
 void b200_ep_dispatch(const at::Tensor& hidden_states, const at::Tensor& topk_ids, const at::Tensor& topk_weights,
                       at::Tensor& send_counts, at::Tensor& send_pos, at::Tensor& workspace,
                       const at::Tensor& tables, int64_t ep_rank, int64_t num_local_experts, int64_t capacity,
-                      bool quantized) {
+                      bool quantized, const std::optional<at::Tensor>& expert_slot) {
   check_cuda(hidden_states, "hidden_states");
   TORCH_CHECK(hidden_states.dim() == 2 && hidden_states.is_contiguous(), "hidden_states must be contiguous [T, H]");
   const int64_t T = hidden_states.size(0), H = hidden_states.size(1);
@@ -469,7 +469,14 @@ void b200_ep_dispatch(const at::Tensor& hidden_states, const at::Tensor& topk_id
               "send_counts must be int32 [ep]");
   TORCH_CHECK(send_pos.scalar_type() == at::kInt && send_pos.numel() == T * ep && send_pos.is_contiguous(),
               "send_pos must be int32 [T, ep]");
-  const b200moe_ep_peers pe = make_peers(tables, ep_rank, num_local_experts, K, H, capacity, quantized);
+  b200moe_ep_peers pe = make_peers(tables, ep_rank, num_local_experts, K, H, capacity, quantized);
+  if (expert_slot.has_value()) {
+    check_cuda(*expert_slot, "expert_slot");
+    TORCH_CHECK(expert_slot->scalar_type() == at::kInt && expert_slot->is_contiguous() &&
+                expert_slot->numel() == ep * num_local_experts && expert_slot->device() == hidden_states.device(),
+                "expert_slot must be int32 [ep * num_local_experts] on the device of hidden_states");
+    pe.expert_slot = expert_slot->data_ptr<int32_t>();
+  }
   const size_t need = b200moe_ep_dispatch_workspace_bytes(T, (int)ep);
   TORCH_CHECK((size_t)workspace.numel() * workspace.element_size() >= need, "workspace of ", need, " bytes needed");
   const c10::cuda::CUDAGuard guard(hidden_states.device());
@@ -563,7 +570,7 @@ TORCH_LIBRARY_FRAGMENT(_moe_C, m) {
   m.def(
       "b200_ep_dispatch(Tensor hidden_states, Tensor topk_ids, Tensor topk_weights, Tensor(a!) send_counts, "
       "Tensor(b!) send_pos, Tensor(c!) workspace, Tensor tables, int ep_rank, int num_local_experts, "
-      "int capacity, bool quantized) -> ()");
+      "int capacity, bool quantized, Tensor? expert_slot=None) -> ()");
   m.def(
       "b200_ep_mask_unused(Tensor anchor, Tensor tables, int ep_rank, int num_local_experts, int topk, "
       "int hidden, int capacity, bool quantized) -> ()");

@@ -39,6 +39,35 @@ def owner_map(num_experts_total: int, ep_size: int, device) -> torch.Tensor:
     return (torch.arange(num_experts_total, device=device) // e_local).to(torch.int32)
 
 
+def balanced_expert_slots(expert_load, ep_size: int) -> torch.Tensor:
+    """An expert placement that evens out the ranks' load: int32 [E] (CPU), a permutation
+    ``expert -> slot`` in which rank ``r`` holds the experts of slots ``[r * E_local, (r + 1) *
+    E_local)``.  ``expert_load`` [E] is a load estimate per expert (e.g. the routed-slot histogram
+    of a calibration batch).  Longest-processing-time greedy: experts in descending load, each to
+    the least loaded rank that still has a free slot."""
+    load = torch.as_tensor(expert_load, dtype=torch.float64).cpu()
+    E = load.numel()
+    if E % ep_size:
+        raise ValueError("the expert count must be divisible by the expert-parallel size")
+    e_local = E // ep_size
+    rank_load, rank_fill = [0.0] * ep_size, [0] * ep_size
+    slot = torch.empty(E, dtype=torch.int32)
+    for e in torch.argsort(load, descending=True, stable=True).tolist():
+        r = min((r for r in range(ep_size) if rank_fill[r] < e_local), key=lambda r: (rank_load[r], r))
+        slot[e] = r * e_local + rank_fill[r]
+        rank_fill[r] += 1
+        rank_load[r] += float(load[e])
+    return slot
+
+
+def experts_in_slots(expert_slot: torch.Tensor, rank: int, num_local_experts: int) -> torch.Tensor:
+    """int64 [E_local]: the global expert held in each local slot of ``rank`` (the order in which
+    that rank's weights are stacked) for a placement ``expert -> slot``."""
+    inverse = torch.empty_like(expert_slot, dtype=torch.int64)
+    inverse[expert_slot.long()] = torch.arange(expert_slot.numel(), dtype=torch.int64)
+    return inverse[rank * num_local_experts:(rank + 1) * num_local_experts]
+
+
 def check_count_matrix(sent: torch.Tensor, received: torch.Tensor, rank: int, capacity: Optional[int] = None):
     """Consistency of one exchange: ``sent`` [ep, ep] holds what every rank says it sent to
     every rank (row = source), ``received`` [ep] what this rank was told it received from
@@ -130,7 +159,10 @@ class EpPeerFusedMoe:
     """Fused-MoE layer with expert parallelism over peer memory (CUDA).
 
     ``w13`` / ``w2`` (and scales, biases) hold this rank's ``num_local_experts`` experts in
-    the layouts ``XpuFusedMoe`` takes.  ``apply`` has the signature of ``XpuFusedMoe.apply``
+    the layouts ``XpuFusedMoe`` takes.  Expert ``g`` is local expert ``g % E_local`` of rank
+    ``g // E_local``, or - with ``expert_slot`` (int32 [E] on the device, the same permutation
+    ``expert -> slot`` on every rank, e.g. from ``balanced_expert_slots``) - local expert
+    ``slot % E_local`` of rank ``slot // E_local``.  ``apply`` has the signature of ``XpuFusedMoe.apply``
     with *global* expert ids in ``topk_ids``; all ranks call it together.  ``max_tokens`` is
     the largest token count any rank passes to one call (the receive regions are sized for
     it); ``peers`` provides the peer-addressable memory and the barrier
@@ -153,9 +185,15 @@ class EpPeerFusedMoe:
 
     def __init__(self, w13, w13_scales, w13_bias, w2, w2_scales, w2_bias, n_experts_per_token, activation,
                  num_local_experts, peers, max_tokens: int, hidden_size: int,
-                 gemm1_clamp_limit: Optional[float] = None, out_dtype=torch.bfloat16):
+                 gemm1_clamp_limit: Optional[float] = None, out_dtype=torch.bfloat16,
+                 expert_slot: Optional[torch.Tensor] = None):
         from .fused_moe_interface import XpuFusedMoe
         self.peers = peers
+        if expert_slot is not None:
+            if expert_slot.numel() != num_local_experts * peers.ep_size:
+                raise ValueError("expert_slot must have one entry per expert of the whole group")
+            expert_slot = expert_slot.to(device=w13.device, dtype=torch.int32).contiguous()
+        self.expert_slot = expert_slot
         self.ep_size, self.ep_rank = peers.ep_size, peers.ep_rank
         self.num_local_experts = num_local_experts
         self.topk = n_experts_per_token
@@ -226,7 +264,8 @@ class EpPeerFusedMoe:
         self._tokens = T
         self._mark("routing")
         torch.ops._moe_C.b200_ep_dispatch(hidden_states, topk_ids, topk_weights, self.send_counts,
-                                          self.send_pos[:T], self._workspace, self._peer_tables(), *self._common())
+                                          self.send_pos[:T], self._workspace, self._peer_tables(), *self._common(),
+                                          self.expert_slot)
         self._mark("dispatch")
 
     def experts_and_combine(self):
