@@ -458,6 +458,225 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, i
   return B200MOE_OK;
 }
 
+
+// ---------------------------------------------------------------------------------
+// 16-bit prefill on CTA pairs.  The 256-token tile above is bound by what a CTA brings into
+// shared memory per K block (16 KB of weights + 32 KB of tokens for 4.2 MFLOP).  Here a
+// cluster of two CTAs shares the 256 tokens of a tile and covers 256 features: each CTA loads
+// its own 128 features' weights and one half of the tokens (32 KB per CTA and K block), the
+// even CTA issues tcgen05.mma with cta_group::2 (M = 256: 128 weight rows from each CTA, N = 256:
+// 128 token rows from each CTA) for both, and each CTA's tensor memory receives the 128 x 256
+// accumulator of its own features, which its epilogue warps store as above.  A 16-bit GEMM
+// hands its accumulator over once per tile, so the longer way a hand-over takes between two
+// SMs does not matter here (it does in the fp8 kernel, which hands over every K block).
+// Barriers: `full` and `acc_empty` of the even CTA collect both CTAs' loads and arrivals;
+// `empty` and `acc_full` are signalled in both CTAs by a multicast tcgen05.commit.
+constexpr int kPairTok = 256;
+constexpr int kPairStageBytes = kWTileBytes + 128 * 128;   // this CTA's weights + its half of the tokens
+constexpr int kPairStages = 6;
+constexpr size_t kPairSmem = 1024 + (size_t)kPairStages * kPairStageBytes + sizeof(Ctrl<kPairTok, false>);
+
+template <bool kWKn>
+__global__ void __launch_bounds__(kTcThreads, 1)
+grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                            const __grid_constant__ CUtensorMap tmap_w, const TcParams p) {
+  constexpr int kChunk = 32;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  Ctrl<kPairTok, false>* ctrl = reinterpret_cast<Ctrl<kPairTok, false>*>(smem + kPairStages * kPairStageBytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t cta = ptx::cluster_ctarank();
+  const int walker = (int)ptx::cluster_id_x(), walkers = (int)ptx::cluster_count_x();
+  const int pair_tiles = (p.n_tiles + 1) / 2;   // feature tiles of 2 x 128
+
+  if (warp == 0) {
+    build_tile_prefix<kPairTok>(p.rows_per_expert, p.num_experts, pair_tiles, ctrl->row_start, ctrl->tile_start);
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_w);
+    }
+  } else if (warp == 1) {
+    ptx::tmem_alloc_pair(&ctrl->tmem_base, 512);
+    ptx::tmem_relinquish_pair();
+  } else if (warp == 2 && lane == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      ptx::mbar_init(&ctrl->full[s], 1);
+      ptx::mbar_init(&ctrl->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&ctrl->acc_full[a], 1);
+      ptx::mbar_init(&ctrl->acc_empty[a], 2 * kEpiWarps);   // the epilogue warps of both CTAs
+    }
+    ctrl->abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();   // both CTAs' barriers and tensor memory exist before either signals the other
+  ptx::tc_fence_after();
+
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const int total_tiles = ctrl->tile_start[p.num_experts];
+  const int* tile_start = ctrl->tile_start;
+  const int* row_start = ctrl->row_start;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      int cursor = 0;
+      bool ok = true;
+      for (int t = walker; t < total_tiles && ok; t += walkers) {
+        TileInfo ti;
+        locate_tile<kPairTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
+        const int n0 = (ti.n_tile * 2 + (int)cta) * kFeat;       // past N: the load is zero-filled
+        const int row = ti.row0 + (int)cta * 128;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* wdst = smem + s * kPairStageBytes;
+          // the even CTA's barrier counts the bytes of both CTAs
+          if (cta == 0) ptx::mbar_expect_tx(&ctrl->full[s], 2 * kPairStageBytes);
+          const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&ctrl->full[s]), 0);
+          const int k0 = kb * 64;
+          if (!kWKn) {
+            ptx::tma_load_3d_pair(wdst, &tmap_w, bar, k0, n0, ti.e);
+          } else {
+            ptx::tma_load_3d_pair(wdst, &tmap_w, bar, n0, k0, ti.e);
+            ptx::tma_load_3d_pair(wdst + kWTileBytes / 2, &tmap_w, bar, n0 + 64, k0, ti.e);
+          }
+          ptx::tma_load_2d_pair(wdst + kWTileBytes, &tmap_a, bar, k0, row);
+          if (++s == (uint32_t)kPairStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA) -----------------------
+    if (cta == 0) {
+      uint32_t s = 0, ph = 0, acc_it = 0;
+      bool ok = true;
+      const uint32_t smem_base = ptx::smem_u32(smem);
+      constexpr uint32_t kWLbo = !kWKn ? 16u : 8192u;
+      constexpr uint32_t kWStep = !kWKn ? 32u : 2048u;
+      const uint32_t idesc = (p.idesc & ~((0x3fu << 17) | (0x1fu << 24))) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+      for (int t = walker; t < total_tiles && ok; t += walkers) {
+        const uint32_t a = acc_it & 1;
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_empty[a], ((acc_it >> 1) & 1) ^ 1, abort_flag))) break;
+        ptx::tc_fence_after();
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->full[s], ph, abort_flag))) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t st_addr = smem_base + s * kPairStageBytes;
+          const uint64_t wdesc0 = ptx::make_smem_desc(st_addr, kWLbo, 1024);
+          const uint64_t adesc0 = ptx::make_smem_desc(st_addr + kWTileBytes, 16, 1024);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            ptx::umma_f16_pair_elect(tmem_base + a * kPairTok, wdesc0 + (uint64_t)((j * kWStep) >> 4),
+                                     adesc0 + (uint64_t)((j * 32) >> 4), idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          ptx::umma_commit_pair_elect(&ctrl->empty[s]);
+          if (++s == (uint32_t)kPairStages) { s = 0; ph ^= 1; }
+        }
+        if (ok) { ptx::umma_commit_pair_elect(&ctrl->acc_full[a]); ++acc_it; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;
+    const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+    const uint32_t acc_empty0 = ptx::map_to_cta(ptx::smem_u32(&ctrl->acc_empty[0]), 0);
+    uint32_t acc_it = 0;
+    int cursor = 0;
+    for (int t = walker; t < total_tiles; t += walkers) {
+      TileInfo ti;
+      locate_tile<kPairTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
+      const int n_tile = ti.n_tile * 2 + (int)cta;
+      const int feat = n_tile * kFeat + q * 32 + lane;
+      const float bias_v = (p.bias != nullptr && feat < p.n) ? load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat) : 0.f;
+      const uint32_t a = acc_it & 1;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
+        *abort_flag = 1; break;
+      }
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < kPairTok; c0 += kChunk) {
+        if (c0 < ti.valid) {
+          uint32_t v[kChunk];
+          ptx::tmem_ld_32x32(tmem_base + a * kPairTok + c0 + lane_sel, v);
+          ptx::tmem_wait_ld();
+          float vals[kChunk];
+#pragma unroll
+          for (int i = 0; i < kChunk; ++i) vals[i] = __uint_as_float(v[i]) + bias_v;
+          if (p.swiglu) {
+            const float c_lim = p.clamp > 0.f ? p.clamp : INFINITY;
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
+              const float x = vals[i];
+              const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+              float gate = (lane & 1) ? other : x;
+              float up = (lane & 1) ? x : other;
+              gate = fminf(fminf(gate, c_lim), p.limit);
+              up = fminf(fmaxf(up, -c_lim), c_lim);
+              up = fminf(fmaxf(up, -p.limit), p.limit);
+              vals[i] = (up + 1.0f) * gate * __fdividef(1.0f, 1.0f + __expf(-gate * p.alpha));
+            }
+            store_block_transposed<kChunk, 16>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
+                                               (int64_t)ti.row0 + c0, ti.valid - c0, p.m, p.n >> 1,
+                                               (n_tile * kFeat + q * 32) >> 1, lane);
+          } else {
+            store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
+                                               (int64_t)ti.row0 + c0, ti.valid - c0, p.m, p.n,
+                                               n_tile * kFeat + q * 32, lane);
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(acc_empty0 + a * 8);
+      ++acc_it;
+    }
+  }
+
+  // Teardown: neither CTA frees tensor memory or leaves while the other may still use its
+  // shared memory, its barriers or MMAs in flight (every thread of both CTAs gets here after
+  // bounded waits).
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    if (*abort_flag != 0) __nanosleep(20000);
+    ptx::tmem_dealloc_pair(tmem_base, 512);
+  }
+  if (tid == 0 && *abort_flag != 0) report_timeout(p.status);
+}
+
+// Clusters of two CTAs, as many as the device runs at once (at most `max_pairs`).
+template <bool kWKn>
+int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, int max_pairs, cudaStream_t st) {
+  auto kern = grouped_gemm_tc_pair_kernel<kWKn>;
+  static SmemConfig configured;
+  if (int rc = configured.ensure(kern, kPairSmem)) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kPairSmem; cfg.stream = st;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  static std::atomic<int> resident[kMaxDevices];
+  const int dev = current_device();
+  int pairs = resident[dev].load(std::memory_order_relaxed);
+  if (pairs == 0) {
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    B200_CUDA_OK(cudaOccupancyMaxActiveClusters(&pairs, kern, &cfg));
+    if (pairs < 1) return fail(B200MOE_E_CUDA, "grouped GEMM: the device runs no cluster of two CTAs of the pair kernel");
+    resident[dev].store(pairs, std::memory_order_relaxed);
+  }
+  if (pairs > max_pairs) pairs = max_pairs;
+  cfg.gridDim = dim3(2 * pairs);
+  B200_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tw, p));
+  return B200MOE_OK;
+}
+
 }  // namespace
 
 // Returns B200MOE_E_UNSUPPORTED (without a launch) for requests the
@@ -547,6 +766,20 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   const int64_t tile_bound = ((a->m + bt - 1) / bt + a->num_experts) * (int64_t)p.n_tiles;
   int grid = sm_count();
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
+
+  // 16-bit prefill: the CTA-pair kernel (impl 3 / 4 force the single-CTA / the pair form)
+  if (!a_fp8 && !gated && bt == 256 && a->impl != 3 && p.n_tiles >= 2) {
+    CUtensorMap ta_half;
+    cuuint64_t dims[2] = {(cuuint64_t)a->k, (cuuint64_t)a->m};
+    cuuint64_t strides[1] = {(cuuint64_t)a->k * es};
+    cuuint32_t box[2] = {(cuuint32_t)kpb, 128};
+    if (int rc = encode_map(&ta_half, dt, 2, a->a, dims, strides, box)) return rc;
+    const int64_t pair_bound = ((a->m + 255) / 256 + a->num_experts) * (int64_t)((p.n_tiles + 1) / 2);
+    int max_pairs = grid / 2 < 1 ? 1 : grid / 2;
+    if (pair_bound < max_pairs) max_pairs = (int)pair_bound;
+    return kn ? launch_tc_pair<true>(ta_half, tw, p, max_pairs, st) : launch_tc_pair<false>(ta_half, tw, p, max_pairs, st);
+  }
+
   if (tile_bound < grid) grid = (int)tile_bound;
   if (grid < 1) grid = 1;
 
