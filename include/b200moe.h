@@ -354,7 +354,9 @@ typedef struct {
                              memory): set to 1 if a bounded wait gave up; may be
                              NULL                                                 */
   int impl;               /* 0 = auto, 1 = tensor-core kernel, 2 = plain-CUDA
-                             checking kernel                                      */
+                             checking kernel, 3 = tensor-core kernel without the
+                             CTA-pair form (16-bit prefill tiles then run one CTA
+                             per tile; same results)                              */
   int max_ctas;           /* >0: the persistent tensor-core kernel uses at most this
                              many CTAs (leaves SMs to a concurrent collective);
                              0 = one per SM                                       */

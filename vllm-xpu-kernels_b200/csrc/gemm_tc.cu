@@ -667,10 +667,13 @@ int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams&
   int pairs = resident[dev].load(std::memory_order_relaxed);
   if (pairs == 0) {
     cfg.gridDim = dim3(2 * (sm_count() / 2));
-    B200_CUDA_OK(cudaOccupancyMaxActiveClusters(&pairs, kern, &cfg));
-    if (pairs < 1) return fail(B200MOE_E_CUDA, "grouped GEMM: the device runs no cluster of two CTAs of the pair kernel");
+    if (cudaOccupancyMaxActiveClusters(&pairs, kern, &cfg) != cudaSuccess || pairs < 1) {
+      (void)cudaGetLastError();
+      pairs = -1;   // this device (a partition with too few SMs per GPC, say) runs no such cluster
+    }
     resident[dev].store(pairs, std::memory_order_relaxed);
   }
+  if (pairs < 0) return B200MOE_E_UNSUPPORTED;   // the caller takes the single-CTA kernel
   if (pairs > max_pairs) pairs = max_pairs;
   cfg.gridDim = dim3(2 * pairs);
   B200_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, ta, tw, p));
@@ -777,7 +780,8 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
     const int64_t pair_bound = ((a->m + 255) / 256 + a->num_experts) * (int64_t)((p.n_tiles + 1) / 2);
     int max_pairs = grid / 2 < 1 ? 1 : grid / 2;
     if (pair_bound < max_pairs) max_pairs = (int)pair_bound;
-    return kn ? launch_tc_pair<true>(ta_half, tw, p, max_pairs, st) : launch_tc_pair<false>(ta_half, tw, p, max_pairs, st);
+    const int rc = kn ? launch_tc_pair<true>(ta_half, tw, p, max_pairs, st) : launch_tc_pair<false>(ta_half, tw, p, max_pairs, st);
+    if (rc != B200MOE_E_UNSUPPORTED) return rc;
   }
 
   if (tile_bound < grid) grid = (int)tile_bound;
