@@ -388,8 +388,12 @@ def launches_per_step(cfg, T, layer, ep_world, transport) -> int:
 def stage_times(cfg, layer, step, x, logits, bias, reps=5):
     """Per-stage device time of a step (single GPU): the layer is given a hook that records a
     CUDA event after every stage; averaged over `reps` steps outside the timed region."""
+    import torch.distributed as dist
     acc = {}
     for _ in range(reps):
+        if dist.is_initialized():     # ranks start a step together, as they do inside the timed loop
+            torch.cuda.synchronize()
+            dist.barrier()
         timer = StageTimer()
         layer.stage_hook = timer.mark
         timer.mark("start")
@@ -599,7 +603,18 @@ def run_point(args, cfg, T, world, rank, local_rank, dev, dist):
         loads = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(loads, mine)
         loads = [float(v) for v in loads]
-        line["ep"] = {"rows_sent": sent, "rows_sent_remote": remote,
+        # each rank's own work per step (its stage times without the waits at the barriers) and
+        # the time of its two GEMM stages: tells a slow GPU from an uneven load
+        st = line.get("stages_ms") or {}
+        mine = torch.tensor([sum(v for k, v in st.items() if not k.startswith("barrier")),
+                             st.get("local_gemm1", 0.0) + st.get("local_gemm2", 0.0),
+                             st.get("dispatch", 0.0) + st.get("combine", 0.0)], device=dev)
+        busy = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(busy, mine)
+        line["ep"] = {"busy_ms_by_rank": [round(float(b[0]), 3) for b in busy],
+                      "gemm_ms_by_rank": [round(float(b[1]), 3) for b in busy],
+                      "exchange_ms_by_rank": [round(float(b[2]), 3) for b in busy],
+                      "rows_sent": sent, "rows_sent_remote": remote,
                       "dispatch_bytes_remote": remote * (row + cfg.K * 8),
                       "combine_bytes_remote": recvd * cfg.H * 2,
                       "placement": ("experts placed by the load of a calibration batch (%d tokens, seed %d)"
