@@ -39,25 +39,59 @@ def owner_map(num_experts_total: int, ep_size: int, device) -> torch.Tensor:
     return (torch.arange(num_experts_total, device=device) // e_local).to(torch.int32)
 
 
-def balanced_expert_slots(expert_load, ep_size: int) -> torch.Tensor:
+def balanced_expert_slots(expert_load, ep_size: int, tolerance: float = 1.02) -> torch.Tensor:
     """An expert placement that evens out the ranks' load: int32 [E] (CPU), a permutation
     ``expert -> slot`` in which rank ``r`` holds the experts of slots ``[r * E_local, (r + 1) *
     E_local)``.  ``expert_load`` [E] is a load estimate per expert (e.g. the routed-slot histogram
-    of a calibration batch).  Longest-processing-time greedy: experts in descending load, each to
-    the least loaded rank that still has a free slot."""
+    of a calibration batch).
+
+    Starts from the contiguous split and swaps one expert of the busiest rank with one of the
+    idlest until the busiest rank is within ``tolerance`` of the mean: few experts move, so a
+    router that picks a token's experts from a few groups of neighbouring experts still finds
+    most of them on one rank and a token's row travels to few ranks.  If swapping stalls above the
+    tolerance, the result of a longest-processing-time greedy (experts in descending load, each to
+    the least loaded rank with a free slot) is returned when it is better balanced."""
     load = torch.as_tensor(expert_load, dtype=torch.float64).cpu()
     E = load.numel()
     if E % ep_size:
         raise ValueError("the expert count must be divisible by the expert-parallel size")
     e_local = E // ep_size
+
+    def imbalance(slot):
+        per_rank = torch.zeros(ep_size, dtype=torch.float64).index_add_(0, slot.long() // e_local, load)
+        return float(per_rank.max() / per_rank.mean().clamp(min=1e-30))
+
+    # (a) swaps from the contiguous split
+    slot = torch.arange(E, dtype=torch.int64)
+    for _ in range(4 * E):
+        owner = slot // e_local
+        per_rank = torch.zeros(ep_size, dtype=torch.float64).index_add_(0, owner, load)
+        hi, lo = int(per_rank.argmax()), int(per_rank.argmin())
+        if per_rank[hi] <= tolerance * per_rank.mean():
+            break
+        gap = (per_rank[hi] - per_rank[lo]) / 2
+        e_hi, e_lo = (owner == hi).nonzero().flatten(), (owner == lo).nonzero().flatten()
+        moved = load[e_hi].unsqueeze(1) - load[e_lo].unsqueeze(0)      # load a swap takes from hi to lo
+        score = torch.where((moved > 0) & (moved < 2 * gap), (moved - gap).abs(),
+                            torch.full_like(moved, float("inf")))
+        if not bool(torch.isfinite(score.min())):
+            break
+        i, j = divmod(int(score.argmin()), score.shape[1])
+        a, b = int(e_hi[i]), int(e_lo[j])
+        slot[a], slot[b] = slot[b].clone(), slot[a].clone()
+    swapped = slot.to(torch.int32)
+    if imbalance(swapped) <= tolerance:
+        return swapped
+
+    # (b) longest-processing-time greedy
     rank_load, rank_fill = [0.0] * ep_size, [0] * ep_size
-    slot = torch.empty(E, dtype=torch.int32)
+    greedy = torch.empty(E, dtype=torch.int32)
     for e in torch.argsort(load, descending=True, stable=True).tolist():
         r = min((r for r in range(ep_size) if rank_fill[r] < e_local), key=lambda r: (rank_load[r], r))
-        slot[e] = r * e_local + rank_fill[r]
+        greedy[e] = r * e_local + rank_fill[r]
         rank_fill[r] += 1
         rank_load[r] += float(load[e])
-    return slot
+    return greedy if imbalance(greedy) < imbalance(swapped) else swapped
 
 
 def experts_in_slots(expert_slot: torch.Tensor, rank: int, num_local_experts: int) -> torch.Tensor:
