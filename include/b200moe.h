@@ -355,8 +355,9 @@ typedef struct {
                              NULL                                                 */
   int impl;               /* 0 = auto, 1 = tensor-core kernel, 2 = plain-CUDA
                              checking kernel, 3 = tensor-core kernel without the
-                             CTA-pair form (16-bit prefill tiles then run one CTA
-                             per tile; same results)                              */
+                             CTA-pair forms (16-bit prefill tiles then run one CTA
+                             per tile; same results), 4 = tensor-core kernel with
+                             the CTA-pair form wherever one exists                */
   int max_ctas;           /* >0: the persistent tensor-core kernel uses at most this
                              many CTAs (leaves SMs to a concurrent collective);
                              0 = one per SM                                       */

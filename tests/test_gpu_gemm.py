@@ -204,11 +204,14 @@ def test_tensor_core_kernel_matches_checking_kernel_on_mixtral_tile_shapes(nativ
     ([900, 700], 192, 256, 0, torch.bfloat16),                   # an odd number of 128-feature tiles
     ([900, 700], 640, 320, 2, torch.bfloat16),                   # SwigluOAI epilogue
     ([1100, 800], 384, 320, 0, torch.float16),
+    ([300, 0, 1400, 513, 1000], 768, 384, 1, torch.bfloat16),    # SiLU-and-mul: gate in one CTA, up in the other
+    ([900, 700], 512, 320, 1, torch.float16),
 ])
 def test_16bit_prefill_cta_pair_kernel_matches_the_single_cta_kernel(native, layout, rows_list, N, K, epi, dtype):
-    """From 97 rows per expert on, 16-bit GEMMs run on clusters of two CTAs that share a 256-token
-    tile (tcgen05.mma cta_group::2); impl=3 forces the single-CTA kernel of the same tile.  Both
-    against each other (same products, same fp32 accumulation) and against the checking kernel."""
+    """16-bit prefill GEMMs run on clusters of two CTAs that share a 256-token tile (tcgen05.mma
+    cta_group::2; impl=4 forces that form, impl=3 the single-CTA kernels).  With the SiLU epilogue
+    the two CTAs hold gate and up and exchange chunks through shared memory.  Both forms against
+    each other (same products, same fp32 accumulation) and against the checking kernel."""
     E, M = len(rows_list), sum(rows_list)
     g = torch.Generator().manual_seed(N + K)
     rows = torch.tensor(rows_list, dtype=torch.int32)
@@ -218,7 +221,7 @@ def test_16bit_prefill_cta_pair_kernel_matches_the_single_cta_kernel(native, lay
     wd = (w.transpose(1, 2).contiguous() if layout == "kn" else w).to(DEV)
     lay = 2 if layout == "kn" else 1
     args = (a.to(DEV), None, wd, None, bias.to(DEV), rows.to(DEV), N, K)
-    pair = grouped_gemm(*args, layout=lay, epilogue=epi, impl=TC, out_dtype=dtype)
+    pair = grouped_gemm(*args, layout=lay, epilogue=epi, impl=4, out_dtype=dtype)
     single = grouped_gemm(*args, layout=lay, epilogue=epi, impl=3, out_dtype=dtype)
     check = grouped_gemm(*args, layout=lay, epilogue=epi, impl=CHECK, out_dtype=dtype)
     assert torch.equal(pair[:M], single[:M])

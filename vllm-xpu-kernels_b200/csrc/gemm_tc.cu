@@ -475,20 +475,38 @@ constexpr int kPairTok = 256;
 constexpr int kPairStageBytes = kWTileBytes + 128 * 128;   // this CTA's weights + its half of the tokens
 constexpr int kPairStages = 6;
 constexpr size_t kPairSmem = 1024 + (size_t)kPairStages * kPairStageBytes + sizeof(Ctrl<kPairTok, false>);
+// kGated (SiLU-and-mul): the even CTA takes the 128 gate features j0.., the odd one the up features
+// n/2 + j0.. of the same tokens.  The odd CTA's epilogue warps send their accumulator chunks
+// (bias added, fp32) into the even CTA's shared memory, whose warps apply silu(gate) * up and
+// store [M, n/2]: one stage of the ring makes room for the exchange buffers (per epilogue warp two
+// buffers of 32 features x 32 tokens fp32) and their barriers.
+constexpr int kPairGatedStages = 5;
+constexpr int kPairXBuf = 32 * 32 * 4;
+struct PairXchg {
+  uint64_t full[kEpiWarps][2];    // in the even CTA: a chunk has arrived
+  uint64_t empty[kEpiWarps][2];   // in the odd CTA: the even CTA has read the chunk
+};
+constexpr size_t kPairGatedSmem = 1024 + (size_t)kPairGatedStages * kPairStageBytes + kEpiWarps * 2 * kPairXBuf +
+                                  sizeof(PairXchg) + sizeof(Ctrl<kPairTok, false>);
 
-template <bool kWKn>
+template <bool kWKn, bool kGated>
 __global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_w, const TcParams p) {
   constexpr int kChunk = 32;
+  constexpr int kStagesP = kGated ? kPairGatedStages : kPairStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  Ctrl<kPairTok, false>* ctrl = reinterpret_cast<Ctrl<kPairTok, false>*>(smem + kPairStages * kPairStageBytes);
+  uint8_t* xbuf = smem + kStagesP * kPairStageBytes;                               // kGated only
+  PairXchg* xc = reinterpret_cast<PairXchg*>(xbuf + kEpiWarps * 2 * kPairXBuf);   // kGated only
+  Ctrl<kPairTok, false>* ctrl = reinterpret_cast<Ctrl<kPairTok, false>*>(
+      smem + kStagesP * kPairStageBytes + (kGated ? kEpiWarps * 2 * kPairXBuf + sizeof(PairXchg) : 0));
   volatile int* abort_flag = &ctrl->abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t cta = ptx::cluster_ctarank();
   const int walker = (int)ptx::cluster_id_x(), walkers = (int)ptx::cluster_count_x();
-  const int pair_tiles = (p.n_tiles + 1) / 2;   // feature tiles of 2 x 128
+  // plain: feature tiles of 2 x 128; gated: one pair tile per 128 gate features (p.n_tiles counts those)
+  const int pair_tiles = kGated ? p.n_tiles : (p.n_tiles + 1) / 2;
 
   if (warp == 0) {
     build_tile_prefix<kPairTok>(p.rows_per_expert, p.num_experts, pair_tiles, ctrl->row_start, ctrl->tile_start);
@@ -500,13 +518,20 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::tmem_alloc_pair(&ctrl->tmem_base, 512);
     ptx::tmem_relinquish_pair();
   } else if (warp == 2 && lane == 0) {
-    for (int s = 0; s < kPairStages; ++s) {
+    for (int s = 0; s < kStagesP; ++s) {
       ptx::mbar_init(&ctrl->full[s], 1);
       ptx::mbar_init(&ctrl->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&ctrl->acc_full[a], 1);
       ptx::mbar_init(&ctrl->acc_empty[a], 2 * kEpiWarps);   // the epilogue warps of both CTAs
+    }
+    if (kGated) {
+      for (int w = 0; w < kEpiWarps; ++w)
+        for (int b = 0; b < 2; ++b) {
+          ptx::mbar_init(&xc->full[w][b], 1);
+          ptx::mbar_init(&xc->empty[w][b], 1);
+        }
     }
     ctrl->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -530,7 +555,8 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = walker; t < total_tiles && ok; t += walkers) {
         TileInfo ti;
         locate_tile<kPairTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
-        const int n0 = (ti.n_tile * 2 + (int)cta) * kFeat;       // past N: the load is zero-filled
+        // past N: the load is zero-filled
+        const int n0 = kGated ? (cta == 0 ? 0 : (p.n >> 1)) + ti.n_tile * kFeat : (ti.n_tile * 2 + (int)cta) * kFeat;
         const int row = ti.row0 + (int)cta * 128;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ptx::mbar_wait(&ctrl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
@@ -546,7 +572,7 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tma_load_3d_pair(wdst + kWTileBytes / 2, &tmap_w, bar, n0 + 64, k0, ti.e);
           }
           ptx::tma_load_2d_pair(wdst + kWTileBytes, &tmap_a, bar, k0, row);
-          if (++s == (uint32_t)kPairStages) { s = 0; ph ^= 1; }
+          if (++s == (uint32_t)kStagesP) { s = 0; ph ^= 1; }
         }
       }
     }
@@ -574,7 +600,7 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::umma_f16_pair_elect(tmem_base + a * kPairTok, wdesc0 + (uint64_t)((j * kWStep) >> 4),
                                      adesc0 + (uint64_t)((j * 32) >> 4), idesc, (kb > 0 || j > 0) ? 1u : 0u);
           ptx::umma_commit_pair_elect(&ctrl->empty[s]);
-          if (++s == (uint32_t)kPairStages) { s = 0; ph ^= 1; }
+          if (++s == (uint32_t)kStagesP) { s = 0; ph ^= 1; }
         }
         if (ok) { ptx::umma_commit_pair_elect(&ctrl->acc_full[a]); ++acc_it; }
       }
@@ -586,18 +612,27 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t acc_empty0 = ptx::map_to_cta(ptx::smem_u32(&ctrl->acc_empty[0]), 0);
     uint32_t acc_it = 0;
     int cursor = 0;
-    for (int t = walker; t < total_tiles; t += walkers) {
+    // gated: this warp's exchange buffers in the even CTA, the barriers on both sides, and how
+    // many chunks have gone through them
+    const int ew = warp - 2;
+    const uint32_t xbuf0 = ptx::map_to_cta(ptx::smem_u32(xbuf + ew * 2 * kPairXBuf), 0);
+    const uint32_t xfull0 = ptx::map_to_cta(ptx::smem_u32(&xc->full[ew][0]), 0);
+    const uint32_t xempty1 = ptx::map_to_cta(ptx::smem_u32(&xc->empty[ew][0]), 1);
+    uint32_t xit = 0;
+    bool ok = true;
+    for (int t = walker; t < total_tiles && ok; t += walkers) {
       TileInfo ti;
       locate_tile<kPairTok>(tile_start, row_start, t, cursor, ti, p.w_experts);
-      const int n_tile = ti.n_tile * 2 + (int)cta;
-      const int feat = n_tile * kFeat + q * 32 + lane;
+      const int n_tile = kGated ? ti.n_tile : ti.n_tile * 2 + (int)cta;
+      // the feature (row of W and of the bias) this thread's accumulator lane belongs to
+      const int feat = (kGated && cta == 1 ? (p.n >> 1) : 0) + n_tile * kFeat + q * 32 + lane;
       const float bias_v = (p.bias != nullptr && feat < p.n) ? load_bias(p.bias, p.out_f16, (int64_t)ti.e * p.n + feat) : 0.f;
       const uint32_t a = acc_it & 1;
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctrl->acc_full[a], (acc_it >> 1) & 1, abort_flag))) {
         *abort_flag = 1; break;
       }
       ptx::tc_fence_after();
-#pragma unroll
+#pragma unroll(kGated ? 1 : kPairTok / kChunk)
       for (int c0 = 0; c0 < kPairTok; c0 += kChunk) {
         if (c0 < ti.valid) {
           uint32_t v[kChunk];
@@ -606,7 +641,48 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           float vals[kChunk];
 #pragma unroll
           for (int i = 0; i < kChunk; ++i) vals[i] = __uint_as_float(v[i]) + bias_v;
-          if (p.swiglu) {
+          if (kGated) {
+            const uint32_t b = xit & 1, par = (xit >> 1) & 1;
+            if (cta == 1) {
+              // up: wait until the even CTA has read this buffer's previous chunk, then send
+              if (!__all_sync(0xffffffffu, ptx::mbar_wait_cluster(&xc->empty[ew][b], par ^ 1, abort_flag))) {
+                *abort_flag = 1; ok = false; break;
+              }
+              if (p.clamp > 0.f) {
+#pragma unroll
+                for (int i = 0; i < kChunk; ++i) vals[i] = fminf(fmaxf(vals[i], -p.clamp), p.clamp);
+              }
+              const uint32_t dst = xbuf0 + b * kPairXBuf + lane * 16;     // [token quad][lane] 16-byte cells
+#pragma unroll
+              for (int i = 0; i < kChunk; i += 4)
+                ptx::st_cluster_v4(dst + (i >> 2) * 512, vals[i], vals[i + 1], vals[i + 2], vals[i + 3]);
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive_cluster_release(xfull0 + b * 8);
+            } else {
+              // gate: take the up chunk of the same features and tokens, activate, store
+              if (!__all_sync(0xffffffffu, ptx::mbar_wait_cluster(&xc->full[ew][b], par, abort_flag))) {
+                *abort_flag = 1; ok = false; break;
+              }
+              const uint32_t src = ptx::smem_u32(xbuf + ew * 2 * kPairXBuf) + b * kPairXBuf + lane * 16;
+#pragma unroll
+              for (int i = 0; i < kChunk; i += 4) {
+                const float4 u4 = ptx::lds128f(src + (i >> 2) * 512);
+                const float uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  float g = vals[i + k];
+                  if (p.clamp > 0.f) g = fminf(g, p.clamp);
+                  vals[i + k] = g * __fdividef(1.0f, 1.0f + __expf(-g)) * uu[k];
+                }
+              }
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive_cluster_release(xempty1 + b * 8);
+              store_block_transposed<kChunk, 32>(ctrl->xpose[warp - 2], vals, p.d, p.out_f16,
+                                                 (int64_t)ti.row0 + c0, ti.valid - c0, p.m, p.n >> 1,
+                                                 n_tile * kFeat + q * 32, lane);
+            }
+            ++xit;
+          } else if (p.swiglu) {
             const float c_lim = p.clamp > 0.f ? p.clamp : INFINITY;
 #pragma unroll
             for (int i = 0; i < kChunk; ++i) {
@@ -629,6 +705,7 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      if (!ok) break;
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(acc_empty0 + a * 8);
@@ -651,16 +728,17 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 // Clusters of two CTAs, as many as the device runs at once (at most `max_pairs`).
-template <bool kWKn>
+template <bool kWKn, bool kGated>
 int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tw, const TcParams& p, int max_pairs, cudaStream_t st) {
-  auto kern = grouped_gemm_tc_pair_kernel<kWKn>;
+  auto kern = grouped_gemm_tc_pair_kernel<kWKn, kGated>;
+  constexpr size_t kSmem = kGated ? kPairGatedSmem : kPairSmem;
   static SmemConfig configured;
-  if (int rc = configured.ensure(kern, kPairSmem)) return rc;
+  if (int rc = configured.ensure(kern, kSmem)) return rc;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kPairSmem; cfg.stream = st;
+  cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kSmem; cfg.stream = st;
   cfg.attrs = attr; cfg.numAttrs = 1;
   static std::atomic<int> resident[kMaxDevices];
   const int dev = current_device();
@@ -732,8 +810,18 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   else if (avg <= 40) bt = 64;
   else if (avg <= 96) bt = 128;   // measured on skewed routing: 128 rows per expert are 13 % faster at 256
   else bt = 256;
-  // two accumulators per stage: tensor memory holds the gated form up to 128-token tiles
-  if (gated && bt > 128) bt = 128;
+  // two accumulators per stage: tensor memory holds the gated form up to 128-token tiles; beyond,
+  // a CTA pair splits gate and up between its two CTAs (whole 128-feature tiles only)
+  // (whole 128-feature tiles only).  The pair's epilogue passes the up half through the other
+  // CTA's shared memory chunk by chunk, which a tile's MMAs hide from K = 4096 on; with 256-token
+  // tiles it also wants segments that fill them.  Measured, gemm1 of the Mixtral shape: 1024 rows
+  // per expert 1.33 ms against 1.59 (single-CTA gated tile) and 1.42 (plain pair + silu_and_mul),
+  // 128 rows per expert 0.39 against 0.31; N=2816, K=2048, 1024 rows: 0.120 against 0.096.
+  // (impl 4 forces the pair form, impl 3 the single-CTA forms.)
+  const bool gated_pair = gated && !a_fp8 && a->impl != 3 && (a->n / 2) % kFeat == 0 &&
+                          (a->impl == 4 || (avg > 192 && a->k >= 4096));
+  if (gated_pair || (a->impl == 4 && !a_fp8 && !gated)) bt = 256;
+  else if (gated && bt > 128) bt = 128;
 
   // prefill-sized fp8 segments: the token-major kernels (one scale register per thread and K block)
   if (a_fp8 && bt >= 128) return grouped_gemm_tc_fp8t(a, st);
@@ -771,17 +859,21 @@ int grouped_gemm_tc(const b200moe_gemm_args* a, cudaStream_t st) {
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
 
   // 16-bit prefill: the CTA-pair kernel (impl 3 / 4 force the single-CTA / the pair form)
-  if (!a_fp8 && !gated && bt == 256 && a->impl != 3 && p.n_tiles >= 2) {
+  if (!a_fp8 && bt == 256 && a->impl != 3 && (gated ? gated_pair : p.n_tiles >= 2)) {
     CUtensorMap ta_half;
     cuuint64_t dims[2] = {(cuuint64_t)a->k, (cuuint64_t)a->m};
     cuuint64_t strides[1] = {(cuuint64_t)a->k * es};
     cuuint32_t box[2] = {(cuuint32_t)kpb, 128};
     if (int rc = encode_map(&ta_half, dt, 2, a->a, dims, strides, box)) return rc;
-    const int64_t pair_bound = ((a->m + 255) / 256 + a->num_experts) * (int64_t)((p.n_tiles + 1) / 2);
+    const int64_t pair_bound = ((a->m + 255) / 256 + a->num_experts) * (int64_t)(gated ? p.n_tiles : (p.n_tiles + 1) / 2);
     int max_pairs = grid / 2 < 1 ? 1 : grid / 2;
     if (pair_bound < max_pairs) max_pairs = (int)pair_bound;
-    const int rc = kn ? launch_tc_pair<true>(ta_half, tw, p, max_pairs, st) : launch_tc_pair<false>(ta_half, tw, p, max_pairs, st);
+    const int rc = gated ? (kn ? launch_tc_pair<true, true>(ta_half, tw, p, max_pairs, st)
+                               : launch_tc_pair<false, true>(ta_half, tw, p, max_pairs, st))
+                         : (kn ? launch_tc_pair<true, false>(ta_half, tw, p, max_pairs, st)
+                               : launch_tc_pair<false, false>(ta_half, tw, p, max_pairs, st));
     if (rc != B200MOE_E_UNSUPPORTED) return rc;
+    if (gated) bt = 128;   // no clusters on this device: the single-CTA gated tile
   }
 
   if (tile_bound < grid) grid = (int)tile_bound;

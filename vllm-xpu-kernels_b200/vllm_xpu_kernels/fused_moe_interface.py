@@ -291,16 +291,18 @@ class XpuFusedMoe:
                               and fuse_activation is not False)
         self._fp8_fused_min_rows = 12 if fuse_activation else FP8_FUSED_MIN_ROWS
         # 16-bit weights with SiLU: the tensor-core kernel pairs gate and up tiles in two
-        # accumulators, which tensor memory holds for token tiles up to 128 - the sizes it picks up
-        # to 96 routed rows per expert.  Beyond that the 256-token tile plus a separate
-        # silu_and_mul is faster, so the fused form is taken per call below that size
+        # accumulators, which tensor memory holds for token tiles up to 128; for long expert
+        # segments and K >= 4096 a CTA pair splits gate and up between its CTAs on 256-token
+        # tiles.  With whole 128-feature tiles (I % 128 == 0) the fused form is taken at every
+        # size; otherwise up to 96 routed rows per expert, where 128-token tiles are picked anyway
         # (fuse_activation=True forces it at every size).
         is_16bit = not (is_fp8 or is_mxfp4 or is_mxfp8 or is_block_fp8 or is_int4)
         # SwigluOAI keeps gate and up of a feature on neighbouring accumulator lanes: one accumulator,
         # every tile size, so it is fused at every size.
         self._w16_fused_ok = (is_16bit and self._act_kind in ("silu", "swigluoai") and self.inter_size % 16 == 0
                               and fuse_activation is not False)
-        self._w16_fused_max_rows = None if (fuse_activation or self._act_kind == "swigluoai") else 96
+        self._w16_fused_max_rows = None if (fuse_activation or self._act_kind == "swigluoai"
+                                            or self.inter_size % 128 == 0) else 96
         if fuse_activation is None:
             # fused where the tensor-core kernel of this recipe has the epilogue
             fuse_activation = self.is_mxfp4 and self._act_kind == "swigluoai"
