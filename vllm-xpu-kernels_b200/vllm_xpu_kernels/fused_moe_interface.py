@@ -187,8 +187,9 @@ class XpuFusedMoe:
     activation inside the first grouped GEMM's epilogue instead of a separate
     pass over ``[T*K, 2I]``.  ``None`` (default) picks it where the tensor-core
     kernel of the recipe has that epilogue and it pays: MXFP4 and 16-bit
-    weights with SwigluOAI always; 16-bit weights with SiLU up to 96 routed
-    rows per expert; block-scaled fp8 with SiLU (where the epilogue also
+    weights with SwigluOAI always; 16-bit weights with SiLU always when the
+    intermediate size is a multiple of 128 (else up to 96 routed rows per
+    expert); block-scaled fp8 with SiLU (where the epilogue also
     quantises gemm2's input to e4m3 per 1x128 group, with the same values as
     the two-kernel form) from ``FP8_FUSED_MIN_ROWS`` routed rows per expert on.
     ``True`` forces it wherever a kernel has it, ``False`` never fuses.
