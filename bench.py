@@ -349,6 +349,15 @@ def time_gemms(cfg, layer, ids, T, dev, iters, ep_world=1, ep_rank=0):
               7.0, 0.0, 0, 0)
             g(a2, s2, layer.w2, layer.gemm2_wei_scales, layer.w2_bias, d2, rows, H, I, E, 0, 0, 1.702, 7.0,
               0.0, 0, 0)
+    elif not fp8 and layer.fuses_activation(M) == "epilogue":
+        # 16-bit layer with the gated activation inside gemm1's epilogue: time that form
+        d1 = torch.empty(M, I, dtype=torch.bfloat16, device=dev)
+        g = torch.ops._xpu_C.b200_grouped_gemm
+        epi = 1 if cfg.activation == "silu" else 2
+
+        def both():
+            g(a1, None, layer.w13, None, layer.w13_bias, d1, rows, 2 * I, H, E, 0, epi, 1.702, 7.0, 0.0, 0, 0)
+            f(a2, None, layer.w2, None, layer.w2_bias, d2, rows, H, I, E)
     else:
         def both():
             f(a1, s1, layer.w13, layer.gemm1_wei_scales, layer.w13_bias, d1, rows, 2 * I, H, E)
