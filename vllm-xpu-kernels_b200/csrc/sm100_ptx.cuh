@@ -327,13 +327,6 @@ __device__ __forceinline__ void setmaxnreg_inc() {
 }
 // 32 lanes x N consecutive 32-bit columns written from registers: thread i
 // writes lane (base lane + i).
-__device__ __forceinline__ void tmem_st_32x1(uint32_t taddr, uint32_t r0) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(r0) : "memory");
-}
-__device__ __forceinline__ void tmem_st_32x2(uint32_t taddr, uint32_t r0, uint32_t r1) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(r0), "r"(r1)
-               : "memory");
-}
 __device__ __forceinline__ void tmem_st_32x4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2,
                                              uint32_t r3) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0),
@@ -372,23 +365,6 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
          ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-template <bool kFp8>
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                     uint32_t idesc, uint32_t accumulate) {
-  if (kFp8) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
 // Instruction descriptor of tcgen05.mma kind::mxf8f6f4.block_scale with e8m0
 // scales: a_fmt / b_fmt 0 = e4m3, 1 = e5m2, 3 = e2m3, 4 = e3m2, 5 = e2m1; both
 // operands K-major; fp32 accumulate.  The scale byte (0..3) of the 32-bit scale
@@ -397,30 +373,15 @@ __host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_fmt, uint32_t b_
                                                      uint32_t N) {
   return (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24);
 }
-// D[tmem_d] (+)= (A * 2^(sfa-127)) * (B * 2^(sfb-127)) over K = 32; sfa / sfb are
-// tensor-memory addresses of the scale columns (one byte per row, replicated in
-// the four lane quarters).
-__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                        uint32_t idesc, uint32_t accumulate, uint32_t sfa,
-                                        uint32_t sfb) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-      : "memory");
-}
-// Makes `bar` receive one arrival when all MMAs issued so far by this thread
-// have completed.
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-
-// The same two instructions for a warp that runs the issue loop convergently (all lanes hold
-// the same operands): one elected lane issues.  A warp-uniform loop lets the compiler keep
+// tcgen05.mma and tcgen05.commit for a warp that runs the issue loop convergently (all lanes
+// hold the same operands): one elected lane issues.  A warp-uniform loop lets the compiler keep
 // descriptors and barrier addresses in uniform registers (measured on the fp8 kernel: 4 MMAs
-// and 2 commits issue in 370 instead of 640 cycles).
+// and 2 commits issue in 370 instead of 640 cycles).  A commit makes `bar` receive one arrival
+// when all MMAs issued so far by that lane have completed.
+//
+// Block-scaled form: D[tmem_d] (+)= (A * 2^(sfa-127)) * (B * 2^(sfb-127)) over K = 32; sfa / sfb
+// are tensor-memory addresses of the scale columns (one byte per row, replicated in the four
+// lane quarters).
 __device__ __forceinline__ void umma_mx_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                               uint32_t idesc, uint32_t accumulate, uint32_t sfa,
                                               uint32_t sfb) {
@@ -534,10 +495,6 @@ __device__ __forceinline__ void cp_async_mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.wait_all;" ::: "memory");
-}
-
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 }  // namespace ptx
