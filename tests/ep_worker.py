@@ -62,31 +62,44 @@ def cpu_worker(rank, world, port, T, result_queue):
         err = float((out.float() - ref.float()).abs().max())
 
         # the default schedule: one row per (token, destination rank) with the token's local expert
-        # ids and weights, top-k layer on the owner, one partial sum per (token, rank) back
-        K = ids.shape[1]
-        dest = ids.long() // E_local
-        hit = dest.unsqueeze(1) == torch.arange(world).view(1, world, 1)            # [T, ep, K]
-        rank_ids = torch.where(hit.any(dim=2), torch.arange(world).view(1, world), -1).int()
-        loc_ids = torch.where(hit, (ids.long() % E_local).unsqueeze(1), -1).int()
-        loc_w = torch.where(hit, tw.unsqueeze(1), 0.0).float()
-        p_rows, _, p_counts, p_pos = to.remap_hidden_states(x, None, rank_ids, None, world)
-        Tn = x.shape[0]
-        pos = p_pos.reshape(-1).long()
-        pos = torch.where(pos >= 0, pos, Tn * world)
-        s_ids = torch.empty(Tn * world + 1, K, dtype=torch.int32)
-        s_w = torch.empty(Tn * world + 1, K)
-        s_ids.index_copy_(0, pos, loc_ids.reshape(-1, K))
-        s_w.index_copy_(0, pos, loc_w.reshape(-1, K))
-        ps, pr = a2a.exchange_counts(p_counts)
-        n = sum(ps)
-        assert n <= M and n == int((rank_ids >= 0).sum())
-        r_rows, _, r_ids, r_w = a2a.dispatch((p_rows[:n], None, s_ids[:n], s_w[:n]), ps, pr)
-        part = to.fused_moe_staged(r_rows, d13[lo:lo + E_local], None, d2[lo:lo + E_local], None, r_w, r_ids,
-                                   E_local) if r_rows.shape[0] else r_rows
-        back = a2a.combine(part, ps, pr)
-        out_p = to.moe_gather(back, torch.ones(Tn, world), p_pos, x.dtype)
+        # ids and weights, top-k layer on the owner, one partial sum per (token, rank) back.
+        # `slots` [T, K] says where each routed expert lives (slot // E_local = rank, slot % E_local
+        # = local expert), `held` which global experts this rank stacks, in local order.
+        def per_rank_schedule(slots, held):
+            K = slots.shape[1]
+            dest = slots.long() // E_local
+            hit = dest.unsqueeze(1) == torch.arange(world).view(1, world, 1)            # [T, ep, K]
+            rank_ids = torch.where(hit.any(dim=2), torch.arange(world).view(1, world), -1).int()
+            loc_ids = torch.where(hit, (slots.long() % E_local).unsqueeze(1), -1).int()
+            loc_w = torch.where(hit, tw.unsqueeze(1), 0.0).float()
+            p_rows, _, p_counts, p_pos = to.remap_hidden_states(x, None, rank_ids, None, world)
+            Tn = x.shape[0]
+            pos = p_pos.reshape(-1).long()
+            pos = torch.where(pos >= 0, pos, Tn * world)
+            s_ids = torch.empty(Tn * world + 1, K, dtype=torch.int32)
+            s_w = torch.empty(Tn * world + 1, K)
+            s_ids.index_copy_(0, pos, loc_ids.reshape(-1, K))
+            s_w.index_copy_(0, pos, loc_w.reshape(-1, K))
+            ps, pr = a2a.exchange_counts(p_counts)
+            n = sum(ps)
+            assert n <= M and n == int((rank_ids >= 0).sum())
+            r_rows, _, r_ids, r_w = a2a.dispatch((p_rows[:n], None, s_ids[:n], s_w[:n]), ps, pr)
+            part = to.fused_moe_staged(r_rows, d13[held], None, d2[held], None, r_w, r_ids,
+                                       E_local) if r_rows.shape[0] else r_rows
+            back = a2a.combine(part, ps, pr)
+            return to.moe_gather(back, torch.ones(Tn, world), p_pos, x.dtype)
+
+        out_p = per_rank_schedule(ids, torch.arange(lo, lo + E_local))
         # every partial sum is rounded to 16 bits before the last addition
         err = max(err, float((out_p.float() - ref.float()).abs().max()))
+
+        # the same with the experts placed by a load estimate instead of contiguously: ids are
+        # relabelled through the placement, every rank stacks the experts of its slots
+        from vllm_xpu_kernels.ep_moe import balanced_expert_slots, experts_in_slots
+        slot = balanced_expert_slots(torch.arange(cfg.E, dtype=torch.float64) ** 2 + 1, world)
+        assert not torch.equal(slot.long(), torch.arange(cfg.E))
+        out_s = per_rank_schedule(slot.long()[ids.long()], experts_in_slots(slot, rank, E_local))
+        err = max(err, float((out_s.float() - ref.float()).abs().max()))
         result_queue.put((rank, err, s_spl, r_spl))
     finally:
         dist.destroy_process_group()
