@@ -398,14 +398,22 @@ class EpFusedMoe:
     ``per_rank_rows`` (default): one row per (token, destination rank) as described in the
     module docstring.  ``per_rank_rows=False``: one row per (token, expert), top-1 on the
     owner, weighted reduction on the source - more traffic, fewer small launches.
+    ``expert_slot``: a placement ``expert -> slot`` as for ``EpPeerFusedMoe`` (the routed ids are
+    relabelled through it before anything else).
     """
 
     def __init__(self, w13, w13_scales, w13_bias, w2, w2_scales, w2_bias,
                  n_experts_per_token, activation, num_local_experts,
                  group: Optional[dist.ProcessGroup] = None,
-                 gemm1_clamp_limit: Optional[float] = None, per_rank_rows: bool = True):
+                 gemm1_clamp_limit: Optional[float] = None, per_rank_rows: bool = True,
+                 expert_slot: Optional[torch.Tensor] = None):
         from .fused_moe_interface import XpuFusedMoe
         self.a2a = EpAllToAll(group)
+        if expert_slot is not None:
+            if expert_slot.numel() != num_local_experts * self.a2a.ep_size:
+                raise ValueError("expert_slot must have one entry per expert of the whole group")
+            expert_slot = expert_slot.to(device=w13.device, dtype=torch.int64).contiguous()
+        self.expert_slot = expert_slot
         self.ep_size, self.ep_rank = self.a2a.ep_size, self.a2a.ep_rank
         self.num_local_experts = num_local_experts
         self.num_experts_total = num_local_experts * self.ep_size
@@ -418,6 +426,9 @@ class EpFusedMoe:
         self.quant = self.local.is_block_fp8
 
     def apply(self, output, hidden_states, topk_weights, topk_ids):
+        if self.expert_slot is not None:
+            ids = topk_ids.long()
+            topk_ids = torch.where(ids >= 0, self.expert_slot[ids.clamp(min=0)], ids).to(topk_ids.dtype)
         if self.per_rank_rows:
             return self._apply_per_rank(output, hidden_states, topk_weights, topk_ids)
         T, H = hidden_states.shape
