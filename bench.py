@@ -10,7 +10,9 @@ block-fp8 layer (H=7168, I=2048, 256 experts, grouped sigmoid top-8) at 8192 tok
 the configuration the 1/2/4/8-GPU metric is quoted on.  With N > 1 (launched under
 torch.distributed.run) the experts are sharded evenly over the ranks and tokens are dispatched
 to their experts' ranks and combined back over NVLink peer memory (``--parallelism ep``, the
-default at N > 1); ``--parallelism replicas`` runs N independent copies instead.
+default at N > 1; ``--ep-placement`` says which rank holds which experts: evened out by the expert
+histogram of a calibration batch, or contiguous); ``--parallelism replicas`` runs N independent
+copies instead.
 
 Rank 0 prints one JSON line: whole-job tokens/s with inputs resident in HBM (``value``), the
 same metric through the public API with host buffers and the copies inside the timed region
